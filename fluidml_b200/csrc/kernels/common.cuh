@@ -1,0 +1,135 @@
+// Shared host/device helpers of the kernel library: status handling, operand checking,
+// dimension collapsing and the device status word.
+#pragma once
+#include "fluidml_cuda.h"
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+namespace fml {
+
+constexpr int kMaxDims = FML_MAX_RANK;
+
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+#define FML_CUDA(call)                                                                     \
+  do {                                                                                     \
+    cudaError_t e__ = (call);                                                              \
+    if (e__ != cudaSuccess) return ::fml::cuda_fail(e__, #call);                           \
+  } while (0)
+#define FML_REQUIRE(cond, status, ...)                                                     \
+  do {                                                                                     \
+    if (!(cond)) {                                                                         \
+      ::fml::set_error(__VA_ARGS__);                                                       \
+      return status;                                                                       \
+    }                                                                                      \
+  } while (0)
+
+// Bits of the device status word (one int per device, written by kernels with atomicOr).
+constexpr int kStatusTimeout = 1;
+constexpr int kStatusIndexRange = 2;
+int *device_status_word();  // device pointer for the current device (allocated on first use)
+
+inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+  case FML_F32: case FML_I32: return 4;
+  case FML_I64: return 8;
+  case FML_BOOL: return 1;
+  default: return 0;
+  }
+}
+
+inline int64_t numel(const fml_tensor *t) {
+  int64_t n = 1;
+  for (int i = 0; i < t->rank; ++i) n *= t->shape[i];
+  return n;
+}
+
+inline bool valid_tensor(const fml_tensor *t) {
+  if (!t || t->rank < 0 || t->rank > kMaxDims || dtype_size(t->dtype) == 0) return false;
+  for (int i = 0; i < t->rank; ++i)
+    if (t->shape[i] < 0) return false;
+  return numel(t) == 0 || t->data != nullptr;
+}
+
+inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+// An iteration space over the output's logical shape with one stride vector per operand
+// (operand 0 is the output).  After collapse(): size-1 dims removed, adjacent dims merged
+// when every operand walks them contiguously, so most tensors become 1-3 dims.
+template <int NOPS> struct Iter {
+  int rank;
+  int64_t shape[kMaxDims];
+  int64_t stride[NOPS][kMaxDims];
+  int64_t total;
+};
+
+// Strides of `t` expanded to the output's rank by numpy broadcasting (right-aligned,
+// size-1 dims -> stride 0).  Returns false when the shapes do not broadcast.
+inline bool broadcast_strides(const fml_tensor *t, const fml_tensor *out, int64_t *s) {
+  if (t->rank > out->rank) return false;
+  for (int i = 0; i < out->rank; ++i) {
+    int ti = i - (out->rank - t->rank);
+    if (ti < 0) { s[i] = 0; continue; }
+    if (t->shape[ti] == out->shape[i]) s[i] = t->shape[ti] == 1 ? 0 : t->stride[ti];
+    else if (t->shape[ti] == 1) s[i] = 0;
+    else return false;
+  }
+  return true;
+}
+
+template <int NOPS> inline void collapse(Iter<NOPS> &it) {
+  int r = 0;
+  int64_t shape[kMaxDims], stride[NOPS][kMaxDims];
+  for (int i = 0; i < it.rank; ++i) {
+    if (it.shape[i] == 1) continue;
+    bool merge = r > 0;
+    if (merge)
+      for (int o = 0; o < NOPS; ++o)
+        if (stride[o][r - 1] != it.stride[o][i] * it.shape[i]) { merge = false; break; }
+    if (merge) {
+      shape[r - 1] *= it.shape[i];
+      for (int o = 0; o < NOPS; ++o) stride[o][r - 1] = it.stride[o][i];
+    } else {
+      shape[r] = it.shape[i];
+      for (int o = 0; o < NOPS; ++o) stride[o][r] = it.stride[o][i];
+      ++r;
+    }
+  }
+  if (r == 0) {
+    shape[0] = 1;
+    for (int o = 0; o < NOPS; ++o) stride[o][0] = 0;
+    r = 1;
+  }
+  it.rank = r;
+  it.total = 1;
+  for (int i = 0; i < r; ++i) {
+    it.shape[i] = shape[i];
+    it.total *= shape[i];
+    for (int o = 0; o < NOPS; ++o) it.stride[o][i] = stride[o][i];
+  }
+}
+
+template <int NOPS>
+__device__ __forceinline__ void offsets_of(const Iter<NOPS> &it, int64_t lin, int64_t *off) {
+#pragma unroll
+  for (int o = 0; o < NOPS; ++o) off[o] = 0;
+  for (int d = it.rank - 1; d >= 0; --d) {
+    int64_t q = lin / it.shape[d], c = lin - q * it.shape[d];
+    lin = q;
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) off[o] += c * it.stride[o][d];
+  }
+}
+
+inline int grid_for(int64_t work, int block, int max_blocks = 148 * 16) {
+  int64_t g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  if (g > max_blocks) g = max_blocks;
+  return static_cast<int>(g);
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace fml

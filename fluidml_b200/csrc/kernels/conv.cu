@@ -1,0 +1,217 @@
+// Convolution and pooling.
+//
+// group == 1: implicit GEMM (M = N*OH*OW output pixels, N = OC, K = IC*KH*KW) on a 64x64
+// output tile; the im2col gather happens while filling the shared-memory A tile, so padding
+// is implicit (out-of-image taps read as zero) and no padded copy or scratch is needed.
+// group == C (depthwise, multiplier 1): one thread per output element.
+// 1-D convolutions are the 2-D kernels with H = 1.
+#include "gemm_common.cuh"
+
+namespace fml {
+namespace {
+
+struct ConvArgs {
+  int64_t N, IC, IH, IW, OC, OH, OW, KH, KW;
+  int64_t ph, pw, sh, sw, dh, dw;
+  int64_t xs[4], ws[4], ys[4];  // element strides n/c/h/w, o/i/h/w, n/c/h/w
+  int64_t bias_stride;
+  const float *x, *w, *bias;
+  float *y;
+  int act;
+};
+
+__device__ __forceinline__ float conv_act(int act, float v) {
+  switch (act) {
+  case FML_ACT_RELU: return fmaxf(v, 0.0f);
+  case FML_ACT_TANH: return tanhf(v);
+  case FML_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+  default: return v;
+  }
+}
+
+constexpr int CB = 64, CK = 16;
+
+__global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
+  __shared__ float As[CK][CB + 4];
+  __shared__ float Bs[CK][CB + 4];
+  const int64_t Mtot = a.N * a.OH * a.OW, Ktot = a.IC * a.KH * a.KW;
+  const int64_t m0 = (int64_t)blockIdx.y * CB, n0 = (int64_t)blockIdx.x * CB;
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  float acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < Ktot; k0 += CK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = t + i * 256;
+      {  // A: pixel-fast mapping (consecutive threads = consecutive output pixels)
+        const int mm = e & 63, kk = e >> 6;
+        const int64_t gm = m0 + mm, gk = k0 + kk;
+        float v = 0.0f;
+        if (gm < Mtot && gk < Ktot) {
+          const int64_t ow = gm % a.OW, oh = (gm / a.OW) % a.OH, n = gm / (a.OW * a.OH);
+          const int64_t kw = gk % a.KW, kh = (gk / a.KW) % a.KH, ic = gk / (a.KW * a.KH);
+          const int64_t ih = oh * a.sh - a.ph + kh * a.dh, iw = ow * a.sw - a.pw + kw * a.dw;
+          if (ih >= 0 && ih < a.IH && iw >= 0 && iw < a.IW)
+            v = a.x[n * a.xs[0] + ic * a.xs[1] + ih * a.xs[2] + iw * a.xs[3]];
+        }
+        As[kk][mm] = v;
+      }
+      {  // B: k-fast mapping (OIHW weights are contiguous in k for one output channel)
+        const int kk = e & 15, nn = e >> 4;
+        const int64_t gn = n0 + nn, gk = k0 + kk;
+        float v = 0.0f;
+        if (gn < a.OC && gk < Ktot) {
+          const int64_t kw = gk % a.KW, kh = (gk / a.KW) % a.KH, ic = gk / (a.KW * a.KH);
+          v = a.w[gn * a.ws[0] + ic * a.ws[1] + kh * a.ws[2] + kw * a.ws[3]];
+        }
+        Bs[kk][nn] = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < CK; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { av[i] = As[kk][tx * 4 + i]; bv[i] = Bs[kk][ty * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  // threads along tx own consecutive pixels: stores to NCHW are contiguous in ow
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t gm = m0 + tx * 4 + i, oc = n0 + ty * 4 + j;
+      if (gm < Mtot && oc < a.OC) {
+        const int64_t ow = gm % a.OW, oh = (gm / a.OW) % a.OH, n = gm / (a.OW * a.OH);
+        float v = acc[i][j];
+        if (a.bias) v += a.bias[oc * a.bias_stride];
+        a.y[n * a.ys[0] + oc * a.ys[1] + oh * a.ys[2] + ow * a.ys[3]] = conv_act(a.act, v);
+      }
+    }
+}
+
+__global__ void conv_depthwise_kernel(ConvArgs a) {
+  const int64_t total = a.N * a.OC * a.OH * a.OW;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t ow = e % a.OW, oh = (e / a.OW) % a.OH, c = (e / (a.OW * a.OH)) % a.OC,
+                  n = e / (a.OW * a.OH * a.OC);
+    float s = 0.0f;
+    for (int64_t kh = 0; kh < a.KH; ++kh) {
+      const int64_t ih = oh * a.sh - a.ph + kh * a.dh;
+      if (ih < 0 || ih >= a.IH) continue;
+      for (int64_t kw = 0; kw < a.KW; ++kw) {
+        const int64_t iw = ow * a.sw - a.pw + kw * a.dw;
+        if (iw < 0 || iw >= a.IW) continue;
+        s = fmaf(a.x[n * a.xs[0] + c * a.xs[1] + ih * a.xs[2] + iw * a.xs[3]],
+                 a.w[c * a.ws[0] + kh * a.ws[2] + kw * a.ws[3]], s);
+      }
+    }
+    if (a.bias) s += a.bias[c * a.bias_stride];
+    a.y[n * a.ys[0] + c * a.ys[1] + oh * a.ys[2] + ow * a.ys[3]] = conv_act(a.act, s);
+  }
+}
+
+struct PoolArgs {
+  int64_t N, C, OH, OW, KH, KW, sh, sw;
+  int64_t xs[4], ys[4];
+  const float *x;
+  float *y;
+  int mode;
+};
+
+__global__ void pool2d_kernel(PoolArgs a) {
+  const int64_t total = a.N * a.C * a.OH * a.OW;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t ow = e % a.OW, oh = (e / a.OW) % a.OH, c = (e / (a.OW * a.OH)) % a.C,
+                  n = e / (a.OW * a.OH * a.C);
+    const float *src = a.x + n * a.xs[0] + c * a.xs[1] + oh * a.sh * a.xs[2] + ow * a.sw * a.xs[3];
+    float r = a.mode ? 0.0f : -3.402823466e+38f;
+    for (int64_t kh = 0; kh < a.KH; ++kh)
+      for (int64_t kw = 0; kw < a.KW; ++kw) {
+        const float v = src[kh * a.xs[2] + kw * a.xs[3]];
+        r = a.mode ? r + v : fmaxf(r, v);
+      }
+    if (a.mode) r = r / (float)(a.KH * a.KW);
+    a.y[n * a.ys[0] + c * a.ys[1] + oh * a.ys[2] + ow * a.ys[3]] = r;
+  }
+}
+
+}  // namespace
+}  // namespace fml
+
+using namespace fml;
+
+extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
+                        const fml_tensor *y, const fml_conv_params *p, void *stream) {
+  FML_REQUIRE(valid_tensor(x) && valid_tensor(w) && valid_tensor(y) && p, FML_BAD_ARG, "fml_conv: bad argument");
+  FML_REQUIRE(x->dtype == FML_F32 && w->dtype == FML_F32 && y->dtype == FML_F32, FML_UNSUPPORTED, "fml_conv: fp32 only");
+  FML_REQUIRE((x->rank == 3 || x->rank == 4) && w->rank == x->rank && y->rank == x->rank, FML_BAD_ARG,
+              "fml_conv: 1-D or 2-D NCHW/OIHW tensors expected");
+  const int nd = x->rank - 2;
+  ConvArgs a;
+  a.N = x->shape[0]; a.IC = x->shape[1]; a.OC = w->shape[0];
+  a.IH = nd == 2 ? x->shape[2] : 1; a.IW = x->shape[nd + 1];
+  a.OH = nd == 2 ? y->shape[2] : 1; a.OW = y->shape[nd + 1];
+  a.KH = nd == 2 ? w->shape[2] : 1; a.KW = w->shape[nd + 1];
+  a.ph = nd == 2 ? p->pads_begin[0] : 0; a.pw = nd == 2 ? p->pads_begin[1] : p->pads_begin[0];
+  a.sh = nd == 2 ? p->strides[0] : 1; a.sw = nd == 2 ? p->strides[1] : p->strides[0];
+  a.dh = nd == 2 ? p->dilations[0] : 1; a.dw = nd == 2 ? p->dilations[1] : p->dilations[0];
+  FML_REQUIRE(a.sh >= 1 && a.sw >= 1 && a.dh >= 1 && a.dw >= 1, FML_BAD_ARG, "fml_conv: strides/dilations must be >= 1");
+  FML_REQUIRE(y->shape[0] == a.N && y->shape[1] == a.OC, FML_BAD_ARG, "fml_conv: output shape");
+  const int64_t group = p->group <= 0 ? 1 : p->group;
+  FML_REQUIRE(group == 1 || (group == a.IC && a.OC == a.IC && w->shape[1] == 1), FML_UNSUPPORTED,
+              "fml_conv: group must be 1 or depthwise with multiplier 1");
+  FML_REQUIRE(group != 1 || w->shape[1] == a.IC, FML_BAD_ARG, "fml_conv: weight input channels");
+  a.xs[0] = x->stride[0]; a.xs[1] = x->stride[1]; a.xs[2] = nd == 2 ? x->stride[2] : 0; a.xs[3] = x->stride[nd + 1];
+  a.ws[0] = w->stride[0]; a.ws[1] = w->stride[1]; a.ws[2] = nd == 2 ? w->stride[2] : 0; a.ws[3] = w->stride[nd + 1];
+  a.ys[0] = y->stride[0]; a.ys[1] = y->stride[1]; a.ys[2] = nd == 2 ? y->stride[2] : 0; a.ys[3] = y->stride[nd + 1];
+  a.x = (const float *)x->data; a.w = (const float *)w->data; a.y = (float *)y->data;
+  a.bias = nullptr; a.bias_stride = 0;
+  if (bias) {
+    FML_REQUIRE(valid_tensor(bias) && bias->dtype == FML_F32 && numel(bias) == a.OC, FML_BAD_ARG,
+                "fml_conv: bias must hold one value per output channel");
+    a.bias = (const float *)bias->data;
+    for (int i = 0; i < bias->rank; ++i) if (bias->shape[i] != 1) a.bias_stride = bias->stride[i];
+  }
+  a.act = p->act;
+  const int64_t M = a.N * a.OH * a.OW;
+  if (M == 0 || a.OC == 0) return FML_OK;
+  cudaStream_t s = as_stream(stream);
+  if (group == 1) {
+    FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");
+    dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));
+    FML_REQUIRE(grid.y <= 65535, FML_UNSUPPORTED, "fml_conv: too many output pixels for one launch");
+    conv_igemm_kernel<<<grid, 256, 0, s>>>(a);
+  } else {
+    conv_depthwise_kernel<<<grid_for(M * a.OC, 256), 256, 0, s>>>(a);
+  }
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t *kernel,
+                          const int64_t *strides, void *stream) {
+  FML_REQUIRE(valid_tensor(x) && valid_tensor(y) && kernel && strides, FML_BAD_ARG, "fml_pool2d: bad argument");
+  FML_REQUIRE(x->dtype == FML_F32 && y->dtype == FML_F32 && x->rank == 4 && y->rank == 4, FML_UNSUPPORTED,
+              "fml_pool2d: fp32 NCHW only");
+  PoolArgs a;
+  a.N = y->shape[0]; a.C = y->shape[1]; a.OH = y->shape[2]; a.OW = y->shape[3];
+  a.KH = kernel[0]; a.KW = kernel[1]; a.sh = strides[0]; a.sw = strides[1];
+  FML_REQUIRE(a.KH >= 1 && a.KW >= 1 && a.sh >= 1 && a.sw >= 1, FML_BAD_ARG, "fml_pool2d: kernel/strides");
+  FML_REQUIRE((a.OH - 1) * a.sh + a.KH <= x->shape[2] && (a.OW - 1) * a.sw + a.KW <= x->shape[3] &&
+                  x->shape[0] == a.N && x->shape[1] == a.C,
+              FML_BAD_ARG, "fml_pool2d: window leaves the input (pools take no padding)");
+  for (int i = 0; i < 4; ++i) { a.xs[i] = x->stride[i]; a.ys[i] = y->stride[i]; }
+  a.x = (const float *)x->data; a.y = (float *)y->data; a.mode = mode;
+  const int64_t total = a.N * a.C * a.OH * a.OW;
+  if (total == 0) return FML_OK;
+  pool2d_kernel<<<grid_for(total, 256), 256, 0, as_stream(stream)>>>(a);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}

@@ -1,0 +1,312 @@
+// Strided N-ary elementwise kernels: Add/Mul/Div/Sub/Pow/Equal (broadcast), their
+// scalar-constant variants, the unary math ops, bias+GELU and Where.
+//
+// HBM-bound: each output element is read-modify-written once.  When every operand's
+// innermost collapsed dimension is contiguous (or broadcast) and 16-byte aligned the kernel
+// moves float4 per thread; otherwise it falls back to one element per thread with the
+// offsets rebuilt from the collapsed shape.
+#include "common.cuh"
+
+namespace fml {
+namespace {
+
+__device__ __forceinline__ float gelu_erf(float t, float c0, float c1, float c2) {
+  return t * (erff(t / c0) + c1) * c2;
+}
+
+__device__ __forceinline__ float ew_apply(int op, float a, float b, float p0, float p1) {
+  switch (op) {
+  case FML_ADD: return a + b;
+  case FML_MUL: return a * b;
+  case FML_DIV: return a / b;
+  case FML_SUB: return a - b;
+  case FML_POW: return powf(a, b);
+  case FML_ADD_SCALAR: return a + p0;
+  case FML_MUL_SCALAR: return a * p0;
+  case FML_DIV_SCALAR: return a / p0;
+  case FML_RSUB_SCALAR: return p0 - a;
+  case FML_POW_SCALAR: return powf(a, p0);
+  case FML_CLIP: return fminf(fmaxf(a, p0), p1);
+  case FML_RSUB_MUL_SCALAR: return (p0 - a) * p1;
+  case FML_ERF: return erff(a);
+  case FML_TANH: return tanhf(a);
+  case FML_SQRT: return sqrtf(a);
+  case FML_NEG: return -a;
+  case FML_RELU: return fmaxf(a, 0.0f);
+  case FML_SIGMOID: return 1.0f / (1.0f + expf(-a));
+  case FML_EXP: return expf(a);
+  case FML_SILU: return a / (1.0f + expf(-a));
+  default: return a;
+  }
+}
+
+__device__ __forceinline__ int64_t ew_apply_i64(int op, int64_t a, int64_t b, int64_t p0) {
+  switch (op) {
+  case FML_ADD: return a + b;
+  case FML_MUL: return a * b;
+  case FML_SUB: return a - b;
+  case FML_ADD_SCALAR: return a + p0;
+  case FML_MUL_SCALAR: return a * p0;
+  case FML_RSUB_SCALAR: return p0 - a;
+  default: return a;
+  }
+}
+
+// operand 0 = out, 1 = a, 2 = b
+__global__ void ew_f32_generic(Iter<3> it, int op, float *out, const float *a, const float *b,
+                               float p0, float p1) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    float bv = b ? b[off[2]] : 0.0f;
+    out[off[0]] = ew_apply(op, a[off[1]], bv, p0, p1);
+  }
+}
+
+// Innermost dim: out stride 1, a/b stride 1 or 0; inner extent a multiple of 4.
+__global__ void ew_f32_vec4(Iter<3> it, int op, float *out, const float *a, const float *b,
+                            float p0, float p1) {
+  const int64_t inner4 = it.shape[it.rank - 1] >> 2;
+  const int64_t total4 = it.total >> 2;
+  const bool a_vec = it.stride[1][it.rank - 1] == 1, b_vec = b && it.stride[2][it.rank - 1] == 1;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = i / inner4, c4 = i - row * inner4;
+    int64_t off[3] = {c4 * 4, a_vec ? c4 * 4 : 0, b_vec ? c4 * 4 : 0};
+    for (int d = it.rank - 2; d >= 0; --d) {
+      int64_t q = row / it.shape[d], c = row - q * it.shape[d];
+      row = q;
+      off[0] += c * it.stride[0][d];
+      off[1] += c * it.stride[1][d];
+      off[2] += c * it.stride[2][d];
+    }
+    float4 av, bv = make_float4(0.f, 0.f, 0.f, 0.f), r;
+    if (a_vec) av = *reinterpret_cast<const float4 *>(a + off[1]);
+    else { float s = a[off[1]]; av = make_float4(s, s, s, s); }
+    if (b) {
+      if (b_vec) bv = *reinterpret_cast<const float4 *>(b + off[2]);
+      else { float s = b[off[2]]; bv = make_float4(s, s, s, s); }
+    }
+    r.x = ew_apply(op, av.x, bv.x, p0, p1);
+    r.y = ew_apply(op, av.y, bv.y, p0, p1);
+    r.z = ew_apply(op, av.z, bv.z, p0, p1);
+    r.w = ew_apply(op, av.w, bv.w, p0, p1);
+    *reinterpret_cast<float4 *>(out + off[0]) = r;
+  }
+}
+
+__global__ void ew_i64_generic(Iter<3> it, int op, int64_t *out, const int64_t *a,
+                               const int64_t *b, int64_t p0) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    out[off[0]] = ew_apply_i64(op, a[off[1]], b ? b[off[2]] : 0, p0);
+  }
+}
+
+__global__ void ew_equal_i64(Iter<3> it, uint8_t *out, const int64_t *a, const int64_t *b,
+                             int64_t p0) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    out[off[0]] = a[off[1]] == (b ? b[off[2]] : p0);
+  }
+}
+
+__global__ void ew_not(Iter<3> it, uint8_t *out, const uint8_t *a) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    out[off[0]] = !a[off[1]];
+  }
+}
+
+template <typename TI, typename TO>
+__global__ void ew_cast(Iter<3> it, TO *out, const TI *a) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    out[off[0]] = static_cast<TO>(a[off[1]]);
+  }
+}
+
+// operand 0 = out, 1 = x, 2 = bias
+__global__ void bias_gelu_generic(Iter<3> it, float *out, const float *x, const float *bias,
+                                  float c0, float c1, float c2) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    offsets_of(it, i, off);
+    out[off[0]] = gelu_erf(x[off[1]] + bias[off[2]], c0, c1, c2);
+  }
+}
+
+// operand 0 = out, 1 = cond, 2 = x, 3 = y
+__global__ void where_generic(Iter<4> it, float *out, const uint8_t *cond, const float *x,
+                              const float *y, float y_scalar) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[4];
+    offsets_of(it, i, off);
+    out[off[0]] = cond[off[1]] ? x[off[2]] : (y ? y[off[3]] : y_scalar);
+  }
+}
+
+template <int N>
+int make_iter(Iter<N> &it, const fml_tensor *out, const fml_tensor *const *ins, const char *who) {
+  FML_REQUIRE(valid_tensor(out), FML_BAD_ARG, "%s: bad output tensor", who);
+  it.rank = out->rank;
+  for (int i = 0; i < out->rank; ++i) {
+    it.shape[i] = out->shape[i];
+    it.stride[0][i] = out->stride[i];
+  }
+  for (int o = 1; o < N; ++o) {
+    if (!ins[o - 1]) {
+      for (int i = 0; i < out->rank; ++i) it.stride[o][i] = 0;
+      continue;
+    }
+    FML_REQUIRE(valid_tensor(ins[o - 1]), FML_BAD_ARG, "%s: bad input tensor %d", who, o - 1);
+    FML_REQUIRE(broadcast_strides(ins[o - 1], out, it.stride[o]), FML_BAD_ARG,
+                "%s: input %d does not broadcast to the output shape", who, o - 1);
+  }
+  collapse(it);
+  return FML_OK;
+}
+
+bool vec4_ok(const Iter<3> &it, const void *out, const void *a, const void *b) {
+  int l = it.rank - 1;
+  if (it.shape[l] % 4 != 0 || it.stride[0][l] != 1) return false;
+  if (!aligned16(out) || !aligned16(a) || (b && !aligned16(b))) return false;
+  if (it.stride[1][l] != 1 && it.stride[1][l] != 0) return false;
+  if (b && it.stride[2][l] != 1 && it.stride[2][l] != 0) return false;
+  for (int d = 0; d < l; ++d)
+    for (int o = 0; o < 3; ++o)
+      if (it.stride[o][d] % 4 != 0) return false;
+  return true;
+}
+
+}  // namespace
+}  // namespace fml
+
+using namespace fml;
+
+extern "C" int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b,
+                               const fml_tensor *out, double p0, double p1, void *stream) {
+  FML_REQUIRE(a && out, FML_BAD_ARG, "fml_elementwise: null tensor");
+  const bool binary = op <= FML_EQUAL;
+  FML_REQUIRE(!binary || b, FML_BAD_ARG, "fml_elementwise: binary op %d needs two inputs", op);
+  if (!binary) b = nullptr;
+  Iter<3> it;
+  const fml_tensor *ins[2] = {a, b};
+  int st = make_iter(it, out, ins, "fml_elementwise");
+  if (st != FML_OK) return st;
+  if (it.total == 0) return FML_OK;
+  cudaStream_t s = as_stream(stream);
+  const int block = 256;
+  const int grid = grid_for(it.total, block);
+
+  if (op == FML_CAST) {
+#define CAST_CASE(TI, CI, TO, CO)                                                          \
+  if (a->dtype == CI && out->dtype == CO) {                                                \
+    ew_cast<TI, TO><<<grid, block, 0, s>>>(it, (TO *)out->data, (const TI *)a->data);      \
+    FML_CUDA(cudaGetLastError());                                                          \
+    return FML_OK;                                                                         \
+  }
+    CAST_CASE(int64_t, FML_I64, float, FML_F32)
+    CAST_CASE(int32_t, FML_I32, float, FML_F32)
+    CAST_CASE(uint8_t, FML_BOOL, float, FML_F32)
+    CAST_CASE(int64_t, FML_I64, int32_t, FML_I32)
+    CAST_CASE(int32_t, FML_I32, int64_t, FML_I64)
+    CAST_CASE(uint8_t, FML_BOOL, int64_t, FML_I64)
+    CAST_CASE(uint8_t, FML_BOOL, int32_t, FML_I32)
+    CAST_CASE(float, FML_F32, int64_t, FML_I64)
+    CAST_CASE(float, FML_F32, int32_t, FML_I32)
+    CAST_CASE(int64_t, FML_I64, int64_t, FML_I64)
+    CAST_CASE(float, FML_F32, float, FML_F32)
+#undef CAST_CASE
+    FML_REQUIRE(false, FML_UNSUPPORTED, "fml_elementwise: cast %d -> %d", a->dtype, out->dtype);
+  }
+  if (op == FML_COPY) {
+    FML_REQUIRE(a->dtype == out->dtype, FML_BAD_ARG, "fml_elementwise: copy changes dtype");
+    return fml_copy_strided(a, out, stream);
+  }
+  if (op == FML_NOT) {
+    FML_REQUIRE(a->dtype == FML_BOOL && out->dtype == FML_BOOL, FML_UNSUPPORTED,
+                "fml_elementwise: Not takes bool");
+    ew_not<<<grid, block, 0, s>>>(it, (uint8_t *)out->data, (const uint8_t *)a->data);
+    FML_CUDA(cudaGetLastError());
+    return FML_OK;
+  }
+  if (op == FML_EQUAL || op == FML_EQUAL_SCALAR) {
+    FML_REQUIRE(a->dtype == FML_I64 && out->dtype == FML_BOOL && (!b || b->dtype == FML_I64),
+                FML_UNSUPPORTED, "fml_elementwise: Equal takes int64 and yields bool");
+    ew_equal_i64<<<grid, block, 0, s>>>(it, (uint8_t *)out->data, (const int64_t *)a->data,
+                                        b ? (const int64_t *)b->data : nullptr, (int64_t)p0);
+    FML_CUDA(cudaGetLastError());
+    return FML_OK;
+  }
+  FML_REQUIRE(a->dtype == out->dtype && (!b || b->dtype == a->dtype), FML_BAD_ARG,
+              "fml_elementwise: operand dtypes differ");
+  if (a->dtype == FML_I64) {
+    FML_REQUIRE(op == FML_ADD || op == FML_MUL || op == FML_SUB || op == FML_ADD_SCALAR ||
+                    op == FML_MUL_SCALAR || op == FML_RSUB_SCALAR,
+                FML_UNSUPPORTED, "fml_elementwise: op %d has no int64 kernel", op);
+    ew_i64_generic<<<grid, block, 0, s>>>(it, op, (int64_t *)out->data, (const int64_t *)a->data,
+                                          b ? (const int64_t *)b->data : nullptr, (int64_t)p0);
+    FML_CUDA(cudaGetLastError());
+    return FML_OK;
+  }
+  FML_REQUIRE(a->dtype == FML_F32, FML_UNSUPPORTED, "fml_elementwise: dtype %d", a->dtype);
+  FML_REQUIRE(op != FML_EQUAL && (op <= FML_POW || (op >= FML_ADD_SCALAR && op <= FML_RSUB_MUL_SCALAR) ||
+                                  (op >= FML_ERF && op <= FML_SILU)),
+              FML_UNSUPPORTED, "fml_elementwise: unknown op %d", op);
+  const float *bp = b ? (const float *)b->data : nullptr;
+  if (vec4_ok(it, out->data, a->data, bp)) {
+    ew_f32_vec4<<<grid_for(it.total / 4, block), block, 0, s>>>(
+        it, op, (float *)out->data, (const float *)a->data, bp, (float)p0, (float)p1);
+  } else {
+    ew_f32_generic<<<grid, block, 0, s>>>(it, op, (float *)out->data, (const float *)a->data, bp,
+                                          (float)p0, (float)p1);
+  }
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor *out,
+                             float c0, float c1, float c2, void *stream) {
+  FML_REQUIRE(x && bias && out, FML_BAD_ARG, "fml_bias_gelu: null tensor");
+  FML_REQUIRE(x->dtype == FML_F32 && bias->dtype == FML_F32 && out->dtype == FML_F32,
+              FML_UNSUPPORTED, "fml_bias_gelu: fp32 only");
+  Iter<3> it;
+  const fml_tensor *ins[2] = {x, bias};
+  int st = make_iter(it, out, ins, "fml_bias_gelu");
+  if (st != FML_OK) return st;
+  if (it.total == 0) return FML_OK;
+  bias_gelu_generic<<<grid_for(it.total, 256), 256, 0, as_stream(stream)>>>(
+      it, (float *)out->data, (const float *)x->data, (const float *)bias->data, c0, c1, c2);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_tensor *y,
+                         float y_scalar, const fml_tensor *out, void *stream) {
+  FML_REQUIRE(cond && x && out, FML_BAD_ARG, "fml_where: null tensor");
+  FML_REQUIRE(cond->dtype == FML_BOOL && x->dtype == FML_F32 && out->dtype == FML_F32 &&
+                  (!y || y->dtype == FML_F32),
+              FML_UNSUPPORTED, "fml_where: cond bool, x/y/out fp32");
+  Iter<4> it;
+  const fml_tensor *ins[3] = {cond, x, y};
+  int st = make_iter(it, out, ins, "fml_where");
+  if (st != FML_OK) return st;
+  if (it.total == 0) return FML_OK;
+  where_generic<<<grid_for(it.total, 256), 256, 0, as_stream(stream)>>>(
+      it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
+      y ? (const float *)y->data : nullptr, y_scalar);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}

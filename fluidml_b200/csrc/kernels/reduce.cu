@@ -1,0 +1,370 @@
+// Row reductions: Softmax (optionally fused with the attention-score divide and mask add),
+// LayerNormalization (optionally fused with the residual add), ReduceMean, CumSum.
+//
+// HBM-bound.  One warp owns one row; when the reduced axis is contiguous and a multiple of
+// four floats the row is read once with 16-byte loads and kept in registers for the
+// max/sum (softmax) or mean/variance (LayerNorm) passes, then written once.  Reductions
+// use warp shuffles only; no shared memory and no scratch buffer is needed.
+#include "common.cuh"
+
+namespace fml {
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Row iteration: operand 0 = out, 1 = in, 2 = aux0 (mask / residual).  The reduced axis is
+// removed from `rows`; its extent and per-operand strides are passed separately.
+struct RowArgs {
+  Iter<3> rows;
+  int64_t len;
+  int64_t axis_stride[3];
+};
+
+// ---- softmax -----------------------------------------------------------------------
+template <int NV>  // float4 per lane
+__global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const float *mask,
+                                 float divisor) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (row >= a.rows.total) return;
+  int64_t off[3];
+  offsets_of(a.rows, row, off);
+  const int64_t n4 = a.len >> 2;
+  const float4 *x4 = reinterpret_cast<const float4 *>(in + off[1]);
+  const bool mvec = mask && a.axis_stride[2] == 1;
+  float4 v[NV];
+  float mx = -3.402823466e+38f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    int64_t c = lane + 32 * i;
+    if (c < n4) {
+      float4 t = x4[c];
+      if (divisor != 1.0f) { t.x = t.x / divisor; t.y = t.y / divisor; t.z = t.z / divisor; t.w = t.w / divisor; }
+      if (mask) {
+        float4 m;
+        if (mvec) m = *reinterpret_cast<const float4 *>(mask + off[2] + c * 4);
+        else { float s = mask[off[2]]; m = make_float4(s, s, s, s); }
+        t.x += m.x; t.y += m.y; t.z += m.z; t.w += m.w;
+      }
+      v[i] = t;
+      mx = fmaxf(mx, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < n4) {
+      v[i].x = expf(v[i].x - mx); v[i].y = expf(v[i].y - mx);
+      v[i].z = expf(v[i].z - mx); v[i].w = expf(v[i].w - mx);
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  sum = warp_sum(sum);
+  float4 *y4 = reinterpret_cast<float4 *>(out + off[0]);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    int64_t c = lane + 32 * i;
+    if (c < n4) y4[c] = make_float4(v[i].x / sum, v[i].y / sum, v[i].z / sum, v[i].w / sum);
+  }
+}
+
+__global__ void softmax_rows_generic(RowArgs a, float *out, const float *in, const float *mask,
+                                     float divisor) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (row >= a.rows.total) return;
+  int64_t off[3];
+  offsets_of(a.rows, row, off);
+  auto load = [&](int64_t c) {
+    float t = in[off[1] + c * a.axis_stride[1]];
+    if (divisor != 1.0f) t = t / divisor;
+    if (mask) t += mask[off[2] + c * a.axis_stride[2]];
+    return t;
+  };
+  float mx = -3.402823466e+38f;
+  for (int64_t c = lane; c < a.len; c += 32) mx = fmaxf(mx, load(c));
+  mx = warp_max(mx);
+  float sum = 0.0f;
+  for (int64_t c = lane; c < a.len; c += 32) sum += expf(load(c) - mx);
+  sum = warp_sum(sum);
+  for (int64_t c = lane; c < a.len; c += 32)
+    out[off[0] + c * a.axis_stride[0]] = expf(load(c) - mx) / sum;
+}
+
+// ---- LayerNorm ---------------------------------------------------------------------
+template <int NV>
+__global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const float *res,
+                                   const float *gamma, const float *beta, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (row >= a.rows.total) return;
+  int64_t off[3];
+  offsets_of(a.rows, row, off);
+  const int64_t n4 = a.len >> 2;
+  const float4 *x4 = reinterpret_cast<const float4 *>(in + off[1]);
+  const float4 *r4 = res ? reinterpret_cast<const float4 *>(res + off[2]) : nullptr;
+  float4 v[NV];
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    int64_t c = lane + 32 * i;
+    if (c < n4) {
+      float4 t = x4[c];
+      if (r4) { float4 r = r4[c]; t.x += r.x; t.y += r.y; t.z += r.z; t.w += r.w; }
+      v[i] = t;
+      s += (t.x + t.y) + (t.z + t.w);
+    }
+  }
+  const float mean = warp_sum(s) / (float)a.len;
+  float q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < n4) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+  }
+  const float var = warp_sum(q) / (float)a.len;
+  const float inv = 1.0f / sqrtf(var + eps);
+  const float4 *g4 = reinterpret_cast<const float4 *>(gamma), *b4 = reinterpret_cast<const float4 *>(beta);
+  float4 *y4 = reinterpret_cast<float4 *>(out + off[0]);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    int64_t c = lane + 32 * i;
+    if (c < n4) {
+      float4 g = g4[c], b = b4[c];
+      y4[c] = make_float4(v[i].x * inv * g.x + b.x, v[i].y * inv * g.y + b.y,
+                          v[i].z * inv * g.z + b.z, v[i].w * inv * g.w + b.w);
+    }
+  }
+}
+
+__global__ void layernorm_rows_generic(RowArgs a, float *out, const float *in, const float *res,
+                                       const float *gamma, int64_t gstride, const float *beta,
+                                       int64_t bstride, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (row >= a.rows.total) return;
+  int64_t off[3];
+  offsets_of(a.rows, row, off);
+  auto load = [&](int64_t c) {
+    float t = in[off[1] + c * a.axis_stride[1]];
+    if (res) t += res[off[2] + c * a.axis_stride[2]];
+    return t;
+  };
+  float s = 0.0f;
+  for (int64_t c = lane; c < a.len; c += 32) s += load(c);
+  const float mean = warp_sum(s) / (float)a.len;
+  float q = 0.0f;
+  for (int64_t c = lane; c < a.len; c += 32) { float d = load(c) - mean; q += d * d; }
+  const float inv = 1.0f / sqrtf(warp_sum(q) / (float)a.len + eps);
+  for (int64_t c = lane; c < a.len; c += 32)
+    out[off[0] + c * a.axis_stride[0]] = (load(c) - mean) * inv * gamma[c * gstride] + beta[c * bstride];
+}
+
+// ---- ReduceMean / CumSum -------------------------------------------------------------
+struct ReduceArgs {
+  Iter<2> keep;    // over the output shape: operand 0 = out, 1 = in (reduced axes stride 0 in out view)
+  int rrank;
+  int64_t rshape[kMaxDims], rstride[kMaxDims];
+  int64_t count;
+};
+
+__global__ void reduce_mean_kernel(ReduceArgs a, float *out, const float *in) {
+  const int lane = threadIdx.x & 31;
+  const int64_t o = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (o >= a.keep.total) return;
+  int64_t off[2];
+  offsets_of(a.keep, o, off);
+  float s = 0.0f;
+  for (int64_t r = lane; r < a.count; r += 32) {
+    int64_t l = r, io = off[1];
+    for (int d = a.rrank - 1; d >= 0; --d) {
+      int64_t q = l / a.rshape[d];
+      io += (l - q * a.rshape[d]) * a.rstride[d];
+      l = q;
+    }
+    s += in[io];
+  }
+  s = warp_sum(s);
+  if (lane == 0) out[off[0]] = s / (float)a.count;
+}
+
+__global__ void cumsum_kernel(RowArgs a, int64_t *out, const int64_t *in) {
+  const int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (row >= a.rows.total) return;
+  int64_t off[3];
+  offsets_of(a.rows, row, off);
+  int64_t s = 0;
+  for (int64_t c = 0; c < a.len; ++c) {
+    s += in[off[1] + c * a.axis_stride[1]];
+    out[off[0] + c * a.axis_stride[0]] = s;
+  }
+}
+
+int make_rows(RowArgs &a, const fml_tensor *out, const fml_tensor *in, const fml_tensor *aux,
+              int axis, const char *who) {
+  FML_REQUIRE(valid_tensor(in) && valid_tensor(out), FML_BAD_ARG, "%s: bad tensor", who);
+  FML_REQUIRE(in->rank == out->rank && in->rank >= 1, FML_BAD_ARG, "%s: rank mismatch", who);
+  if (axis < 0) axis += in->rank;
+  FML_REQUIRE(axis >= 0 && axis < in->rank, FML_BAD_ARG, "%s: axis out of range", who);
+  for (int i = 0; i < in->rank; ++i)
+    FML_REQUIRE(in->shape[i] == out->shape[i], FML_BAD_ARG, "%s: shape mismatch", who);
+  int64_t aux_stride[kMaxDims] = {0};
+  if (aux) {
+    FML_REQUIRE(valid_tensor(aux) && aux->dtype == in->dtype, FML_BAD_ARG, "%s: bad auxiliary tensor", who);
+    FML_REQUIRE(broadcast_strides(aux, in, aux_stride), FML_BAD_ARG,
+                "%s: auxiliary tensor does not broadcast to the input", who);
+  }
+  a.len = in->shape[axis];
+  a.axis_stride[0] = out->stride[axis];
+  a.axis_stride[1] = in->stride[axis];
+  a.axis_stride[2] = aux_stride[axis];
+  a.rows.rank = in->rank;
+  for (int i = 0; i < in->rank; ++i) {
+    a.rows.shape[i] = i == axis ? 1 : in->shape[i];
+    a.rows.stride[0][i] = out->stride[i];
+    a.rows.stride[1][i] = in->stride[i];
+    a.rows.stride[2][i] = aux_stride[i];
+  }
+  collapse(a.rows);
+  return FML_OK;
+}
+
+bool rows_vec_ok(const RowArgs &a, const void *out, const void *in, const void *aux) {
+  if (a.len % 4 != 0 || a.len > 4096) return false;
+  if (a.axis_stride[0] != 1 || a.axis_stride[1] != 1) return false;
+  if (aux && a.axis_stride[2] != 1 && a.axis_stride[2] != 0) return false;
+  if (!aligned16(out) || !aligned16(in) || (aux && !aligned16(aux))) return false;
+  for (int d = 0; d < a.rows.rank; ++d)
+    for (int o = 0; o < 3; ++o)
+      if (a.rows.stride[o][d] % 4 != 0) return false;
+  return true;
+}
+
+}  // namespace
+}  // namespace fml
+
+using namespace fml;
+
+#define DISPATCH_NV(len, KERNEL, ...)                                                      \
+  do {                                                                                     \
+    int64_t per_lane = ((len) / 4 + 31) / 32;                                              \
+    if (per_lane <= 1) KERNEL<1> __VA_ARGS__;                                              \
+    else if (per_lane <= 2) KERNEL<2> __VA_ARGS__;                                         \
+    else if (per_lane <= 4) KERNEL<4> __VA_ARGS__;                                         \
+    else if (per_lane <= 8) KERNEL<8> __VA_ARGS__;                                         \
+    else if (per_lane <= 16) KERNEL<16> __VA_ARGS__;                                       \
+    else KERNEL<32> __VA_ARGS__;                                                           \
+  } while (0)
+
+extern "C" int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
+                           const fml_tensor *out, int axis, void *stream) {
+  FML_REQUIRE(in && out, FML_BAD_ARG, "fml_softmax: null tensor");
+  FML_REQUIRE(in->dtype == FML_F32 && out->dtype == FML_F32, FML_UNSUPPORTED, "fml_softmax: fp32 only");
+  FML_REQUIRE(divisor != 0.0f, FML_BAD_ARG, "fml_softmax: divisor is zero");
+  RowArgs a;
+  int st = make_rows(a, out, in, mask, axis, "fml_softmax");
+  if (st != FML_OK) return st;
+  if (a.rows.total == 0 || a.len == 0) return FML_OK;
+  cudaStream_t s = as_stream(stream);
+  const unsigned grid = (unsigned)((a.rows.total * 32 + 255) / 256);
+  const float *mp = mask ? (const float *)mask->data : nullptr;
+  if (rows_vec_ok(a, out->data, in->data, mp)) {
+    DISPATCH_NV(a.len, softmax_rows_vec, <<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, mp, divisor));
+  } else {
+    softmax_rows_generic<<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, mp, divisor);
+  }
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_layernorm(const fml_tensor *in, const fml_tensor *residual,
+                             const fml_tensor *scale, const fml_tensor *bias, const fml_tensor *out,
+                             int axis, float eps, void *stream) {
+  FML_REQUIRE(in && out && scale && bias, FML_BAD_ARG, "fml_layernorm: null tensor");
+  FML_REQUIRE(in->dtype == FML_F32 && out->dtype == FML_F32 && scale->dtype == FML_F32 &&
+                  bias->dtype == FML_F32, FML_UNSUPPORTED, "fml_layernorm: fp32 only");
+  RowArgs a;
+  int st = make_rows(a, out, in, residual, axis, "fml_layernorm");
+  if (st != FML_OK) return st;
+  FML_REQUIRE(valid_tensor(scale) && valid_tensor(bias) && numel(scale) == a.len && numel(bias) == a.len,
+              FML_BAD_ARG, "fml_layernorm: scale/bias must hold one value per normalised element");
+  if (a.rows.total == 0 || a.len == 0) return FML_OK;
+  cudaStream_t s = as_stream(stream);
+  const unsigned grid = (unsigned)((a.rows.total * 32 + 255) / 256);
+  const float *rp = residual ? (const float *)residual->data : nullptr;
+  // stride of the (single) non-unit dim of scale / bias
+  auto vec_stride = [](const fml_tensor *t) {
+    for (int i = 0; i < t->rank; ++i) if (t->shape[i] != 1) return t->stride[i];
+    return (int64_t)1;
+  };
+  const int64_t gs = vec_stride(scale), bs = vec_stride(bias);
+  const bool res_vec = !residual || a.axis_stride[2] == 1;
+  if (rows_vec_ok(a, out->data, in->data, rp) && res_vec && gs == 1 && bs == 1 &&
+      aligned16(scale->data) && aligned16(bias->data)) {
+    DISPATCH_NV(a.len, layernorm_rows_vec, <<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps));
+  } else {
+    layernorm_rows_generic<<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, rp,
+                                                (const float *)scale->data, gs,
+                                                (const float *)bias->data, bs, eps);
+  }
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_reduce_mean(const fml_tensor *in, const fml_tensor *out, const int32_t *reduce,
+                               void *stream) {
+  FML_REQUIRE(valid_tensor(in) && valid_tensor(out) && reduce, FML_BAD_ARG, "fml_reduce_mean: bad argument");
+  FML_REQUIRE(in->dtype == FML_F32 && out->dtype == FML_F32 && in->rank == out->rank, FML_BAD_ARG,
+              "fml_reduce_mean: fp32, keepdims layout");
+  ReduceArgs a;
+  a.keep.rank = in->rank;
+  a.rrank = 0;
+  a.count = 1;
+  for (int i = 0; i < in->rank; ++i) {
+    if (reduce[i]) {
+      FML_REQUIRE(out->shape[i] == 1, FML_BAD_ARG, "fml_reduce_mean: reduced dims must be 1 in the output");
+      a.keep.shape[i] = 1;
+      a.keep.stride[0][i] = 0;
+      a.keep.stride[1][i] = 0;
+      a.rshape[a.rrank] = in->shape[i];
+      a.rstride[a.rrank++] = in->stride[i];
+      a.count *= in->shape[i];
+    } else {
+      FML_REQUIRE(out->shape[i] == in->shape[i], FML_BAD_ARG, "fml_reduce_mean: shape mismatch");
+      a.keep.shape[i] = in->shape[i];
+      a.keep.stride[0][i] = out->stride[i];
+      a.keep.stride[1][i] = in->stride[i];
+    }
+  }
+  collapse(a.keep);
+  if (a.keep.total == 0 || a.count == 0) return FML_OK;
+  reduce_mean_kernel<<<(unsigned)((a.keep.total * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(
+      a, (float *)out->data, (const float *)in->data);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_cumsum(const fml_tensor *in, const fml_tensor *out, int axis, void *stream) {
+  FML_REQUIRE(in && out, FML_BAD_ARG, "fml_cumsum: null tensor");
+  FML_REQUIRE(in->dtype == FML_I64 && out->dtype == FML_I64, FML_UNSUPPORTED, "fml_cumsum: int64 only");
+  RowArgs a;
+  int st = make_rows(a, out, in, nullptr, axis, "fml_cumsum");
+  if (st != FML_OK) return st;
+  if (a.rows.total == 0) return FML_OK;
+  cumsum_kernel<<<grid_for(a.rows.total, 128, 1 << 20), 128, 0, as_stream(stream)>>>(
+      a, (int64_t *)out->data, (const int64_t *)in->data);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}

@@ -1,0 +1,136 @@
+// Runtime plumbing of the C ABI: error text, device selection, buffers, copies, streams and
+// the per-device status word that kernels with bounded waits or clamped indices write.
+#include "common.cuh"
+#include <cstdarg>
+#include <mutex>
+
+namespace fml {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  set_error("%s: %s", what, cudaGetErrorString(e));
+  return e == cudaErrorMemoryAllocation ? FML_OUT_OF_MEMORY : FML_CUDA_ERROR;
+}
+
+static int *g_status[64] = {nullptr};
+static std::mutex g_status_mu;
+
+int *device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  if (!g_status[dev]) {
+    int *p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+}  // namespace fml
+
+using namespace fml;
+
+extern "C" {
+
+const char *fml_last_error(void) { return g_error; }
+
+int fml_device_count(int *count) {
+  FML_REQUIRE(count, FML_BAD_ARG, "fml_device_count: null argument");
+  FML_CUDA(cudaGetDeviceCount(count));
+  return FML_OK;
+}
+
+int fml_set_device(int device) {
+  FML_CUDA(cudaSetDevice(device));
+  return FML_OK;
+}
+
+int fml_malloc(void **ptr, size_t bytes) {
+  FML_REQUIRE(ptr, FML_BAD_ARG, "fml_malloc: null argument");
+  FML_CUDA(cudaMalloc(ptr, bytes ? bytes : 1));
+  return FML_OK;
+}
+
+int fml_free(void *ptr) {
+  FML_CUDA(cudaFree(ptr));
+  return FML_OK;
+}
+
+int fml_memset(void *ptr, int value, size_t bytes, void *stream) {
+  FML_CUDA(cudaMemsetAsync(ptr, value, bytes, as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream) {
+  FML_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
+  FML_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream) {
+  FML_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_host_alloc_pinned(void **ptr, size_t bytes) {
+  FML_REQUIRE(ptr, FML_BAD_ARG, "fml_host_alloc_pinned: null argument");
+  FML_CUDA(cudaMallocHost(ptr, bytes ? bytes : 1));
+  return FML_OK;
+}
+
+int fml_host_free_pinned(void *ptr) {
+  FML_CUDA(cudaFreeHost(ptr));
+  return FML_OK;
+}
+
+int fml_stream_create(void **stream) {
+  FML_REQUIRE(stream, FML_BAD_ARG, "fml_stream_create: null argument");
+  cudaStream_t s;
+  FML_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = s;
+  return FML_OK;
+}
+
+int fml_stream_destroy(void *stream) {
+  FML_CUDA(cudaStreamDestroy(as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_stream_sync(void *stream) {
+  FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_check_device(void *stream) {
+  FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  int *w = device_status_word();
+  FML_REQUIRE(w, FML_CUDA_ERROR, "fml_check_device: no status word");
+  int v = 0;
+  FML_CUDA(cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v) FML_CUDA(cudaMemset(w, 0, sizeof(int)));
+  if (v & kStatusTimeout) {
+    set_error("a bounded device-side wait expired");
+    return FML_DEVICE_TIMEOUT;
+  }
+  if (v & kStatusIndexRange) {
+    set_error("a gather index was outside the table and was clamped");
+    return FML_INDEX_OUT_OF_RANGE;
+  }
+  return FML_OK;
+}
+
+}  // extern "C"

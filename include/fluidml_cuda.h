@@ -1,0 +1,254 @@
+/*
+ * fluidml_cuda.h -- C ABI of the sm_100a kernel library that sits under Kernel::Run.
+ *
+ * In the reference every operator kernel emits a linalg.generic over strided memrefs that
+ * LLVM compiles for the CPU (src/structure/kernel/kernel/<op>.cpp, lowered by
+ * src/worker/lower.cpp:37-59).  Each entry point below replaces one family of those
+ * emitters with a CUDA launch on device memory.  All tensors are described the way the
+ * reference addresses them: a base pointer, a static shape and ELEMENT strides derived
+ * from a layout permutation (src/utils/utils.cpp:64-102).
+ *
+ * Conventions
+ *   - every pointer inside an fml_tensor is a DEVICE pointer; fml_tensor structs
+ *     themselves live on the host and are read during the call;
+ *   - dtype codes are the ONNX TensorProto codes the reference uses
+ *     (src/utils/type.cpp:8-23);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream); calls only
+ *     enqueue work, they never synchronise, and they may be stream-captured unless a
+ *     function says otherwise;
+ *   - the return value is an fml_status; nothing is launched when it is not FML_OK.
+ *     The reference has no error path (asserts or __builtin_unreachable,
+ *     e.g. src/worker/converter.cpp:268-274); bad arguments here are reported, never UB.
+ */
+#ifndef FLUIDML_CUDA_H_
+#define FLUIDML_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FML_MAX_RANK 8
+
+typedef enum fml_status {
+  FML_OK = 0,
+  FML_BAD_ARG = 1,        /* null pointer, rank/shape mismatch, axis out of range        */
+  FML_UNSUPPORTED = 2,    /* dtype or variant no kernel exists for                        */
+  FML_MISALIGNED = 3,     /* a fast path was forced on operands that cannot take it       */
+  FML_CUDA_ERROR = 4,     /* a CUDA runtime/driver call failed; see fml_last_error()      */
+  FML_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up (read by fml_check_device)*/
+  FML_OUT_OF_MEMORY = 6,
+  FML_INDEX_OUT_OF_RANGE = 7 /* a gather index fell outside the table (it was clamped)    */
+} fml_status;
+
+typedef enum fml_dtype {
+  FML_F32 = 1, FML_I32 = 6, FML_I64 = 7, FML_BOOL = 9
+} fml_dtype;
+
+typedef struct fml_tensor {
+  void *data;
+  int32_t dtype;
+  int32_t rank;
+  int64_t shape[FML_MAX_RANK];
+  int64_t stride[FML_MAX_RANK]; /* in elements; 0 is allowed on inputs (broadcast)        */
+} fml_tensor;
+
+/* ---------------------------------------------------------------- runtime plumbing
+ * What mlir::ExecutionEngine + malloc gave the reference runner
+ * (src/worker/runner.cpp:56-120): device selection, buffers, copies, streams. */
+const char *fml_last_error(void);
+int fml_device_count(int *count);
+int fml_set_device(int device);
+int fml_malloc(void **ptr, size_t bytes);
+int fml_free(void *ptr);
+int fml_memset(void *ptr, int value, size_t bytes, void *stream);
+int fml_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+int fml_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+int fml_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+int fml_host_alloc_pinned(void **ptr, size_t bytes);
+int fml_host_free_pinned(void *ptr);
+int fml_stream_create(void **stream);
+int fml_stream_destroy(void *stream);
+int fml_stream_sync(void *stream);
+/* Reads and clears the device status word kernels write when a bounded wait expires or a
+ * gather index is clamped.  Synchronises `stream`.  Returns FML_OK, FML_DEVICE_TIMEOUT or
+ * FML_INDEX_OUT_OF_RANGE. */
+int fml_check_device(void *stream);
+
+/* ---------------------------------------------------------------- elementwise
+ * Binary ops broadcast numpy-style (right-aligned; size-1 dims pinned to index 0), as
+ * GetBroadcastAffineMaps does (src/structure/kernel/kernel/utils.cpp:15-51).  A scalar
+ * constant operand is a rank-0 tensor or, cheaper, FML_*_SCALAR ops taking it in p0. */
+typedef enum fml_ew_op {
+  /* binary: out = a (op) b                       reference kernel                        */
+  FML_ADD = 0,     /* add.cpp:83-124   AddCommonKernel                                    */
+  FML_MUL = 1,     /* mul.cpp:56-99    MulCommonKernel                                    */
+  FML_DIV = 2,     /* div.cpp:70-105   DivCommonKernel (true division)                    */
+  FML_SUB = 3,     /* sub.cpp:71-99    SubCommonKernel                                    */
+  FML_POW = 4,     /* pow.cpp:15-61    PowKernel with a tensor exponent (ONNX)            */
+  FML_EQUAL = 5,   /* equal.cpp:14-51  int64 == int64 -> bool                             */
+  /* unary with scalar p0 (b == NULL)                                                    */
+  FML_ADD_SCALAR = 16,  /* add.cpp:22-79   AddConstantKernel      out = a + p0            */
+  FML_MUL_SCALAR = 17,  /* mul.cpp:19-54   MulConstantKernel      out = a * p0            */
+  FML_DIV_SCALAR = 18,  /* div.cpp:18-66   DivConstantRhsKernel   out = a / p0            */
+  FML_RSUB_SCALAR = 19, /* sub.cpp:16-67   SubConstantLhsKernel   out = p0 - a            */
+  FML_POW_SCALAR = 20,  /* pow.cpp:15-61   PowKernel              out = powf(a, p0)       */
+  FML_EQUAL_SCALAR = 21,/* equal.cpp:14-51 EqualKernel            out = (a == (int64)p0)  */
+  FML_CLIP = 22,        /* clip.cpp:13-48  ClipKernel             out = min(max(a,p0),p1) */
+  FML_RSUB_MUL_SCALAR = 23, /* unsqueeze_sub_mul.cpp:19-70        out = (p0 - a) * p1     */
+  /* unary, no parameter                                                                 */
+  FML_ERF = 32,     /* erf.cpp:18-45                                                      */
+  FML_TANH = 33,    /* tanh.cpp:12-40                                                     */
+  FML_SQRT = 34,    /* sqrt.cpp:13-36                                                     */
+  FML_NEG = 35,     /* neg.cpp:17-40                                                      */
+  FML_RELU = 36,    /* relu.cpp:12-46                                                     */
+  FML_SIGMOID = 37, /* no reference kernel (parser.cpp:320-326 rejects it): ONNX          */
+  FML_NOT = 38,     /* not.cpp:11-41                                                      */
+  FML_COPY = 39,    /* dropout.cpp:13-33 (identity); same-dtype strided copy              */
+  FML_CAST = 40,    /* cast.cpp:12-62; also int -> f32                                    */
+  FML_EXP = 41,
+  FML_SILU = 42     /* x * sigmoid(x): Sigmoid followed by Mul, fused                     */
+} fml_ew_op;
+
+int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b, const fml_tensor *out,
+                    double p0, double p1, void *stream);
+
+/* AddDivErfAddMulMulKernel (add_div_erf_add_mul_mul.cpp:29-132):
+ * t = x + bias ; out = t * (erf(t / c0) + c1) * c2   (bias + exact GELU in one pass). */
+int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor *out,
+                  float c0, float c1, float c2, void *stream);
+
+/* WhereConstantCond{ConstantScalarY,ConstantTensorY}Kernel (where.cpp:30-80, :90-150):
+ * out = cond ? x : y, all broadcast to out.  y == NULL takes the scalar y_scalar. */
+int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_tensor *y, float y_scalar,
+              const fml_tensor *out, void *stream);
+
+/* ---------------------------------------------------------------- data movement
+ * fml_copy_strided: out[i] = in[i] for every logical index i of the common shape.  The
+ * host expresses Transpose (transpose.cpp:19-48: a permuted-stride view of the input),
+ * Slice (slice.cpp:17-55: an offset view), Concat2 (concat.cpp:18-68: two calls into
+ * offset views of the output) and the interior of Pad (pad.cpp:15-51) through it.
+ * Bit-exact for every dtype. */
+int fml_copy_strided(const fml_tensor *in, const fml_tensor *out, void *stream);
+
+/* ReshapeKernel / UnsqueezeKernel / SqueezeKernel / FlattenKernel (reshape.cpp:18-64,
+ * unsqueeze.cpp:20-63, squeeze.cpp:17-54, flatten.cpp:15-63): the e-th element in logical
+ * row-major order of `in` becomes the e-th element of `out`, whatever the two layouts. */
+int fml_reshape_copy(const fml_tensor *in, const fml_tensor *out, void *stream);
+
+/* Gather (gather.cpp:100-139, :149-186, :195-272): out[pre.., i.., post..] =
+ * data[pre.., indices[i..], post..], int64 indices (device memory).  Indices outside
+ * [0, data.shape[axis]) are clamped and recorded in the device status word. */
+int fml_gather(const fml_tensor *data, const fml_tensor *indices, const fml_tensor *out,
+               int axis, void *stream);
+
+/* GatherConstantDataTensorAddTensorLhsAddTensorLhsKernel (gather_add_add.cpp:25-163):
+ * out = table[ids] + add0 + add1 (word + position + token-type embeddings), add0/add1
+ * broadcast to out; either may be NULL. */
+int fml_embedding(const fml_tensor *table, const fml_tensor *ids, const fml_tensor *add0,
+                  const fml_tensor *add1, const fml_tensor *out, void *stream);
+
+/* PadKernel (pad.cpp:15-51), constant mode with value 0 (the reference leaves the border
+ * untouched and relies on a zeroed arena). */
+int fml_pad(const fml_tensor *in, const fml_tensor *out, const int64_t *pads_begin, void *stream);
+
+/* ---------------------------------------------------------------- reductions
+ * SoftmaxKernel (softmax.cpp:22-139) in one pass.  With `mask` != NULL and/or
+ * divisor != 1 it computes softmax(in / divisor + mask) (mask broadcast to in): the
+ * Div + Add + Softmax chain of attention fused.  No scratch (the reference needs one
+ * float per row, src/structure/flow/node.cpp:1355-1368). */
+int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
+                const fml_tensor *out, int axis, void *stream);
+
+/* LayerNormalizationConstantScaleBiasKernel (layer_normalization.cpp:33-220) in one pass:
+ * mean, biased variance about the mean, y = (x-mean) * (1/sqrtf(var+eps)) * scale + bias.
+ * With `residual` != NULL the input is in + residual (Add + LayerNorm fused).  No scratch
+ * (the reference needs one float per row, node.cpp:972-985). */
+int fml_layernorm(const fml_tensor *in, const fml_tensor *residual, const fml_tensor *scale,
+                  const fml_tensor *bias, const fml_tensor *out, int axis, float eps,
+                  void *stream);
+
+/* ReduceMeanKernel (reduce_mean.cpp:16-98), keepdims = 1; `reduce[i]` != 0 marks a reduced
+ * axis. */
+int fml_reduce_mean(const fml_tensor *in, const fml_tensor *out, const int32_t *reduce,
+                    void *stream);
+
+/* CumSumKernel (cum_sum.cpp:53-87): int64, forward, inclusive. */
+int fml_cumsum(const fml_tensor *in, const fml_tensor *out, int axis, void *stream);
+
+/* ---------------------------------------------------------------- GEMM
+ * MatMulKernel (matmul.cpp:28-59 with the broadcast maps of utils.cpp:62-146) and
+ * GemmConstantBiasKernel (gemm.cpp:39-182).  C[.., m, n] = sum_k A[.., m, k] * B[.., k, n]
+ * over the last two dims, leading dims broadcast.  transA/transB of Gemm are expressed by
+ * the caller through strides.  The epilogue is applied to the fp32 accumulator in this
+ * order:   v = acc / divisor ; v = alpha * v + beta * bias ; v = act(v) ; v += residual.
+ * `bias` and `residual` broadcast to C.
+ */
+typedef enum fml_gemm_act {
+  FML_ACT_NONE = 0,
+  FML_ACT_GELU_ERF = 1, /* v * (erf(v / c0) + c1) * c2, constants in act_param[3]         */
+  FML_ACT_RELU = 2,
+  FML_ACT_TANH = 3,
+  FML_ACT_SIGMOID = 4
+} fml_gemm_act;
+
+typedef enum fml_gemm_precision {
+  FML_GEMM_AUTO = 0,   /* 3xTF32 tensor-core path when operands allow it, else fp32 FMA   */
+  FML_GEMM_FP32 = 1,   /* CUDA-core fp32 FMA, any strides                                 */
+  FML_GEMM_3XTF32 = 2, /* tcgen05, hi/lo split: error ~2^-21 relative per product         */
+  FML_GEMM_TF32 = 3    /* tcgen05, single pass: error ~2^-11 relative per product         */
+} fml_gemm_precision;
+
+typedef struct fml_gemm_params {
+  int32_t precision;   /* fml_gemm_precision                                              */
+  int32_t act;         /* fml_gemm_act                                                    */
+  float divisor;       /* 1 = none                                                        */
+  float alpha, beta;   /* Gemm attributes; MatMul uses 1, 1                               */
+  float act_param[3];
+  int32_t split_k;     /* 0 = let the library choose                                      */
+  int32_t tile_n;      /* 0 = let the library choose (32, 64 or 128)                      */
+} fml_gemm_params;
+
+void fml_gemm_default_params(fml_gemm_params *p);
+
+/* Scratch bytes the chosen configuration needs (split-K partial sums and tile counters).
+ * 0 when no split is used.  The workspace must be zero-filled once before its first use;
+ * the kernel leaves its counters at zero again. */
+int fml_gemm_workspace_bytes(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                             const fml_gemm_params *p, size_t *bytes);
+
+int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+             const fml_tensor *bias, const fml_tensor *residual, const fml_gemm_params *p,
+             void *workspace, size_t workspace_bytes, void *stream);
+
+/* Reports which path fml_gemm would take for these operands: 0 = fp32 FMA, 1 = tcgen05. */
+int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                               const fml_gemm_params *p, int *uses);
+
+/* ---------------------------------------------------------------- convolution, pooling
+ * ConvWithoutPaddingKernel / ConvWithPaddingKernel (conv.cpp:27-280): NCHW x OIHW, 1-D or
+ * 2-D, group == 1 or depthwise (group == C, multiplier 1) as in the reference (:103-149).
+ * ONNX semantics for strides, dilations, zero padding and per-channel bias (the reference
+ * ignores strides/dilations, :68-76, and adds bias[1] everywhere, :181-184).  Padding is
+ * implicit: no padded copy, so the node needs no scratch (reference: node.cpp:500-519). */
+typedef struct fml_conv_params {
+  int64_t pads_begin[2], strides[2], dilations[2];
+  int64_t group;
+  int32_t act;       /* fml_gemm_act applied after bias (Relu fusion)                     */
+  int32_t precision; /* fml_gemm_precision for the group == 1 implicit-GEMM path          */
+} fml_conv_params;
+
+int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
+             const fml_tensor *y, const fml_conv_params *p, void *stream);
+
+/* MaxPoolWithoutPaddingKernel / AveragePoolWithoutPaddingKernel (maxpool.cpp:17-82,
+ * averagepool.cpp:19-87): 2-D windows, no padding.  mode 0 = max, 1 = average. */
+int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t *kernel,
+               const int64_t *strides, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLUIDML_CUDA_H_ */

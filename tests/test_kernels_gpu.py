@@ -1,0 +1,332 @@
+"""GPU parity of the memory-bound kernels against the CPU oracle, through the C ABI.
+
+Bit-exact for data movement (Transpose / Reshape / Gather / Slice / Concat / Where / Pad);
+fp32 elementwise and reductions within the tolerance written beside each case.
+"""
+import itertools
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from fluidml_b200 import cabi
+from fluidml_b200.cabi import DeviceTensor as DT
+from oracle import oracle as orc
+
+RNG = np.random.Generator(np.random.PCG64(1234))
+
+
+def rnd(*shape):
+    return RNG.standard_normal(shape).astype(np.float32)
+
+
+def relerr(got, ref):
+    ref = ref.astype(np.float64)
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(1e-30, np.abs(ref).max()))
+
+
+# ------------------------------------------------------------------ elementwise
+BIN_CASES = [
+    ((1, 128, 768), (768,)),            # bias add
+    ((1, 128, 768), (1, 128, 768)),     # residual
+    ((1, 12, 128, 128), (1, 1, 1, 128)),  # attention mask
+    ((3, 5, 7), (5, 1)),                # ragged broadcast, odd sizes
+    ((2, 1, 3), (1, 4, 3)),             # both sides broadcast
+    ((0, 4), (4,)),                     # empty
+]
+
+
+@pytest.mark.parametrize("op,name", [(cabi.ADD, "Add"), (cabi.MUL, "Mul"), (cabi.SUB, "Sub"),
+                                     (cabi.DIV, "Div")])
+@pytest.mark.parametrize("sa,sb", BIN_CASES)
+def test_binary_broadcast(op, name, sa, sb):
+    a, b = rnd(*sa), rnd(*sb) + 3.0
+    so = np.broadcast_shapes(sa, sb)
+    ref = orc.binary(name, a, b, np.empty(so, np.float32))
+    out = DT(so, np.float32)
+    cabi.elementwise(op, DT.from_numpy(a), DT.from_numpy(b), out)
+    assert np.array_equal(out.numpy(), ref)  # one IEEE operation per element: bit-exact
+
+
+@pytest.mark.parametrize("layouts", [((0, 1, 2), (2, 0, 1), (1, 2, 0)), ((2, 1, 0), (0, 1, 2), (0, 2, 1))])
+def test_binary_any_layout(layouts):
+    la, lb, lo = layouts
+    a, b = rnd(4, 6, 8), rnd(4, 6, 8)
+    out = DT((4, 6, 8), np.float32, lo)
+    cabi.elementwise(cabi.ADD, DT.from_numpy(a, la), DT.from_numpy(b, lb), out)
+    assert np.array_equal(out.numpy(), a + b)
+
+
+@pytest.mark.parametrize("op,name,p0,p1,tol", [
+    (cabi.ERF, "Erf", 0, 0, 2e-6), (cabi.TANH, "Tanh", 0, 0, 2e-6), (cabi.SQRT, "Sqrt", 0, 0, 0),
+    (cabi.NEG, "Neg", 0, 0, 0), (cabi.RELU, "Relu", 0, 0, 0), (cabi.SIGMOID, "Sigmoid", 0, 0, 2e-6),
+    (cabi.CLIP, "Clip", -0.5, 0.75, 0)])
+def test_unary(op, name, p0, p1, tol):
+    x = np.abs(rnd(1, 128, 3072)) if name == "Sqrt" else rnd(1, 128, 3072)
+    ref = orc.unary(name, x, np.empty_like(x), p0, p1)
+    out = DT(x.shape, np.float32)
+    cabi.elementwise(op, DT.from_numpy(x), None, out, p0, p1)
+    got = out.numpy()
+    if tol == 0:
+        assert np.array_equal(got, ref)
+    else:  # libm vs CUDA math library: a few ulp
+        assert np.abs(got - ref).max() <= tol
+
+
+def test_scalar_variants():
+    x = rnd(1, 12, 128, 128)
+    for op, ref in ((cabi.ADD_SCALAR, x + np.float32(1.0)), (cabi.MUL_SCALAR, x * np.float32(0.5)),
+                    (cabi.DIV_SCALAR, x / np.float32(8.0)), (cabi.RSUB_SCALAR, np.float32(1.0) - x)):
+        p0 = {cabi.ADD_SCALAR: 1.0, cabi.MUL_SCALAR: 0.5, cabi.DIV_SCALAR: 8.0, cabi.RSUB_SCALAR: 1.0}[op]
+        out = DT(x.shape, np.float32)
+        cabi.elementwise(op, DT.from_numpy(x), None, out, p0)
+        assert np.array_equal(out.numpy(), ref)
+    p = np.float32(3.0)
+    out = DT(x.shape, np.float32)
+    cabi.elementwise(cabi.POW_SCALAR, DT.from_numpy(np.abs(x)), None, out, 3.0)
+    assert relerr(out.numpy(), np.abs(x).astype(np.float64) ** 3) < 1e-6
+    # mask preprocessing (1 - m) * lowest, fused
+    m = (RNG.random((2, 1, 1, 128)) > 0.3).astype(np.float32)
+    out = DT(m.shape, np.float32)
+    lowest = float(np.finfo(np.float32).min)
+    cabi.elementwise(cabi.RSUB_MUL_SCALAR, DT.from_numpy(m), None, out, 1.0, lowest)
+    assert np.array_equal(out.numpy(), (np.float32(1.0) - m) * np.float32(lowest))
+
+
+def test_int64_and_bool_ops():
+    a = RNG.integers(-50, 50, (3, 17)).astype(np.int64)
+    b = RNG.integers(-50, 50, (17,)).astype(np.int64)
+    for op, ref in ((cabi.ADD, a + b), (cabi.MUL, a * b), (cabi.SUB, a - b)):
+        out = DT(a.shape, np.int64)
+        cabi.elementwise(op, DT.from_numpy(a), DT.from_numpy(b), out)
+        assert np.array_equal(out.numpy(), ref)
+    out = DT(a.shape, np.bool_)
+    cabi.elementwise(cabi.EQUAL_SCALAR, DT.from_numpy(a), None, out, 3)
+    assert np.array_equal(out.numpy(), a == 3)
+    nb = DT(a.shape, np.bool_)
+    cabi.elementwise(cabi.NOT, out, None, nb)
+    assert np.array_equal(nb.numpy(), a != 3)
+    f = DT(a.shape, np.float32)
+    cabi.elementwise(cabi.CAST, DT.from_numpy(a), None, f)
+    assert np.array_equal(f.numpy(), a.astype(np.float32))
+
+
+def test_bias_gelu_matches_unfused_chain():
+    x, b = rnd(1, 128, 3072), rnd(3072)
+    c0, c1, c2 = np.float32(np.sqrt(2.0)), np.float32(1.0), np.float32(0.5)
+    t = orc.binary("Add", x, b, np.empty_like(x))
+    e = orc.unary("Erf", orc.binary("Div", t, np.asarray(c0), np.empty_like(x)), np.empty_like(x))
+    ref = (t * (e + c1)) * c2
+    out = DT(x.shape, np.float32)
+    cabi.bias_gelu(DT.from_numpy(x), DT.from_numpy(b), out, c0, c1, c2)
+    assert np.abs(out.numpy() - ref).max() <= 4e-6
+
+
+def test_where():
+    cond = np.tril(np.ones((64, 64), np.bool_)).reshape(1, 1, 64, 64)
+    x = rnd(2, 4, 64, 64)
+    lowest = float(np.finfo(np.float32).min)
+    out = DT(x.shape, np.float32)
+    cabi.where(DT.from_numpy(cond), DT.from_numpy(x), None, lowest, out)
+    ref = orc.where(cond, x, np.asarray(lowest, np.float32), np.empty_like(x))
+    assert np.array_equal(out.numpy(), ref)
+    y = rnd(64)
+    cabi.where(DT.from_numpy(cond), DT.from_numpy(x), DT.from_numpy(y), 0.0, out)
+    assert np.array_equal(out.numpy(), np.where(cond, x, y))
+
+
+# ------------------------------------------------------------------ data movement (bit-exact)
+@pytest.mark.parametrize("shape,perm", [((1, 128, 12, 64), (0, 2, 1, 3)), ((1, 128, 12, 64), (0, 2, 3, 1)),
+                                        ((1, 12, 128, 64), (0, 2, 1, 3)), ((5, 7, 3), (2, 0, 1)),
+                                        ((33, 65), (1, 0)), ((2, 3, 4, 5), (3, 2, 1, 0))])
+@pytest.mark.parametrize("dtype", [np.float32, np.int64, np.bool_])
+def test_transpose_bit_exact(shape, perm, dtype):
+    x = (RNG.integers(0, 2**31 - 1, shape)).astype(dtype)
+    oshape = tuple(shape[p] for p in perm)
+    ref = orc.transpose(x, np.empty(oshape, dtype), perm)
+    assert np.array_equal(ref, x.transpose(perm))
+    src = DT.from_numpy(x)
+    out = DT(oshape, dtype)
+    view = src.view(oshape, [src.strides[p] for p in perm])  # Transpose = permuted-stride view
+    cabi.copy_strided(view, out)
+    assert np.array_equal(out.numpy(), ref)
+
+
+@pytest.mark.parametrize("li,lo", [((0, 1, 2), (0, 1, 2, 3)), ((2, 0, 1), (0, 1, 2, 3)),
+                                   ((0, 1, 2), (3, 1, 0, 2)), ((1, 2, 0), (2, 3, 1, 0))])
+def test_reshape_logical_order_any_layout(li, lo):
+    x = rnd(2, 16, 24)
+    ref = orc.reshape(x, np.empty((2, 16, 4, 6), np.float32))
+    assert np.array_equal(ref, x.reshape(2, 16, 4, 6))
+    out = DT((2, 16, 4, 6), np.float32, lo)
+    cabi.reshape_copy(DT.from_numpy(x, li), out)
+    assert np.array_equal(out.numpy(), ref)
+
+
+def test_gather_variants():
+    table = rnd(30522, 768)
+    ids = RNG.integers(0, 30522, (1, 128)).astype(np.int64)
+    ref = orc.gather(table, ids, np.empty((1, 128, 768), np.float32), 0)
+    out = DT((1, 128, 768), np.float32)
+    cabi.gather(DT.from_numpy(table), DT.from_numpy(ids), out, 0)
+    assert np.array_equal(out.numpy(), ref)
+    cabi.check_device()
+    x = rnd(2, 128, 768)
+    out = DT((2, 768), np.float32)
+    cabi.gather(DT.from_numpy(x), DT.from_numpy(np.asarray(0, np.int64)), out, 1)
+    assert np.array_equal(out.numpy(), x[:, 0, :])
+    idx = np.array([[3, 0], [5, 5]], np.int64)
+    x = rnd(4, 6, 5)
+    out = DT((4, 2, 2, 5), np.float32)
+    cabi.gather(DT.from_numpy(x, (2, 0, 1)), DT.from_numpy(idx), out, 1)
+    assert np.array_equal(out.numpy(), np.take(x, idx, axis=1))
+
+
+def test_gather_out_of_range_is_reported_not_faulted():
+    table = rnd(10, 8)
+    ids = np.array([1, 12, -3], np.int64)
+    out = DT((3, 8), np.float32)
+    cabi.gather(DT.from_numpy(table), DT.from_numpy(ids), out, 0)
+    with pytest.raises(cabi.FmlError) as e:
+        cabi.check_device()
+    assert e.value.status == 7
+    got = out.numpy()
+    assert np.array_equal(got[0], table[1]) and np.array_equal(got[1], table[9]) and np.array_equal(got[2], table[0])
+    cabi.check_device()  # cleared
+
+
+def test_embedding_fused():
+    table, pos, typ = rnd(1000, 768), rnd(1, 128, 768), rnd(768)
+    ids = RNG.integers(0, 1000, (2, 128)).astype(np.int64)
+    out = DT((2, 128, 768), np.float32)
+    cabi.embedding(DT.from_numpy(table), DT.from_numpy(ids), DT.from_numpy(pos), DT.from_numpy(typ), out)
+    assert np.array_equal(out.numpy(), (table[ids] + pos) + typ)
+
+
+def test_slice_concat_pad_through_views():
+    x = rnd(2, 4, 16, 64)
+    src = DT.from_numpy(x)
+    # Slice [.., 16:48] on the last axis
+    out = DT((2, 4, 16, 32), np.float32)
+    cabi.copy_strided(src.view((2, 4, 16, 32), src.strides, 16), out)
+    assert np.array_equal(out.numpy(), x[..., 16:48])
+    # Concat(-x2, x1) as in rotary
+    cat = DT((2, 4, 16, 64), np.float32)
+    cabi.copy_strided(src.view((2, 4, 16, 32), src.strides, 32), cat.view((2, 4, 16, 32), cat.strides, 0))
+    cabi.copy_strided(src.view((2, 4, 16, 32), src.strides, 0), cat.view((2, 4, 16, 32), cat.strides, 32))
+    assert np.array_equal(cat.numpy(), np.concatenate([x[..., 32:], x[..., :32]], -1))
+    p = DT((2, 4, 18, 67), np.float32)
+    cabi.pad(src, p, [0, 0, 1, 2])
+    ref = orc.pad(x, np.empty((2, 4, 18, 67), np.float32), [0, 0, 1, 2])
+    assert np.array_equal(p.numpy(), ref)
+
+
+# ------------------------------------------------------------------ reductions
+@pytest.mark.parametrize("shape,axis", [((1, 12, 128, 128), -1), ((1, 12, 128, 768), 3), ((4, 7, 33), -1),
+                                        ((3, 50, 6), 1), ((2, 5000), 1)])
+def test_softmax(shape, axis):
+    x = rnd(*shape) * 3
+    ref = orc.softmax(x, np.empty_like(x), axis)
+    out = DT(shape, np.float32)
+    cabi.softmax(DT.from_numpy(x), None, 1.0, out, axis)
+    got = out.numpy()
+    assert np.abs(got - ref).max() <= 1e-6  # expf ulp differences, values in [0,1]
+    assert np.abs(got.sum(axis) - 1).max() < 1e-5
+
+
+def test_softmax_fused_scale_mask_matches_chain():
+    s = rnd(2, 12, 128, 128) * 4
+    m = (RNG.random((2, 1, 1, 128)) > 0.2).astype(np.float32)
+    mask = (np.float32(1.0) - m) * np.float32(np.finfo(np.float32).min)
+    chain = orc.binary("Add", orc.binary("Div", s, np.asarray(8.0, np.float32), np.empty_like(s)), mask,
+                       np.empty_like(s))
+    ref = orc.softmax(chain, np.empty_like(s), -1)
+    out = DT(s.shape, np.float32)
+    cabi.softmax(DT.from_numpy(s), DT.from_numpy(mask), 8.0, out, -1)
+    assert np.abs(out.numpy() - ref).max() <= 1e-6
+
+
+@pytest.mark.parametrize("shape,eps", [((1, 128, 768), 1e-12), ((4, 512, 1024), 1e-5), ((3, 10, 50), 1e-5)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_layernorm(shape, eps, residual):
+    x, r = rnd(*shape) * 2 + 0.5, rnd(*shape)
+    g, b = rnd(shape[-1]) + 1, rnd(shape[-1])
+    xin = x + r if residual else x
+    ref = orc.layernorm(xin, g, b, np.empty_like(x), -1, np.float32(eps), acc64=True)
+    out = DT(shape, np.float32)
+    cabi.layernorm(DT.from_numpy(x), DT.from_numpy(r) if residual else None, DT.from_numpy(g),
+                   DT.from_numpy(b), out, -1, eps)
+    # fp32 sums in a different order than the oracle's fp64: 1e-5 of the output scale
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
+def test_layernorm_strided_axis():
+    x = rnd(6, 40, 9)
+    g, b = rnd(40) + 1, rnd(40)
+    ref = orc.layernorm(x, g, b, np.empty_like(x), 1, np.float32(1e-5), acc64=True)
+    out = DT(x.shape, np.float32, (1, 2, 0))
+    cabi.layernorm(DT.from_numpy(x, (2, 0, 1)), None, DT.from_numpy(g), DT.from_numpy(b), out, 1, 1e-5)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
+def test_reduce_mean_cumsum():
+    x = rnd(2, 32, 7, 7)
+    out = DT((2, 32, 1, 1), np.float32)
+    cabi.reduce_mean(DT.from_numpy(x), out, [2, 3])
+    ref = orc.reduce_mean(x, np.empty((2, 32, 1, 1), np.float32), [2, 3])
+    assert relerr(out.numpy(), ref) <= 1e-6
+    v = RNG.integers(0, 5, (3, 40)).astype(np.int64)
+    o = DT(v.shape, np.int64)
+    cabi.cumsum(DT.from_numpy(v), o, 1)
+    assert np.array_equal(o.numpy(), np.cumsum(v, 1))
+
+
+# ------------------------------------------------------------------ conv / pool
+@pytest.mark.parametrize("cfg", [
+    dict(x=(1, 3, 32, 32), w=(16, 3, 3, 3), pads=(1, 1), strides=(1, 1), dil=(1, 1), group=1),
+    dict(x=(2, 8, 14, 14), w=(12, 8, 3, 3), pads=(1, 1), strides=(2, 2), dil=(1, 1), group=1),
+    dict(x=(1, 16, 9, 9), w=(8, 16, 1, 1), pads=(0, 0), strides=(1, 1), dil=(1, 1), group=1),
+    dict(x=(1, 12, 20, 20), w=(12, 1, 5, 5), pads=(2, 2), strides=(2, 2), dil=(1, 1), group=12),
+    dict(x=(2, 24, 64), w=(24, 1, 9), pads=(4,), strides=(1,), dil=(1,), group=24),
+    dict(x=(1, 4, 12, 12), w=(6, 4, 3, 3), pads=(2, 2), strides=(1, 1), dil=(2, 2), group=1),
+])
+def test_conv(cfg):
+    x, w = rnd(*cfg["x"]), rnd(*cfg["w"]) * 0.2
+    b = rnd(cfg["w"][0])
+    nd = len(cfg["x"]) - 2
+    osp = [(cfg["x"][2 + i] + 2 * cfg["pads"][i] - cfg["dil"][i] * (cfg["w"][2 + i] - 1) - 1) // cfg["strides"][i] + 1
+           for i in range(nd)]
+    oshape = (cfg["x"][0], cfg["w"][0], *osp)
+    ref = orc.conv(x, w, b, np.empty(oshape, np.float32), cfg["pads"], cfg["strides"], cfg["dil"], cfg["group"],
+                   acc64=True)
+    out = DT(oshape, np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), out, cfg["pads"], cfg["strides"], cfg["dil"],
+              cfg["group"])
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("mode,shape,k,s", [(0, (1, 64, 32, 32), (2, 2), (2, 2)), (1, (2, 1280, 7, 7), (7, 7), (1, 1)),
+                                            (0, (1, 3, 9, 11), (3, 2), (2, 3))])
+def test_pool(mode, shape, k, s):
+    x = rnd(*shape)
+    oshape = (shape[0], shape[1], (shape[2] - k[0]) // s[0] + 1, (shape[3] - k[1]) // s[1] + 1)
+    ref = orc.pool2d(x, np.empty(oshape, np.float32), mode, k, s)
+    out = DT(oshape, np.float32)
+    cabi.pool2d(DT.from_numpy(x), out, mode, k, s)
+    if mode == 0:
+        assert np.array_equal(out.numpy(), ref)
+    else:
+        assert relerr(out.numpy(), ref) <= 1e-6
+
+
+def test_bad_arguments_are_reported():
+    a, b = DT.from_numpy(rnd(4, 5)), DT.from_numpy(rnd(4, 6))
+    out = DT((4, 5), np.float32)
+    with pytest.raises(cabi.FmlError) as e:
+        cabi.elementwise(cabi.ADD, a, b, out)
+    assert e.value.status == 1
+    with pytest.raises(cabi.FmlError):
+        cabi.softmax(a, None, 1.0, out, 5)
+    with pytest.raises(cabi.FmlError):
+        cabi.copy_strided(a, DT((5, 4), np.float32))
