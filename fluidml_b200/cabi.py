@@ -230,11 +230,12 @@ def gemm_params(precision=GEMM_AUTO, act=ACT_NONE, divisor=1.0, alpha=1.0, beta=
     return p
 
 
-def gemm_workspace_bytes(a, b, c, params) -> int:
-    n = ctypes.c_size_t()
+def gemm_workspace_bytes(a, b, c, params):
+    """(partial_bytes, counter_bytes) of the split-K scratch for this configuration."""
+    n, m = ctypes.c_size_t(), ctypes.c_size_t()
     check(lib().fml_gemm_workspace_bytes(_ref(a), _ref(b), _ref(c), ctypes.byref(params),
-                                         ctypes.byref(n)))
-    return n.value
+                                         ctypes.byref(n), ctypes.byref(m)))
+    return n.value, m.value
 
 
 def gemm_uses_tensor_cores(a, b, c, params) -> bool:
@@ -244,17 +245,21 @@ def gemm_uses_tensor_cores(a, b, c, params) -> bool:
     return bool(u.value)
 
 
-def gemm(a, b, c, bias=None, residual=None, params=None, workspace: Optional[DeviceBuffer] = None,
-         stream=None):
+def gemm(a, b, c, bias=None, residual=None, params=None, workspace=None, stream=None):
+    """`workspace` is a (partials, counters) pair of DeviceBuffers; when omitted and the
+    configuration splits K, a zeroed pair is allocated and returned for reuse."""
     params = params or gemm_params()
     if workspace is None:
-        n = gemm_workspace_bytes(a, b, c, params)
-        if n:
-            workspace = DeviceBuffer(n)
-            workspace.zero()
+        nb, nc = gemm_workspace_bytes(a, b, c, params)
+        if nb:
+            workspace = (DeviceBuffer(nb), DeviceBuffer(nc))
+            workspace[1].zero()
+    part, cnt = workspace if workspace else (None, None)
     check(lib().fml_gemm(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual), ctypes.byref(params),
-                         ctypes.c_void_p(workspace.ptr) if workspace else None,
-                         ctypes.c_size_t(workspace.nbytes if workspace else 0), stream))
+                         ctypes.c_void_p(part.ptr) if part else None,
+                         ctypes.c_size_t(part.nbytes if part else 0),
+                         ctypes.c_void_p(cnt.ptr) if cnt else None,
+                         ctypes.c_size_t(cnt.nbytes if cnt else 0), stream))
     return workspace
 
 

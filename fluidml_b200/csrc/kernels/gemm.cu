@@ -195,14 +195,15 @@ static int resolve(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c
 
 extern "C" int fml_gemm_workspace_bytes(const fml_tensor *a, const fml_tensor *b,
                                         const fml_tensor *c, const fml_gemm_params *gp,
-                                        size_t *bytes) {
-  FML_REQUIRE(bytes, FML_BAD_ARG, "fml_gemm_workspace_bytes: null argument");
+                                        size_t *partial_bytes, size_t *counter_bytes) {
+  FML_REQUIRE(partial_bytes && counter_bytes, FML_BAD_ARG, "fml_gemm_workspace_bytes: null argument");
   GemmProblem p;
   TcPlan plan;
   bool use_tc = false;
   int st = resolve(a, b, c, nullptr, nullptr, gp, p, plan, use_tc);
   if (st != FML_OK) return st;
-  *bytes = use_tc ? plan.ws_bytes : 0;
+  *partial_bytes = use_tc ? plan.partial_bytes : 0;
+  *counter_bytes = use_tc ? plan.counter_bytes : 0;
   return FML_OK;
 }
 
@@ -220,8 +221,8 @@ extern "C" int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor 
 
 extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
                         const fml_tensor *bias, const fml_tensor *residual,
-                        const fml_gemm_params *gp, void *workspace, size_t workspace_bytes,
-                        void *stream) {
+                        const fml_gemm_params *gp, void *partials, size_t partial_bytes,
+                        void *counters, size_t counter_bytes, void *stream) {
   GemmProblem p;
   TcPlan plan;
   bool use_tc = false;
@@ -229,6 +230,7 @@ extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tens
   if (st != FML_OK) return st;
   if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
   GemmEpilogue e = make_epilogue(*gp, bias != nullptr, residual != nullptr);
-  if (use_tc) return launch_gemm_tc(p, e, plan, workspace, workspace_bytes, as_stream(stream));
+  if (use_tc)
+    return launch_gemm_tc(p, e, plan, partials, partial_bytes, counters, counter_bytes, as_stream(stream));
   return launch_gemm_simt(p, e, as_stream(stream));
 }

@@ -57,12 +57,13 @@ struct TcPlan {
   int b_mn_major; // 0: B tile is K-major (b_sk == 1), 1: MN-major (b_sn == 1)
   int three_pass; // 1: 3xTF32, 0: single TF32
   size_t smem_bytes;
-  size_t ws_bytes;
+  size_t partial_bytes, counter_bytes;
 };
 
 // Whether the operands can be fed to TMA/UMMA directly, and with which plan.
 bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan);
 int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan,
-                   void *workspace, size_t workspace_bytes, cudaStream_t s);
+                   void *partials, size_t partial_bytes, void *counters, size_t counter_bytes,
+                   cudaStream_t s);
 
 }  // namespace fml

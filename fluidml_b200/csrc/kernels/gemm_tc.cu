@@ -137,15 +137,19 @@ __device__ __forceinline__ void epi_bar_sync() {  // the 128 epilogue threads on
 // Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
 //   K-major tile (rows of 128 bytes = 32 k values): 8-row groups 1024 bytes apart (SBO);
 //     the leading-dimension offset is unused for swizzled K-major operands.
-//   MN-major tile (rows of 128 bytes = 32 n values, one row per k): 8-k groups 1024 bytes
-//     apart (SBO), 32-n column groups `lbo_bytes` apart (LBO).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   MN-major tile (rows of 128 bytes = 32 n values, one row per k).  32-bit MN-major
+//     operands exist only in the "128-byte swizzle, 32-byte atom" mode (layout type 1; TMA
+//     writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B): the pattern repeats every 4 k
+//     rows, so 4-k groups are 512 bytes apart (SBO) and 32-n column groups `lbo_bytes`
+//     apart (LBO).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type = 2u) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;  // descriptor version for this architecture
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  d |= (uint64_t)layout_type << 61;  // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte atom
   return d;
 }
 
@@ -245,6 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t idesc = instr_desc(BN, a.b_mn_major);
       const uint32_t ready = a.three_pass ? bar_conv : bar_full;
       const uint32_t b_lbo = a.b_mn_major ? (uint32_t)(kBK * 128) : 16u;
+      const uint32_t b_sbo = a.b_mn_major ? 512u : 1024u, b_type = a.b_mn_major ? 1u : 2u;
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         const int s = it % a.stages;
@@ -261,11 +266,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t a_off = (uint32_t)j * 32u;
           const uint32_t b_off = a.b_mn_major ? (uint32_t)j * 1024u : (uint32_t)j * 32u;
           const uint64_t da = smem_desc(sa + a_off, 16u, 1024u);
-          const uint64_t db = smem_desc(sb + b_off, b_lbo, 1024u);
+          const uint64_t db = smem_desc(sb + b_off, b_lbo, b_sbo, b_type);
           const uint32_t first = (it == 0 && j == 0) ? 0u : 1u;
           if (a.three_pass) {
             const uint64_t dal = smem_desc(sal + a_off, 16u, 1024u);
-            const uint64_t dbl = smem_desc(sbl + b_off, b_lbo, 1024u);
+            const uint64_t dbl = smem_desc(sbl + b_off, b_lbo, b_sbo, b_type);
             umma_tf32(tmem_base, dal, db, idesc, first);
             umma_tf32(tmem_base, da, dbl, idesc, 1u);
             umma_tf32(tmem_base, da, db, idesc, 1u);
@@ -435,7 +440,7 @@ EncodeTiledFn encode_fn() {
 // 4-D map: (inner contiguous dim, row dim, batch0, batch1), fp32, 128-byte swizzle.
 int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t rows, int64_t row_stride,
              int64_t nb0, int64_t b0_stride, int64_t nb1, int64_t b1_stride, int box_inner,
-             int box_rows) {
+             int box_rows, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = encode_fn();
   FML_REQUIRE(fn, FML_CUDA_ERROR, "fml_gemm: cuTensorMapEncodeTiled is not available");
   // extent-1 dims take any valid stride
@@ -447,7 +452,7 @@ int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t rows, i
   cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   FML_REQUIRE(r == CUDA_SUCCESS, FML_CUDA_ERROR, "fml_gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
   return FML_OK;
@@ -505,12 +510,13 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
   if (stages < 1) return false;
   plan.stages = stages;
   plan.smem_bytes = stages * stage + (3 * stages + 1) * 8 + 16 + 1024;
-  plan.ws_bytes = sk > 1 ? (size_t)tiles * sk * kBM * tn * 4 + (size_t)tiles * 4 + 256 : 0;
+  plan.partial_bytes = sk > 1 ? (size_t)tiles * sk * kBM * tn * 4 : 0;
+  plan.counter_bytes = sk > 1 ? (size_t)tiles * 4 : 0;
   return true;
 }
 
-int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, void *workspace,
-                   size_t workspace_bytes, cudaStream_t s) {
+int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, void *partials,
+                   size_t partial_bytes, void *counters, size_t counter_bytes, cudaStream_t s) {
   TcArgs a;
   a.p = p; a.e = e;
   a.tile_n = plan.tile_n; a.split_k = plan.split_k; a.stages = plan.stages;
@@ -523,21 +529,25 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
   FML_REQUIRE(a.status, FML_CUDA_ERROR, "fml_gemm: no device status word");
   a.ws_partial = nullptr; a.ws_counter = nullptr;
   if (plan.split_k > 1) {
-    FML_REQUIRE(workspace && workspace_bytes >= plan.ws_bytes, FML_BAD_ARG,
-                "fml_gemm: split-K needs %zu workspace bytes, got %zu", plan.ws_bytes, workspace_bytes);
-    FML_REQUIRE(aligned16(workspace), FML_MISALIGNED, "fml_gemm: workspace must be 16-byte aligned");
-    const size_t tiles = (size_t)a.tiles_m * a.tiles_n * p.nb0 * p.nb1;
-    a.ws_counter = reinterpret_cast<unsigned *>(workspace);
-    a.ws_partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(workspace) +
-                                             ((tiles * 4 + 255) / 256) * 256);
+    FML_REQUIRE(partials && partial_bytes >= plan.partial_bytes && counters &&
+                    counter_bytes >= plan.counter_bytes, FML_BAD_ARG,
+                "fml_gemm: split-K needs %zu partial and %zu counter bytes, got %zu and %zu",
+                plan.partial_bytes, plan.counter_bytes, partial_bytes, counter_bytes);
+    FML_REQUIRE(aligned16(partials) && ((uintptr_t)counters & 3) == 0, FML_MISALIGNED,
+                "fml_gemm: partials must be 16-byte and counters 4-byte aligned");
+    a.ws_counter = reinterpret_cast<unsigned *>(counters);
+    a.ws_partial = reinterpret_cast<float *>(partials);
   }
   CUtensorMap map_a, map_b;
-  int st = make_map(&map_a, p.a, p.K, p.M, p.a_sm, p.nb0, p.a_b0, p.nb1, p.a_b1, kBK, kBM);
+  int st = make_map(&map_a, p.a, p.K, p.M, p.a_sm, p.nb0, p.a_b0, p.nb1, p.a_b1, kBK, kBM,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != FML_OK) return st;
   if (!plan.b_mn_major)
-    st = make_map(&map_b, p.b, p.K, p.N, p.b_sn, p.nb0, p.b_b0, p.nb1, p.b_b1, kBK, plan.tile_n);
+    st = make_map(&map_b, p.b, p.K, p.N, p.b_sn, p.nb0, p.b_b0, p.nb1, p.b_b1, kBK, plan.tile_n,
+                  CU_TENSOR_MAP_SWIZZLE_128B);
   else
-    st = make_map(&map_b, p.b, p.N, p.K, p.b_sk, p.nb0, p.b_b0, p.nb1, p.b_b1, 32, kBK);
+    st = make_map(&map_b, p.b, p.N, p.K, p.b_sk, p.nb0, p.b_b0, p.nb1, p.b_b1, 32, kBK,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (st != FML_OK) return st;
   static bool attr_set[64] = {false};
   int dev = 0;

@@ -213,15 +213,23 @@ typedef struct fml_gemm_params {
 
 void fml_gemm_default_params(fml_gemm_params *p);
 
-/* Scratch bytes the chosen configuration needs (split-K partial sums and tile counters).
- * 0 when no split is used.  The workspace must be zero-filled once before its first use;
- * the kernel leaves its counters at zero again. */
+/* Scratch the chosen configuration needs when it splits K (both 0 otherwise):
+ *   partial_bytes  fp32 partial tiles; contents need no initialisation and are dead after
+ *                  the call, so a planner may give the bytes to other tenants between calls
+ *                  (the reference's node scratch has the same [i,i] lifetime,
+ *                  src/worker/planner.cpp:283-291);
+ *   counter_bytes  one arrival counter per output tile; must be zero before the first call
+ *                  and is left zero by every call, so GEMM launches that are ordered on one
+ *                  stream may share one counter buffer.  It must not be shared by launches
+ *                  that can overlap, and must not be handed to other tenants. */
 int fml_gemm_workspace_bytes(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
-                             const fml_gemm_params *p, size_t *bytes);
+                             const fml_gemm_params *p, size_t *partial_bytes,
+                             size_t *counter_bytes);
 
 int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
              const fml_tensor *bias, const fml_tensor *residual, const fml_gemm_params *p,
-             void *workspace, size_t workspace_bytes, void *stream);
+             void *partials, size_t partial_bytes, void *counters, size_t counter_bytes,
+             void *stream);
 
 /* Reports which path fml_gemm would take for these operands: 0 = fp32 FMA, 1 = tcgen05. */
 int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
