@@ -21,13 +21,15 @@ CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(ROOT, "build", "obj")
 INCLUDE = os.path.join(ROOT, "include")
-NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CXX = os.environ.get("CXX", "g++")
+# The toolchain is named explicitly: a CXX inherited from the environment may point at a
+# wrapper that links libstdc++ statically, which breaks inside a Python process.
+NVCC = os.environ.get("FLUIDML_NVCC", "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("FLUIDML_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
 
 KERNELS_SO = os.path.join(LIBDIR, "libfluidml_b200_kernels.so")
 HOST_SO = os.path.join(LIBDIR, "libfluidml_b200.so")
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+NVCC_FLAGS = ["-ccbin", CXX, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", os.path.join(CSRC, "kernels")]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I", INCLUDE, "-I", os.path.join(CSRC, "host"),
              "-I", "/usr/local/cuda/include"]

@@ -1,0 +1,333 @@
+// Executor: the public facade (include/worker/executor.h) and its C ABI
+// (include/fluidml_executor.h).  Compile = Parser -> Converter -> fusion passes ->
+// TopologicalSort -> (DP layout search) -> lowering -> memory plan -> Builder -> Runner,
+// the same stage order as src/worker/executor.cpp:91-133.
+#include "worker/executor.h"
+#include "converter.h"
+#include "dp.h"
+#include "fluidml_executor.h"
+#include "fusion.h"
+#include "json.h"
+#include "parser.h"
+#include "planner.h"
+#include "program.h"
+#include <cstdlib>
+#include <sstream>
+
+namespace fluidml {
+namespace worker {
+namespace {
+
+enum class LayoutMode { kPlain, kDP };
+
+std::string EnvOr(const char *key, const std::string &dflt) {
+  const char *v = std::getenv(key);
+  return v && *v ? std::string(v) : dflt;
+}
+
+int ParsePrecision(const std::string &v) {
+  if (v == "auto") return FML_GEMM_AUTO;
+  if (v == "fp32") return FML_GEMM_FP32;
+  if (v == "3xtf32") return FML_GEMM_3XTF32;
+  if (v == "tf32") return FML_GEMM_TF32;
+  throw Error("gemm_precision must be one of auto, fp32, 3xtf32, tf32 (got '" + v + "')");
+}
+
+class ExecutorImpl : public Executor {
+public:
+  ExecutorImpl(std::string &&name, size_t epoch, LayoutMode layout, MemoryPlanKind plan)
+      : name_(std::move(name)), epoch_(epoch ? epoch : 1), layout_(layout), plan_(plan) {
+    SetOption("device", EnvOr("FLUIDML_DEVICE", "0"));
+    SetOption("gemm_precision", EnvOr("FLUIDML_GEMM_PRECISION", "auto"));
+    SetOption("fusion", EnvOr("FLUIDML_FUSION", "1"));
+    SetOption("cuda_graph", EnvOr("FLUIDML_CUDA_GRAPH", "1"));
+    SetOption("alignment", EnvOr("FLUIDML_ALIGNMENT", "256"));
+    SetOption("dp_cost", EnvOr("FLUIDML_DP_COST", "model"));
+  }
+
+  void SetOption(const std::string &key, const std::string &value) override {
+    if (key == "device") options_.device = std::stoi(value);
+    else if (key == "gemm_precision") options_.gemm_precision = ParsePrecision(value);
+    else if (key == "fusion") options_.fusion = value != "0";
+    else if (key == "cuda_graph") options_.cuda_graph = value != "0";
+    else if (key == "alignment") {
+      options_.alignment = (size_t)std::stoul(value);
+      if (options_.alignment < 16 || (options_.alignment & (options_.alignment - 1)))
+        throw Error("alignment must be a power of two >= 16");
+    } else if (key == "dp_cost") {
+      if (value != "model" && value != "constant") throw Error("dp_cost must be 'model' or 'constant'");
+      options_.dp_constant_cost = value == "constant";
+    } else throw Error("unknown option '" + key + "'");
+  }
+
+  void Compile(std::istream &input, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json) override {
+    CompileGraph(Parser::Run(input), mlir, llvm, json);
+  }
+
+  void Compile(std::string_view input, std::optional<std::string_view> mlir,
+               std::optional<std::string_view> llvm, std::optional<std::string_view> json) override {
+    std::ofstream fm, fl, fj;
+    auto open = [](std::ofstream &f, const std::optional<std::string_view> &p) -> std::ofstream * {
+      if (!p) return nullptr;
+      f.open(std::string(*p));
+      if (!f) throw Error("cannot write '" + std::string(*p) + "'");
+      return &f;
+    };
+    std::ofstream *pm = open(fm, mlir), *pl = open(fl, llvm), *pj = open(fj, json);
+    CompileGraph(Parser::Run(std::string(input)), pm, pl, pj);
+  }
+
+  void CompileBuffer(const void *data, size_t size, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json,
+                     bool dry_run = false) {
+    CompileGraph(Parser::Run((const uint8_t *)data, size), mlir, llvm, json, dry_run);
+  }
+
+  size_t Invoke(const std::unordered_map<std::string, void *> &args) override {
+    if (!runner_) throw Error("Invoke called before Compile");
+    return runner_->Run(args, epoch_);
+  }
+
+  std::string GetStatsJson() const override { return stats_.Dump(); }
+
+private:
+  // `dry_run`: stop before anything touches the device (planning only).
+  void CompileGraph(graph::Graph graph, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json,
+                    bool dry_run = false) {
+    runner_.reset();
+    flow::Flow flow = Converter::Run(graph);
+    graph = graph::Graph();  // constants now live in the flow's regions
+
+    // Arena the reference would plan for this model: unfused flow, default layouts, its own
+    // kernels' scratch sizes, no alignment (src/worker/planner.cpp:236-293).
+    size_t reference_greedy = 0, reference_linear = 0;
+    {
+      const flow::Sequence seq = Planner::TopologicalSort(flow);
+      const std::vector<memory::Info> infos = Planner::Lifetimes(seq, /*reference_scratch=*/true);
+      reference_greedy = Planner::Plan(infos, MemoryPlanKind::kGreedy, 1).GetMaximum();
+      reference_linear = Planner::Plan(infos, MemoryPlanKind::kLinear, 1).GetMaximum();
+    }
+    const size_t nodes_before_fusion = flow.nodes.size();
+    if (options_.fusion) FusionPasses::Run(flow);
+
+    flow::Sequence sequence = Planner::TopologicalSort(flow);
+    json::Value dp_json = json::Value::Object();
+    json::Value plan_json = json::Value::Object();
+    if (layout_ == LayoutMode::kDP) {
+      evaluation::DynamicProgrammingTable table(options_.dp_constant_cost, options_.gemm_precision);
+      evaluation::DynamicProgrammingPlan plan = table.Run(flow);
+      for (const auto &r : sequence.regions)
+        if (plan.HasLayout(r->name)) r->layout = plan.GetLayout(r->name);
+      dp_json = table.ToJson();
+      plan_json = plan.ToJson();
+    }
+
+    kernel::KernelOptions ko;
+    ko.gemm_precision = options_.gemm_precision;
+    const AliasMap aliases = Lowering::ComputeAliases(sequence, ko);
+    const size_t counter_bytes = Lowering::ComputeScratch(sequence, ko);
+    const std::vector<memory::Info> infos = Lowering::Lifetimes(sequence, aliases);
+    const memory::Index index = Planner::Plan(infos, plan_, options_.alignment);
+    const size_t unaligned = Planner::Plan(infos, plan_, 1).GetMaximum();
+
+    std::unique_ptr<Program> program;
+    if (!dry_run) program = Builder::Run(flow, sequence, index, aliases, counter_bytes, options_);
+
+    stats_ = json::Value::Object();
+    stats_.Set("name", json::Value(name_));
+    stats_.Set("mode", json::Value(std::string(layout_ == LayoutMode::kDP ? "dp" : "plain") +
+                                   (plan_ == MemoryPlanKind::kGreedy ? "_greedy" : "_linear")));
+    stats_.Set("peak_arena_bytes", json::Value((double)index.GetMaximum()));
+    stats_.Set("peak_arena_bytes_unaligned", json::Value((double)unaligned));
+    stats_.Set("reference_arena_bytes_greedy", json::Value((double)reference_greedy));
+    stats_.Set("reference_arena_bytes_linear", json::Value((double)reference_linear));
+    stats_.Set("counter_bytes", json::Value((double)counter_bytes));
+    stats_.Set("graph_nodes", json::Value((double)nodes_before_fusion));
+    stats_.Set("flow_nodes", json::Value((double)flow.nodes.size()));
+    stats_.Set("aliased_nodes", json::Value((double)aliases.size()));
+    json::Value seq = json::Value::Array();
+    for (const auto &n : sequence.nodes) {
+      json::Value e = json::Value::Object();
+      e.Set("name", json::Value(n->name));
+      e.Set("kind", json::Value(flow::KindName(n->kind)));
+      e.Set("alias", json::Value(aliases.count(n->output.get()) != 0));
+      e.Set("output", json::Value(n->output->name));
+      e.Set("scratch", json::Value((double)n->buffer_size));
+      seq.Push(e);
+    }
+    stats_.Set("sequence", seq);
+    if (program) {
+      stats_.Set("weight_bytes", json::Value((double)program->weight_bytes));
+      stats_.Set("interface_bytes", json::Value((double)program->io_bytes));
+      stats_.Set("launches", json::Value((double)program->launches.size()));
+      json::Value hist = json::Value::Object();
+      for (const auto &kv : program->kernel_histogram) hist.Set(kv.first, json::Value((double)kv.second));
+      stats_.Set("kernels", hist);
+    }
+
+    if (mlir && program) {  // the launch plan, one line per launch
+      for (const auto &l : program->launches) *mlir << l.kernel << "  // node " << l.node << "\n";
+    }
+    if (llvm) {  // region table: where every tensor lives and how it is laid out
+      for (const auto &r : sequence.regions) {
+        *llvm << r->name << " " << GetStringFromType(r->meta.GetType()) << " [";
+        for (size_t i = 0; i < r->meta.GetRank(); ++i) *llvm << (i ? "," : "") << r->meta.GetShape()[i];
+        *llvm << "] layout [";
+        for (size_t i = 0; i < r->layout.size(); ++i) *llvm << (i ? "," : "") << r->layout[i];
+        *llvm << "] ";
+        auto it = aliases.find(r.get());
+        if (it != aliases.end()) *llvm << "alias-of " << it->second->name;
+        else if (r->kind == flow::Region::kInner && index.Has(r->name)) *llvm << "arena+" << index.Get(r->name);
+        else *llvm << (r->kind == flow::Region::kConstant ? "constant" : r->kind == flow::Region::kInput ? "input" : r->kind == flow::Region::kOutput ? "output" : "unused");
+        *llvm << "\n";
+      }
+    }
+    if (json) {
+      json::Value root = json::Value::Object();
+      root.Set("dp_table", dp_json);
+      root.Set("plan", plan_json);
+      json::Value arena = json::Value::Object();
+      for (const auto &kv : index.All()) {
+        json::Value e = json::Value::Array();
+        e.Push(json::Value((double)kv.second.first));
+        e.Push(json::Value((double)kv.second.second));
+        arena.Set(kv.first, e);
+      }
+      json::Value a = json::Value::Object();
+      a.Set("tenants", arena);
+      a.Set("stats", stats_);
+      root.Set("arena", a);
+      *json << root.Dump();
+    }
+    if (program) runner_ = std::make_unique<Runner>(std::move(program), options_);
+  }
+
+  std::string name_;
+  size_t epoch_;
+  LayoutMode layout_;
+  MemoryPlanKind plan_;
+  Options options_;
+  std::unique_ptr<Runner> runner_;
+  json::Value stats_ = json::Value::Object();
+
+};
+
+}  // namespace
+
+std::unique_ptr<Executor> Executor::MakePlainLinear(std::string &&name, size_t epoch) {
+  return std::make_unique<ExecutorImpl>(std::move(name), epoch, LayoutMode::kPlain, MemoryPlanKind::kLinear);
+}
+std::unique_ptr<Executor> Executor::MakePlainGreedy(std::string &&name, size_t epoch) {
+  return std::make_unique<ExecutorImpl>(std::move(name), epoch, LayoutMode::kPlain, MemoryPlanKind::kGreedy);
+}
+std::unique_ptr<Executor> Executor::MakeDPGreedy(std::string &&name, size_t epoch) {
+  return std::make_unique<ExecutorImpl>(std::move(name), epoch, LayoutMode::kDP, MemoryPlanKind::kGreedy);
+}
+
+}  // namespace worker
+}  // namespace fluidml
+
+// ------------------------------------------------------------------------------ C ABI
+struct fml_executor {
+  std::unique_ptr<fluidml::worker::Executor> impl;
+  std::string error, stats;
+};
+
+namespace {
+template <typename F> int Guard(fml_executor *e, F &&f) {
+  try {
+    f();
+    if (e) e->error.clear();
+    return 0;
+  } catch (const std::out_of_range &ex) {
+    if (e) e->error = std::string("missing argument: ") + ex.what();
+    return 2;
+  } catch (const std::exception &ex) {
+    if (e) e->error = ex.what();
+    return 1;
+  }
+}
+std::ofstream *OpenOpt(std::ofstream &f, const char *path) {
+  if (!path) return nullptr;
+  f.open(path);
+  if (!f) throw fluidml::Error(std::string("cannot write '") + path + "'");
+  return &f;
+}
+}  // namespace
+
+extern "C" {
+
+int fml_executor_create(const char *name, int mode, size_t epoch, fml_executor **out) {
+  if (!out || !name) return 1;
+  *out = nullptr;
+  auto *e = new fml_executor();
+  int st = Guard(e, [&] {
+    using fluidml::worker::Executor;
+    switch (mode) {
+    case FML_EXECUTOR_PLAIN_LINEAR: e->impl = Executor::MakePlainLinear(std::string(name), epoch); break;
+    case FML_EXECUTOR_PLAIN_GREEDY: e->impl = Executor::MakePlainGreedy(std::string(name), epoch); break;
+    case FML_EXECUTOR_DP_GREEDY: e->impl = Executor::MakeDPGreedy(std::string(name), epoch); break;
+    default: throw fluidml::Error("unknown executor mode");
+    }
+  });
+  *out = e;  // returned even on failure so the message can be read; destroy it either way
+  return st;
+}
+
+void fml_executor_destroy(fml_executor *e) { delete e; }
+
+const char *fml_executor_last_error(const fml_executor *e) { return e ? e->error.c_str() : "null executor"; }
+
+int fml_executor_set_option(fml_executor *e, const char *key, const char *value) {
+  if (!e || !e->impl || !key || !value) return 1;
+  return Guard(e, [&] { e->impl->SetOption(key, value); });
+}
+
+int fml_executor_compile_file(fml_executor *e, const char *onnx_path, const char *mlir_path,
+                              const char *llvm_path, const char *json_path) {
+  if (!e || !e->impl || !onnx_path) return 1;
+  return Guard(e, [&] {
+    e->impl->Compile(std::string_view(onnx_path),
+                     mlir_path ? std::optional<std::string_view>(mlir_path) : std::nullopt,
+                     llvm_path ? std::optional<std::string_view>(llvm_path) : std::nullopt,
+                     json_path ? std::optional<std::string_view>(json_path) : std::nullopt);
+  });
+}
+
+int fml_executor_compile_buffer(fml_executor *e, const void *onnx_bytes, size_t size,
+                                const char *mlir_path, const char *llvm_path, const char *json_path) {
+  if (!e || !e->impl || !onnx_bytes) return 1;
+  return Guard(e, [&] {
+    std::ofstream fm, fl, fj;
+    std::ofstream *pm = OpenOpt(fm, mlir_path), *pl = OpenOpt(fl, llvm_path), *pj = OpenOpt(fj, json_path);
+    static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->CompileBuffer(onnx_bytes, size, pm, pl, pj);
+  });
+}
+
+int fml_executor_invoke(fml_executor *e, const char *const *names, void *const *buffers, size_t count,
+                        size_t *ns_per_epoch) {
+  if (!e || !e->impl || (count && (!names || !buffers))) return 1;
+  return Guard(e, [&] {
+    std::unordered_map<std::string, void *> args;
+    for (size_t i = 0; i < count; ++i) args[names[i]] = buffers[i];
+    size_t ns = e->impl->Invoke(args);
+    if (ns_per_epoch) *ns_per_epoch = ns;
+  });
+}
+
+int fml_executor_plan_buffer(fml_executor *e, const void *onnx_bytes, size_t size, const char *llvm_path,
+                             const char *json_path) {
+  if (!e || !e->impl || !onnx_bytes) return 1;
+  return Guard(e, [&] {
+    std::ofstream fl, fj;
+    std::ofstream *pl = OpenOpt(fl, llvm_path), *pj = OpenOpt(fj, json_path);
+    static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->CompileBuffer(onnx_bytes, size, nullptr, pl, pj, true);
+  });
+}
+
+const char *fml_executor_stats_json(fml_executor *e) {
+  if (!e || !e->impl) return "{}";
+  e->stats = e->impl->GetStatsJson();
+  return e->stats.c_str();
+}
+
+}  // extern "C"

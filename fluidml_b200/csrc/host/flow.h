@@ -70,6 +70,7 @@ struct Node {
   int act = 0;
   float act_param[3] = {1.4142135381698608f, 1.0f, 0.5f};
   bool has_bias = false, has_residual = false, has_mask = false;
+  bool b_is_const = false;  // FusedGemm: B is a captured constant (consts[0]) rather than inputs[1]
   // Scratch bytes the REFERENCE kernel of this kind needs (one float per row for Softmax and
   // LayerNorm, a padded copy for ConvWithPadding); used to report the reference-equivalent
   // arena.  The CUDA kernels need none of it.

@@ -1,0 +1,306 @@
+#include "fusion.h"
+#include "fluidml_cuda.h"
+#include <algorithm>
+#include <unordered_map>
+#include <unordered_set>
+
+namespace fluidml {
+namespace worker {
+namespace {
+
+using flow::Kind;
+using flow::NodePtr;
+using flow::RegionPtr;
+
+struct Rewriter {
+  flow::Flow &f;
+  std::unordered_map<const flow::Region *, std::vector<NodePtr>> consumers;
+  std::unordered_map<const flow::Region *, NodePtr> producer;
+  std::unordered_set<const flow::Node *> dead;
+
+  explicit Rewriter(flow::Flow &flow) : f(flow) { Index(); }
+
+  void Index() {
+    consumers.clear();
+    producer.clear();
+    for (const auto &n : f.nodes) {
+      if (dead.count(n.get())) continue;
+      producer[n->output.get()] = n;
+      for (const auto &r : n->inputs) consumers[r.get()].push_back(n);
+    }
+  }
+  // The only consumer of `r`, provided `r` is an inner tensor nobody else reads.
+  NodePtr Sole(const RegionPtr &r) {
+    if (r->kind != flow::Region::kInner) return nullptr;
+    auto it = consumers.find(r.get());
+    if (it == consumers.end() || it->second.size() != 1) return nullptr;
+    return it->second[0];
+  }
+  NodePtr SoleOfKind(const RegionPtr &r, Kind k) {
+    NodePtr n = Sole(r);
+    return n && n->kind == k ? n : nullptr;
+  }
+  void Kill(const NodePtr &n) { dead.insert(n.get()); }
+  void Commit() {
+    f.nodes.erase(std::remove_if(f.nodes.begin(), f.nodes.end(),
+                                 [&](const NodePtr &n) { return dead.count(n.get()) != 0; }),
+                  f.nodes.end());
+    dead.clear();
+    Index();
+  }
+};
+
+bool IsConst(const RegionPtr &r) { return r->kind == flow::Region::kConstant; }
+
+// The operand of a two-input node that is not `x`.
+RegionPtr Other(const NodePtr &n, const RegionPtr &x) { return n->inputs[0] == x ? n->inputs[1] : n->inputs[0]; }
+
+bool IsGemmLike(const NodePtr &n) {
+  return n->kind == Kind::MatMul || n->kind == Kind::FusedGemm || n->kind == Kind::GemmConstantBias;
+}
+
+// MatMul / Gemm -> FusedGemm, keeping operands and attributes.
+void PromoteToFusedGemm(const NodePtr &n) {
+  if (n->kind == Kind::FusedGemm) return;
+  if (n->kind == Kind::MatMul) {
+    if (IsConst(n->inputs[1])) {
+      n->consts = {n->inputs[1]};
+      n->inputs = {n->inputs[0]};
+      n->b_is_const = true;
+    }
+  } else {  // GemmConstantBias: consts = {B, C}
+    n->b_is_const = true;
+    n->has_bias = true;
+  }
+  n->kind = Kind::FusedGemm;
+}
+
+// ---- gather_add_fusion.cpp: Gather(table, ids) + constT + constT -> one embedding kernel
+bool FuseEmbedding(Rewriter &rw, const NodePtr &g) {
+  if (g->kind != Kind::GatherConstantDataTensor || g->consts[0]->meta.GetType() != Type::kFloat32) return false;
+  NodePtr a0 = rw.SoleOfKind(g->output, Kind::AddCommon);
+  if (!a0 || !IsConst(Other(a0, g->output))) return false;
+  NodePtr a1 = rw.SoleOfKind(a0->output, Kind::AddCommon);
+  if (!a1 || !IsConst(Other(a1, a0->output))) return false;
+  g->kind = Kind::GatherConstantDataTensorAddTensorLhsAddTensorLhs;
+  g->consts = {g->consts[0], Other(a0, g->output), Other(a1, a0->output)};
+  g->output = a1->output;
+  rw.Kill(a0);
+  rw.Kill(a1);
+  return true;
+}
+
+// ---- unsqueeze_sub_mul_fusion.cpp: Unsqueeze(+Unsqueeze) -> c - x -> * m
+bool FuseMask(Rewriter &rw, const NodePtr &u) {
+  if (u->kind != Kind::Unsqueeze || u->inputs[0]->meta.GetType() != Type::kFloat32) return false;
+  std::vector<NodePtr> chain = {u};
+  NodePtr cur = u;
+  while (NodePtr nx = rw.SoleOfKind(cur->output, Kind::Unsqueeze)) { chain.push_back(nx); cur = nx; }
+  NodePtr sub = rw.SoleOfKind(cur->output, Kind::SubConstantLhs);
+  if (!sub) return false;
+  NodePtr mul = rw.SoleOfKind(sub->output, Kind::MulConstant);
+  if (!mul) return false;
+  u->kind = Kind::UnsqueezeSubLhsScalarMulRhsScalar;
+  u->value = sub->value;
+  u->value2 = mul->value;
+  u->output = mul->output;
+  for (size_t i = 1; i < chain.size(); ++i) rw.Kill(chain[i]);
+  rw.Kill(sub);
+  rw.Kill(mul);
+  return true;
+}
+
+// ---- MatMul/Gemm + constant bias -> epilogue
+bool FuseBias(Rewriter &rw, const NodePtr &mm) {
+  if (mm->kind != Kind::MatMul && !(mm->kind == Kind::FusedGemm && !mm->has_bias && !mm->has_mask && mm->act == 0 && !mm->has_residual)) return false;
+  NodePtr add = rw.SoleOfKind(mm->output, Kind::AddCommon);
+  if (!add) return false;
+  RegionPtr bias = Other(add, mm->output);
+  if (!IsConst(bias) || bias->meta.GetType() != Type::kFloat32) return false;
+  if (add->output->meta != mm->output->meta) return false;  // the bias must not widen the result
+  PromoteToFusedGemm(mm);
+  mm->consts.push_back(bias);
+  mm->has_bias = true;
+  mm->output = add->output;
+  rw.Kill(add);
+  return true;
+}
+
+// ---- add_div_erf_add_mul_fusion.cpp: t -> t/c0 -> erf -> +c1 -> t*(.) -> *c2
+// `t` is produced by `src`; returns the final Mul node and the constants.
+bool MatchGelu(Rewriter &rw, const RegionPtr &t, NodePtr &div, NodePtr &erf, NodePtr &add, NodePtr &mul0, NodePtr &mul1) {
+  if (t->kind != flow::Region::kInner) return false;
+  auto it = rw.consumers.find(t.get());
+  if (it == rw.consumers.end() || it->second.size() != 2) return false;
+  div = mul0 = nullptr;
+  for (const auto &c : it->second) {
+    if (c->kind == Kind::DivConstantRhs) div = c;
+    else if (c->kind == Kind::MulCommon) mul0 = c;
+  }
+  if (!div || !mul0) return false;
+  erf = rw.SoleOfKind(div->output, Kind::Erf);
+  if (!erf) return false;
+  add = rw.SoleOfKind(erf->output, Kind::AddConstant);
+  if (!add) return false;
+  if (rw.Sole(add->output) != mul0 || Other(mul0, t) != add->output) return false;
+  mul1 = rw.SoleOfKind(mul0->output, Kind::MulConstant);
+  return mul1 != nullptr;
+}
+
+bool FuseGeluIntoGemm(Rewriter &rw, const NodePtr &mm) {
+  if (!IsGemmLike(mm) || mm->act != 0 || mm->has_residual) return false;
+  NodePtr div, erf, add, mul0, mul1;
+  if (!MatchGelu(rw, mm->output, div, erf, add, mul0, mul1)) return false;
+  PromoteToFusedGemm(mm);
+  mm->act = FML_ACT_GELU_ERF;
+  mm->act_param[0] = (float)div->value;
+  mm->act_param[1] = (float)add->value;
+  mm->act_param[2] = (float)mul1->value;
+  mm->output = mul1->output;
+  for (const auto &k : {div, erf, add, mul0, mul1}) rw.Kill(k);
+  return true;
+}
+
+// Add(x, const bias) followed by the GELU chain, when no GEMM produced x: the reference's
+// AddDivErfAddMulMul kernel.
+bool FuseBiasGelu(Rewriter &rw, const NodePtr &a) {
+  if (a->kind != Kind::AddCommon) return false;
+  RegionPtr bias, x;
+  if (IsConst(a->inputs[0]) && !IsConst(a->inputs[1])) { bias = a->inputs[0]; x = a->inputs[1]; }
+  else if (IsConst(a->inputs[1]) && !IsConst(a->inputs[0])) { bias = a->inputs[1]; x = a->inputs[0]; }
+  else return false;
+  if (a->output->meta != x->meta) return false;
+  NodePtr div, erf, add, mul0, mul1;
+  if (!MatchGelu(rw, a->output, div, erf, add, mul0, mul1)) return false;
+  a->kind = Kind::AddDivErfAddMulMul;
+  a->inputs = {x};
+  a->consts = {bias};
+  a->act_param[0] = (float)div->value;
+  a->act_param[1] = (float)add->value;
+  a->act_param[2] = (float)mul1->value;
+  a->output = mul1->output;
+  for (const auto &k : {div, erf, add, mul0, mul1}) rw.Kill(k);
+  return true;
+}
+
+// ---- GEMM -> Tanh / Relu / Sigmoid
+bool FuseActivation(Rewriter &rw, const NodePtr &mm) {
+  const bool conv = mm->kind == Kind::ConvWithPadding || mm->kind == Kind::ConvWithoutPadding;
+  if (!(IsGemmLike(mm) || conv) || mm->act != 0 || mm->has_residual) return false;
+  NodePtr act = rw.Sole(mm->output);
+  if (!act) return false;
+  int code = act->kind == Kind::Tanh ? FML_ACT_TANH : act->kind == Kind::Relu ? FML_ACT_RELU
+             : act->kind == Kind::Sigmoid ? FML_ACT_SIGMOID : 0;
+  if (!code) return false;
+  if (!conv) PromoteToFusedGemm(mm);
+  mm->act = code;
+  mm->output = act->output;
+  rw.Kill(act);
+  return true;
+}
+
+// ---- GEMM + residual Add -> epilogue
+bool FuseResidual(Rewriter &rw, const NodePtr &mm) {
+  if (!IsGemmLike(mm) || mm->has_residual) return false;
+  NodePtr add = rw.SoleOfKind(mm->output, Kind::AddCommon);
+  if (!add) return false;
+  RegionPtr res = Other(add, mm->output);
+  if (IsConst(res) || res->meta != mm->output->meta || add->output->meta != mm->output->meta) return false;
+  // the residual must not itself depend on this GEMM: it would, only if the GEMM's output had
+  // another consumer, which Sole() excluded
+  PromoteToFusedGemm(mm);
+  mm->inputs.push_back(res);
+  mm->has_residual = true;
+  mm->output = add->output;
+  rw.Kill(add);
+  return true;
+}
+
+// ---- Add(x, r) -> LayerNorm, when the Add did not fold into a GEMM
+bool FuseAddLayerNorm(Rewriter &rw, const NodePtr &add) {
+  if (add->kind != Kind::AddCommon || IsConst(add->inputs[0]) || IsConst(add->inputs[1])) return false;
+  if (add->inputs[0]->meta != add->output->meta || add->inputs[1]->meta != add->output->meta) return false;
+  NodePtr ln = rw.SoleOfKind(add->output, Kind::LayerNormalizationConstantScaleBias);
+  if (!ln) return false;
+  ln->kind = Kind::FusedLayerNorm;
+  ln->inputs = {add->inputs[0], add->inputs[1]};
+  ln->has_residual = true;
+  rw.Kill(add);
+  return true;
+}
+
+// ---- x / c -> + mask -> Softmax  (attention scores)
+bool FuseScaledMaskedSoftmax(Rewriter &rw, const NodePtr &div) {
+  if (div->kind != Kind::DivConstantRhs) return false;
+  NodePtr nx = rw.Sole(div->output);
+  if (!nx) return false;
+  NodePtr add = nullptr, sm = nullptr;
+  if (nx->kind == Kind::AddCommon) {
+    add = nx;
+    if (add->output->meta != div->output->meta) return false;
+    sm = rw.SoleOfKind(add->output, Kind::Softmax);
+  } else if (nx->kind == Kind::Softmax) {
+    sm = nx;
+  }
+  if (!sm || sm->axis != (int64_t)sm->output->meta.GetRank() - 1) return false;
+  sm->kind = Kind::FusedSoftmax;
+  sm->divisor = (float)div->value;
+  sm->inputs = {div->inputs[0]};
+  if (add) {
+    sm->inputs.push_back(Other(add, div->output));
+    sm->has_mask = true;
+    rw.Kill(add);
+  }
+  rw.Kill(div);
+  return true;
+}
+
+// ---- Sigmoid(x) * x
+bool FuseSilu(Rewriter &rw, const NodePtr &sg) {
+  if (sg->kind != Kind::Sigmoid) return false;
+  NodePtr mul = rw.SoleOfKind(sg->output, Kind::MulCommon);
+  if (!mul || Other(mul, sg->output) != sg->inputs[0]) return false;
+  sg->kind = Kind::Silu;
+  sg->output = mul->output;
+  rw.Kill(mul);
+  return true;
+}
+
+}  // namespace
+
+size_t FusionPasses::Run(flow::Flow &flow) {
+  const size_t before = flow.nodes.size();
+  Rewriter rw(flow);
+  using Pass = bool (*)(Rewriter &, const NodePtr &);
+  // order matters: bias before GELU / activation before residual, residual before Add+LN
+  const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseSilu};
+  for (Pass pass : passes) {
+    bool again = true;
+    while (again) {
+      again = false;
+      for (size_t i = 0; i < flow.nodes.size(); ++i) {
+        const NodePtr n = flow.nodes[i];
+        if (rw.dead.count(n.get())) continue;
+        if (pass(rw, n)) { rw.Commit(); again = true; break; }
+      }
+    }
+  }
+  // drop tensors nothing refers to any more
+  std::unordered_set<const flow::Region *> live;
+  for (const auto &n : flow.nodes) {
+    live.insert(n->output.get());
+    for (const auto &r : n->inputs) live.insert(r.get());
+    for (const auto &r : n->consts) live.insert(r.get());
+  }
+  std::vector<RegionPtr> kept;
+  for (const auto &r : flow.regions) {
+    if (live.count(r.get()) || r->kind == flow::Region::kInput || r->kind == flow::Region::kOutput) kept.push_back(r);
+    else flow.by_name.erase(r->name);
+  }
+  flow.regions = std::move(kept);
+  return before - flow.nodes.size();
+}
+
+}  // namespace worker
+}  // namespace fluidml

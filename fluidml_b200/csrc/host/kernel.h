@@ -1,0 +1,108 @@
+// Host-side Kernel objects.  In the reference a Kernel's Run() EMITS MLIR for one operator
+// (include/structure/kernel/kernel/kernel.h:9-88); here Run() RECORDS the CUDA launches of
+// that operator into a launch plan, calling the C ABI of the kernel library when the plan
+// is replayed.  The taxonomy is the reference's: four arity x scratch signatures and one
+// concrete class per operator kernel, with the same GetKernelName() strings.
+#pragma once
+#include "flow.h"
+#include "fluidml_cuda.h"
+#include <functional>
+
+namespace fluidml {
+namespace kernel {
+
+// One recorded launch: a closure over tensor descriptors and scalars.  Returns fml_status.
+struct Launch {
+  std::string node, kernel;
+  std::function<int(void *stream)> fn;
+};
+
+class LaunchRecorder {
+public:
+  void Add(std::string kernel, std::function<int(void *)> fn) {
+    launches_.push_back({current_node_, std::move(kernel), std::move(fn)});
+  }
+  void SetNode(const std::string &name) { current_node_ = name; }
+  const std::vector<Launch> &Launches() const { return launches_; }
+
+private:
+  std::string current_node_;
+  std::vector<Launch> launches_;
+};
+
+// Scratch handed to kernels that need it (split-K GEMM): partial tiles from the arena and the
+// persistent tile counters.
+struct Buffer {
+  void *partials = nullptr;
+  size_t partial_bytes = 0;
+  void *counters = nullptr;
+  size_t counter_bytes = 0;
+};
+
+class Kernel {
+public:
+  virtual ~Kernel() = default;
+  virtual std::string GetKernelName() const = 0;
+  // Uniform entry used by the builder; the four signature classes route it to their Run().
+  virtual void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &inputs,
+                      const fml_tensor &output, const Buffer &buffer) const = 0;
+  // Scratch this kernel needs for these operands (0 for most).
+  virtual void GetBufferSize(const std::vector<fml_tensor> &inputs, const fml_tensor &output,
+                             size_t *partial_bytes, size_t *counter_bytes) const {
+    *partial_bytes = 0;
+    *counter_bytes = 0;
+  }
+  // True when, for these operands, the output can simply alias the input's memory (no launch).
+  virtual bool IsAlias(const fml_tensor &input, const fml_tensor &output) const { return false; }
+
+protected:
+  Kernel() = default;
+};
+
+class SingleInputWithoutBufferKernel : public Kernel {
+public:
+  virtual void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const = 0;
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &out,
+              const Buffer &) const override { Run(rec, in.at(0), out); }
+};
+
+class SingleInputWithBufferKernel : public Kernel {
+public:
+  virtual void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output,
+                   const Buffer &buffer) const = 0;
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &out,
+              const Buffer &b) const override { Run(rec, in.at(0), out, b); }
+};
+
+class DoubleInputsWithoutBufferKernel : public Kernel {
+public:
+  virtual void Run(LaunchRecorder &rec, const fml_tensor &lhs, const fml_tensor &rhs,
+                   const fml_tensor &output) const = 0;
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &out,
+              const Buffer &) const override { Run(rec, in.at(0), in.at(1), out); }
+};
+
+class DoubleInputsWithBufferKernel : public Kernel {
+public:
+  virtual void Run(LaunchRecorder &rec, const fml_tensor &lhs, const fml_tensor &rhs,
+                   const fml_tensor &output, const Buffer &buffer) const = 0;
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &out,
+              const Buffer &b) const override { Run(rec, in.at(0), in.at(1), out, b); }
+};
+
+// Maps a constant region to its device view (uploaded by the builder).
+using ConstResolver = std::function<fml_tensor(const flow::RegionPtr &)>;
+
+struct KernelOptions {
+  int gemm_precision = FML_GEMM_AUTO;  // fml_gemm_precision for MatMul / Gemm / Conv
+};
+
+// node -> kernel object (reference: SelectKernel, src/worker/utils.cpp:80-335).
+std::unique_ptr<Kernel> SelectKernel(const flow::Node &node, const ConstResolver &resolve,
+                                     const KernelOptions &options);
+
+// Describes a region as an fml_tensor over `data` with the strides of its layout.
+fml_tensor MakeTensor(const flow::Region &region, void *data);
+
+}  // namespace kernel
+}  // namespace fluidml

@@ -1,0 +1,291 @@
+#include "program.h"
+#include <algorithm>
+#include <cstdlib>
+
+namespace fluidml {
+namespace worker {
+
+namespace {
+
+void Check(int status, const std::string &what) {
+  if (status != FML_OK) throw Error(what + ": " + fml_last_error());
+}
+
+size_t AlignUp(size_t v, size_t a) { return a <= 1 ? v : (v + a - 1) / a * a; }
+
+// A placeholder base address with the alignment every planned tenant has.
+void *const kPlaceholder = reinterpret_cast<void *>(static_cast<uintptr_t>(1) << 20);
+
+kernel::ConstResolver PlaceholderResolver() {
+  return [](const flow::RegionPtr &r) { return kernel::MakeTensor(*r, kPlaceholder); };
+}
+
+const flow::RegionPtr &Owner(const AliasMap &aliases, const flow::RegionPtr &r) {
+  auto it = aliases.find(r.get());
+  return it == aliases.end() ? r : it->second;
+}
+
+// Row-major logical bytes -> bytes in the region's physical order (builder.cpp:280-296).
+std::vector<uint8_t> PermuteConstant(const flow::Region &r) {
+  const std::vector<uint8_t> &src = r.constant->Bytes();
+  if (utils::IsDefaultLayout(r.layout)) return src;
+  const size_t es = GetSizeFromType(r.meta.GetType());
+  const std::vector<int64_t> &shape = r.meta.GetShape();
+  const std::vector<int64_t> strides = r.GetStrides();
+  std::vector<uint8_t> dst(src.size());
+  const size_t rank = shape.size();
+  std::vector<int64_t> idx(rank, 0);
+  const int64_t n = r.meta.GetElementsNum();
+  for (int64_t e = 0; e < n; ++e) {
+    int64_t off = 0;
+    for (size_t d = 0; d < rank; ++d) off += idx[d] * strides[d];
+    memcpy(dst.data() + off * es, src.data() + e * es, es);
+    for (size_t d = rank; d-- > 0;) {
+      if (++idx[d] < shape[d]) break;
+      idx[d] = 0;
+    }
+  }
+  return dst;
+}
+
+}  // namespace
+
+AliasMap Lowering::ComputeAliases(const flow::Sequence &sequence, const kernel::KernelOptions &ko) {
+  AliasMap aliases;
+  const kernel::ConstResolver resolve = PlaceholderResolver();
+  for (const auto &node : sequence.nodes) {
+    if (node->inputs.size() != 1 || node->output->kind != flow::Region::kInner) continue;
+    std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
+    const fml_tensor in = kernel::MakeTensor(*node->inputs[0], kPlaceholder);
+    const fml_tensor out = kernel::MakeTensor(*node->output, kPlaceholder);
+    if (!k->IsAlias(in, out)) continue;
+    aliases[node->output.get()] = Owner(aliases, node->inputs[0]);
+  }
+  return aliases;
+}
+
+size_t Lowering::ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko) {
+  size_t counters = 0;
+  const kernel::ConstResolver resolve = PlaceholderResolver();
+  for (const auto &node : sequence.nodes) {
+    std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
+    std::vector<fml_tensor> ins;
+    for (const auto &r : node->inputs) ins.push_back(kernel::MakeTensor(*r, kPlaceholder));
+    size_t pb = 0, cb = 0;
+    k->GetBufferSize(ins, kernel::MakeTensor(*node->output, kPlaceholder), &pb, &cb);
+    node->buffer_size = pb;
+    counters = std::max(counters, cb);
+  }
+  return counters;
+}
+
+std::vector<memory::Info> Lowering::Lifetimes(const flow::Sequence &sequence, const AliasMap &aliases) {
+  std::unordered_map<const flow::Region *, std::pair<size_t, size_t>> life;
+  auto touch = [&](const flow::RegionPtr &r0, size_t i) {
+    const flow::RegionPtr &r = Owner(aliases, r0);
+    if (!r->NeedMemoryAllocation()) return;
+    auto it = life.find(r.get());
+    if (it == life.end()) life[r.get()] = {i, i};
+    else { it->second.first = std::min(it->second.first, i); it->second.second = std::max(it->second.second, i); }
+  };
+  for (size_t i = 0; i < sequence.nodes.size(); ++i) {
+    for (const auto &r : sequence.nodes[i]->inputs) touch(r, i);
+    touch(sequence.nodes[i]->output, i);
+  }
+  std::vector<memory::Info> infos;
+  for (const auto &r : sequence.regions) {
+    auto it = life.find(r.get());
+    if (it == life.end()) continue;
+    infos.push_back({r->name, it->second.first, it->second.second, r->meta.GetSize()});
+  }
+  for (size_t i = 0; i < sequence.nodes.size(); ++i)
+    if (sequence.nodes[i]->buffer_size > 0)
+      infos.push_back({sequence.nodes[i]->name, i, i, sequence.nodes[i]->buffer_size});
+  return infos;
+}
+
+Program::~Program() {
+  if (arena) fml_free(arena);
+  if (weights) fml_free(weights);
+  if (io) fml_free(io);
+  if (counters) fml_free(counters);
+}
+
+std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequence &sequence,
+                                      const memory::Index &index, const AliasMap &aliases,
+                                      size_t counter_bytes, const Options &options) {
+  auto prog = std::make_unique<Program>();
+  Check(fml_set_device(options.device), "selecting the device");
+  Check(fml_warmup(), "initialising the kernel library");
+
+  // ---- constants referenced by any node: one blob, each at a 256-byte boundary
+  std::unordered_map<const flow::Region *, size_t> const_offset;
+  std::vector<uint8_t> blob;
+  auto add_const = [&](const flow::RegionPtr &r) {
+    if (r->kind != flow::Region::kConstant || const_offset.count(r.get())) return;
+    const size_t off = AlignUp(blob.size(), 256);
+    const std::vector<uint8_t> bytes = PermuteConstant(*r);
+    blob.resize(off + std::max<size_t>(bytes.size(), 1));
+    memcpy(blob.data() + off, bytes.data(), bytes.size());
+    const_offset[r.get()] = off;
+  };
+  for (const auto &node : sequence.nodes) {
+    for (const auto &r : node->inputs) add_const(r);
+    for (const auto &r : node->consts) add_const(r);
+  }
+  prog->weight_bytes = blob.size();
+  Check(fml_malloc(&prog->weights, blob.size()), "allocating the weight blob");
+  if (!blob.empty()) {
+    Check(fml_memcpy_h2d(prog->weights, blob.data(), blob.size(), nullptr), "uploading the weights");
+    Check(fml_stream_sync(nullptr), "uploading the weights");
+  }
+
+  // ---- arena (zeroed once), interface buffers, split-K counters
+  prog->arena_bytes = index.GetMaximum();
+  Check(fml_malloc(&prog->arena, prog->arena_bytes), "allocating the arena");
+  Check(fml_memset(prog->arena, 0, prog->arena_bytes, nullptr), "clearing the arena");
+  std::unordered_map<const flow::Region *, size_t> io_offset;
+  size_t io_bytes = 0;
+  for (const auto &r : flow.regions) {
+    if (r->kind != flow::Region::kInput && r->kind != flow::Region::kOutput) continue;
+    io_offset[r.get()] = io_bytes;
+    io_bytes = AlignUp(io_bytes + r->meta.GetSize(), 256);
+  }
+  prog->io_bytes = io_bytes;
+  Check(fml_malloc(&prog->io, io_bytes), "allocating the interface buffers");
+  Check(fml_memset(prog->io, 0, io_bytes, nullptr), "clearing the interface buffers");
+  prog->counter_bytes = AlignUp(std::max<size_t>(counter_bytes, 4), 256);
+  Check(fml_malloc(&prog->counters, prog->counter_bytes), "allocating the split-K counters");
+  Check(fml_memset(prog->counters, 0, prog->counter_bytes, nullptr), "clearing the split-K counters");
+  Check(fml_stream_sync(nullptr), "initialising device memory");
+
+  auto base_of = [&](const flow::RegionPtr &r0) -> void * {
+    const flow::RegionPtr &r = Owner(aliases, r0);
+    switch (r->kind) {
+    case flow::Region::kConstant: {
+      auto it = const_offset.find(r.get());
+      if (it == const_offset.end()) throw Error("constant '" + r->name + "' was never uploaded");
+      return (char *)prog->weights + it->second;
+    }
+    case flow::Region::kInput:
+    case flow::Region::kOutput: return (char *)prog->io + io_offset.at(r.get());
+    default:
+      if (!index.Has(r->name)) throw Error("tensor '" + r->name + "' has no place in the arena");
+      return (char *)prog->arena + index.Get(r->name);
+    }
+  };
+  // An aliased region keeps its own shape and layout over its owner's bytes.
+  auto tensor_of = [&](const flow::RegionPtr &r) { return kernel::MakeTensor(*r, base_of(r)); };
+  const kernel::ConstResolver resolve = [&](const flow::RegionPtr &r) { return tensor_of(r); };
+
+  for (const std::string &name : flow.inputs) {
+    const flow::RegionPtr r = flow.Get(name);
+    prog->inputs.push_back({name, base_of(r), r->meta.GetSize()});
+  }
+  for (const std::string &name : flow.outputs) {
+    const flow::RegionPtr r = flow.Get(name);
+    prog->outputs.push_back({name, base_of(r), r->meta.GetSize()});
+  }
+
+  kernel::KernelOptions ko;
+  ko.gemm_precision = options.gemm_precision;
+  kernel::LaunchRecorder rec;
+  for (const auto &node : sequence.nodes) {
+    if (aliases.count(node->output.get())) { ++prog->aliased_nodes; continue; }
+    std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
+    std::vector<fml_tensor> ins;
+    for (const auto &r : node->inputs) ins.push_back(tensor_of(r));
+    const fml_tensor out = tensor_of(node->output);
+    kernel::Buffer buf;
+    size_t pb = 0, cb = 0;
+    k->GetBufferSize(ins, out, &pb, &cb);
+    if (pb > node->buffer_size || cb > prog->counter_bytes)
+      throw Error("node '" + node->name + "' needs more scratch than was planned for it");
+    if (pb > 0) {
+      buf.partials = (char *)prog->arena + index.Get(node->name);
+      buf.partial_bytes = node->buffer_size;
+      buf.counters = prog->counters;
+      buf.counter_bytes = prog->counter_bytes;
+    }
+    rec.SetNode(node->name);
+    k->Launch(rec, ins, out, buf);
+  }
+  prog->launches = rec.Launches();
+  for (const auto &l : prog->launches) ++prog->kernel_histogram[l.kernel];
+  return prog;
+}
+
+// ------------------------------------------------------------------------------ Runner
+Runner::Runner(std::unique_ptr<Program> program, const Options &options)
+    : program_(std::move(program)), options_(options) {
+  Check(fml_set_device(options_.device), "selecting the device");
+  Check(fml_stream_create(&stream_), "creating the stream");
+  Check(fml_event_create(&ev_start_), "creating an event");
+  Check(fml_event_create(&ev_stop_), "creating an event");
+  // One eager pass: validates every launch and lets the library do its lazy set-up before
+  // anything is captured.
+  for (const auto &l : program_->launches) {
+    int st = l.fn(stream_);
+    if (st != FML_OK) throw Error("node '" + l.node + "' (" + l.kernel + "): " + fml_last_error());
+  }
+  Check(fml_check_device(stream_), "first forward pass");
+  if (options_.cuda_graph && !program_->launches.empty()) {
+    Check(fml_graph_begin_capture(stream_), "starting the graph capture");
+    for (const auto &l : program_->launches) {
+      int st = l.fn(stream_);
+      if (st != FML_OK) {
+        const std::string msg = fml_last_error();
+        fml_graph_abort_capture(stream_);
+        throw Error("capturing node '" + l.node + "' (" + l.kernel + "): " + msg);
+      }
+    }
+    Check(fml_graph_end_capture(stream_, &graph_exec_), "instantiating the graph");
+  }
+}
+
+Runner::~Runner() {
+  if (stream_) fml_stream_sync(stream_);
+  if (graph_exec_) fml_graph_destroy(graph_exec_);
+  if (ev_start_) fml_event_destroy(ev_start_);
+  if (ev_stop_) fml_event_destroy(ev_stop_);
+  if (stream_) fml_stream_destroy(stream_);
+}
+
+void Runner::Replay() {
+  if (graph_exec_) {
+    Check(fml_graph_launch(graph_exec_, stream_), "launching the graph");
+    return;
+  }
+  for (const auto &l : program_->launches) {
+    int st = l.fn(stream_);
+    if (st != FML_OK) throw Error("node '" + l.node + "' (" + l.kernel + "): " + fml_last_error());
+  }
+}
+
+size_t Runner::Run(const std::unordered_map<std::string, void *> &args, size_t epoch) {
+  if (epoch == 0) epoch = 1;
+  Check(fml_set_device(options_.device), "selecting the device");
+  // args.at() throws std::out_of_range for a missing name, as the reference does
+  // (src/worker/runner.cpp:70); look everything up before touching the device.
+  std::vector<void *> in_host, out_host;
+  for (const auto &b : program_->inputs) in_host.push_back(args.at(b.name));
+  for (const auto &b : program_->outputs) out_host.push_back(args.at(b.name));
+  for (size_t i = 0; i < in_host.size(); ++i) {
+    if (!in_host[i]) throw Error("input '" + program_->inputs[i].name + "' is a null pointer");
+    Check(fml_memcpy_h2d(program_->inputs[i].device, in_host[i], program_->inputs[i].bytes, stream_), "copying an input");
+  }
+  Check(fml_event_record(ev_start_, stream_), "recording an event");
+  for (size_t e = 0; e < epoch; ++e) Replay();
+  Check(fml_event_record(ev_stop_, stream_), "recording an event");
+  for (size_t i = 0; i < out_host.size(); ++i) {
+    if (!out_host[i]) throw Error("output '" + program_->outputs[i].name + "' is a null pointer");
+    Check(fml_memcpy_d2h(out_host[i], program_->outputs[i].device, program_->outputs[i].bytes, stream_), "copying an output");
+  }
+  Check(fml_check_device(stream_), "forward pass");
+  float ms = 0.0f;
+  Check(fml_event_elapsed_ms(ev_start_, ev_stop_, &ms), "reading the timer");
+  return (size_t)((double)ms * 1e6 / (double)epoch);
+}
+
+}  // namespace worker
+}  // namespace fluidml

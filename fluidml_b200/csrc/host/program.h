@@ -1,0 +1,89 @@
+// Lowering of a planned flow to a device program and its execution:
+//   Lowering   which regions alias which (no-op reshapes, transposes that are pure stride
+//              permutations), per-node scratch sizes;
+//   Builder    replaces GeneralBuilder (src/worker/builder.cpp:149-608): uploads constants
+//              physically permuted to their layouts (:273-361), binds every region to the
+//              arena / weight blob / interface buffers, and walks the sequence calling
+//              kernel->Launch to record the launch plan;
+//   Runner     replaces Lower + Runner (src/worker/lower.cpp:37-59, runner.cpp:56-120):
+//              captures the launch plan into a CUDA graph once; per Invoke copies inputs in,
+//              replays the graph `epoch` times between two events, copies outputs out and
+//              returns the average nanoseconds per replay.
+#pragma once
+#include "kernel.h"
+#include "memory.h"
+#include <map>
+#include <unordered_map>
+
+namespace fluidml {
+namespace worker {
+
+struct Options {
+  int device = 0;
+  int gemm_precision = FML_GEMM_AUTO;
+  bool fusion = true;
+  bool cuda_graph = true;
+  size_t alignment = 256;
+  bool dp_constant_cost = false;
+};
+
+// region -> the region whose memory it shares (itself when it owns memory).
+using AliasMap = std::unordered_map<const flow::Region *, flow::RegionPtr>;
+
+class Lowering {
+public:
+  // Walks the sequence; a single-input node whose kernel reports IsAlias() for the operands'
+  // strides, and whose output is an inner region, shares its input's memory.
+  static AliasMap ComputeAliases(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
+  // Fills node->buffer_size (split-K partial bytes) and returns the largest counter buffer any
+  // node needs.  Uses aligned placeholder addresses: planned offsets are multiples of the
+  // alignment, so the real operands take the same path.
+  static size_t ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
+  // Lifetimes with aliases merged into their owners.
+  static std::vector<memory::Info> Lifetimes(const flow::Sequence &sequence, const AliasMap &aliases);
+};
+
+struct IoBinding {
+  std::string name;
+  void *device = nullptr;
+  size_t bytes = 0;
+};
+
+struct Program {
+  std::vector<kernel::Launch> launches;
+  std::vector<IoBinding> inputs, outputs;
+  void *arena = nullptr, *weights = nullptr, *io = nullptr, *counters = nullptr;
+  size_t arena_bytes = 0, weight_bytes = 0, io_bytes = 0, counter_bytes = 0;
+  size_t aliased_nodes = 0;
+  std::map<std::string, int> kernel_histogram;
+  ~Program();
+  Program() = default;
+  Program(const Program &) = delete;
+};
+
+class Builder {
+public:
+  static std::unique_ptr<Program> Run(const flow::Flow &flow, const flow::Sequence &sequence,
+                                      const memory::Index &index, const AliasMap &aliases,
+                                      size_t counter_bytes, const Options &options);
+};
+
+class Runner {
+public:
+  Runner(std::unique_ptr<Program> program, const Options &options);
+  ~Runner();
+  // `args`: name -> host pointer for every interface tensor.  Returns ns per epoch.
+  size_t Run(const std::unordered_map<std::string, void *> &args, size_t epoch);
+  const Program &GetProgram() const { return *program_; }
+
+private:
+  void Replay();
+  std::unique_ptr<Program> program_;
+  Options options_;
+  void *stream_ = nullptr;
+  void *graph_exec_ = nullptr;
+  void *ev_start_ = nullptr, *ev_stop_ = nullptr;
+};
+
+}  // namespace worker
+}  // namespace fluidml

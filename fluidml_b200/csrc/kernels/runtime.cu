@@ -115,6 +115,76 @@ int fml_stream_sync(void *stream) {
   return FML_OK;
 }
 
+int fml_event_create(void **event) {
+  FML_REQUIRE(event, FML_BAD_ARG, "fml_event_create: null argument");
+  cudaEvent_t e;
+  FML_CUDA(cudaEventCreate(&e));
+  *event = e;
+  return FML_OK;
+}
+
+int fml_event_destroy(void *event) {
+  FML_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return FML_OK;
+}
+
+int fml_event_record(void *event, void *stream) {
+  FML_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_event_sync(void *event) {
+  FML_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+  return FML_OK;
+}
+
+int fml_event_elapsed_ms(void *start, void *stop, float *ms) {
+  FML_REQUIRE(ms, FML_BAD_ARG, "fml_event_elapsed_ms: null argument");
+  FML_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+  return FML_OK;
+}
+
+int fml_graph_begin_capture(void *stream) {
+  FML_CUDA(cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeThreadLocal));
+  return FML_OK;
+}
+
+int fml_graph_end_capture(void *stream, void **graph_exec) {
+  FML_REQUIRE(graph_exec, FML_BAD_ARG, "fml_graph_end_capture: null argument");
+  *graph_exec = nullptr;
+  cudaGraph_t graph = nullptr;
+  FML_CUDA(cudaStreamEndCapture(as_stream(stream), &graph));
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+  *graph_exec = exec;
+  return FML_OK;
+}
+
+int fml_graph_abort_capture(void *stream) {
+  cudaGraph_t graph = nullptr;
+  cudaStreamEndCapture(as_stream(stream), &graph);
+  if (graph) cudaGraphDestroy(graph);
+  cudaGetLastError();
+  return FML_OK;
+}
+
+int fml_graph_launch(void *graph_exec, void *stream) {
+  FML_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), as_stream(stream)));
+  return FML_OK;
+}
+
+int fml_graph_destroy(void *graph_exec) {
+  FML_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec)));
+  return FML_OK;
+}
+
+int fml_warmup(void) {
+  FML_REQUIRE(device_status_word(), FML_CUDA_ERROR, "fml_warmup: cannot allocate the device status word");
+  return FML_OK;
+}
+
 int fml_check_device(void *stream) {
   FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
   int *w = device_status_word();

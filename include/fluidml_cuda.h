@@ -72,6 +72,23 @@ int fml_host_free_pinned(void *ptr);
 int fml_stream_create(void **stream);
 int fml_stream_destroy(void *stream);
 int fml_stream_sync(void *stream);
+/* Events and CUDA-graph capture, so a host that links only this library can time and replay
+ * a recorded launch list (the reference timed a JIT'd function with std::chrono,
+ * src/worker/runner.cpp:101-112). */
+int fml_event_create(void **event);
+int fml_event_destroy(void *event);
+int fml_event_record(void *event, void *stream);
+int fml_event_sync(void *event);
+int fml_event_elapsed_ms(void *start, void *stop, float *ms);
+int fml_graph_begin_capture(void *stream);
+int fml_graph_end_capture(void *stream, void **graph_exec); /* instantiates; NULL exec on error */
+int fml_graph_abort_capture(void *stream);
+int fml_graph_launch(void *graph_exec, void *stream);
+int fml_graph_destroy(void *graph_exec);
+/* Allocates whatever the library creates lazily on first use (status word, attribute
+ * settings) so that later calls can be stream-captured. */
+int fml_warmup(void);
+
 /* Reads and clears the device status word kernels write when a bounded wait expires or a
  * gather index is clamped.  Synchronises `stream`.  Returns FML_OK, FML_DEVICE_TIMEOUT or
  * FML_INDEX_OUT_OF_RANGE. */
