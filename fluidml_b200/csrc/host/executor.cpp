@@ -89,6 +89,18 @@ public:
 
   std::string GetStatsJson() const override { return stats_.Dump(); }
 
+  std::string ProfileJson(const std::unordered_map<std::string, void *> &args, size_t passes) {
+    if (!runner_) throw Error("Profile called before Compile");
+    json::Value o = json::Value::Object();
+    for (const auto &kv : runner_->Profile(args, passes ? passes : 1)) {
+      json::Value e = json::Value::Object();
+      e.Set("us", json::Value(kv.second.us));
+      e.Set("launches", json::Value((double)kv.second.launches));
+      o.Set(kv.first, e);
+    }
+    return o.Dump();
+  }
+
 private:
   // `dry_run`: stop before anything touches the device (planning only).
   void CompileGraph(graph::Graph graph, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json,
@@ -194,6 +206,15 @@ private:
       }
       json::Value a = json::Value::Object();
       a.Set("tenants", arena);
+      json::Value lives = json::Value::Object();
+      for (const memory::Info &i : infos) {
+        json::Value e = json::Value::Array();
+        e.Push(json::Value((double)i.start));
+        e.Push(json::Value((double)i.end));
+        e.Push(json::Value((double)i.size));
+        lives.Set(i.name, e);
+      }
+      a.Set("lifetimes", lives);
       a.Set("stats", stats_);
       root.Set("arena", a);
       *json << root.Dump();
@@ -321,6 +342,17 @@ int fml_executor_plan_buffer(fml_executor *e, const void *onnx_bytes, size_t siz
     std::ofstream fl, fj;
     std::ofstream *pl = OpenOpt(fl, llvm_path), *pj = OpenOpt(fj, json_path);
     static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->CompileBuffer(onnx_bytes, size, nullptr, pl, pj, true);
+  });
+}
+
+int fml_executor_profile(fml_executor *e, const char *const *names, void *const *buffers, size_t count,
+                         size_t passes, const char **json_out) {
+  if (!e || !e->impl || !json_out || (count && (!names || !buffers))) return 1;
+  return Guard(e, [&] {
+    std::unordered_map<std::string, void *> args;
+    for (size_t i = 0; i < count; ++i) args[names[i]] = buffers[i];
+    e->stats = static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->ProfileJson(args, passes);
+    *json_out = e->stats.c_str();
   });
 }
 

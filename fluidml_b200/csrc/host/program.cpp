@@ -287,5 +287,36 @@ size_t Runner::Run(const std::unordered_map<std::string, void *> &args, size_t e
   return (size_t)((double)ms * 1e6 / (double)epoch);
 }
 
+std::map<std::string, Runner::KernelTime> Runner::Profile(const std::unordered_map<std::string, void *> &args,
+                                                          size_t passes) {
+  Check(fml_set_device(options_.device), "selecting the device");
+  for (const auto &b : program_->inputs)
+    Check(fml_memcpy_h2d(b.device, args.at(b.name), b.bytes, stream_), "copying an input");
+  const size_t n = program_->launches.size();
+  std::vector<void *> events(2 * (n + 1), nullptr);
+  for (auto &e : events) Check(fml_event_create(&e), "creating an event");
+  std::map<std::string, KernelTime> out;
+  for (size_t p = 0; p < passes; ++p) {
+    for (size_t i = 0; i < n; ++i) {
+      Check(fml_event_record(events[2 * i], stream_), "recording an event");
+      int st = program_->launches[i].fn(stream_);
+      if (st != FML_OK) throw Error("node '" + program_->launches[i].node + "': " + fml_last_error());
+      Check(fml_event_record(events[2 * i + 1], stream_), "recording an event");
+    }
+    Check(fml_event_record(events[2 * n], stream_), "recording an event");
+    Check(fml_event_record(events[2 * n + 1], stream_), "recording an event");
+    Check(fml_check_device(stream_), "profiled forward pass");
+    for (size_t i = 0; i <= n; ++i) {
+      float ms = 0;
+      Check(fml_event_elapsed_ms(events[2 * i], events[2 * i + 1], &ms), "reading the timer");
+      KernelTime &k = out[i < n ? program_->launches[i].kernel : std::string("(empty event pair)")];
+      k.us += (double)ms * 1e3;
+      k.launches += 1;
+    }
+  }
+  for (auto &e : events) fml_event_destroy(e);
+  return out;
+}
+
 }  // namespace worker
 }  // namespace fluidml

@@ -75,6 +75,12 @@ public:
   // `args`: name -> host pointer for every interface tensor.  Returns ns per epoch.
   size_t Run(const std::unordered_map<std::string, void *> &args, size_t epoch);
   const Program &GetProgram() const { return *program_; }
+  // Tracing: replays the launch list eagerly `passes` times with an event pair around every
+  // launch (weights are cold in each pass, as in a real forward pass) and returns the summed
+  // microseconds and launch count per kernel name, plus the cost of an empty event pair under
+  // the key "(empty event pair)".
+  struct KernelTime { double us = 0; size_t launches = 0; };
+  std::map<std::string, KernelTime> Profile(const std::unordered_map<std::string, void *> &args, size_t passes);
 
 private:
   void Replay();

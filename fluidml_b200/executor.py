@@ -110,6 +110,16 @@ class Executor:
         self._check(lib().fml_executor_invoke(self._h, c_names, c_ptrs, ctypes.c_size_t(n), ctypes.byref(ns)))
         return ns.value
 
+    def profile(self, args: Dict[str, np.ndarray], passes: int = 1) -> dict:
+        """Per-kernel device time of `passes` eager forward passes (event pair per launch)."""
+        names = [k.encode() for k in args]
+        ptrs = [a.ctypes.data for a in args.values()]
+        n = len(names)
+        out = ctypes.c_char_p()
+        self._check(lib().fml_executor_profile(self._h, (ctypes.c_char_p * n)(*names), (ctypes.c_void_p * n)(*ptrs),
+                                               ctypes.c_size_t(n), ctypes.c_size_t(passes), ctypes.byref(out)))
+        return _json.loads(out.value.decode())
+
     def stats(self) -> dict:
         return _json.loads(lib().fml_executor_stats_json(self._h).decode())
 
@@ -122,29 +132,16 @@ class Executor:
             pass
 
 
+_PINNED_OWNERS = []  # page-locked blocks live until the process exits
+
+
 def pinned_empty(shape, dtype) -> np.ndarray:
-    """A numpy array over page-locked host memory (kept alive by the array's base)."""
+    """A numpy array over page-locked host memory (cudaMallocHost)."""
     dtype = np.dtype(dtype)
-    n = int(np.prod(shape)) * dtype.itemsize
+    count = int(np.prod(shape))
+    nbytes = max(count * dtype.itemsize, 1)
     p = ctypes.c_void_p()
-    cabi.check(cabi.lib().fml_host_alloc_pinned(ctypes.byref(p), ctypes.c_size_t(max(n, 1))))
-
-    class _Owner:
-        def __init__(self, ptr):
-            self.ptr = ptr
-
-        def __del__(self):
-            try:
-                cabi.lib().fml_host_free_pinned(ctypes.c_void_p(self.ptr))
-            except Exception:
-                pass
-
-    owner = _Owner(p.value)
-    buf = (ctypes.c_uint8 * max(n, 1)).from_address(p.value)
-    arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
-    arr = arr.view()
-    _PINNED[id(buf)] = (owner, buf)
-    return arr
-
-
-_PINNED = {}
+    cabi.check(cabi.lib().fml_host_alloc_pinned(ctypes.byref(p), ctypes.c_size_t(nbytes)))
+    buf = (ctypes.c_uint8 * nbytes).from_address(p.value)
+    _PINNED_OWNERS.append(buf)
+    return np.frombuffer(buf, dtype=dtype, count=count).reshape(shape)

@@ -45,6 +45,13 @@ int fml_executor_invoke(fml_executor *e, const char *const *names, void *const *
 int fml_executor_plan_buffer(fml_executor *e, const void *onnx_bytes, size_t size,
                              const char *llvm_path, const char *json_path);
 
+/* Tracing (the reference's only tracing is the Runner's wall clock, src/worker/runner.cpp:
+ * 101-119): replays the compiled launch list eagerly `passes` times with an event pair
+ * around every launch and returns {"<KernelName>": {"us": total, "launches": n}, ...} as JSON
+ * owned by the handle.  Only the inputs in `names` are read; outputs are not copied back. */
+int fml_executor_profile(fml_executor *e, const char *const *names, void *const *buffers,
+                         size_t count, size_t passes, const char **json_out);
+
 /* JSON text owned by the handle, valid until the next call on it. */
 const char *fml_executor_stats_json(fml_executor *e);
 

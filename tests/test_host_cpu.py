@@ -1,0 +1,268 @@
+"""Host-side logic and the C ABI surface, without a GPU."""
+import ctypes
+import json
+import os
+import re
+import tempfile
+
+import numpy as np
+import pytest
+
+from fluidml_b200 import cabi, executor, models
+from fluidml_b200.executor import Executor
+from fluidml_b200.onnx_lite import FLOAT, INT64, Model, Node, ValueInfo
+from oracle import oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ------------------------------------------------------------------ ABI surface
+@pytest.mark.parametrize("header,loader", [("fluidml_cuda.h", cabi.lib), ("fluidml_executor.h", executor.lib)])
+def test_every_declared_symbol_is_exported(header, loader):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(fml_[a-z0-9_]+)\s*\(", text)))
+    assert len(names) > 10
+    lib = loader()
+    for n in names:
+        assert hasattr(lib, n), f"{header}: {n} is declared but not exported"
+
+
+def test_kernel_calls_validate_arguments_without_a_device():
+    # argument checking happens before any CUDA call, so it is testable here
+    t = cabi.Tensor()
+    st = cabi.lib().fml_elementwise(cabi.ADD, None, None, ctypes.byref(t), ctypes.c_double(0), ctypes.c_double(0), None)
+    assert st == 1 and b"null" in cabi.lib().fml_last_error()
+    assert cabi.lib().fml_gemm(None, None, None, None, None, None, None, 0, None, 0, None) == 1
+
+
+# ------------------------------------------------------------------ addressing helpers vs oracle
+def test_gen_strides_and_orders_match_oracle():
+    L = executor.lib()
+    for shape in ([2, 3, 4], [5], [1, 12, 128, 64], [7, 1, 3]):
+        r = len(shape)
+        for layout in orc.gen_all_orders(r):
+            out = (ctypes.c_longlong * r)()
+            assert L.fml_host_gen_strides((ctypes.c_longlong * r)(*shape), (ctypes.c_longlong * r)(*layout), r, out) == 0
+            assert list(out) == orc.gen_strides(shape, layout) == cabi.gen_strides(shape, layout)
+    for n in range(0, 6):
+        cnt = L.fml_host_gen_all_orders(n, None)
+        buf = (ctypes.c_longlong * max(1, cnt * n))()
+        L.fml_host_gen_all_orders(n, buf)
+        assert [list(buf[i * n:(i + 1) * n]) for i in range(cnt)] == orc.gen_all_orders(n)
+
+
+def test_broadcast_shapes_match_oracle():
+    L = executor.lib()
+    cases = [([1, 1, 3], [2, 3]), ([2, 3], [4, 3]), ([5, 1, 7], [1, 6, 7]), ([], [3])]
+    for a, b in cases:
+        out = (ctypes.c_longlong * 8)()
+        r = L.fml_host_broadcast_shape((ctypes.c_longlong * max(1, len(a)))(*a), len(a),
+                                       (ctypes.c_longlong * max(1, len(b)))(*b), len(b), 0, out)
+        ref = orc.broadcast_shape(a, b)
+        assert (None if r < 0 else list(out[:r])) == ref
+    for a, b in [([2, 1, 3], [3, 2]), ([2, 3], [4, 2]), ([1, 12, 128, 64], [1, 12, 64, 128])]:
+        out = (ctypes.c_longlong * 8)()
+        r = L.fml_host_broadcast_shape((ctypes.c_longlong * len(a))(*a), len(a), (ctypes.c_longlong * len(b))(*b), len(b), 1, out)
+        assert (None if r < 0 else list(out[:r])) == orc.broadcast_matmul_shape(a, b)
+
+
+# ------------------------------------------------------------------ memory planner vs the reference's own code
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libfluidml_ref_memory.so")
+
+
+def _plan(lib, fn, greedy, names, start, end, size, alignment=None):
+    n = len(names)
+    c_names = (ctypes.c_char_p * n)(*[s.encode() for s in names])
+    arr = lambda v: (ctypes.c_size_t * n)(*v)
+    off, mx = (ctypes.c_size_t * n)(), ctypes.c_size_t()
+    args = [greedy, n, c_names, arr(start), arr(end), arr(size)]
+    if alignment is not None:
+        args.append(ctypes.c_size_t(alignment))
+    assert getattr(lib, fn)(*args, off, ctypes.byref(mx)) == 0
+    return list(off), mx.value
+
+
+def _no_overlap(start, end, size, off):
+    n = len(start)
+    for i in range(n):
+        for j in range(i + 1, n):
+            if start[i] <= end[j] and start[j] <= end[i] and size[i] and size[j]:
+                assert off[i] + size[i] <= off[j] or off[j] + size[j] <= off[i], (i, j)
+
+
+@pytest.mark.skipif(not os.path.exists(REF_SO), reason="reference memory planner was not built (oracle/Makefile ref)")
+@pytest.mark.parametrize("seed", range(12))
+def test_memory_plans_equal_the_reference(seed):
+    ref = ctypes.CDLL(REF_SO)
+    rng = np.random.Generator(np.random.PCG64(seed))
+    n = int(rng.integers(1, 60))
+    start = [int(v) for v in rng.integers(0, 40, n)]
+    end = [s + int(v) for s, v in zip(start, rng.integers(0, 12, n))]
+    # distinct sizes: the reference's order among equal sizes is its heap's, ours reproduces the
+    # same heap, but distinct sizes make the comparison independent of that
+    size = [int(v) * 64 for v in rng.permutation(np.arange(1, n + 1))]
+    names = [f"t{i}" for i in range(n)]
+    for greedy in (0, 1):
+        want = _plan(ref, "ref_memory_plan", greedy, names, start, end, size)
+        got = _plan(executor.lib(), "fml_host_memory_plan", greedy, names, start, end, size, 1)
+        assert got == want
+        if greedy:
+            _no_overlap(start, end, size, got[0])
+
+
+@pytest.mark.skipif(not os.path.exists(REF_SO), reason="reference memory planner was not built")
+def test_memory_plan_ties_follow_the_reference_heap():
+    ref = ctypes.CDLL(REF_SO)
+    names = [f"t{i}" for i in range(9)]
+    start, end, size = [0, 0, 1, 2, 2, 3, 5, 5, 6], [1, 3, 2, 4, 6, 5, 7, 8, 8], [256, 512, 256, 512, 256, 1024, 256, 512, 256]
+    assert _plan(executor.lib(), "fml_host_memory_plan", 1, names, start, end, size, 1) == \
+        _plan(ref, "ref_memory_plan", 1, names, start, end, size)
+
+
+def test_aligned_plan_never_overlaps_and_is_aligned():
+    rng = np.random.Generator(np.random.PCG64(7))
+    n = 80
+    start = [int(v) for v in rng.integers(0, 50, n)]
+    end = [s + int(v) for s, v in zip(start, rng.integers(0, 9, n))]
+    size = [int(v) for v in rng.integers(1, 5000, n)]
+    names = [f"t{i}" for i in range(n)]
+    for greedy in (0, 1):
+        off, mx = _plan(executor.lib(), "fml_host_memory_plan", greedy, names, start, end, size, 256)
+        assert all(o % 256 == 0 for o in off)
+        _no_overlap(start, end, size, off)
+        assert mx == max(o + s for o, s in zip(off, size))
+
+
+# ------------------------------------------------------------------ parser / converter
+def tiny(nodes, inits, inputs, outputs, infos=()):
+    m = Model(name="tiny", nodes=nodes, initializers=inits)
+    m.inputs = [ValueInfo(*i) for i in inputs]
+    m.outputs = [ValueInfo(*o) for o in outputs]
+    m.value_info = [ValueInfo(*v) for v in infos]
+    return m.to_bytes()
+
+
+def kinds_of(onnx_bytes, factory=Executor.make_plain_greedy, **opts):
+    ex = factory("t")
+    for k, v in opts.items():
+        ex.set_option(k, v)
+    return [n["kind"] for n in ex.plan(onnx_bytes)["sequence"]]
+
+
+def test_parser_reads_what_the_writer_wrote():
+    m = models.build_bert(layers=1, vocab=300, hidden=64, heads=4, ffn=128, seq=16)
+    st = Executor.make_plain_linear("b").set_option("fusion", 0).plan(m.to_bytes())
+    assert st["graph_nodes"] == len(m.nodes) == st["flow_nodes"]
+    with pytest.raises(RuntimeError, match="truncated|ONNX|graph"):
+        Executor.make_plain_linear("b").plan(m.to_bytes()[:1000])
+    with pytest.raises(RuntimeError, match="not an ONNX model"):
+        Executor.make_plain_linear("b").plan(b"\x08\x01")
+    bad = tiny([Node("Sin", ["x"], ["y"])], {}, [("x", FLOAT, (2,))], [("y", FLOAT, (2,))])
+    with pytest.raises(RuntimeError, match="unsupported ONNX operator 'Sin'"):
+        Executor.make_plain_linear("b").plan(bad)
+    missing = tiny([Node("Relu", ["x"], ["h"]), Node("Relu", ["h"], ["y"])], {}, [("x", FLOAT, (2,))], [("y", FLOAT, (2,))])
+    with pytest.raises(RuntimeError, match="value_info"):
+        Executor.make_plain_linear("b").plan(missing)
+
+
+def test_converter_variant_selection():
+    f32 = np.float32
+    io = dict(inputs=[("x", FLOAT, (2, 3))], outputs=[("y", FLOAT, (2, 3))])
+    one = lambda op, ins, inits, **at: tiny([Node(op, ins, ["y"], attrs=at)], inits, **io)
+    s, t = np.asarray(2.0, f32), np.ones((3,), f32)
+    assert kinds_of(one("Add", ["x", "c"], {"c": s})) == ["AddConstant"]
+    assert kinds_of(one("Add", ["c", "x"], {"c": s})) == ["AddConstant"]
+    assert kinds_of(one("Add", ["x", "c"], {"c": t})) == ["AddCommon"]
+    assert kinds_of(one("Mul", ["c", "x"], {"c": t})) == ["MulCommon"]
+    assert kinds_of(one("Div", ["x", "c"], {"c": s})) == ["DivConstantRhs"]
+    assert kinds_of(one("Sub", ["c", "x"], {"c": s})) == ["SubConstantLhs"]
+    assert kinds_of(one("Pow", ["x", "c"], {"c": s})) == ["Pow"]
+    for op, ins, inits in (("Div", ["x", "c"], {"c": t}), ("Sub", ["x", "c"], {"c": s}), ("Pow", ["x", "c"], {"c": t})):
+        with pytest.raises(RuntimeError, match=op):  # patterns the reference leaves unreachable
+            kinds_of(one(op, ins, inits))
+    # Conv: all-zero pads -> WithoutPadding, else WithPadding
+    w = np.ones((4, 3, 3, 3), f32)
+    conv = lambda pads, oh: tiny([Node("Conv", ["x", "w"], ["y"], attrs=dict(pads=pads, strides=[1, 1], dilations=[1, 1], kernel_shape=[3, 3], group=1))],
+                                 {"w": w}, [("x", FLOAT, (1, 3, 8, 8))], [("y", FLOAT, (1, 4, oh, oh))])
+    assert kinds_of(conv([0, 0, 0, 0], 6)) == ["ConvWithoutPadding"]
+    assert kinds_of(conv([1, 1, 1, 1], 8)) == ["ConvWithPadding"]
+    # Gather: the three operand patterns
+    tab = np.ones((10, 4), f32)
+    assert kinds_of(tiny([Node("Gather", ["t", "i"], ["y"], attrs=dict(axis=0))], {"t": tab}, [("i", INT64, (2, 3))], [("y", FLOAT, (2, 3, 4))])) == ["GatherConstantDataTensor"]
+    assert kinds_of(tiny([Node("Gather", ["x", "i"], ["y"], attrs=dict(axis=1))], {"i": np.asarray(0, np.int64)}, [("x", FLOAT, (2, 5, 4))], [("y", FLOAT, (2, 4))])) == ["GatherConstantIndexScalar"]
+    assert kinds_of(tiny([Node("Gather", ["x", "i"], ["y"], attrs=dict(axis=1))], {"i": np.asarray([1, 2], np.int64)}, [("x", FLOAT, (2, 5, 4))], [("y", FLOAT, (2, 2, 4))])) == ["GatherConstantIndicesTensor"]
+
+
+# ------------------------------------------------------------------ fusion, order, plans on BERT
+@pytest.fixture(scope="module")
+def bert_bytes():
+    return models.build_bert(layers=2, vocab=500).to_bytes()
+
+
+def test_fusion_passes_on_bert(bert_bytes):
+    unfused = kinds_of(bert_bytes, fusion=0)
+    fused = kinds_of(bert_bytes, fusion=1)
+    assert len(fused) < len(unfused)
+    assert fused.count("FusedGemm") == 2 * 6 + 1          # q,k,v,o,ffn1,ffn2 per layer + pooler
+    assert fused.count("FusedSoftmax") == 2 and "Softmax" not in fused
+    assert "GatherConstantDataTensorAddTensorLhsAddTensorLhs" in fused and "UnsqueezeSubLhsScalarMulRhsScalar" in fused
+    for gone in ("Erf", "DivConstantRhs", "AddCommon", "Tanh", "MulConstant"):
+        assert gone not in fused, gone
+
+
+@pytest.mark.parametrize("factory", [Executor.make_plain_linear, Executor.make_plain_greedy, Executor.make_dp_greedy])
+def test_plan_is_consistent(bert_bytes, factory):
+    with tempfile.TemporaryDirectory() as d:
+        ex = factory("bert")
+        st = ex.plan(bert_bytes, json=os.path.join(d, "p.json"))
+        dump = json.load(open(os.path.join(d, "p.json")))
+    assert set(dump) == {"dp_table", "plan", "arena"}
+    lives, tenants = dump["arena"]["lifetimes"], dump["arena"]["tenants"]
+    names = list(lives)
+    start, end, size = ([lives[n][i] for n in names] for i in range(3))
+    off = [tenants[n][0] for n in names]
+    _no_overlap(start, end, size, off)
+    assert all(o % 256 == 0 for o in off)
+    assert st["peak_arena_bytes"] == max(o + s for o, s in zip(off, size))
+    # execution order respects data dependencies: every alias/consumer comes after its producer
+    seen = set()
+    for n in st["sequence"]:
+        seen.add(n["output"])
+    assert len(seen) == len(st["sequence"])
+    if "linear" in st["mode"]:
+        assert st["peak_arena_bytes"] >= sum(size)
+    else:
+        assert st["peak_arena_bytes"] < sum(size)
+
+
+def test_dp_layout_search(bert_bytes):
+    plain = Executor.make_plain_greedy("b").plan(bert_bytes)
+    with tempfile.TemporaryDirectory() as d:
+        dp = Executor.make_dp_greedy("b").plan(bert_bytes, json=os.path.join(d, "p.json"))
+        dump = json.load(open(os.path.join(d, "p.json")))
+    # the search turns the four head transposes of every layer into aliases
+    n_alias = lambda st: sum(1 for n in st["sequence"] if n["kind"] == "Transpose" and n["alias"])
+    assert n_alias(plain) == 0 and n_alias(dp) == 2 * 4
+    # dump schema of the reference: dp_table.evaluator.<Kernel>[{..._shape, ..._layout, time_cost}], plan.<tensor>[layout]
+    ev = dump["dp_table"]["evaluator"]
+    assert "TransposeKernel" in ev and "FusedGemmKernel" in ev
+    rec = ev["TransposeKernel"][0]
+    assert {"input_shape", "input_layout", "output_shape", "output_layout", "time_cost"} <= set(rec)
+    assert all(sorted(v) == list(range(len(v))) for v in dump["plan"].values())
+    # constant-cost mode (the reference's -DDP_DEBUG): nothing to gain, layouts stay default
+    flat = Executor.make_dp_greedy("b").set_option("dp_cost", "constant").plan(bert_bytes)
+    assert n_alias(flat) == 0
+
+
+def test_arena_report(bert_bytes):
+    st = Executor.make_dp_greedy("b").plan(bert_bytes)
+    assert st["reference_arena_bytes_greedy"] < st["reference_arena_bytes_linear"]
+    assert st["peak_arena_bytes_unaligned"] <= st["peak_arena_bytes"]
+
+
+def test_options_are_validated():
+    ex = Executor.make_plain_greedy("x")
+    for k, v in (("gemm_precision", "fp64"), ("alignment", "24"), ("dp_cost", "measured"), ("nonsense", "1")):
+        with pytest.raises(RuntimeError):
+            ex.set_option(k, v)
