@@ -230,12 +230,17 @@ def gemm_params(precision=GEMM_AUTO, act=ACT_NONE, divisor=1.0, alpha=1.0, beta=
     return p
 
 
-def gemm_workspace_bytes(a, b, c, params):
-    """(partial_bytes, counter_bytes) of the split-K scratch for this configuration."""
-    n, m = ctypes.c_size_t(), ctypes.c_size_t()
-    check(lib().fml_gemm_workspace_bytes(_ref(a), _ref(b), _ref(c), ctypes.byref(params),
-                                         ctypes.byref(n), ctypes.byref(m)))
-    return n.value, m.value
+class GemmPlanInfo(ctypes.Structure):
+    _fields_ = [("uses_tensor_cores", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("split_k", ctypes.c_int32),
+                ("stages", ctypes.c_int32), ("b_mn_major", ctypes.c_int32), ("three_pass", ctypes.c_int32),
+                ("shared_memory_bytes", ctypes.c_uint64)]
+
+
+def gemm_plan(a, b, c, params) -> GemmPlanInfo:
+    """Tile / split-K / pipeline depth the library picks for these operands (host only)."""
+    info = GemmPlanInfo()
+    check(lib().fml_gemm_plan(_ref(a), _ref(b), _ref(c), ctypes.byref(params), ctypes.byref(info)))
+    return info
 
 
 def gemm_uses_tensor_cores(a, b, c, params) -> bool:
@@ -245,22 +250,9 @@ def gemm_uses_tensor_cores(a, b, c, params) -> bool:
     return bool(u.value)
 
 
-def gemm(a, b, c, bias=None, residual=None, params=None, workspace=None, stream=None):
-    """`workspace` is a (partials, counters) pair of DeviceBuffers; when omitted and the
-    configuration splits K, a zeroed pair is allocated and returned for reuse."""
+def gemm(a, b, c, bias=None, residual=None, params=None, stream=None):
     params = params or gemm_params()
-    if workspace is None:
-        nb, nc = gemm_workspace_bytes(a, b, c, params)
-        if nb:
-            workspace = (DeviceBuffer(nb), DeviceBuffer(nc))
-            workspace[1].zero()
-    part, cnt = workspace if workspace else (None, None)
-    check(lib().fml_gemm(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual), ctypes.byref(params),
-                         ctypes.c_void_p(part.ptr) if part else None,
-                         ctypes.c_size_t(part.nbytes if part else 0),
-                         ctypes.c_void_p(cnt.ptr) if cnt else None,
-                         ctypes.c_size_t(cnt.nbytes if cnt else 0), stream))
-    return workspace
+    check(lib().fml_gemm(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual), ctypes.byref(params), stream))
 
 
 def conv(x, w, bias, y, pads_begin, strides, dilations, group=1, act=ACT_NONE, stream=None):

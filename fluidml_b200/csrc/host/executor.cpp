@@ -43,6 +43,7 @@ public:
     SetOption("cuda_graph", EnvOr("FLUIDML_CUDA_GRAPH", "1"));
     SetOption("alignment", EnvOr("FLUIDML_ALIGNMENT", "256"));
     SetOption("dp_cost", EnvOr("FLUIDML_DP_COST", "model"));
+    SetOption("autotune", EnvOr("FLUIDML_AUTOTUNE", "1"));
   }
 
   void SetOption(const std::string &key, const std::string &value) override {
@@ -50,6 +51,7 @@ public:
     else if (key == "gemm_precision") options_.gemm_precision = ParsePrecision(value);
     else if (key == "fusion") options_.fusion = value != "0";
     else if (key == "cuda_graph") options_.cuda_graph = value != "0";
+    else if (key == "autotune") options_.autotune = value != "0";
     else if (key == "alignment") {
       options_.alignment = (size_t)std::stoul(value);
       if (options_.alignment < 16 || (options_.alignment & (options_.alignment - 1)))
@@ -136,13 +138,13 @@ private:
     kernel::KernelOptions ko;
     ko.gemm_precision = options_.gemm_precision;
     const AliasMap aliases = Lowering::ComputeAliases(sequence, ko);
-    const size_t counter_bytes = Lowering::ComputeScratch(sequence, ko);
+    Lowering::ComputeScratch(sequence, ko);
     const std::vector<memory::Info> infos = Lowering::Lifetimes(sequence, aliases);
     const memory::Index index = Planner::Plan(infos, plan_, options_.alignment);
     const size_t unaligned = Planner::Plan(infos, plan_, 1).GetMaximum();
 
     std::unique_ptr<Program> program;
-    if (!dry_run) program = Builder::Run(flow, sequence, index, aliases, counter_bytes, options_);
+    if (!dry_run) program = Builder::Run(flow, sequence, index, aliases, options_);
 
     stats_ = json::Value::Object();
     stats_.Set("name", json::Value(name_));
@@ -152,7 +154,6 @@ private:
     stats_.Set("peak_arena_bytes_unaligned", json::Value((double)unaligned));
     stats_.Set("reference_arena_bytes_greedy", json::Value((double)reference_greedy));
     stats_.Set("reference_arena_bytes_linear", json::Value((double)reference_linear));
-    stats_.Set("counter_bytes", json::Value((double)counter_bytes));
     stats_.Set("graph_nodes", json::Value((double)nodes_before_fusion));
     stats_.Set("flow_nodes", json::Value((double)flow.nodes.size()));
     stats_.Set("aliased_nodes", json::Value((double)aliases.size()));

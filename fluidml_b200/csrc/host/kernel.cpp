@@ -404,7 +404,7 @@ public:
     fml_gemm_params params;
     bool has_const_b = false, has_bias = false, has_residual = false, bias_is_input = false;
     fml_tensor const_b{}, bias{};
-    bool trans_a = false, trans_b = false;
+    bool trans_a = false, trans_b = false, autotune = false;
   };
   explicit GemmLikeKernel(Config c) : c_(c) {}
   std::string GetKernelName() const override { return c_.name; }
@@ -420,22 +420,20 @@ public:
     if (c_.has_bias && c_.bias_is_input) bias = in.at(k++);
     if (c_.has_residual) res = in.at(k++);
   }
-  void GetBufferSize(const std::vector<fml_tensor> &in, const fml_tensor &output, size_t *pb,
-                     size_t *cb) const override {
-    fml_tensor a, b, bias, res;
-    Resolve(in, a, b, bias, res);
-    if (fml_gemm_workspace_bytes(&a, &b, &output, &c_.params, pb, cb) != FML_OK)
-      throw Error(std::string(c_.name) + ": " + fml_last_error());
-  }
   void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output,
               const Buffer &buf) const override {
     fml_tensor a, b, bias{}, res{};
     Resolve(in, a, b, bias, res);
-    const Config c = c_;
-    const Buffer w = buf;
+    Config c = c_;
+    if (c.autotune) {  // device buffers are live while the builder records: try the candidates now
+      fml_gemm_params tuned;
+      if (fml_gemm_autotune(&a, &b, &output, c.has_bias ? &bias : nullptr, c.has_residual ? &res : nullptr,
+                            &c.params, nullptr, &tuned) != FML_OK)
+        throw Error(std::string(c.name) + ": " + fml_last_error());
+      c.params = tuned;
+    }
     rec.Add(c.name, [=](void *s) {
-      return fml_gemm(&a, &b, &output, c.has_bias ? &bias : nullptr, c.has_residual ? &res : nullptr,
-                      &c.params, w.partials, w.partial_bytes, w.counters, w.counter_bytes, s);
+      return fml_gemm(&a, &b, &output, c.has_bias ? &bias : nullptr, c.has_residual ? &res : nullptr, &c.params, s);
     });
   }
 
@@ -554,12 +552,14 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
     GemmLikeKernel::Config c;
     c.name = "MatMulKernel";
     c.params = DefaultGemmParams(options);
+    c.autotune = options.autotune;
     return std::make_unique<GemmLikeKernel>(c);
   }
   case Kind::GemmConstantBias: {
     GemmLikeKernel::Config c;
     c.name = "GemmConstantWeightsBiasKernel";
     c.params = DefaultGemmParams(options);
+    c.autotune = options.autotune;
     c.params.alpha = n.alpha;
     c.params.beta = n.beta;
     c.has_const_b = true;
@@ -574,6 +574,7 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
     GemmLikeKernel::Config c;
     c.name = "FusedGemmKernel";
     c.params = DefaultGemmParams(options);
+    c.autotune = options.autotune;
     c.params.alpha = n.alpha;
     c.params.beta = n.beta;
     c.params.divisor = n.divisor;

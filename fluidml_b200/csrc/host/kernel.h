@@ -30,13 +30,13 @@ private:
   std::vector<Launch> launches_;
 };
 
-// Scratch handed to kernels that need it (split-K GEMM): partial tiles from the arena and the
-// persistent tile counters.
+// Scratch from the arena for kernels that ask for some through GetBufferSize(), with the
+// lifetime of the one node (the reference's per-node buffer, src/worker/planner.cpp:283-291).
+// None of the CUDA kernels needs any at present: Softmax and LayerNorm reduce in registers,
+// Conv pads implicitly and split-K GEMMs reduce inside a cluster.
 struct Buffer {
-  void *partials = nullptr;
-  size_t partial_bytes = 0;
-  void *counters = nullptr;
-  size_t counter_bytes = 0;
+  void *data = nullptr;
+  size_t bytes = 0;
 };
 
 class Kernel {
@@ -46,11 +46,11 @@ public:
   // Uniform entry used by the builder; the four signature classes route it to their Run().
   virtual void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &inputs,
                       const fml_tensor &output, const Buffer &buffer) const = 0;
-  // Scratch this kernel needs for these operands (0 for most).
-  virtual void GetBufferSize(const std::vector<fml_tensor> &inputs, const fml_tensor &output,
-                             size_t *partial_bytes, size_t *counter_bytes) const {
-    *partial_bytes = 0;
-    *counter_bytes = 0;
+  // Scratch bytes this kernel needs for these operands.
+  virtual size_t GetBufferSize(const std::vector<fml_tensor> &inputs, const fml_tensor &output) const {
+    (void)inputs;
+    (void)output;
+    return 0;
   }
   // True when, for these operands, the output can simply alias the input's memory (no launch).
   virtual bool IsAlias(const fml_tensor &input, const fml_tensor &output) const { return false; }
@@ -95,6 +95,7 @@ using ConstResolver = std::function<fml_tensor(const flow::RegionPtr &)>;
 
 struct KernelOptions {
   int gemm_precision = FML_GEMM_AUTO;  // fml_gemm_precision for MatMul / Gemm / Conv
+  bool autotune = false;               // tune GEMM tiles on the device while recording (needs real buffers)
 };
 
 // node -> kernel object (reference: SelectKernel, src/worker/utils.cpp:80-335).

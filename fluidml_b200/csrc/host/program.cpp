@@ -64,19 +64,14 @@ AliasMap Lowering::ComputeAliases(const flow::Sequence &sequence, const kernel::
   return aliases;
 }
 
-size_t Lowering::ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko) {
-  size_t counters = 0;
+void Lowering::ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko) {
   const kernel::ConstResolver resolve = PlaceholderResolver();
   for (const auto &node : sequence.nodes) {
     std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
     std::vector<fml_tensor> ins;
     for (const auto &r : node->inputs) ins.push_back(kernel::MakeTensor(*r, kPlaceholder));
-    size_t pb = 0, cb = 0;
-    k->GetBufferSize(ins, kernel::MakeTensor(*node->output, kPlaceholder), &pb, &cb);
-    node->buffer_size = pb;
-    counters = std::max(counters, cb);
+    node->buffer_size = k->GetBufferSize(ins, kernel::MakeTensor(*node->output, kPlaceholder));
   }
-  return counters;
 }
 
 std::vector<memory::Info> Lowering::Lifetimes(const flow::Sequence &sequence, const AliasMap &aliases) {
@@ -108,12 +103,11 @@ Program::~Program() {
   if (arena) fml_free(arena);
   if (weights) fml_free(weights);
   if (io) fml_free(io);
-  if (counters) fml_free(counters);
 }
 
 std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequence &sequence,
                                       const memory::Index &index, const AliasMap &aliases,
-                                      size_t counter_bytes, const Options &options) {
+                                      const Options &options) {
   auto prog = std::make_unique<Program>();
   Check(fml_set_device(options.device), "selecting the device");
   Check(fml_warmup(), "initialising the kernel library");
@@ -140,7 +134,7 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
     Check(fml_stream_sync(nullptr), "uploading the weights");
   }
 
-  // ---- arena (zeroed once), interface buffers, split-K counters
+  // ---- arena (zeroed once) and interface buffers
   prog->arena_bytes = index.GetMaximum();
   Check(fml_malloc(&prog->arena, prog->arena_bytes), "allocating the arena");
   Check(fml_memset(prog->arena, 0, prog->arena_bytes, nullptr), "clearing the arena");
@@ -154,9 +148,6 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
   prog->io_bytes = io_bytes;
   Check(fml_malloc(&prog->io, io_bytes), "allocating the interface buffers");
   Check(fml_memset(prog->io, 0, io_bytes, nullptr), "clearing the interface buffers");
-  prog->counter_bytes = AlignUp(std::max<size_t>(counter_bytes, 4), 256);
-  Check(fml_malloc(&prog->counters, prog->counter_bytes), "allocating the split-K counters");
-  Check(fml_memset(prog->counters, 0, prog->counter_bytes, nullptr), "clearing the split-K counters");
   Check(fml_stream_sync(nullptr), "initialising device memory");
 
   auto base_of = [&](const flow::RegionPtr &r0) -> void * {
@@ -189,6 +180,7 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
 
   kernel::KernelOptions ko;
   ko.gemm_precision = options.gemm_precision;
+  ko.autotune = options.autotune;
   kernel::LaunchRecorder rec;
   for (const auto &node : sequence.nodes) {
     if (aliases.count(node->output.get())) { ++prog->aliased_nodes; continue; }
@@ -197,15 +189,12 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
     for (const auto &r : node->inputs) ins.push_back(tensor_of(r));
     const fml_tensor out = tensor_of(node->output);
     kernel::Buffer buf;
-    size_t pb = 0, cb = 0;
-    k->GetBufferSize(ins, out, &pb, &cb);
-    if (pb > node->buffer_size || cb > prog->counter_bytes)
+    const size_t need = k->GetBufferSize(ins, out);
+    if (need > node->buffer_size)
       throw Error("node '" + node->name + "' needs more scratch than was planned for it");
-    if (pb > 0) {
-      buf.partials = (char *)prog->arena + index.Get(node->name);
-      buf.partial_bytes = node->buffer_size;
-      buf.counters = prog->counters;
-      buf.counter_bytes = prog->counter_bytes;
+    if (need > 0) {
+      buf.data = (char *)prog->arena + index.Get(node->name);
+      buf.bytes = node->buffer_size;
     }
     rec.SetNode(node->name);
     k->Launch(rec, ins, out, buf);

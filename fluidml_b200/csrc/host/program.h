@@ -25,6 +25,7 @@ struct Options {
   bool cuda_graph = true;
   size_t alignment = 256;
   bool dp_constant_cost = false;
+  bool autotune = true;  // tune GEMM tile / split-K choices on the device at Compile
 };
 
 // region -> the region whose memory it shares (itself when it owns memory).
@@ -35,10 +36,10 @@ public:
   // Walks the sequence; a single-input node whose kernel reports IsAlias() for the operands'
   // strides, and whose output is an inner region, shares its input's memory.
   static AliasMap ComputeAliases(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
-  // Fills node->buffer_size (split-K partial bytes) and returns the largest counter buffer any
-  // node needs.  Uses aligned placeholder addresses: planned offsets are multiples of the
-  // alignment, so the real operands take the same path.
-  static size_t ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
+  // Fills node->buffer_size with what each node's kernel asks for.  Uses aligned placeholder
+  // addresses: planned offsets are multiples of the alignment, so the real operands take the
+  // same path.
+  static void ComputeScratch(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
   // Lifetimes with aliases merged into their owners.
   static std::vector<memory::Info> Lifetimes(const flow::Sequence &sequence, const AliasMap &aliases);
 };
@@ -52,8 +53,8 @@ struct IoBinding {
 struct Program {
   std::vector<kernel::Launch> launches;
   std::vector<IoBinding> inputs, outputs;
-  void *arena = nullptr, *weights = nullptr, *io = nullptr, *counters = nullptr;
-  size_t arena_bytes = 0, weight_bytes = 0, io_bytes = 0, counter_bytes = 0;
+  void *arena = nullptr, *weights = nullptr, *io = nullptr;
+  size_t arena_bytes = 0, weight_bytes = 0, io_bytes = 0;
   size_t aliased_nodes = 0;
   std::map<std::string, int> kernel_histogram;
   ~Program();
@@ -65,7 +66,7 @@ class Builder {
 public:
   static std::unique_ptr<Program> Run(const flow::Flow &flow, const flow::Sequence &sequence,
                                       const memory::Index &index, const AliasMap &aliases,
-                                      size_t counter_bytes, const Options &options);
+                                      const Options &options);
 };
 
 class Runner {

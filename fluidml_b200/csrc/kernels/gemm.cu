@@ -1,6 +1,10 @@
 // GEMM front end: shape analysis, the fp32 FMA kernel for operands the tensor-core path
 // cannot take (arbitrary strides, tiny or unaligned shapes), and the C-ABI entry points.
 #include "gemm_common.cuh"
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
 
 namespace fml {
 
@@ -193,17 +197,21 @@ static int resolve(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c
   return FML_OK;
 }
 
-extern "C" int fml_gemm_workspace_bytes(const fml_tensor *a, const fml_tensor *b,
-                                        const fml_tensor *c, const fml_gemm_params *gp,
-                                        size_t *partial_bytes, size_t *counter_bytes) {
-  FML_REQUIRE(partial_bytes && counter_bytes, FML_BAD_ARG, "fml_gemm_workspace_bytes: null argument");
+extern "C" int fml_gemm_plan(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                             const fml_gemm_params *gp, fml_gemm_plan_info *info) {
+  FML_REQUIRE(info, FML_BAD_ARG, "fml_gemm_plan: null argument");
   GemmProblem p;
   TcPlan plan;
   bool use_tc = false;
   int st = resolve(a, b, c, nullptr, nullptr, gp, p, plan, use_tc);
   if (st != FML_OK) return st;
-  *partial_bytes = use_tc ? plan.partial_bytes : 0;
-  *counter_bytes = use_tc ? plan.counter_bytes : 0;
+  memset(info, 0, sizeof(*info));
+  info->uses_tensor_cores = use_tc ? 1 : 0;
+  if (use_tc) {
+    info->tile_n = plan.tile_n; info->split_k = plan.split_k; info->stages = plan.stages;
+    info->b_mn_major = plan.b_mn_major; info->three_pass = plan.three_pass;
+    info->shared_memory_bytes = plan.smem_bytes;
+  }
   return FML_OK;
 }
 
@@ -221,8 +229,7 @@ extern "C" int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor 
 
 extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
                         const fml_tensor *bias, const fml_tensor *residual,
-                        const fml_gemm_params *gp, void *partials, size_t partial_bytes,
-                        void *counters, size_t counter_bytes, void *stream) {
+                        const fml_gemm_params *gp, void *stream) {
   GemmProblem p;
   TcPlan plan;
   bool use_tc = false;
@@ -230,7 +237,74 @@ extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tens
   if (st != FML_OK) return st;
   if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
   GemmEpilogue e = make_epilogue(*gp, bias != nullptr, residual != nullptr);
-  if (use_tc)
-    return launch_gemm_tc(p, e, plan, partials, partial_bytes, counters, counter_bytes, as_stream(stream));
+  if (use_tc) return launch_gemm_tc(p, e, plan, as_stream(stream));
   return launch_gemm_simt(p, e, as_stream(stream));
+}
+
+// One-off on-device tuning of (tile_n, split_k) for one GEMM, cached per problem signature.
+// The reference tunes its MatMul / Gemm kernels the same way -- by running the candidates
+// (there: six loop orders on the CPU, src/structure/kernel/generator/matmul.cpp:100-123) and
+// keeping the fastest per layout triple.
+extern "C" int fml_gemm_autotune(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                                 const fml_tensor *bias, const fml_tensor *residual,
+                                 const fml_gemm_params *gp, void *stream, fml_gemm_params *tuned) {
+  FML_REQUIRE(gp && tuned, FML_BAD_ARG, "fml_gemm_autotune: null argument");
+  *tuned = *gp;
+  GemmProblem p;
+  TcPlan plan;
+  bool use_tc = false;
+  int st = resolve(a, b, c, bias, residual, gp, p, plan, use_tc);
+  if (st != FML_OK) return st;
+  if (!use_tc || gp->tile_n != 0 || gp->split_k != 0) return FML_OK;  // nothing to choose
+  char key[256];
+  snprintf(key, sizeof(key), "%lld,%lld,%lld,%lld,%lld|%d%d|%d,%d,%d,%d|%lld,%lld", (long long)p.M, (long long)p.N,
+           (long long)p.K, (long long)p.nb0, (long long)p.nb1, plan.b_mn_major, plan.three_pass, gp->act,
+           bias != nullptr, residual != nullptr, gp->divisor != 1.0f, (long long)p.c_sm, (long long)p.c_sn);
+  static std::map<std::string, std::pair<int, int>> cache;
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { tuned->tile_n = it->second.first; tuned->split_k = it->second.second; return FML_OK; }
+  }
+  cudaStream_t s = as_stream(stream);
+  cudaEvent_t e0, e1;
+  FML_CUDA(cudaEventCreate(&e0));
+  FML_CUDA(cudaEventCreate(&e1));
+  const GemmEpilogue epi = make_epilogue(*gp, bias != nullptr, residual != nullptr);
+  const int tn_opts[] = {32, 48, 64, 96, 128, 192, 256};
+  const int sk_opts[] = {1, 2, 4, 8};
+  float best = 1e30f;
+  int best_tn = plan.tile_n, best_sk = plan.split_k;
+  std::vector<std::pair<int, int>> seen;
+  for (int tn : tn_opts)
+    for (int sk : sk_opts) {
+      fml_gemm_params q = *gp;
+      q.tile_n = tn;
+      q.split_k = sk;
+      TcPlan cand;
+      if (!plan_gemm_tc(p, q, cand)) continue;
+      const std::pair<int, int> id(cand.tile_n, cand.split_k);
+      bool dup = false;
+      for (const auto &x : seen) dup = dup || x == id;
+      if (dup) continue;
+      seen.push_back(id);
+      const int reps = 6;
+      if (launch_gemm_tc(p, epi, cand, s) != FML_OK) { cudaGetLastError(); continue; }  // warm-up; skip what cannot launch
+      cudaEventRecord(e0, s);
+      bool ok = true;
+      for (int r = 0; r < reps && ok; ++r) ok = launch_gemm_tc(p, epi, cand, s) == FML_OK;
+      cudaEventRecord(e1, s);
+      if (cudaEventSynchronize(e1) != cudaSuccess || !ok) { cudaGetLastError(); continue; }
+      float ms = 0;
+      cudaEventElapsedTime(&ms, e0, e1);
+      if (ms < best) { best = ms; best_tn = cand.tile_n; best_sk = cand.split_k; }
+    }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  tuned->tile_n = best_tn;
+  tuned->split_k = best_sk;
+  std::lock_guard<std::mutex> lock(mu);
+  cache[key] = {best_tn, best_sk};
+  return FML_OK;
 }

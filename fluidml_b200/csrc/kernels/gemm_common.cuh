@@ -62,8 +62,6 @@ struct TcPlan {
 
 // Whether the operands can be fed to TMA/UMMA directly, and with which plan.
 bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan);
-int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan,
-                   void *partials, size_t partial_bytes, void *counters, size_t counter_bytes,
-                   cudaStream_t s);
+int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, cudaStream_t s);
 
 }  // namespace fml

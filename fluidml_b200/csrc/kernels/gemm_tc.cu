@@ -1,8 +1,8 @@
 // tcgen05 GEMM for sm_100a: TMA-fed shared-memory ring, UMMA kind::tf32 with the fp32
-// accumulator tile in tensor memory (TMEM), warp-specialised roles, split-K with a
-// fixed-order reduction.  Replaces the loop nests the reference generates for
-// MatMulKernel (src/structure/kernel/kernel/matmul.cpp:28-59) and GemmConstantBiasKernel
-// (gemm.cpp:39-182).
+// accumulator tile in tensor memory (TMEM), warp-specialised roles, split-K across a
+// thread-block cluster with the partial sums reduced through distributed shared memory.
+// Replaces the loop nests the reference generates for MatMulKernel
+// (src/structure/kernel/kernel/matmul.cpp:28-59) and GemmConstantBiasKernel (gemm.cpp:39-182).
 //
 // Tile: 128 (M) x tile_n (N) per CTA, k consumed in blocks of 32 floats (one 128-byte
 // swizzle span).  Roles, 192 threads:
@@ -11,23 +11,31 @@
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma (4 k-steps of 8 per block, x3 in
 //               the 3xTF32 mode) and tcgen05.commit to empty[s] / accum;
 //   warps 2-5   3xTF32 only: split each landed stage into hi = x & 0xffffe000 and
-//               lo = x - hi (exact) and publish it on conv[s]; afterwards the epilogue:
-//               tcgen05.ld the accumulator (one TMEM lane = one output row per thread),
-//               apply divisor / bias / activation / residual and store.
+//               lo = x - hi (exact) and publish it on conv[s]; afterwards the epilogue.
 // 3xTF32 issues lo*hi, hi*lo, hi*hi into the same accumulator, so products carry ~2^-21
 // relative error instead of TF32's 2^-11 while the weights still cross HBM once as fp32.
 //
-// Split-K: every split writes its partial tile to the workspace; the split that arrives
-// last on the tile's counter sums all partials in split order 0..S-1 (so the result does
-// not depend on arrival order), applies the epilogue and resets the counter.
+// Epilogue.  Each epilogue thread owns one TMEM lane = one output row; writing rows straight
+// to global memory would scatter every store instruction over 32 cache lines.  Instead the
+// accumulator tile is staged in shared memory (the pipeline stages are free by then) and read
+// back with consecutive threads on consecutive columns, so bias / residual loads and the
+// stores of C are full 128-byte lines.
 //
-// Every mbarrier wait is bounded: when a wait gives up the kernel records
-// kStatusTimeout in the device status word, stops issuing work, drains what it can with
-// bounded waits, frees its TMEM and returns.
+// Split-K.  The S splits of one output tile form a cluster (1, S, 1): they are co-scheduled,
+// each keeps its partial tile in its own shared memory, and after a cluster barrier CTA r
+// sums rows [r*128/S, (r+1)*128/S) over all S partial tiles in rank order 0..S-1 (so the
+// result does not depend on timing), applies the epilogue and stores them.  No global
+// scratch, no atomics.
 //
-// Each CTA loads its own tiles; no load in this file is shared between CTAs or devices.
+// Every mbarrier wait is bounded: when a wait gives up the kernel records kStatusTimeout in
+// the device status word, stops issuing work, still takes part in the cluster barriers,
+// frees its TMEM and returns.
+//
+// Each CTA loads its own tiles with plain TMA loads; nothing here is shared between CTAs
+// at load time, and nothing reads another device's memory.
 #include "gemm_common.cuh"
 #include <cuda.h>
+#include <algorithm>
 
 namespace fml {
 namespace {
@@ -37,16 +45,27 @@ constexpr int kBK = 32;                 // floats per k block = 128 bytes
 constexpr int kABytes = kBM * kBK * 4;  // 16 KiB
 constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr size_t kSmemBudget = 200 * 1024;
 
 struct TcArgs {
   GemmProblem p;
   GemmEpilogue e;
   int tile_n, split_k, stages, b_mn_major, three_pass;
   int tiles_m, tiles_n, kb_total, kb_per_split;
-  float *ws_partial;
-  unsigned *ws_counter;
   int *status;
+  unsigned long long *trace;  // optional: 16 stamps per CTA (fml_debug_set_gemm_trace)
 };
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(slot)                                                                        \
+  do {                                                                                     \
+    if (a.trace)                                                                           \
+      a.trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = ((slot) >= 8 ? (unsigned long long)clock64() : gtime()); \
+  } while (0)
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -130,8 +149,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void epi_bar_sync() {  // the 128 epilogue threads only
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of every CTA in the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_smem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
@@ -148,7 +178,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version for this architecture
+  d |= (uint64_t)1 << 46;            // descriptor version for this architecture
   d |= (uint64_t)layout_type << 61;  // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte atom
   return d;
 }
@@ -159,7 +189,126 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- epilogue loops
+// The loop over output elements is instantiated per (activation, bias, residual, scaling)
+// combination so that its body is a few dozen instructions: with every variant inlined behind
+// run-time branches the body no longer fits the instruction cache close to the scheduler and
+// each iteration stalls on instruction fetch.
+struct EpiCtx {
+  const float *staging;
+  uint32_t staging_addr;
+  int pitch, BN, S, r0, r1, et;
+  int64_t m_base, n_base, M, N;
+  float *C;
+  int64_t c_sm, c_sn;
+  const float *bias;
+  int64_t bias_sm, bias_sn;
+  const float *res;
+  int64_t res_sm, res_sn;
+  GemmEpilogue e;
+};
+
+template <int ACT, bool BIAS, bool RES, bool SCALE>
+__device__ __forceinline__ float epi_op(const GemmEpilogue &e, float v, float bv, float rv) {
+  if (SCALE) {
+    if (e.divisor != 1.0f) v = v / e.divisor;
+    v = BIAS ? e.alpha * v + e.beta * bv : e.alpha * v;
+  } else if (BIAS) {
+    v = v + bv;
+  }
+  if (ACT == FML_ACT_GELU_ERF) v = v * (erff(v / e.c0) + e.c1) * e.c2;
+  else if (ACT == FML_ACT_RELU) v = fmaxf(v, 0.0f);
+  else if (ACT == FML_ACT_TANH) v = tanhf(v);
+  else if (ACT == FML_ACT_SIGMOID) v = 1.0f / (1.0f + expf(-v));
+  if (RES) v += rv;
+  return v;
+}
+
+// Sum of the S partial tiles at one staging offset, in rank order; the loads are issued
+// together so their latencies overlap.
+__device__ __forceinline__ float4 gather4(const EpiCtx &x, int r, int c) {
+  if (x.S == 1) return *reinterpret_cast<const float4 *>(x.staging + (size_t)r * x.pitch + c);
+  const uint32_t off = x.staging_addr + (uint32_t)(r * x.pitch + c) * 4u;
+  float4 t[8];
+#pragma unroll
+  for (int rank = 0; rank < 8; ++rank) {
+    if (rank < x.S) {
+      const uint32_t addr = cluster_smem_addr(off, (uint32_t)rank);
+      asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(t[rank].x), "=f"(t[rank].y), "=f"(t[rank].z), "=f"(t[rank].w) : "r"(addr) : "memory");
+    }
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int rank = 0; rank < 8; ++rank)
+    if (rank < x.S) { acc.x += t[rank].x; acc.y += t[rank].y; acc.z += t[rank].z; acc.w += t[rank].w; }
+  return acc;
+}
+
+template <int ACT, bool BIAS, bool RES, bool SCALE, bool VEC>
+__device__ __noinline__ void epilogue_rows(const EpiCtx x) {
+  const int quads = x.BN >> 2;
+  const int count = (x.r1 - x.r0) * quads;
+  for (int i = x.et; i < count; i += 128) {
+    const int r = x.r0 + i / quads, c = (i - (i / quads) * quads) * 4;
+    const int64_t m = x.m_base + r, n = x.n_base + c;
+    const float4 acc = gather4(x, r, c);
+    if (m >= x.M) continue;
+    if (VEC) {
+      float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), rv = bv, o;
+      if (BIAS) {
+        if (x.bias_sn == 1) bv = *reinterpret_cast<const float4 *>(x.bias + m * x.bias_sm + n);
+        else { const float b = x.bias[m * x.bias_sm]; bv = make_float4(b, b, b, b); }
+      }
+      if (RES) rv = *reinterpret_cast<const float4 *>(x.res + m * x.res_sm + n);
+      o.x = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.x, bv.x, rv.x);
+      o.y = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.y, bv.y, rv.y);
+      o.z = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.z, bv.z, rv.z);
+      o.w = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.w, bv.w, rv.w);
+      *reinterpret_cast<float4 *>(x.C + m * x.c_sm + n) = o;
+    } else {
+      const float av[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int64_t nn = n + j;
+        if (nn < x.N) {
+          const float bv = BIAS ? x.bias[m * x.bias_sm + nn * x.bias_sn] : 0.0f;
+          const float rv = RES ? x.res[m * x.res_sm + nn * x.res_sn] : 0.0f;
+          x.C[m * x.c_sm + nn * x.c_sn] = epi_op<ACT, BIAS, RES, SCALE>(x.e, av[j], bv, rv);
+        }
+      }
+    }
+  }
+}
+
+template <int ACT, bool BIAS, bool RES>
+__device__ __forceinline__ void epilogue_dispatch3(const EpiCtx &x, bool scale, bool vec) {
+  if (scale) { if (vec) epilogue_rows<ACT, BIAS, RES, true, true>(x); else epilogue_rows<ACT, BIAS, RES, true, false>(x); }
+  else { if (vec) epilogue_rows<ACT, BIAS, RES, false, true>(x); else epilogue_rows<ACT, BIAS, RES, false, false>(x); }
+}
+template <int ACT>
+__device__ __forceinline__ void epilogue_dispatch2(const EpiCtx &x, bool scale, bool vec) {
+  const bool b = x.bias != nullptr, r = x.res != nullptr;
+  if (b && r) epilogue_dispatch3<ACT, true, true>(x, scale, vec);
+  else if (b) epilogue_dispatch3<ACT, true, false>(x, scale, vec);
+  else if (r) epilogue_dispatch3<ACT, false, true>(x, scale, vec);
+  else epilogue_dispatch3<ACT, false, false>(x, scale, vec);
+}
+__device__ __forceinline__ void epilogue_dispatch(const EpiCtx &x, bool vec) {
+  const bool scale = x.e.divisor != 1.0f || x.e.alpha != 1.0f || (x.bias && x.e.beta != 1.0f);
+  switch (x.e.act) {
+  case FML_ACT_GELU_ERF: epilogue_dispatch2<FML_ACT_GELU_ERF>(x, scale, vec); break;
+  case FML_ACT_RELU: epilogue_dispatch2<FML_ACT_RELU>(x, scale, vec); break;
+  case FML_ACT_TANH: epilogue_dispatch2<FML_ACT_TANH>(x, scale, vec); break;
+  case FML_ACT_SIGMOID: epilogue_dispatch2<FML_ACT_SIGMOID>(x, scale, vec); break;
+  default: epilogue_dispatch2<FML_ACT_NONE>(x, scale, vec); break;
+  }
+}
+
 // ---------------------------------------------------------------- kernel
+// THREE_PASS / B_MN are compile-time so that each variant carries only its own code: the kernel
+// runs every phase once per CTA, and instruction fetch of cold code is a first-order cost.
+template <bool THREE_PASS, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcArgs a) {
@@ -168,38 +317,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~static_cast<uintptr_t>(1023));
   const int BN = a.tile_n;
+  const int pitch = BN + 4;  // staging row pitch in floats: rows 16 bytes apart modulo 128, so the
+                             // 16-byte row-wise writes of a quarter-warp hit distinct banks
   const uint32_t b_bytes = (uint32_t)BN * kBK * 4;
-  const uint32_t stage_bytes = (kABytes + b_bytes) * (a.three_pass ? 2 : 1);
-  // stage layout: A_hi | B_hi | (A_lo | B_lo)
+  const uint32_t stage_bytes = (kABytes + b_bytes) * (THREE_PASS ? 2 : 1);
+  // [ pipeline stages (reused as the epilogue staging tile) | barriers | flags ]
+  const size_t ring_bytes = (size_t)a.stages * stage_bytes;
+  const size_t staging_bytes = ((size_t)kBM * pitch * 4 + 1023) / 1024 * 1024;
+  const size_t data_bytes = ring_bytes > staging_bytes ? ring_bytes : staging_bytes;
   const uint32_t tiles_base = smem_u32(smem);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)a.stages * stage_bytes);
+  float *staging = reinterpret_cast<float *>(smem);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + data_bytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_conv = bar_full + 8u * a.stages;
   const uint32_t bar_empty = bar_conv + 8u * a.stages;
   const uint32_t bar_accum = bar_empty + 8u * a.stages;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * a.stages + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  volatile int *last_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, tile_m = tile / a.tiles_n, tile_n = tile % a.tiles_n;
-  const int split = blockIdx.y;
+  const int split = blockIdx.y;  // == rank inside the (1, S, 1) cluster
   const int z = blockIdx.z, z0 = z % (int)a.p.nb0, z1 = z / (int)a.p.nb0;
-  const int kb0 = split * a.kb_per_split;
+  const int kb0 = min(a.kb_total, split * a.kb_per_split);
   const int kb1 = min(a.kb_total, kb0 + a.kb_per_split);
-  const int nkb = kb1 - kb0;  // >= 1 by construction of the plan
+  const int nkb = kb1 - kb0;  // may be 0 for the last ranks of a cluster
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < BN) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
+    TRACE(0);
+    TRACE(8);
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(bar_full + 8u * s, 1);
-      mbar_init(bar_conv + 8u * s, 128);
+      mbar_init(bar_conv + 8u * s, 4);  // one arrival per converter warp
       mbar_init(bar_empty + 8u * s, 1);
     }
     mbar_init(bar_accum, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
@@ -207,6 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -224,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int k = (kb0 + it) * kBK;
         mbar_expect_tx(bar_full + 8u * s, kABytes + b_bytes);
         tma_load_4d(sa, &map_a, bar_full + 8u * s, k, tile_m * kBM, ca2, ca3);
-        if (!a.b_mn_major) {
+        if (!B_MN) {
           tma_load_4d(sb, &map_b, bar_full + 8u * s, k, tile_n * BN, cb2, cb3);
         } else {
           for (int g = 0; g < BN / 32; ++g)  // one 32-wide column group per box
@@ -246,16 +402,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(BN, a.b_mn_major);
-      const uint32_t ready = a.three_pass ? bar_conv : bar_full;
-      const uint32_t b_lbo = a.b_mn_major ? (uint32_t)(kBK * 128) : 16u;
-      const uint32_t b_sbo = a.b_mn_major ? 512u : 1024u, b_type = a.b_mn_major ? 1u : 2u;
+      const uint32_t idesc = instr_desc(BN, B_MN ? 1 : 0);
+      const uint32_t ready = THREE_PASS ? bar_conv : bar_full;
+      const uint32_t b_lbo = B_MN ? (uint32_t)(kBK * 128) : 16u;
+      const uint32_t b_sbo = B_MN ? 512u : 1024u, b_type = B_MN ? 1u : 2u;
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         const int s = it % a.stages;
         const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
         ok = mbar_wait(ready + 8u * s, ph, abort_flag);
         if (!ok) break;
+        if (it == 0) TRACE(2);
         tc_fence_after();
         const uint32_t sa = tiles_base + (uint32_t)s * stage_bytes, sb = sa + kABytes;
         const uint32_t sal = sb + b_bytes, sbl = sal + kABytes;
@@ -264,11 +421,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // k-step j: 32 bytes further along a K-major row; 8 rows (1024 bytes) further
           // down an MN-major tile
           const uint32_t a_off = (uint32_t)j * 32u;
-          const uint32_t b_off = a.b_mn_major ? (uint32_t)j * 1024u : (uint32_t)j * 32u;
+          const uint32_t b_off = B_MN ? (uint32_t)j * 1024u : (uint32_t)j * 32u;
           const uint64_t da = smem_desc(sa + a_off, 16u, 1024u);
           const uint64_t db = smem_desc(sb + b_off, b_lbo, b_sbo, b_type);
           const uint32_t first = (it == 0 && j == 0) ? 0u : 1u;
-          if (a.three_pass) {
+          if (THREE_PASS) {
             const uint64_t dal = smem_desc(sal + a_off, 16u, 1024u);
             const uint64_t dbl = smem_desc(sbl + b_off, b_lbo, b_sbo, b_type);
             umma_tf32(tmem_base, dal, db, idesc, first);
@@ -281,18 +438,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         umma_commit(bar_empty + 8u * s);  // stage reusable once these MMAs have read it
       }
       if (ok) {
-        umma_commit(bar_accum);
+        TRACE(3);
+        umma_commit(bar_accum);  // with no MMA outstanding (nkb == 0) this arrives at once
       } else {
         atomicOr(a.status, kStatusTimeout);
         *abort_flag = 1;
       }
     }
   } else {
-    // ------------------------------------------------------------ converter + epilogue
+    // ------------------------------------------------------------ converter, then TMEM -> staging
     const int et = threadIdx.x - 64;  // 0..127
     bool ok = true;
-    if (a.three_pass) {
-      const int a_vec = kABytes / 16, b_vec = (int)b_bytes / 16;
+    if (THREE_PASS) {
+      const int b_vec = (int)b_bytes / 16;  // 16-byte units in the B tile: 8 per row of tile_n
       for (int it = 0; it < nkb && ok; ++it) {
         const int s = it % a.stages;
         const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
@@ -311,20 +469,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(hi.z));
           lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(hi.w));
         };
-        for (int i = et; i < a_vec; i += 128) {
-          uint4 hi, lo;
-          split4(hi_a[i], hi, lo);
-          hi_a[i] = hi;
-          lo_a[i] = lo;
+        // A: 1024 units over 128 threads = 8 each; all loads first so their latencies overlap
+        {
+          uint4 x[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = hi_a[et + 128 * j];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 hi, lo;
+            split4(x[j], hi, lo);
+            hi_a[et + 128 * j] = hi;
+            lo_a[et + 128 * j] = lo;
+          }
         }
-        for (int i = et; i < b_vec; i += 128) {
-          uint4 hi, lo;
-          split4(hi_b[i], hi, lo);
-          hi_b[i] = hi;
-          lo_b[i] = lo;
+        for (int base = 0; base < b_vec; base += 512) {  // B: up to 4 units per thread per round
+          uint4 x[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (base + et + 128 * j < b_vec) x[j] = hi_b[base + et + 128 * j];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (base + et + 128 * j < b_vec) {
+              uint4 hi, lo;
+              split4(x[j], hi, lo);
+              hi_b[base + et + 128 * j] = hi;
+              lo_b[base + et + 128 * j] = lo;
+            }
         }
         fence_async_smem();  // make the generic-proxy writes visible to the tensor core
-        mbar_arrive(bar_conv + 8u * s);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_conv + 8u * s);  // 4 arrivals instead of 128 serialised ones
       }
     }
     if (ok) ok = mbar_wait(bar_accum, 0u, abort_flag);
@@ -332,91 +506,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       atomicOr(a.status, kStatusTimeout);
       *abort_flag = 1;
     }
-    // One decision for all 128 epilogue threads, so the named barriers below always see
-    // every one of them: -1 = some role gave up, skip the epilogue.
-    epi_bar_sync();
-    if (et == 0) *last_flag = *abort_flag ? -1 : 0;
-    epi_bar_sync();
-    if (*last_flag == 0) {
-      tc_fence_after();
-      const int q = warp & 3;  // TMEM lane quarter this warp may read
-      const int row = q * 32 + lane;
-      const int64_t m = (int64_t)tile_m * kBM + row;
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-      const int64_t zc = (int64_t)z0 * a.p.c_b0 + (int64_t)z1 * a.p.c_b1;
-      const float *bias = a.p.bias ? a.p.bias + (int64_t)z0 * a.p.bias_b0 + (int64_t)z1 * a.p.bias_b1 : nullptr;
-      const float *res = a.p.res ? a.p.res + (int64_t)z0 * a.p.res_b0 + (int64_t)z1 * a.p.res_b1 : nullptr;
-      float *C = a.p.c + zc;
-      const int64_t n_base = (int64_t)tile_n * BN;
-
-      auto finish = [&](const float *v, int c0) {
-        if (m >= a.p.M) return;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int64_t n = n_base + c0 + i;
-          if (c0 + i < BN && n < a.p.N) {
-            const float bv = bias ? bias[m * a.p.bias_sm + n * a.p.bias_sn] : 0.0f;
-            const float rv = res ? res[m * a.p.res_sm + n * a.p.res_sn] : 0.0f;
-            C[m * a.p.c_sm + n * a.p.c_sn] = gemm_epilogue(a.e, v[i], bv, rv);
-          }
-        }
-      };
-
-      if (a.split_k == 1) {
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-          tmem_ld32(lane_addr + (uint32_t)c0, v);
-          finish(v, c0);
-        }
+    if (et == 0) TRACE(4);
+    // Accumulator row -> staging row.  The ring is free: bar_accum fires after every MMA has
+    // finished reading it, and every load that was issued has been consumed by an MMA.
+    tc_fence_after();
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    float *dst = staging + (size_t)row * pitch;
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      float v[32];
+      if (ok && nkb > 0) {
+        tmem_ld32(lane_addr + (uint32_t)c0, v);
       } else {
-        const int64_t tile_id = (int64_t)z * (a.tiles_m * a.tiles_n) + tile;
-        float *part = a.ws_partial + ((tile_id * a.split_k + split) * kBM + row) * BN;
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-          tmem_ld32(lane_addr + (uint32_t)c0, v);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            if (c0 + i < BN)
-              *reinterpret_cast<float4 *>(part + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        }
-        __threadfence();
-        epi_bar_sync();
-        if (et == 0) {
-          const unsigned old = atomicAdd(a.ws_counter + tile_id, 1u);
-          *last_flag = (old == (unsigned)a.split_k - 1u) ? 1 : 0;
-        }
-        epi_bar_sync();
-        if (*last_flag) {
-          __threadfence();
-          const float *base = a.ws_partial + (tile_id * a.split_k * kBM + row) * BN;
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            float v[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-            for (int sp = 0; sp < a.split_k; ++sp) {
-              const float *src = base + (int64_t)sp * kBM * BN + c0;
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                if (c0 + i < BN) {
-                  const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + i));
-                  v[i] += t.x; v[i + 1] += t.y; v[i + 2] += t.z; v[i + 3] += t.w;
-                }
-              }
-            }
-            finish(v, c0);
-          }
-          if (et == 0) a.ws_counter[tile_id] = 0u;  // ready for the next launch
-        }
+        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
       }
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        if (c0 + i < BN)  // BN is a multiple of 16
+          *reinterpret_cast<float4 *>(dst + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     }
+    if (et == 0) TRACE(7);
   }
 
+  // ---------------------------------------------------------------- reduce + epilogue
   tc_fence_before();
+  __syncthreads();
+  const int S = a.split_k;
+  if (S > 1) cluster_sync_all();  // every rank's partial tile is in its shared memory
+  if (warp >= 2) {
+    const int et = threadIdx.x - 64;
+    const int rows_per = (kBM + S - 1) / S;
+    const int r0 = split * rows_per, r1 = min(kBM, r0 + rows_per);
+    const int64_t zc = (int64_t)z0 * a.p.c_b0 + (int64_t)z1 * a.p.c_b1;
+    const float *bias = a.p.bias ? a.p.bias + (int64_t)z0 * a.p.bias_b0 + (int64_t)z1 * a.p.bias_b1 : nullptr;
+    const float *res = a.p.res ? a.p.res + (int64_t)z0 * a.p.res_b0 + (int64_t)z1 * a.p.res_b1 : nullptr;
+    float *C = a.p.c + zc;
+    const int64_t n_base = (int64_t)tile_n * BN, m_base = (int64_t)tile_m * kBM;
+    EpiCtx x;
+    x.staging = staging; x.staging_addr = smem_u32(staging); x.pitch = pitch; x.BN = BN; x.S = S;
+    x.r0 = r0; x.r1 = r1; x.et = et;
+    x.m_base = m_base; x.n_base = n_base; x.M = a.p.M; x.N = a.p.N;
+    x.C = C; x.c_sm = a.p.c_sm; x.c_sn = a.p.c_sn;
+    x.bias = bias; x.bias_sm = a.p.bias_sm; x.bias_sn = a.p.bias_sn;
+    x.res = res; x.res_sm = a.p.res_sm; x.res_sn = a.p.res_sn;
+    x.e = a.e;
+    // 16-byte path: unit column stride everywhere, every row start and the tile origin on a
+    // 16-byte boundary, no ragged column edge inside this tile
+    auto al4 = [](int64_t v) { return (v & 3) == 0; };
+    bool vec = a.p.c_sn == 1 && al4(a.p.c_sm) && al4(n_base) && n_base + BN <= a.p.N &&
+               ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    if (bias) vec = vec && (a.p.bias_sn == 1 || a.p.bias_sn == 0) && al4(a.p.bias_sm) &&
+                    ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+    if (res) vec = vec && a.p.res_sn == 1 && al4(a.p.res_sm) && ((reinterpret_cast<uintptr_t>(res) & 15) == 0);
+    epilogue_dispatch(x, vec);
+    if (et == 0) TRACE(5);
+  }
+  if (S > 1) cluster_sync_all();  // nobody leaves while a peer may still read its tile
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+  if (threadIdx.x == 0) { TRACE(6); TRACE(9); }
 }
 
 // ---------------------------------------------------------------- host side
@@ -437,7 +590,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 4-D map: (inner contiguous dim, row dim, batch0, batch1), fp32, 128-byte swizzle.
+// 4-D map: (inner contiguous dim, row dim, batch0, batch1), fp32.
 int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t rows, int64_t row_stride,
              int64_t nb0, int64_t b0_stride, int64_t nb1, int64_t b1_stride, int box_inner,
              int box_rows, CUtensorMapSwizzle swizzle) {
@@ -460,6 +613,15 @@ int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t rows, i
 
 bool stride_ok(int64_t s) { return s == 0 || (s > 0 && s % 4 == 0); }
 
+size_t smem_for(int tile_n, int stages, int three_pass) {
+  const size_t stage = (size_t)(kABytes + tile_n * kBK * 4) * (three_pass ? 2 : 1);
+  const size_t staging = ((size_t)kBM * (tile_n + 4) * 4 + 1023) / 1024 * 1024;
+  const size_t data = std::max(stage * stages, staging);
+  return data + (3 * stages + 1) * 8 + 16 + 1024;
+}
+
+unsigned long long *g_trace = nullptr;
+
 }  // namespace
 
 bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan) {
@@ -480,43 +642,62 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
 
   plan.b_mn_major = mn;
   plan.three_pass = gp.precision == FML_GEMM_TF32 ? 0 : 1;
-  int tn = gp.tile_n;
-  if (tn == 0) tn = p.N >= 1024 && p.M >= 1024 ? 128 : 64;
-  if (tn > p.N) tn = (int)((p.N + 15) / 16 * 16);
-  if (mn) tn = (tn + 31) / 32 * 32;  // MN-major B is loaded in 32-column boxes
-  if (tn < 16) tn = 16;
-  if (tn > 256) tn = 256;
-  tn = tn / 16 * 16;
-  plan.tile_n = tn;
-  const int64_t tiles = ((p.M + kBM - 1) / kBM) * ((p.N + tn - 1) / tn) * batch;
   const int kb_total = (int)((p.K + kBK - 1) / kBK);
-  int sk = gp.split_k;
-  if (sk == 0) {
-    // aim at one CTA per SM, keep at least two k blocks per split
-    sk = (int)(148 / tiles);
-    if (sk > kb_total / 2) sk = kb_total / 2;
-    if (sk < 1) sk = 1;
+  const int64_t tiles_m = (p.M + kBM - 1) / kBM;
+
+  // Candidate (tile_n, split) pairs are scored with a small time model: a CTA pulls its A and
+  // B boxes through one SM's shared-memory fill path, all CTAs together cannot beat HBM on the
+  // bytes that are read once, a cluster of S needs S free SMs in one GPC, and every CTA pays
+  // a fixed set-up + epilogue cost.  Explicit tile_n / split_k requests bypass the search.
+  const int tn_opts[] = {32, 48, 64, 96, 128, 192, 256};
+  const int sk_opts[] = {1, 2, 4, 8};
+  const int sk_cap[] = {148, 148, 144, 128};  // CTAs that can be resident for each cluster size
+  double best = 1e30;
+  int best_tn = 0, best_sk = 0;
+  for (int tn : tn_opts) {
+    if (gp.tile_n) tn = gp.tile_n;
+    if (tn > p.N) tn = (int)((p.N + 15) / 16 * 16);
+    if (mn) tn = (tn + 31) / 32 * 32;
+    tn = std::max(16, std::min(256, tn / 16 * 16));
+    for (int si = 0; si < 4; ++si) {
+      int sk = gp.split_k ? gp.split_k : sk_opts[si];
+      if (sk > kb_total) continue;
+      if (smem_for(tn, 1, plan.three_pass) > kSmemBudget + 8192) continue;
+      const int64_t tiles = tiles_m * ((p.N + tn - 1) / tn) * batch;
+      const int64_t ctas = tiles * sk;
+      const int cap = sk <= 1 ? 148 : sk <= 2 ? sk_cap[1] : sk <= 4 ? sk_cap[2] : sk_cap[3];
+      const double waves = (double)((ctas + cap - 1) / cap);
+      const int per = (kb_total + sk - 1) / sk;
+      const double kb_bytes = kABytes + tn * 128.0;
+      const double per_sm_bw = 55e3;  // bytes per microsecond one SM sustains from L2
+      const double t_kb = kb_bytes / per_sm_bw * (plan.three_pass ? 1.6 : 1.0);
+      const double t_fixed = 3.0 + (double)kBM * tn / sk * 4.0 / 20e3 + (sk > 1 ? 0.6 : 0.0);
+      const double t_cta = t_fixed + per * t_kb;
+      const double unique = ((double)p.K * p.N + (double)p.M * p.K) * 4.0 * batch;
+      const double l2_total = (double)ctas * per * kb_bytes;
+      const double t = std::max(std::max(waves * t_cta, unique / 6.5e6), l2_total / 5.0e6);
+      if (t < best) { best = t; best_tn = tn; best_sk = sk; }
+      if (gp.split_k) break;
+    }
+    if (gp.tile_n) break;
   }
-  if (sk > kb_total) sk = kb_total;
-  if (sk > 65535) sk = 65535;
-  // equalise: recompute from the per-split block count so no split is empty
-  const int per = (kb_total + sk - 1) / sk;
-  sk = (kb_total + per - 1) / per;
-  plan.split_k = sk;
-  const size_t stage = (size_t)(kABytes + tn * kBK * 4) * (plan.three_pass ? 2 : 1);
-  int stages = (int)((200 * 1024) / stage);
-  if (stages > 8) stages = 8;
-  if (stages > per) stages = per;
-  if (stages < 1) return false;
+  if (!best_tn) return false;
+  plan.tile_n = best_tn;
+  plan.split_k = best_sk;
+  if (plan.split_k > 8) return false;  // one cluster holds a tile's splits
+  const int per = (kb_total + plan.split_k - 1) / plan.split_k;
+  const size_t stage = (size_t)(kABytes + plan.tile_n * kBK * 4) * (plan.three_pass ? 2 : 1);
+  int stages = (int)(kSmemBudget / stage);
+  stages = std::max(1, std::min(std::min(stages, 8), per));
   plan.stages = stages;
-  plan.smem_bytes = stages * stage + (3 * stages + 1) * 8 + 16 + 1024;
-  plan.partial_bytes = sk > 1 ? (size_t)tiles * sk * kBM * tn * 4 : 0;
-  plan.counter_bytes = sk > 1 ? (size_t)tiles * 4 : 0;
+  plan.smem_bytes = smem_for(plan.tile_n, stages, plan.three_pass);
+  if (plan.smem_bytes > 227 * 1024) return false;
+  plan.partial_bytes = 0;
+  plan.counter_bytes = 0;
   return true;
 }
 
-int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, void *partials,
-                   size_t partial_bytes, void *counters, size_t counter_bytes, cudaStream_t s) {
+int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, cudaStream_t s) {
   TcArgs a;
   a.p = p; a.e = e;
   a.tile_n = plan.tile_n; a.split_k = plan.split_k; a.stages = plan.stages;
@@ -526,18 +707,8 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
   a.kb_total = (int)((p.K + kBK - 1) / kBK);
   a.kb_per_split = (a.kb_total + plan.split_k - 1) / plan.split_k;
   a.status = device_status_word();
+  a.trace = g_trace;
   FML_REQUIRE(a.status, FML_CUDA_ERROR, "fml_gemm: no device status word");
-  a.ws_partial = nullptr; a.ws_counter = nullptr;
-  if (plan.split_k > 1) {
-    FML_REQUIRE(partials && partial_bytes >= plan.partial_bytes && counters &&
-                    counter_bytes >= plan.counter_bytes, FML_BAD_ARG,
-                "fml_gemm: split-K needs %zu partial and %zu counter bytes, got %zu and %zu",
-                plan.partial_bytes, plan.counter_bytes, partial_bytes, counter_bytes);
-    FML_REQUIRE(aligned16(partials) && ((uintptr_t)counters & 3) == 0, FML_MISALIGNED,
-                "fml_gemm: partials must be 16-byte and counters 4-byte aligned");
-    a.ws_counter = reinterpret_cast<unsigned *>(counters);
-    a.ws_partial = reinterpret_cast<float *>(partials);
-  }
   CUtensorMap map_a, map_b;
   int st = make_map(&map_a, p.a, p.K, p.M, p.a_sm, p.nb0, p.a_b0, p.nb1, p.a_b1, kBK, kBM,
                     CU_TENSOR_MAP_SWIZZLE_128B);
@@ -549,17 +720,41 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
     st = make_map(&map_b, p.b, p.N, p.K, p.b_sk, p.nb0, p.b_b0, p.nb1, p.b_b1, 32, kBK,
                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (st != FML_OK) return st;
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const TcArgs);
+  const KernelFn kernels[4] = {gemm_tc_kernel<false, false>, gemm_tc_kernel<false, true>,
+                               gemm_tc_kernel<true, false>, gemm_tc_kernel<true, true>};
+  const KernelFn kernel = kernels[(plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0)];
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
   if (!attr_set[dev & 63]) {
-    FML_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    for (KernelFn k : kernels)
+      FML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[dev & 63] = true;
   }
-  dim3 grid((unsigned)(a.tiles_m * a.tiles_n), (unsigned)plan.split_k, (unsigned)(p.nb0 * p.nb1));
-  gemm_tc_kernel<<<grid, kThreads, plan.smem_bytes, s>>>(map_a, map_b, a);
-  FML_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(a.tiles_m * a.tiles_n), (unsigned)plan.split_k, (unsigned)(p.nb0 * p.nb1));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = plan.smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)plan.split_k;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FML_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, a));
   return FML_OK;
 }
 
 }  // namespace fml
+
+// Tracing hook: when set to a device buffer of 16 x (number of CTAs) u64, every tensor-core GEMM
+// launch stamps %globaltimer at: 0 CTA start, 1 set-up done, 2 first stage landed, 3 last MMA
+// issued, 4 accumulator ready, 5 epilogue done, 6 CTA end, 7 tile staged; 8 / 9 hold clock64()
+// at CTA start / end (SM cycles, to read the SM clock against the timer).  NULL disables it.
+extern "C" void fml_debug_set_gemm_trace(void *device_buffer) {
+  fml::g_trace = static_cast<unsigned long long *>(device_buffer);
+}

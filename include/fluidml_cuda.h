@@ -224,29 +224,38 @@ typedef struct fml_gemm_params {
   float divisor;       /* 1 = none                                                        */
   float alpha, beta;   /* Gemm attributes; MatMul uses 1, 1                               */
   float act_param[3];
-  int32_t split_k;     /* 0 = let the library choose                                      */
-  int32_t tile_n;      /* 0 = let the library choose (32, 64 or 128)                      */
+  int32_t split_k;     /* 0 = let the library choose; at most 8 (one cluster per tile)    */
+  int32_t tile_n;      /* 0 = let the library choose; a multiple of 16 up to 256          */
 } fml_gemm_params;
 
 void fml_gemm_default_params(fml_gemm_params *p);
 
-/* Scratch the chosen configuration needs when it splits K (both 0 otherwise):
- *   partial_bytes  fp32 partial tiles; contents need no initialisation and are dead after
- *                  the call, so a planner may give the bytes to other tenants between calls
- *                  (the reference's node scratch has the same [i,i] lifetime,
- *                  src/worker/planner.cpp:283-291);
- *   counter_bytes  one arrival counter per output tile; must be zero before the first call
- *                  and is left zero by every call, so GEMM launches that are ordered on one
- *                  stream may share one counter buffer.  It must not be shared by launches
- *                  that can overlap, and must not be handed to other tenants. */
-int fml_gemm_workspace_bytes(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
-                             const fml_gemm_params *p, size_t *partial_bytes,
-                             size_t *counter_bytes);
-
+/* Split-K partial sums never leave the chip (they are reduced across a thread-block cluster
+ * through distributed shared memory), so the call needs no scratch buffer. */
 int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
              const fml_tensor *bias, const fml_tensor *residual, const fml_gemm_params *p,
-             void *partials, size_t partial_bytes, void *counters, size_t counter_bytes,
              void *stream);
+
+/* What the library chose for these operands (the counterpart of the loop-order autotuning in
+ * the reference's MatMul / Gemm generators, src/structure/kernel/generator/matmul.cpp:88-131):
+ * uses_tensor_cores 0 = fp32 FMA kernel, 1 = tcgen05; tile_n, split_k and stages are 0 for the
+ * FMA kernel.  Pure host computation. */
+typedef struct fml_gemm_plan_info {
+  int32_t uses_tensor_cores, tile_n, split_k, stages, b_mn_major, three_pass;
+  uint64_t shared_memory_bytes;
+} fml_gemm_plan_info;
+int fml_gemm_plan(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                  const fml_gemm_params *p, fml_gemm_plan_info *info);
+
+/* On-device choice of tile_n and split_k for these operands: runs the candidate
+ * configurations a few times each on `stream` (overwriting C with valid results), keeps the
+ * fastest and remembers it per problem signature.  Synchronises; must not be stream-captured.
+ * `tuned` receives a copy of `p` with tile_n / split_k filled in (unchanged when the fp32 FMA
+ * kernel is used or the caller already fixed them).  The counterpart of the reference's
+ * loop-order autotuning (src/structure/kernel/generator/matmul.cpp:88-131, gemm.cpp:107-151). */
+int fml_gemm_autotune(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                      const fml_tensor *bias, const fml_tensor *residual, const fml_gemm_params *p,
+                      void *stream, fml_gemm_params *tuned);
 
 /* Reports which path fml_gemm would take for these operands: 0 = fp32 FMA, 1 = tcgen05. */
 int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,

@@ -53,7 +53,8 @@ public:
   // ---- additions of this back end (no counterpart in the reference) -------------------
   // Options, set before Compile: "device" (CUDA ordinal), "gemm_precision" (auto | fp32 |
   // 3xtf32 | tf32), "fusion" (0/1), "cuda_graph" (0/1), "alignment" (arena tenant alignment
-  // in bytes), "dp_cost" (model | constant).  Environment variables FLUIDML_<KEY> give the
+  // in bytes), "dp_cost" (model | constant), "autotune" (0/1: time GEMM tile choices on the
+  // device during Compile, as the reference's MatMul/Gemm generators time loop orders).  Environment variables FLUIDML_<KEY> give the
   // defaults.
   virtual void SetOption(const std::string &key, const std::string &value) = 0;
   // Compile-time facts as JSON text: arena bytes (aligned, unaligned, reference-equivalent),

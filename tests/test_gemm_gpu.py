@@ -61,20 +61,33 @@ def test_gemm_precisions(prec, sa, sb, b_kmajor):
     assert relerr(out.numpy(), ref) <= TOL[prec]
 
 
-@pytest.mark.parametrize("split_k,tile_n", [(1, 64), (2, 64), (5, 32), (12, 64), (3, 128), (24, 16)])
+@pytest.mark.parametrize("split_k,tile_n", [(1, 64), (2, 64), (4, 32), (8, 64), (2, 128), (8, 16), (4, 256), (8, 48), (1, 192)])
 def test_gemm_split_k_and_tiles(split_k, tile_n):
     a, b = rnd(128, 768), rnd(768, 768)
     ref = ref_matmul(a, b)
-    out = DT(ref.shape, np.float32)
     p = cabi.gemm_params(precision=cabi.GEMM_3XTF32, split_k=split_k, tile_n=tile_n)
-    ws = cabi.gemm(DT.from_numpy(a), DT.from_numpy(b), out, params=p)
-    first = out.numpy()
-    assert relerr(first, ref) <= TOL[cabi.GEMM_3XTF32]
-    # the workspace counters return to zero: a second launch on the same workspace agrees bit for bit
-    out2 = DT(ref.shape, np.float32)
-    cabi.gemm(DT.from_numpy(a), DT.from_numpy(b), out2, params=p, workspace=ws)
-    cabi.check_device()
-    assert np.array_equal(out2.numpy(), first)
+    for kmajor in (False, True):
+        da, db = DT.from_numpy(a), DT.from_numpy(b, [1, 0] if kmajor else None)
+        out = DT(ref.shape, np.float32)
+        info = cabi.gemm_plan(da, db, out, p)
+        assert info.uses_tensor_cores and info.split_k == split_k
+        cabi.gemm(da, db, out, params=p)
+        first = out.numpy()
+        assert relerr(first, ref) <= TOL[cabi.GEMM_3XTF32]
+        # the cluster reduction adds the partial tiles in rank order: a second launch agrees bit for bit
+        out2 = DT(ref.shape, np.float32)
+        cabi.gemm(da, db, out2, params=p)
+        cabi.check_device()
+        assert np.array_equal(out2.numpy(), first)
+
+
+def test_gemm_auto_plan_fills_the_machine():
+    """The planner's own choice for the benchmark shapes uses split-K clusters of at most 8."""
+    for (m, k, n) in ((128, 768, 768), (128, 768, 3072), (128, 3072, 768)):
+        a, b, c = DT((m, k), np.float32), DT((k, n), np.float32), DT((m, n), np.float32)
+        info = cabi.gemm_plan(a, b, c, cabi.gemm_params(precision=cabi.GEMM_3XTF32))
+        ctas = -(-n // info.tile_n) * info.split_k
+        assert info.uses_tensor_cores and 1 <= info.split_k <= 8 and 64 <= ctas <= 148, (m, k, n, info.tile_n, info.split_k)
 
 
 def test_gemm_epilogues():
