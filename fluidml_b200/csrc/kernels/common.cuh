@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <utility>
 
 namespace fml {
 
@@ -122,6 +123,40 @@ __device__ __forceinline__ void offsets_of(const Iter<NOPS> &it, int64_t lin, in
     for (int o = 0; o < NOPS; ++o) off[o] += c * it.stride[o][d];
   }
 }
+
+// Programmatic dependent launch: every kernel of the library is launched with the
+// "programmatic stream serialization" attribute and starts with pdl_prologue(), so inside a
+// stream (or a captured graph) kernel N+1 may be scheduled, and run its own set-up, while
+// kernel N drains; griddepcontrol.wait returns once kernel N has completed and its writes are
+// visible, and no kernel touches global memory before it.  FLUIDML_PDL=0 turns the attribute
+// off (the device instructions are then no-ops).
+bool pdl_enabled();
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+template <typename... Exp, typename... Act>
+inline cudaError_t launch_kernel(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Act &&...args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Act>(args)...);
+}
+#define FML_LAUNCH(kernel, grid, block, smem, stream, ...)                                 \
+  FML_CUDA(::fml::launch_kernel(kernel, grid, block, smem, stream, __VA_ARGS__))
 
 inline int grid_for(int64_t work, int block, int max_blocks = 148 * 16) {
   int64_t g = (work + block - 1) / block;

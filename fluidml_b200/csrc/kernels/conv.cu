@@ -32,6 +32,7 @@ __device__ __forceinline__ float conv_act(int act, float v) {
 constexpr int CB = 64, CK = 16;
 
 __global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
+  pdl_prologue();
   __shared__ float As[CK][CB + 4];
   __shared__ float Bs[CK][CB + 4];
   const int64_t Mtot = a.N * a.OH * a.OW, Ktot = a.IC * a.KH * a.KW;
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
 }
 
 __global__ void conv_depthwise_kernel(ConvArgs a) {
+  pdl_prologue();
   const int64_t total = a.N * a.OC * a.OH * a.OW;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * blockDim.x) {
@@ -125,6 +127,7 @@ struct PoolArgs {
 };
 
 __global__ void pool2d_kernel(PoolArgs a) {
+  pdl_prologue();
   const int64_t total = a.N * a.C * a.OH * a.OW;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * blockDim.x) {
@@ -187,9 +190,9 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");
     dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));
     FML_REQUIRE(grid.y <= 65535, FML_UNSUPPORTED, "fml_conv: too many output pixels for one launch");
-    conv_igemm_kernel<<<grid, 256, 0, s>>>(a);
+    FML_LAUNCH((conv_igemm_kernel), grid, 256, 0, s, a);
   } else {
-    conv_depthwise_kernel<<<grid_for(M * a.OC, 256), 256, 0, s>>>(a);
+    FML_LAUNCH((conv_depthwise_kernel), grid_for(M * a.OC, 256), 256, 0, s, a);
   }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -211,7 +214,7 @@ extern "C" int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, co
   a.x = (const float *)x->data; a.y = (float *)y->data; a.mode = mode;
   const int64_t total = a.N * a.C * a.OH * a.OW;
   if (total == 0) return FML_OK;
-  pool2d_kernel<<<grid_for(total, 256), 256, 0, as_stream(stream)>>>(a);
+  FML_LAUNCH((pool2d_kernel), grid_for(total, 256), 256, 0, as_stream(stream), a);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }

@@ -13,6 +13,7 @@ namespace {
 
 template <typename T>
 __global__ void copy_generic(Iter<2> it, T *out, const T *in) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[2];
@@ -24,6 +25,7 @@ __global__ void copy_generic(Iter<2> it, T *out, const T *in) {
 // Innermost dim contiguous on both sides, extent (in units of T) a multiple of V.
 template <typename T, int V>
 __global__ void copy_vec(Iter<2> it, T *out, const T *in) {
+  pdl_prologue();
   struct alignas(sizeof(T) * V) Pack { T v[V]; };
   const int64_t innerv = it.shape[it.rank - 1] / V, totalv = it.total / V;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < totalv;
@@ -45,6 +47,7 @@ __global__ void copy_vec(Iter<2> it, T *out, const T *in) {
 template <typename T>
 __global__ void copy_tile(Iter<2> it, int di, int dout, int64_t tiles_i, int64_t tiles_o,
                           T *out, const T *in) {
+  pdl_prologue();
   __shared__ T tile[32][33];
   int64_t b = blockIdx.x;
   const int64_t ti = b % tiles_i; b /= tiles_i;
@@ -83,7 +86,7 @@ int launch_copy(Iter<2> &it, void *out, const void *in, cudaStream_t s) {
     for (int d = 0; d < l && ok; ++d)
       ok = it.stride[0][d] % V == 0 && it.stride[1][d] % V == 0;
     if (ok) {
-      copy_vec<T, V><<<grid_for(it.total / V, 256), 256, 0, s>>>(it, (T *)out, (const T *)in);
+      FML_LAUNCH((copy_vec<T, V>), grid_for(it.total / V, 256), 256, 0, s, it, (T *)out, (const T *)in);
       FML_CUDA(cudaGetLastError());
       return FML_OK;
     }
@@ -100,13 +103,13 @@ int launch_copy(Iter<2> &it, void *out, const void *in, cudaStream_t s) {
     for (int d = 0; d < it.rank; ++d)
       if (d != di && d != dout) blocks *= it.shape[d];
     if (blocks < (int64_t)1 << 31) {
-      copy_tile<T><<<(unsigned)blocks, dim3(32, 8), 0, s>>>(it, di, dout, tiles_i, tiles_o,
+      FML_LAUNCH((copy_tile<T>), (unsigned)blocks, dim3(32, 8), 0, s, it, di, dout, tiles_i, tiles_o,
                                                             (T *)out, (const T *)in);
       FML_CUDA(cudaGetLastError());
       return FML_OK;
     }
   }
-  copy_generic<T><<<grid_for(it.total, 256), 256, 0, s>>>(it, (T *)out, (const T *)in);
+  FML_LAUNCH((copy_generic<T>), grid_for(it.total, 256), 256, 0, s, it, (T *)out, (const T *)in);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }
@@ -121,6 +124,7 @@ struct ReshapeArgs {
 
 template <typename T>
 __global__ void reshape_generic(ReshapeArgs a, T *out, const T *in) {
+  pdl_prologue();
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < a.total;
        e += (int64_t)gridDim.x * blockDim.x) {
     int64_t oo = 0, oi = 0, l = e;
@@ -159,6 +163,7 @@ struct GatherArgs {
 template <typename T>
 __global__ void gather_generic(GatherArgs g, T *out, const T *data, const int64_t *ind,
                                int *status) {
+  pdl_prologue();
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < g.total;
        e += (int64_t)gridDim.x * blockDim.x) {
     int64_t idx[kMaxDims], l = e, oo = 0;
@@ -188,6 +193,7 @@ __global__ void embedding_rows(int64_t rows, int64_t width, int64_t vocab, float
                                const float *add0, int64_t add0_row_stride,
                                const float *add1, int64_t add1_row_stride, int64_t add_rows,
                                int *status) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (warp >= rows) return;
@@ -212,6 +218,7 @@ __global__ void embedding_rows(int64_t rows, int64_t width, int64_t vocab, float
 __global__ void embedding_generic(GatherArgs g, Iter<3> add, float *out, const float *table,
                                   const int64_t *ind, const float *add0, const float *add1,
                                   int *status) {
+  pdl_prologue();
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < g.total;
        e += (int64_t)gridDim.x * blockDim.x) {
     int64_t idx[kMaxDims], l = e, oo = 0, o0 = 0, o1 = 0;
@@ -319,9 +326,9 @@ extern "C" int fml_reshape_copy(const fml_tensor *in, const fml_tensor *out, voi
   for (int i = 0; i < in->rank; ++i) { a.ishape[i] = in->shape[i]; a.istride[i] = in->stride[i]; }
   const int grid = grid_for(n, 256);
   switch (es) {
-  case 4: reshape_generic<uint32_t><<<grid, 256, 0, s>>>(a, (uint32_t *)out->data, (const uint32_t *)in->data); break;
-  case 8: reshape_generic<uint64_t><<<grid, 256, 0, s>>>(a, (uint64_t *)out->data, (const uint64_t *)in->data); break;
-  default: reshape_generic<uint8_t><<<grid, 256, 0, s>>>(a, (uint8_t *)out->data, (const uint8_t *)in->data); break;
+  case 4: FML_LAUNCH((reshape_generic<uint32_t>), grid, 256, 0, s, a, (uint32_t *)out->data, (const uint32_t *)in->data); break;
+  case 8: FML_LAUNCH((reshape_generic<uint64_t>), grid, 256, 0, s, a, (uint64_t *)out->data, (const uint64_t *)in->data); break;
+  default: FML_LAUNCH((reshape_generic<uint8_t>), grid, 256, 0, s, a, (uint8_t *)out->data, (const uint8_t *)in->data); break;
   }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -341,7 +348,7 @@ extern "C" int fml_gather(const fml_tensor *data, const fml_tensor *indices, con
       data->shape[1] % 4 == 0 && data->stride[0] % 4 == 0 && is_row_major(out) &&
       is_row_major(indices) && aligned16(data->data) && aligned16(out->data)) {
     int64_t rows = numel(indices);
-    embedding_rows<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, s>>>(
+    FML_LAUNCH((embedding_rows), (unsigned)((rows * 32 + 255) / 256), 256, 0, s, 
         rows, data->shape[1], data->shape[0], (float *)out->data, (const float *)data->data,
         data->stride[0], (const int64_t *)indices->data, nullptr, 0, nullptr, 0, 1, status);
     FML_CUDA(cudaGetLastError());
@@ -349,9 +356,9 @@ extern "C" int fml_gather(const fml_tensor *data, const fml_tensor *indices, con
   }
   const int grid = grid_for(g.total, 256);
   switch (dtype_size(data->dtype)) {
-  case 4: gather_generic<uint32_t><<<grid, 256, 0, s>>>(g, (uint32_t *)out->data, (const uint32_t *)data->data, (const int64_t *)indices->data, status); break;
-  case 8: gather_generic<uint64_t><<<grid, 256, 0, s>>>(g, (uint64_t *)out->data, (const uint64_t *)data->data, (const int64_t *)indices->data, status); break;
-  default: gather_generic<uint8_t><<<grid, 256, 0, s>>>(g, (uint8_t *)out->data, (const uint8_t *)data->data, (const int64_t *)indices->data, status); break;
+  case 4: FML_LAUNCH((gather_generic<uint32_t>), grid, 256, 0, s, g, (uint32_t *)out->data, (const uint32_t *)data->data, (const int64_t *)indices->data, status); break;
+  case 8: FML_LAUNCH((gather_generic<uint64_t>), grid, 256, 0, s, g, (uint64_t *)out->data, (const uint64_t *)data->data, (const int64_t *)indices->data, status); break;
+  default: FML_LAUNCH((gather_generic<uint8_t>), grid, 256, 0, s, g, (uint8_t *)out->data, (const uint8_t *)data->data, (const int64_t *)indices->data, status); break;
   }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -376,7 +383,7 @@ extern "C" int fml_embedding(const fml_tensor *table, const fml_tensor *ids, con
     FML_REQUIRE(broadcast_strides(adds[o], out, add.stride[o + 1]), FML_BAD_ARG,
                 "fml_embedding: addend does not broadcast to the output");
   }
-  embedding_generic<<<grid_for(g.total, 256), 256, 0, as_stream(stream)>>>(
+  FML_LAUNCH((embedding_generic), grid_for(g.total, 256), 256, 0, as_stream(stream), 
       g, add, (float *)out->data, (const float *)table->data, (const int64_t *)ids->data,
       add0 ? (const float *)add0->data : nullptr, add1 ? (const float *)add1->data : nullptr, status);
   FML_CUDA(cudaGetLastError());

@@ -55,6 +55,7 @@ __device__ __forceinline__ int64_t ew_apply_i64(int op, int64_t a, int64_t b, in
 // operand 0 = out, 1 = a, 2 = b
 __global__ void ew_f32_generic(Iter<3> it, int op, float *out, const float *a, const float *b,
                                float p0, float p1) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -67,6 +68,7 @@ __global__ void ew_f32_generic(Iter<3> it, int op, float *out, const float *a, c
 // Innermost dim: out stride 1, a/b stride 1 or 0; inner extent a multiple of 4.
 __global__ void ew_f32_vec4(Iter<3> it, int op, float *out, const float *a, const float *b,
                             float p0, float p1) {
+  pdl_prologue();
   const int64_t inner4 = it.shape[it.rank - 1] >> 2;
   const int64_t total4 = it.total >> 2;
   const bool a_vec = it.stride[1][it.rank - 1] == 1, b_vec = b && it.stride[2][it.rank - 1] == 1;
@@ -98,6 +100,7 @@ __global__ void ew_f32_vec4(Iter<3> it, int op, float *out, const float *a, cons
 
 __global__ void ew_i64_generic(Iter<3> it, int op, int64_t *out, const int64_t *a,
                                const int64_t *b, int64_t p0) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -108,6 +111,7 @@ __global__ void ew_i64_generic(Iter<3> it, int op, int64_t *out, const int64_t *
 
 __global__ void ew_equal_i64(Iter<3> it, uint8_t *out, const int64_t *a, const int64_t *b,
                              int64_t p0) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -117,6 +121,7 @@ __global__ void ew_equal_i64(Iter<3> it, uint8_t *out, const int64_t *a, const i
 }
 
 __global__ void ew_not(Iter<3> it, uint8_t *out, const uint8_t *a) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -127,6 +132,7 @@ __global__ void ew_not(Iter<3> it, uint8_t *out, const uint8_t *a) {
 
 template <typename TI, typename TO>
 __global__ void ew_cast(Iter<3> it, TO *out, const TI *a) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -138,6 +144,7 @@ __global__ void ew_cast(Iter<3> it, TO *out, const TI *a) {
 // operand 0 = out, 1 = x, 2 = bias
 __global__ void bias_gelu_generic(Iter<3> it, float *out, const float *x, const float *bias,
                                   float c0, float c1, float c2) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[3];
@@ -149,6 +156,7 @@ __global__ void bias_gelu_generic(Iter<3> it, float *out, const float *x, const 
 // operand 0 = out, 1 = cond, 2 = x, 3 = y
 __global__ void where_generic(Iter<4> it, float *out, const uint8_t *cond, const float *x,
                               const float *y, float y_scalar) {
+  pdl_prologue();
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total;
        i += (int64_t)gridDim.x * blockDim.x) {
     int64_t off[4];
@@ -213,7 +221,7 @@ extern "C" int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b,
   if (op == FML_CAST) {
 #define CAST_CASE(TI, CI, TO, CO)                                                          \
   if (a->dtype == CI && out->dtype == CO) {                                                \
-    ew_cast<TI, TO><<<grid, block, 0, s>>>(it, (TO *)out->data, (const TI *)a->data);      \
+    FML_LAUNCH((ew_cast<TI, TO>), grid, block, 0, s, it, (TO *)out->data, (const TI *)a->data);      \
     FML_CUDA(cudaGetLastError());                                                          \
     return FML_OK;                                                                         \
   }
@@ -238,14 +246,14 @@ extern "C" int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b,
   if (op == FML_NOT) {
     FML_REQUIRE(a->dtype == FML_BOOL && out->dtype == FML_BOOL, FML_UNSUPPORTED,
                 "fml_elementwise: Not takes bool");
-    ew_not<<<grid, block, 0, s>>>(it, (uint8_t *)out->data, (const uint8_t *)a->data);
+    FML_LAUNCH((ew_not), grid, block, 0, s, it, (uint8_t *)out->data, (const uint8_t *)a->data);
     FML_CUDA(cudaGetLastError());
     return FML_OK;
   }
   if (op == FML_EQUAL || op == FML_EQUAL_SCALAR) {
     FML_REQUIRE(a->dtype == FML_I64 && out->dtype == FML_BOOL && (!b || b->dtype == FML_I64),
                 FML_UNSUPPORTED, "fml_elementwise: Equal takes int64 and yields bool");
-    ew_equal_i64<<<grid, block, 0, s>>>(it, (uint8_t *)out->data, (const int64_t *)a->data,
+    FML_LAUNCH((ew_equal_i64), grid, block, 0, s, it, (uint8_t *)out->data, (const int64_t *)a->data,
                                         b ? (const int64_t *)b->data : nullptr, (int64_t)p0);
     FML_CUDA(cudaGetLastError());
     return FML_OK;
@@ -256,7 +264,7 @@ extern "C" int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b,
     FML_REQUIRE(op == FML_ADD || op == FML_MUL || op == FML_SUB || op == FML_ADD_SCALAR ||
                     op == FML_MUL_SCALAR || op == FML_RSUB_SCALAR,
                 FML_UNSUPPORTED, "fml_elementwise: op %d has no int64 kernel", op);
-    ew_i64_generic<<<grid, block, 0, s>>>(it, op, (int64_t *)out->data, (const int64_t *)a->data,
+    FML_LAUNCH((ew_i64_generic), grid, block, 0, s, it, op, (int64_t *)out->data, (const int64_t *)a->data,
                                           b ? (const int64_t *)b->data : nullptr, (int64_t)p0);
     FML_CUDA(cudaGetLastError());
     return FML_OK;
@@ -267,10 +275,10 @@ extern "C" int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b,
               FML_UNSUPPORTED, "fml_elementwise: unknown op %d", op);
   const float *bp = b ? (const float *)b->data : nullptr;
   if (vec4_ok(it, out->data, a->data, bp)) {
-    ew_f32_vec4<<<grid_for(it.total / 4, block), block, 0, s>>>(
+    FML_LAUNCH((ew_f32_vec4), grid_for(it.total / 4, block), block, 0, s, 
         it, op, (float *)out->data, (const float *)a->data, bp, (float)p0, (float)p1);
   } else {
-    ew_f32_generic<<<grid, block, 0, s>>>(it, op, (float *)out->data, (const float *)a->data, bp,
+    FML_LAUNCH((ew_f32_generic), grid, block, 0, s, it, op, (float *)out->data, (const float *)a->data, bp,
                                           (float)p0, (float)p1);
   }
   FML_CUDA(cudaGetLastError());
@@ -287,7 +295,7 @@ extern "C" int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const 
   int st = make_iter(it, out, ins, "fml_bias_gelu");
   if (st != FML_OK) return st;
   if (it.total == 0) return FML_OK;
-  bias_gelu_generic<<<grid_for(it.total, 256), 256, 0, as_stream(stream)>>>(
+  FML_LAUNCH((bias_gelu_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const float *)x->data, (const float *)bias->data, c0, c1, c2);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -304,7 +312,7 @@ extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_
   int st = make_iter(it, out, ins, "fml_where");
   if (st != FML_OK) return st;
   if (it.total == 0) return FML_OK;
-  where_generic<<<grid_for(it.total, 256), 256, 0, as_stream(stream)>>>(
+  FML_LAUNCH((where_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
       y ? (const float *)y->data : nullptr, y_scalar);
   FML_CUDA(cudaGetLastError());

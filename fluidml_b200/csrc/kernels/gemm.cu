@@ -91,6 +91,7 @@ namespace {
 constexpr int SB = 64, SK = 16;
 
 __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmProblem p, GemmEpilogue e) {
+  pdl_prologue();
   __shared__ float As[SK][SB + 4];
   __shared__ float Bs[SK][SB + 4];
   const int64_t z = blockIdx.z, z0 = z % p.nb0, z1 = z / p.nb0;
@@ -152,7 +153,7 @@ int launch_gemm_simt(const GemmProblem &p, const GemmEpilogue &e, cudaStream_t s
   FML_REQUIRE(batch <= 65535 && (p.M + SB - 1) / SB <= 65535, FML_UNSUPPORTED,
               "fml_gemm: batch or M too large for the fp32 kernel grid");
   dim3 grid((unsigned)((p.N + SB - 1) / SB), (unsigned)((p.M + SB - 1) / SB), (unsigned)batch);
-  gemm_simt_kernel<<<grid, 256, 0, s>>>(p, e);
+  FML_LAUNCH((gemm_simt_kernel), grid, 256, 0, s, p, e);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }

@@ -36,6 +36,7 @@
 #include "gemm_common.cuh"
 #include <cuda.h>
 #include <algorithm>
+#include <cstdlib>
 
 namespace fml {
 namespace {
@@ -189,126 +190,24 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-// ---------------------------------------------------------------- epilogue loops
-// The loop over output elements is instantiated per (activation, bias, residual, scaling)
-// combination so that its body is a few dozen instructions: with every variant inlined behind
-// run-time branches the body no longer fits the instruction cache close to the scheduler and
-// each iteration stalls on instruction fetch.
-struct EpiCtx {
-  const float *staging;
-  uint32_t staging_addr;
-  int pitch, BN, S, r0, r1, et;
-  int64_t m_base, n_base, M, N;
-  float *C;
-  int64_t c_sm, c_sn;
-  const float *bias;
-  int64_t bias_sm, bias_sn;
-  const float *res;
-  int64_t res_sm, res_sn;
-  GemmEpilogue e;
-};
-
-template <int ACT, bool BIAS, bool RES, bool SCALE>
-__device__ __forceinline__ float epi_op(const GemmEpilogue &e, float v, float bv, float rv) {
-  if (SCALE) {
-    if (e.divisor != 1.0f) v = v / e.divisor;
-    v = BIAS ? e.alpha * v + e.beta * bv : e.alpha * v;
-  } else if (BIAS) {
-    v = v + bv;
-  }
-  if (ACT == FML_ACT_GELU_ERF) v = v * (erff(v / e.c0) + e.c1) * e.c2;
-  else if (ACT == FML_ACT_RELU) v = fmaxf(v, 0.0f);
-  else if (ACT == FML_ACT_TANH) v = tanhf(v);
-  else if (ACT == FML_ACT_SIGMOID) v = 1.0f / (1.0f + expf(-v));
-  if (RES) v += rv;
-  return v;
-}
-
-// Sum of the S partial tiles at one staging offset, in rank order; the loads are issued
-// together so their latencies overlap.
-__device__ __forceinline__ float4 gather4(const EpiCtx &x, int r, int c) {
-  if (x.S == 1) return *reinterpret_cast<const float4 *>(x.staging + (size_t)r * x.pitch + c);
-  const uint32_t off = x.staging_addr + (uint32_t)(r * x.pitch + c) * 4u;
-  float4 t[8];
-#pragma unroll
-  for (int rank = 0; rank < 8; ++rank) {
-    if (rank < x.S) {
-      const uint32_t addr = cluster_smem_addr(off, (uint32_t)rank);
-      asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=f"(t[rank].x), "=f"(t[rank].y), "=f"(t[rank].z), "=f"(t[rank].w) : "r"(addr) : "memory");
-    }
-  }
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-  for (int rank = 0; rank < 8; ++rank)
-    if (rank < x.S) { acc.x += t[rank].x; acc.y += t[rank].y; acc.z += t[rank].z; acc.w += t[rank].w; }
-  return acc;
-}
-
-template <int ACT, bool BIAS, bool RES, bool SCALE, bool VEC>
-__device__ __noinline__ void epilogue_rows(const EpiCtx x) {
-  const int quads = x.BN >> 2;
-  const int count = (x.r1 - x.r0) * quads;
-  for (int i = x.et; i < count; i += 128) {
-    const int r = x.r0 + i / quads, c = (i - (i / quads) * quads) * 4;
-    const int64_t m = x.m_base + r, n = x.n_base + c;
-    const float4 acc = gather4(x, r, c);
-    if (m >= x.M) continue;
-    if (VEC) {
-      float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), rv = bv, o;
-      if (BIAS) {
-        if (x.bias_sn == 1) bv = *reinterpret_cast<const float4 *>(x.bias + m * x.bias_sm + n);
-        else { const float b = x.bias[m * x.bias_sm]; bv = make_float4(b, b, b, b); }
-      }
-      if (RES) rv = *reinterpret_cast<const float4 *>(x.res + m * x.res_sm + n);
-      o.x = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.x, bv.x, rv.x);
-      o.y = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.y, bv.y, rv.y);
-      o.z = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.z, bv.z, rv.z);
-      o.w = epi_op<ACT, BIAS, RES, SCALE>(x.e, acc.w, bv.w, rv.w);
-      *reinterpret_cast<float4 *>(x.C + m * x.c_sm + n) = o;
-    } else {
-      const float av[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int64_t nn = n + j;
-        if (nn < x.N) {
-          const float bv = BIAS ? x.bias[m * x.bias_sm + nn * x.bias_sn] : 0.0f;
-          const float rv = RES ? x.res[m * x.res_sm + nn * x.res_sn] : 0.0f;
-          x.C[m * x.c_sm + nn * x.c_sn] = epi_op<ACT, BIAS, RES, SCALE>(x.e, av[j], bv, rv);
-        }
-      }
-    }
-  }
-}
-
-template <int ACT, bool BIAS, bool RES>
-__device__ __forceinline__ void epilogue_dispatch3(const EpiCtx &x, bool scale, bool vec) {
-  if (scale) { if (vec) epilogue_rows<ACT, BIAS, RES, true, true>(x); else epilogue_rows<ACT, BIAS, RES, true, false>(x); }
-  else { if (vec) epilogue_rows<ACT, BIAS, RES, false, true>(x); else epilogue_rows<ACT, BIAS, RES, false, false>(x); }
-}
+// ---------------------------------------------------------------- epilogue helpers
+// The activation is a template parameter of the kernel and bias / residual / scaling are
+// cheap uniform predicates inside one short loop: every CTA runs each phase of this kernel
+// once, so the cost of a phase is largely the instruction fetch of its (cold) code, and a
+// compact, straight-line epilogue matters more than a branch-free one.
 template <int ACT>
-__device__ __forceinline__ void epilogue_dispatch2(const EpiCtx &x, bool scale, bool vec) {
-  const bool b = x.bias != nullptr, r = x.res != nullptr;
-  if (b && r) epilogue_dispatch3<ACT, true, true>(x, scale, vec);
-  else if (b) epilogue_dispatch3<ACT, true, false>(x, scale, vec);
-  else if (r) epilogue_dispatch3<ACT, false, true>(x, scale, vec);
-  else epilogue_dispatch3<ACT, false, false>(x, scale, vec);
-}
-__device__ __forceinline__ void epilogue_dispatch(const EpiCtx &x, bool vec) {
-  const bool scale = x.e.divisor != 1.0f || x.e.alpha != 1.0f || (x.bias && x.e.beta != 1.0f);
-  switch (x.e.act) {
-  case FML_ACT_GELU_ERF: epilogue_dispatch2<FML_ACT_GELU_ERF>(x, scale, vec); break;
-  case FML_ACT_RELU: epilogue_dispatch2<FML_ACT_RELU>(x, scale, vec); break;
-  case FML_ACT_TANH: epilogue_dispatch2<FML_ACT_TANH>(x, scale, vec); break;
-  case FML_ACT_SIGMOID: epilogue_dispatch2<FML_ACT_SIGMOID>(x, scale, vec); break;
-  default: epilogue_dispatch2<FML_ACT_NONE>(x, scale, vec); break;
-  }
+__device__ __forceinline__ float act_op(const GemmEpilogue &e, float v) {
+  if (ACT == FML_ACT_GELU_ERF) return v * (erff(v / e.c0) + e.c1) * e.c2;
+  if (ACT == FML_ACT_RELU) return fmaxf(v, 0.0f);
+  if (ACT == FML_ACT_TANH) return tanhf(v);
+  if (ACT == FML_ACT_SIGMOID) return 1.0f / (1.0f + expf(-v));
+  return v;
 }
 
 // ---------------------------------------------------------------- kernel
 // THREE_PASS / B_MN are compile-time so that each variant carries only its own code: the kernel
 // runs every phase once per CTA, and instruction fetch of cold code is a first-order cost.
-template <bool THREE_PASS, bool B_MN>
+template <bool THREE_PASS, bool B_MN, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcArgs a) {
@@ -345,6 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < BN) tmem_cols <<= 1;
 
+  pdl_launch_dependents();  // the next kernel may start its own set-up while this one runs
   if (threadIdx.x == 0) {
     TRACE(0);
     TRACE(8);
@@ -362,6 +262,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Barriers, TMEM and descriptors are ready; nothing has touched global memory yet.  From here
+  // on the preceding kernel's results are needed (and its inputs may be overwritten).
+  pdl_wait();
   if (threadIdx.x == 0) TRACE(1);
 
   if (warp == 0) {
@@ -406,6 +309,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t ready = THREE_PASS ? bar_conv : bar_full;
       const uint32_t b_lbo = B_MN ? (uint32_t)(kBK * 128) : 16u;
       const uint32_t b_sbo = B_MN ? 512u : 1024u, b_type = B_MN ? 1u : 2u;
+      // stage-0 descriptors: A | B | A_lo | B_lo (the address field cannot carry out: the whole
+      // ring lies below 256 KiB of shared-memory address space)
+      const uint64_t desc_a = smem_desc(tiles_base, 16u, 1024u);
+      const uint64_t desc_b = smem_desc(tiles_base + kABytes, b_lbo, b_sbo, b_type);
+      const uint64_t desc_al = smem_desc(tiles_base + kABytes + b_bytes, 16u, 1024u);
+      const uint64_t desc_bl = smem_desc(tiles_base + 2 * kABytes + b_bytes, b_lbo, b_sbo, b_type);
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         const int s = it % a.stages;
@@ -414,20 +323,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!ok) break;
         if (it == 0) TRACE(2);
         tc_fence_after();
-        const uint32_t sa = tiles_base + (uint32_t)s * stage_bytes, sb = sa + kABytes;
-        const uint32_t sal = sb + b_bytes, sbl = sal + kABytes;
+        // One thread issues everything, so its instruction count per MMA is on the critical
+        // path: the four descriptors of stage 0 were built before the loop; a stage or k-step
+        // is an add on the 14-bit (address >> 4) field in the low word.
+        const uint32_t soff = ((uint32_t)s * stage_bytes) >> 4;
 #pragma unroll
         for (int j = 0; j < kBK / 8; ++j) {
           // k-step j: 32 bytes further along a K-major row; 8 rows (1024 bytes) further
           // down an MN-major tile
-          const uint32_t a_off = (uint32_t)j * 32u;
-          const uint32_t b_off = B_MN ? (uint32_t)j * 1024u : (uint32_t)j * 32u;
-          const uint64_t da = smem_desc(sa + a_off, 16u, 1024u);
-          const uint64_t db = smem_desc(sb + b_off, b_lbo, b_sbo, b_type);
+          const uint32_t aj = soff + (uint32_t)j * 2u;
+          const uint32_t bj = soff + (B_MN ? (uint32_t)j * 64u : (uint32_t)j * 2u);
+          const uint64_t da = desc_a + aj, db = desc_b + bj;
           const uint32_t first = (it == 0 && j == 0) ? 0u : 1u;
           if (THREE_PASS) {
-            const uint64_t dal = smem_desc(sal + a_off, 16u, 1024u);
-            const uint64_t dbl = smem_desc(sbl + b_off, b_lbo, b_sbo, b_type);
+            const uint64_t dal = desc_al + aj, dbl = desc_bl + bj;
             umma_tf32(tmem_base, dal, db, idesc, first);
             umma_tf32(tmem_base, da, dbl, idesc, 1u);
             umma_tf32(tmem_base, da, db, idesc, 1u);
@@ -461,26 +370,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint4 *hi_b = reinterpret_cast<uint4 *>(st + kABytes);
         uint4 *lo_a = reinterpret_cast<uint4 *>(st + kABytes + b_bytes);
         uint4 *lo_b = reinterpret_cast<uint4 *>(st + 2 * kABytes + b_bytes);
-        auto split4 = [](uint4 x, uint4 &hi, uint4 &lo) {
-          hi.x = x.x & 0xffffe000u; hi.y = x.y & 0xffffe000u;
-          hi.z = x.z & 0xffffe000u; hi.w = x.w & 0xffffe000u;
-          lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(hi.x));
-          lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(hi.y));
-          lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(hi.z));
-          lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(hi.w));
+        // kind::tf32 reads the upper 19 bits of each fp32 operand and ignores the rest
+        // (checked on the device: masking the low 13 bits beforehand changes no output bit), so
+        // the tile TMA delivered already is the "hi" operand; only lo = x - hi is written.
+        auto lo4 = [](uint4 x) {
+          uint4 lo;
+          lo.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(x.x & 0xffffe000u));
+          lo.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xffffe000u));
+          lo.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xffffe000u));
+          lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xffffe000u));
+          return lo;
         };
-        // A: 1024 units over 128 threads = 8 each; all loads first so their latencies overlap
-        {
+        {  // A: 1024 16-byte units over 128 threads = 8 each; loads first so latencies overlap
           uint4 x[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) x[j] = hi_a[et + 128 * j];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 hi, lo;
-            split4(x[j], hi, lo);
-            hi_a[et + 128 * j] = hi;
-            lo_a[et + 128 * j] = lo;
-          }
+          for (int j = 0; j < 8; ++j) lo_a[et + 128 * j] = lo4(x[j]);
         }
         for (int base = 0; base < b_vec; base += 512) {  // B: up to 4 units per thread per round
           uint4 x[4];
@@ -489,12 +395,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (base + et + 128 * j < b_vec) x[j] = hi_b[base + et + 128 * j];
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            if (base + et + 128 * j < b_vec) {
-              uint4 hi, lo;
-              split4(x[j], hi, lo);
-              hi_b[base + et + 128 * j] = hi;
-              lo_b[base + et + 128 * j] = lo;
-            }
+            if (base + et + 128 * j < b_vec) lo_b[base + et + 128 * j] = lo4(x[j]);
         }
         fence_async_smem();  // make the generic-proxy writes visible to the tensor core
         __syncwarp();
@@ -544,14 +445,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const float *res = a.p.res ? a.p.res + (int64_t)z0 * a.p.res_b0 + (int64_t)z1 * a.p.res_b1 : nullptr;
     float *C = a.p.c + zc;
     const int64_t n_base = (int64_t)tile_n * BN, m_base = (int64_t)tile_m * kBM;
-    EpiCtx x;
-    x.staging = staging; x.staging_addr = smem_u32(staging); x.pitch = pitch; x.BN = BN; x.S = S;
-    x.r0 = r0; x.r1 = r1; x.et = et;
-    x.m_base = m_base; x.n_base = n_base; x.M = a.p.M; x.N = a.p.N;
-    x.C = C; x.c_sm = a.p.c_sm; x.c_sn = a.p.c_sn;
-    x.bias = bias; x.bias_sm = a.p.bias_sm; x.bias_sn = a.p.bias_sn;
-    x.res = res; x.res_sm = a.p.res_sm; x.res_sn = a.p.res_sn;
-    x.e = a.e;
     // 16-byte path: unit column stride everywhere, every row start and the tile origin on a
     // 16-byte boundary, no ragged column edge inside this tile
     auto al4 = [](int64_t v) { return (v & 3) == 0; };
@@ -560,7 +453,111 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (bias) vec = vec && (a.p.bias_sn == 1 || a.p.bias_sn == 0) && al4(a.p.bias_sm) &&
                     ((reinterpret_cast<uintptr_t>(bias) & 15) == 0);
     if (res) vec = vec && a.p.res_sn == 1 && al4(a.p.res_sm) && ((reinterpret_cast<uintptr_t>(res) & 15) == 0);
-    epilogue_dispatch(x, vec);
+    const bool scale = a.e.divisor != 1.0f || a.e.alpha != 1.0f || (bias && a.e.beta != 1.0f);
+    const float sc_div = a.e.divisor, sc_alpha = a.e.alpha, sc_beta = a.e.beta;
+    const uint32_t staging_addr = smem_u32(staging);
+    const int quads = BN >> 2;
+    // Thread -> (column quad, row within a pass); rows advance by a constant, so every pointer
+    // below is stepped with one add per iteration (no division, no 64-bit multiply in the loop:
+    // with one warp per scheduler every dependent instruction costs its full latency).
+    const int rows_pass = 128 / quads;          // quads 4..64 -> 32..2 rows per pass
+    const int cq = et % quads, rsub = et / quads;
+    const int r_end = (int)min((int64_t)r1, a.p.M - m_base);  // rows that exist
+    if (vec) {
+      if (rsub < rows_pass) {
+        const int c = cq * 4;
+        const int64_t n = n_base + c;
+        int r = r0 + rsub;
+        const float *sp = staging + (size_t)r * pitch + c;
+        const int sp_step = rows_pass * pitch;
+        uint32_t rank_addr[8];
+        if (S > 1) {
+#pragma unroll
+          for (int rank = 0; rank < 8; ++rank)
+            rank_addr[rank] = rank < S ? cluster_smem_addr(staging_addr + (uint32_t)(r * pitch + c) * 4u, (uint32_t)rank) : 0u;
+        }
+        float *cp = C + (m_base + r) * a.p.c_sm + n;
+        const int64_t c_step = (int64_t)rows_pass * a.p.c_sm;
+        const float *rp = res ? res + (m_base + r) * a.p.res_sm + n : nullptr;
+        const int64_t r_step = (int64_t)rows_pass * a.p.res_sm;
+        const float *bp = bias ? bias + (m_base + r) * a.p.bias_sm + (a.p.bias_sn ? n : 0) : nullptr;
+        const int64_t b_step = (int64_t)rows_pass * a.p.bias_sm;
+        float4 bvec = make_float4(0.f, 0.f, 0.f, 0.f);
+        const bool bias_per_col = bias && a.p.bias_sm == 0 && a.p.bias_sn == 1;  // the usual [N] bias: load once
+        if (bias_per_col) bvec = *reinterpret_cast<const float4 *>(bp);
+        for (; r < r_end; r += rows_pass) {
+          float4 acc;
+          if (S == 1) {
+            acc = *reinterpret_cast<const float4 *>(sp);
+          } else {
+            float4 t[8];
+#pragma unroll
+            for (int rank = 0; rank < 8; ++rank)
+              if (rank < S)
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(t[rank].x), "=f"(t[rank].y), "=f"(t[rank].z), "=f"(t[rank].w)
+                             : "r"(rank_addr[rank]) : "memory");
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int rank = 0; rank < 8; ++rank)
+              if (rank < S) {
+                acc.x += t[rank].x; acc.y += t[rank].y; acc.z += t[rank].z; acc.w += t[rank].w;
+                rank_addr[rank] += (uint32_t)sp_step * 4u;
+              }
+          }
+          if (bias && !bias_per_col) {
+            if (a.p.bias_sn == 1) bvec = *reinterpret_cast<const float4 *>(bp);
+            else { const float t = *bp; bvec = make_float4(t, t, t, t); }
+          }
+          float4 rvec = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (res) rvec = *reinterpret_cast<const float4 *>(rp);
+          float v[4] = {acc.x, acc.y, acc.z, acc.w};
+          const float bv[4] = {bvec.x, bvec.y, bvec.z, bvec.w}, rv[4] = {rvec.x, rvec.y, rvec.z, rvec.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float y = v[j];
+            if (scale) {
+              if (sc_div != 1.0f) y = y / sc_div;
+              y = bias ? sc_alpha * y + sc_beta * bv[j] : sc_alpha * y;
+            } else {
+              y += bv[j];
+            }
+            v[j] = act_op<ACT>(a.e, y) + rv[j];
+          }
+          *reinterpret_cast<float4 *>(cp) = make_float4(v[0], v[1], v[2], v[3]);
+          sp += sp_step; cp += c_step; rp += r_step; bp += b_step;
+        }
+      }
+    } else {
+      // ragged column edge or non-unit strides: one element at a time, indices recomputed
+      const int count = (r1 - r0) * quads;
+      for (int i = et; i < count; i += 128) {
+        const int rr = i / quads;
+        const int r = r0 + rr, c = (i - rr * quads) * 4;
+        const int64_t m = m_base + r;
+        if (m >= a.p.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int64_t n = n_base + c + j;
+          if (n >= a.p.N) continue;
+          float acc = 0.0f;
+          const uint32_t off = staging_addr + (uint32_t)(r * pitch + c + j) * 4u;
+          if (S == 1) acc = staging[(size_t)r * pitch + c + j];
+          else
+            for (int rank = 0; rank < S; ++rank) acc += ld_cluster_f32(cluster_smem_addr(off, (uint32_t)rank));
+          const float bv = bias ? bias[m * a.p.bias_sm + n * a.p.bias_sn] : 0.0f;
+          const float rv = res ? res[m * a.p.res_sm + n * a.p.res_sn] : 0.0f;
+          float y = acc;
+          if (scale) {
+            if (sc_div != 1.0f) y = y / sc_div;
+            y = bias ? sc_alpha * y + sc_beta * bv : sc_alpha * y;
+          } else {
+            y += bv;
+          }
+          C[m * a.p.c_sm + n * a.p.c_sn] = act_op<ACT>(a.e, y) + rv;
+        }
+      }
+    }
     if (et == 0) TRACE(5);
   }
   if (S > 1) cluster_sync_all();  // nobody leaves while a peer may still read its tile
@@ -721,9 +718,15 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (st != FML_OK) return st;
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const TcArgs);
-  const KernelFn kernels[4] = {gemm_tc_kernel<false, false>, gemm_tc_kernel<false, true>,
-                               gemm_tc_kernel<true, false>, gemm_tc_kernel<true, true>};
-  const KernelFn kernel = kernels[(plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0)];
+#define FML_TC_ROW(T, M)                                                                  \
+  gemm_tc_kernel<T, M, FML_ACT_NONE>, gemm_tc_kernel<T, M, FML_ACT_GELU_ERF>,             \
+  gemm_tc_kernel<T, M, FML_ACT_RELU>, gemm_tc_kernel<T, M, FML_ACT_TANH>,                 \
+  gemm_tc_kernel<T, M, FML_ACT_SIGMOID>
+  static const KernelFn kernels[20] = {FML_TC_ROW(false, false), FML_TC_ROW(false, true),
+                                       FML_TC_ROW(true, false), FML_TC_ROW(true, true)};
+#undef FML_TC_ROW
+  const int act = (e.act >= 0 && e.act <= FML_ACT_SIGMOID) ? e.act : 0;
+  const KernelFn kernel = kernels[((plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0)) * 5 + act];
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
@@ -738,13 +741,15 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = plan.smem_bytes;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = (unsigned)plan.split_k;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   FML_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, a));
   return FML_OK;
 }

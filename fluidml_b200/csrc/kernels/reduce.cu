@@ -33,6 +33,7 @@ struct RowArgs {
 template <int NV>  // float4 per lane
 __global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const float *mask,
                                  float divisor) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (row >= a.rows.total) return;
@@ -80,6 +81,7 @@ __global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const f
 
 __global__ void softmax_rows_generic(RowArgs a, float *out, const float *in, const float *mask,
                                      float divisor) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (row >= a.rows.total) return;
@@ -105,6 +107,7 @@ __global__ void softmax_rows_generic(RowArgs a, float *out, const float *in, con
 template <int NV>
 __global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const float *res,
                                    const float *gamma, const float *beta, float eps) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (row >= a.rows.total) return;
@@ -152,6 +155,7 @@ __global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const
 __global__ void layernorm_rows_generic(RowArgs a, float *out, const float *in, const float *res,
                                        const float *gamma, int64_t gstride, const float *beta,
                                        int64_t bstride, float eps) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (row >= a.rows.total) return;
@@ -181,6 +185,7 @@ struct ReduceArgs {
 };
 
 __global__ void reduce_mean_kernel(ReduceArgs a, float *out, const float *in) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t o = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (o >= a.keep.total) return;
@@ -201,6 +206,7 @@ __global__ void reduce_mean_kernel(ReduceArgs a, float *out, const float *in) {
 }
 
 __global__ void cumsum_kernel(RowArgs a, int64_t *out, const int64_t *in) {
+  pdl_prologue();
   const int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (row >= a.rows.total) return;
   int64_t off[3];
@@ -257,15 +263,15 @@ bool rows_vec_ok(const RowArgs &a, const void *out, const void *in, const void *
 
 using namespace fml;
 
-#define DISPATCH_NV(len, KERNEL, ...)                                                      \
+#define DISPATCH_NV(len, KERNEL, grid, stream, ...)                                        \
   do {                                                                                     \
     int64_t per_lane = ((len) / 4 + 31) / 32;                                              \
-    if (per_lane <= 1) KERNEL<1> __VA_ARGS__;                                              \
-    else if (per_lane <= 2) KERNEL<2> __VA_ARGS__;                                         \
-    else if (per_lane <= 4) KERNEL<4> __VA_ARGS__;                                         \
-    else if (per_lane <= 8) KERNEL<8> __VA_ARGS__;                                         \
-    else if (per_lane <= 16) KERNEL<16> __VA_ARGS__;                                       \
-    else KERNEL<32> __VA_ARGS__;                                                           \
+    if (per_lane <= 1) FML_LAUNCH((KERNEL<1>), grid, 256, 0, stream, __VA_ARGS__);         \
+    else if (per_lane <= 2) FML_LAUNCH((KERNEL<2>), grid, 256, 0, stream, __VA_ARGS__);    \
+    else if (per_lane <= 4) FML_LAUNCH((KERNEL<4>), grid, 256, 0, stream, __VA_ARGS__);    \
+    else if (per_lane <= 8) FML_LAUNCH((KERNEL<8>), grid, 256, 0, stream, __VA_ARGS__);    \
+    else if (per_lane <= 16) FML_LAUNCH((KERNEL<16>), grid, 256, 0, stream, __VA_ARGS__);  \
+    else FML_LAUNCH((KERNEL<32>), grid, 256, 0, stream, __VA_ARGS__);                      \
   } while (0)
 
 extern "C" int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
@@ -281,9 +287,9 @@ extern "C" int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float d
   const unsigned grid = (unsigned)((a.rows.total * 32 + 255) / 256);
   const float *mp = mask ? (const float *)mask->data : nullptr;
   if (rows_vec_ok(a, out->data, in->data, mp)) {
-    DISPATCH_NV(a.len, softmax_rows_vec, <<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, mp, divisor));
+    DISPATCH_NV(a.len, softmax_rows_vec, grid, s, a, (float *)out->data, (const float *)in->data, mp, divisor);
   } else {
-    softmax_rows_generic<<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, mp, divisor);
+    FML_LAUNCH((softmax_rows_generic), grid, 256, 0, s, a, (float *)out->data, (const float *)in->data, mp, divisor);
   }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -313,9 +319,9 @@ extern "C" int fml_layernorm(const fml_tensor *in, const fml_tensor *residual,
   const bool res_vec = !residual || a.axis_stride[2] == 1;
   if (rows_vec_ok(a, out->data, in->data, rp) && res_vec && gs == 1 && bs == 1 &&
       aligned16(scale->data) && aligned16(bias->data)) {
-    DISPATCH_NV(a.len, layernorm_rows_vec, <<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps));
+    DISPATCH_NV(a.len, layernorm_rows_vec, grid, s, a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps);
   } else {
-    layernorm_rows_generic<<<grid, 256, 0, s>>>(a, (float *)out->data, (const float *)in->data, rp,
+    FML_LAUNCH((layernorm_rows_generic), grid, 256, 0, s, a, (float *)out->data, (const float *)in->data, rp,
                                                 (const float *)scale->data, gs,
                                                 (const float *)bias->data, bs, eps);
   }
@@ -350,7 +356,7 @@ extern "C" int fml_reduce_mean(const fml_tensor *in, const fml_tensor *out, cons
   }
   collapse(a.keep);
   if (a.keep.total == 0 || a.count == 0) return FML_OK;
-  reduce_mean_kernel<<<(unsigned)((a.keep.total * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(
+  FML_LAUNCH((reduce_mean_kernel), (unsigned)((a.keep.total * 32 + 255) / 256), 256, 0, as_stream(stream), 
       a, (float *)out->data, (const float *)in->data);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
@@ -363,7 +369,7 @@ extern "C" int fml_cumsum(const fml_tensor *in, const fml_tensor *out, int axis,
   int st = make_rows(a, out, in, nullptr, axis, "fml_cumsum");
   if (st != FML_OK) return st;
   if (a.rows.total == 0) return FML_OK;
-  cumsum_kernel<<<grid_for(a.rows.total, 128, 1 << 20), 128, 0, as_stream(stream)>>>(
+  FML_LAUNCH((cumsum_kernel), grid_for(a.rows.total, 128, 1 << 20), 128, 0, as_stream(stream), 
       a, (int64_t *)out->data, (const int64_t *)in->data);
   FML_CUDA(cudaGetLastError());
   return FML_OK;

@@ -2,6 +2,7 @@
 // the per-device status word that kernels with bounded waits or clamped indices write.
 #include "common.cuh"
 #include <cstdarg>
+#include <cstdlib>
 #include <mutex>
 
 namespace fml {
@@ -18,6 +19,14 @@ void set_error(const char *fmt, ...) {
 int cuda_fail(cudaError_t e, const char *what) {
   set_error("%s: %s", what, cudaGetErrorString(e));
   return e == cudaErrorMemoryAllocation ? FML_OUT_OF_MEMORY : FML_CUDA_ERROR;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *v = getenv("FLUIDML_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 static int *g_status[64] = {nullptr};
