@@ -213,8 +213,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                              ~static_cast<uintptr_t>(1023));
+  // (an offset added to the __shared__ array keeps the pointer in the shared state space, so the
+  // converter and epilogue compile to ld/st.shared rather than slower generic accesses)
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int BN = a.tile_n;
   const int pitch = BN + 4;  // staging row pitch in floats: rows 16 bytes apart modulo 128, so the
                              // 16-byte row-wise writes of a quarter-warp hit distinct banks
