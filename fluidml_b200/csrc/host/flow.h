@@ -22,7 +22,15 @@ struct Region {
   // Only inner regions live in the planned arena; interface tensors are caller buffers and
   // constants are baked (reference: src/structure/flow/region.cpp:66,94).
   bool NeedMemoryAllocation() const { return kind == kInner; }
-  std::vector<int64_t> GetStrides() const { return utils::GenStrides(meta.GetShape(), layout); }
+  // A region that is a view of another tensor's bytes (set by the lowering for reshapes,
+  // transposes and slices that need no copy) carries explicit element strides and an element
+  // offset from its owner's base; otherwise the strides follow from the layout.
+  bool is_view = false;
+  std::vector<int64_t> view_strides;
+  int64_t view_offset = 0;
+  std::vector<int64_t> GetStrides() const {
+    return is_view ? view_strides : utils::GenStrides(meta.GetShape(), layout);
+  }
 };
 using RegionPtr = std::shared_ptr<Region>;
 

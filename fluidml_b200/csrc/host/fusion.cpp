@@ -266,6 +266,101 @@ bool FuseSilu(Rewriter &rw, const NodePtr &sg) {
   return true;
 }
 
+// ---- GEMMs that read the same activations with constant weights (the Q, K, V projections):
+// one GEMM over the concatenated weights, the original outputs become column slices of its
+// result (views, no copy).  Fewer launches and one pass over the shared A operand.
+bool MergeSiblingGemms(flow::Flow &f) {
+  auto eligible = [](const NodePtr &n) {
+    if (n->kind != Kind::FusedGemm || !n->b_is_const || n->trans_a || n->trans_b || n->act != 0 ||
+        n->has_residual || n->has_mask || n->divisor != 1.0f || n->alpha != 1.0f || n->beta != 1.0f)
+      return false;
+    if (n->inputs.size() != 1 || n->output->kind != flow::Region::kInner) return false;
+    const RegionPtr &w = n->consts[0];
+    if (w->meta.GetRank() != 2 || w->meta.GetType() != Type::kFloat32 || !utils::IsDefaultLayout(w->layout)) return false;
+    if (n->has_bias && (n->consts.size() < 2 || n->consts[1]->meta.GetRank() != 1)) return false;
+    return true;
+  };
+  for (size_t i = 0; i < f.nodes.size(); ++i) {
+    const NodePtr &first = f.nodes[i];
+    if (!eligible(first)) continue;
+    std::vector<NodePtr> group = {first};
+    for (size_t j = i + 1; j < f.nodes.size(); ++j) {
+      const NodePtr &n = f.nodes[j];
+      if (!eligible(n) || n->inputs[0] != first->inputs[0] || n->has_bias != first->has_bias) continue;
+      if (n->consts[0]->meta.GetShape()[0] != first->consts[0]->meta.GetShape()[0]) continue;
+      const auto &sa = n->output->meta.GetShape(), &sb = first->output->meta.GetShape();
+      if (sa.size() != sb.size() || !std::equal(sa.begin(), sa.end() - 1, sb.begin())) continue;
+      group.push_back(n);
+    }
+    if (group.size() < 2) continue;
+    const int64_t K = first->consts[0]->meta.GetShape()[0];
+    int64_t total = 0;
+    for (const auto &n : group) total += n->consts[0]->meta.GetShape()[1];
+    // concatenated weights [K, total] and bias [total]
+    std::vector<uint8_t> wbytes((size_t)K * total * 4), bbytes((size_t)total * 4);
+    int64_t col = 0;
+    for (const auto &n : group) {
+      const int64_t N = n->consts[0]->meta.GetShape()[1];
+      const uint8_t *src = n->consts[0]->constant->Bytes().data();
+      for (int64_t k = 0; k < K; ++k) memcpy(wbytes.data() + ((size_t)k * total + col) * 4, src + (size_t)k * N * 4, (size_t)N * 4);
+      if (n->has_bias) memcpy(bbytes.data() + (size_t)col * 4, n->consts[1]->constant->Bytes().data(), (size_t)N * 4);
+      col += N;
+    }
+    auto make_const = [&](const std::string &name, std::vector<int64_t> shape, std::vector<uint8_t> bytes) {
+      auto r = std::make_shared<flow::Region>();
+      r->kind = flow::Region::kConstant;
+      r->name = name;
+      r->meta = Meta(Type::kFloat32, shape);
+      r->layout = utils::GenDefaultLayout(shape.size());
+      r->constant = std::make_shared<Tensor>(r->meta, std::move(bytes));
+      f.regions.push_back(r);
+      f.by_name[name] = r;
+      return r;
+    };
+    const std::string base = first->name + "_merged";
+    RegionPtr wcat = make_const(base + ".w", {K, total}, std::move(wbytes));
+    RegionPtr bcat = first->has_bias ? make_const(base + ".b", {total}, std::move(bbytes)) : nullptr;
+    auto merged = std::make_shared<flow::Region>();
+    merged->kind = flow::Region::kInner;
+    merged->name = base;
+    std::vector<int64_t> mshape = first->output->meta.GetShape();
+    mshape.back() = total;
+    merged->meta = Meta(Type::kFloat32, mshape);
+    merged->layout = utils::GenDefaultLayout(mshape.size());
+    f.regions.push_back(merged);
+    f.by_name[base] = merged;
+    // slices that hand the original outputs back
+    std::vector<NodePtr> slices;
+    col = 0;
+    for (const auto &n : group) {
+      auto sl = std::make_shared<flow::Node>();
+      sl->kind = Kind::Slice;
+      sl->name = n->name + "_slice";
+      sl->inputs = {merged};
+      sl->output = n->output;
+      sl->starts.assign(mshape.size(), 0);
+      sl->starts.back() = col;
+      col += n->consts[0]->meta.GetShape()[1];
+      slices.push_back(sl);
+    }
+    first->consts.clear();
+    first->consts.push_back(wcat);
+    if (bcat) first->consts.push_back(bcat);
+    first->output = merged;
+    std::unordered_set<const flow::Node *> gone;
+    for (size_t g = 1; g < group.size(); ++g) gone.insert(group[g].get());
+    std::vector<NodePtr> next;
+    for (const auto &n : f.nodes) {
+      if (gone.count(n.get())) continue;
+      next.push_back(n);
+      if (n == first) next.insert(next.end(), slices.begin(), slices.end());
+    }
+    f.nodes = std::move(next);
+    return true;
+  }
+  return false;
+}
+
 }  // namespace
 
 size_t FusionPasses::Run(flow::Flow &flow) {
@@ -286,6 +381,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
       }
     }
   }
+  while (MergeSiblingGemms(flow)) {}
   // drop tensors nothing refers to any more
   std::unordered_set<const flow::Region *> live;
   for (const auto &n : flow.nodes) {

@@ -14,6 +14,10 @@ fml_tensor MakeTensor(const flow::Region &region, void *data) {
   t.dtype = (int32_t)region.meta.GetType();
   t.rank = (int32_t)region.meta.GetRank();
   if (t.rank > FML_MAX_RANK) throw Error("tensor '" + region.name + "' has more than 8 dimensions");
+  if (region.is_view) {
+    const size_t es = GetSizeFromType(region.meta.GetType());
+    t.data = data ? (char *)data + region.view_offset * (int64_t)es : nullptr;
+  }
   const std::vector<int64_t> strides = region.GetStrides();
   for (int i = 0; i < t.rank; ++i) {
     t.shape[i] = region.meta.GetShape()[i];
@@ -29,6 +33,36 @@ bool SameStrides(const fml_tensor &a, const fml_tensor &b) {
   for (int i = 0; i < a.rank; ++i)
     if (a.shape[i] != b.shape[i] || (a.shape[i] != 1 && a.stride[i] != b.stride[i])) return false;
   return true;
+}
+
+// Strides that address `in` through the shape of `out` without moving data, if they exist:
+// runs of input dims that are contiguous with each other may be split or merged freely.
+bool ReshapeView(const fml_tensor &in, const fml_tensor &out, fml_tensor *view) {
+  *view = out;
+  view->data = in.data;
+  int view_d = out.rank - 1;
+  if (in.rank == 0) {
+    for (int i = 0; i < out.rank; ++i) view->stride[i] = 1;
+    return true;
+  }
+  int64_t chunk_base = in.stride[in.rank - 1], tensor_numel = 1, view_numel = 1;
+  for (int d = in.rank - 1; d >= 0; --d) {
+    tensor_numel *= in.shape[d];
+    if (d == 0 || (in.shape[d - 1] != 1 && in.stride[d - 1] != tensor_numel * chunk_base)) {
+      while (view_d >= 0 && (view_numel < tensor_numel || out.shape[view_d] == 1)) {
+        view->stride[view_d] = view_numel * chunk_base;
+        view_numel *= out.shape[view_d];
+        --view_d;
+      }
+      if (view_numel != tensor_numel) return false;
+      if (d > 0) {
+        chunk_base = in.stride[d - 1];
+        tensor_numel = 1;
+        view_numel = 1;
+      }
+    }
+  }
+  return view_d == -1;
 }
 
 bool RowMajor(const fml_tensor &t) {
@@ -118,7 +152,11 @@ BINARY_KERNEL(SubCommonKernel, FML_SUB)               // sub.cpp:71-99
 class DropoutKernel : public SingleInputWithoutBufferKernel {
 public:
   std::string GetKernelName() const override { return "DropoutKernel"; }
-  bool IsAlias(const fml_tensor &in, const fml_tensor &out) const override { return SameStrides(in, out); }
+  bool GetView(const fml_tensor &in, const fml_tensor &out, fml_tensor *view) const override {
+    *view = in;
+    (void)out;
+    return true;
+  }
   void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
     rec.Add("DropoutKernel", [=](void *s) { return fml_copy_strided(&input, &output, s); });
   }
@@ -190,7 +228,9 @@ class ReshapeLikeKernel : public SingleInputWithoutBufferKernel {
 public:
   explicit ReshapeLikeKernel(const char *name) : name_(name) {}
   std::string GetKernelName() const override { return name_; }
-  bool IsAlias(const fml_tensor &in, const fml_tensor &out) const override { return RowMajor(in) && RowMajor(out); }
+  bool GetView(const fml_tensor &in, const fml_tensor &out, fml_tensor *view) const override {
+    return ReshapeView(in, out, view);
+  }
   void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
     rec.Add(name_, [=](void *s) { return fml_reshape_copy(&input, &output, s); });
   }
@@ -204,8 +244,10 @@ class TransposeKernel : public SingleInputWithoutBufferKernel {
 public:
   explicit TransposeKernel(std::vector<int64_t> perm) : perm_(std::move(perm)) {}
   std::string GetKernelName() const override { return "TransposeKernel"; }
-  bool IsAlias(const fml_tensor &in, const fml_tensor &out) const override {
-    return SameStrides(Permuted(in, perm_), out);
+  bool GetView(const fml_tensor &in, const fml_tensor &out, fml_tensor *view) const override {
+    *view = Permuted(in, perm_);
+    (void)out;
+    return true;
   }
   void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
     const fml_tensor view = Permuted(input, perm_);
@@ -221,14 +263,19 @@ class SliceKernel : public SingleInputWithoutBufferKernel {
 public:
   explicit SliceKernel(std::vector<int64_t> starts) : starts_(std::move(starts)) {}
   std::string GetKernelName() const override { return "SliceKernel"; }
-  void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
-    fml_tensor view = input;
+  bool GetView(const fml_tensor &input, const fml_tensor &output, fml_tensor *view) const override {
+    *view = input;
     int64_t off = 0;
     for (int i = 0; i < input.rank; ++i) {
       off += starts_[i] * input.stride[i];
-      view.shape[i] = output.shape[i];
+      view->shape[i] = output.shape[i];
     }
-    view.data = Offset(input, off);
+    view->data = Offset(input, off);
+    return true;
+  }
+  void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
+    fml_tensor view;
+    GetView(input, output, &view);
     rec.Add(GetKernelName(), [=](void *s) { return fml_copy_strided(&view, &output, s); });
   }
 

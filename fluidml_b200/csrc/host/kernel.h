@@ -52,8 +52,14 @@ public:
     (void)output;
     return 0;
   }
-  // True when, for these operands, the output can simply alias the input's memory (no launch).
-  virtual bool IsAlias(const fml_tensor &input, const fml_tensor &output) const { return false; }
+  // When the output is just another way of addressing the input's bytes (a reshape that
+  // splits or merges contiguous dims, a transpose, a slice), fills `view` with the output's
+  // shape and the strides / data pointer that realise it over `input`, and returns true: the
+  // node then needs no launch and no memory of its own.
+  virtual bool GetView(const fml_tensor &input, const fml_tensor &output, fml_tensor *view) const {
+    (void)input; (void)output; (void)view;
+    return false;
+  }
 
 protected:
   Kernel() = default;

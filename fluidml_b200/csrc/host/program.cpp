@@ -56,10 +56,22 @@ AliasMap Lowering::ComputeAliases(const flow::Sequence &sequence, const kernel::
   for (const auto &node : sequence.nodes) {
     if (node->inputs.size() != 1 || node->output->kind != flow::Region::kInner) continue;
     std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
+    // the input as it will really be addressed (it may itself be a view)
     const fml_tensor in = kernel::MakeTensor(*node->inputs[0], kPlaceholder);
-    const fml_tensor out = kernel::MakeTensor(*node->output, kPlaceholder);
-    if (!k->IsAlias(in, out)) continue;
-    aliases[node->output.get()] = Owner(aliases, node->inputs[0]);
+    flow::Region plain = *node->output;
+    plain.is_view = false;
+    const fml_tensor out = kernel::MakeTensor(plain, kPlaceholder);
+    fml_tensor view;
+    if (!k->GetView(in, out, &view)) continue;
+    // the output becomes a view over the owner's bytes: same element type, explicit strides,
+    // offset measured from the owner's base
+    const flow::RegionPtr &owner = Owner(aliases, node->inputs[0]);
+    const int64_t es = (int64_t)GetSizeFromType(node->output->meta.GetType());
+    flow::Region &o = *node->output;
+    o.is_view = true;
+    o.view_strides.assign(view.stride, view.stride + view.rank);
+    o.view_offset = ((char *)view.data - (char *)kPlaceholder) / es;
+    aliases[node->output.get()] = owner;
   }
   return aliases;
 }

@@ -33,8 +33,9 @@ using AliasMap = std::unordered_map<const flow::Region *, flow::RegionPtr>;
 
 class Lowering {
 public:
-  // Walks the sequence; a single-input node whose kernel reports IsAlias() for the operands'
-  // strides, and whose output is an inner region, shares its input's memory.
+  // Walks the sequence; a single-input node whose kernel can express its output as a view of
+  // its input (GetView), and whose output is an inner region, shares its input's memory: the
+  // output region is marked as a view with explicit strides and offset.
   static AliasMap ComputeAliases(const flow::Sequence &sequence, const kernel::KernelOptions &ko);
   // Fills node->buffer_size with what each node's kernel asks for.  Uses aligned placeholder
   // addresses: planned offsets are multiples of the alignment, so the real operands take the

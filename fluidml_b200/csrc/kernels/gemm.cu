@@ -143,9 +143,6 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmProblem p, GemmEpilo
     }
 }
 
-// One warp per output element group for M == 1 style products is not needed for parity;
-// skinny shapes still go through the tile kernel above.
-
 }  // namespace
 
 int launch_gemm_simt(const GemmProblem &p, const GemmEpilogue &e, cudaStream_t s) {
@@ -239,6 +236,7 @@ extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tens
   if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
   GemmEpilogue e = make_epilogue(*gp, bias != nullptr, residual != nullptr);
   if (use_tc) return launch_gemm_tc(p, e, plan, as_stream(stream));
+  if (skinny_eligible(p)) return launch_gemm_skinny(p, e, as_stream(stream));
   return launch_gemm_simt(p, e, as_stream(stream));
 }
 

@@ -49,6 +49,11 @@ int analyse_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
 
 int launch_gemm_simt(const GemmProblem &p, const GemmEpilogue &e, cudaStream_t s);
 
+// Products with at most 32 rows: a weight-streaming kernel with split-K partials in
+// library-owned scratch memory (one buffer per device and stream).
+bool skinny_eligible(const GemmProblem &p);
+int launch_gemm_skinny(const GemmProblem &p, const GemmEpilogue &e, cudaStream_t s);
+
 // tcgen05 path -------------------------------------------------------------------------
 struct TcPlan {
   int tile_n;     // 16..256, multiple of 16

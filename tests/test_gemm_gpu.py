@@ -164,3 +164,38 @@ def test_gemm_small_and_odd_shapes_fall_back():
         cabi.gemm(DT.from_numpy(a), DT.from_numpy(b), DT((17, 9), np.float32),
                   params=cabi.gemm_params(precision=cabi.GEMM_TF32))
     assert e.value.status == 3
+
+
+SKINNY = [  # (M, K, N): pooler, VGG classifier heads at batch 1, ragged edges, several rows
+    (1, 768, 768), (1, 25088, 4096), (1, 4096, 1000), (4, 1000, 130), (32, 515, 97), (7, 64, 33), (2, 3, 5),
+]
+
+
+@pytest.mark.parametrize("m,k,n", SKINNY)
+@pytest.mark.parametrize("b_kmajor", [False, True])
+def test_gemm_skinny_rows_stream_the_weights(m, k, n, b_kmajor):
+    """Products with at most 32 rows run on the weight-streaming kernel (split-K partials in
+    library scratch).  Two launches in a row agree bit for bit: the partials are added in split
+    order and the tile counters reset themselves."""
+    a, b, bias = rnd(m, k), rnd(k, n), rnd(n)
+    ref = ref_matmul(a, b).astype(np.float64) + bias
+    da, db = DT.from_numpy(a), DT.from_numpy(b, [1, 0] if b_kmajor else None)
+    p = cabi.gemm_params(precision=cabi.GEMM_FP32)
+    outs = []
+    for _ in range(2):
+        out = DT((m, n), np.float32)
+        cabi.gemm(da, db, out, DT.from_numpy(bias), None, p)
+        outs.append(out.numpy())
+    cabi.check_device()
+    assert relerr(outs[0], ref) <= 1e-5
+    assert np.array_equal(outs[0], outs[1])
+
+
+def test_gemm_skinny_batched_and_tanh():
+    a, b, bias = rnd(3, 2, 300), rnd(3, 300, 70), rnd(70)
+    ref = np.tanh(ref_matmul(a, b).astype(np.float64) + bias)
+    out = DT((3, 2, 70), np.float32)
+    cabi.gemm(DT.from_numpy(a), DT.from_numpy(b), out, DT.from_numpy(bias), None,
+              cabi.gemm_params(act=cabi.ACT_TANH))
+    cabi.check_device()
+    assert relerr(out.numpy(), ref) <= 1e-5
