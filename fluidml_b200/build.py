@@ -30,7 +30,8 @@ KERNELS_SO = os.path.join(LIBDIR, "libfluidml_b200_kernels.so")
 HOST_SO = os.path.join(LIBDIR, "libfluidml_b200.so")
 
 NVCC_FLAGS = ["-ccbin", CXX, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", os.path.join(CSRC, "kernels")]
+              "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", os.path.join(CSRC, "kernels"),
+              *os.environ.get("FLUIDML_NVCC_EXTRA", "").split()]  # e.g. -DFML_KERNEL_TRACE for a debug build
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I", INCLUDE, "-I", os.path.join(CSRC, "host"),
              "-I", "/usr/local/cuda/include"]
 

@@ -46,7 +46,8 @@ class GemmParams(ctypes.Structure):
     _fields_ = [("precision", ctypes.c_int32), ("act", ctypes.c_int32),
                 ("divisor", ctypes.c_float), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("act_param", ctypes.c_float * 3), ("split_k", ctypes.c_int32),
-                ("tile_n", ctypes.c_int32)]
+                ("tile_n", ctypes.c_int32), ("l2_prefetch", ctypes.c_void_p),
+                ("l2_prefetch_bytes", ctypes.c_uint64)]
 
 
 class ConvParams(ctypes.Structure):
@@ -202,6 +203,16 @@ def pad(src, out, pads_begin, stream=None):
 
 def softmax(x, mask, divisor, out, axis, stream=None):
     check(lib().fml_softmax(_ref(x), _ref(mask), ctypes.c_float(divisor), _ref(out), int(axis), stream))
+
+
+def attention(q, kt, v, mask, divisor, out, stream=None):
+    check(lib().fml_attention(_ref(q), _ref(kt), _ref(v), _ref(mask), ctypes.c_float(divisor), _ref(out), stream))
+
+
+def attention_supported(s_q, s_k, d, d_v) -> bool:
+    f = lib().fml_attention_supported
+    f.argtypes = [ctypes.c_int64] * 4
+    return bool(f(s_q, s_k, d, d_v))
 
 
 def layernorm(x, residual, scale, bias, out, axis, eps, stream=None):

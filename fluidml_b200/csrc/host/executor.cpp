@@ -44,6 +44,7 @@ public:
     SetOption("alignment", EnvOr("FLUIDML_ALIGNMENT", "256"));
     SetOption("dp_cost", EnvOr("FLUIDML_DP_COST", "model"));
     SetOption("autotune", EnvOr("FLUIDML_AUTOTUNE", "1"));
+    SetOption("weight_prefetch", EnvOr("FLUIDML_WEIGHT_PREFETCH", "1"));
   }
 
   void SetOption(const std::string &key, const std::string &value) override {
@@ -52,6 +53,7 @@ public:
     else if (key == "fusion") options_.fusion = value != "0";
     else if (key == "cuda_graph") options_.cuda_graph = value != "0";
     else if (key == "autotune") options_.autotune = value != "0";
+    else if (key == "weight_prefetch") options_.weight_prefetch = value != "0";
     else if (key == "alignment") {
       options_.alignment = (size_t)std::stoul(value);
       if (options_.alignment < 16 || (options_.alignment & (options_.alignment - 1)))

@@ -51,6 +51,7 @@ enum class Kind {
   FusedSoftmax,    // softmax(x / divisor + mask)
   FusedLayerNorm,  // LayerNorm(x + residual)
   Silu,            // x * sigmoid(x)
+  FusedAttention,  // softmax(Q K^T / divisor + mask) V; inputs: Q, K^T, V, [mask]
 };
 const char *KindName(Kind k);
 

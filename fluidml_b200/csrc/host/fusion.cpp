@@ -255,6 +255,34 @@ bool FuseScaledMaskedSoftmax(Rewriter &rw, const NodePtr &div) {
   return true;
 }
 
+// ---- MatMul(Q, K^T) -> [scaled, masked] Softmax -> MatMul(P, V): one attention kernel when
+// K and V of a head fit in shared memory
+bool FuseAttention(Rewriter &rw, const NodePtr &qk) {
+  if (qk->kind != Kind::MatMul || qk->inputs.size() != 2 || IsConst(qk->inputs[0]) || IsConst(qk->inputs[1])) return false;
+  NodePtr sm = rw.Sole(qk->output);
+  if (!sm || (sm->kind != Kind::Softmax && sm->kind != Kind::FusedSoftmax) || sm->inputs[0] != qk->output) return false;
+  const size_t rank = sm->output->meta.GetRank();
+  if (rank < 2 || rank > 4 || sm->axis != (int64_t)rank - 1) return false;
+  NodePtr pv = rw.SoleOfKind(sm->output, Kind::MatMul);
+  if (!pv || pv->inputs.size() != 2 || pv->inputs[0] != sm->output || IsConst(pv->inputs[1])) return false;
+  const RegionPtr &q = qk->inputs[0], &kt = qk->inputs[1], &v = pv->inputs[1];
+  const auto &qs = q->meta.GetShape(), &ks = kt->meta.GetShape(), &vs = v->meta.GetShape();
+  if (qs.size() != rank || ks.size() != rank || vs.size() != rank) return false;
+  if (q->meta.GetType() != Type::kFloat32 || kt->meta.GetType() != Type::kFloat32 || v->meta.GetType() != Type::kFloat32) return false;
+  for (size_t i = 0; i + 2 < rank; ++i)
+    if (qs[i] != ks[i] || qs[i] != vs[i]) return false;  // no batch broadcasting between the operands
+  if (!fml_attention_supported(qs[rank - 2], ks[rank - 1], qs[rank - 1], vs[rank - 1])) return false;
+  qk->kind = Kind::FusedAttention;
+  qk->inputs = {q, kt, v};
+  qk->divisor = sm->kind == Kind::FusedSoftmax ? sm->divisor : 1.0f;
+  qk->has_mask = sm->kind == Kind::FusedSoftmax && sm->has_mask;
+  if (qk->has_mask) qk->inputs.push_back(sm->inputs[1]);
+  qk->output = pv->output;
+  rw.Kill(sm);
+  rw.Kill(pv);
+  return true;
+}
+
 // ---- Sigmoid(x) * x
 bool FuseSilu(Rewriter &rw, const NodePtr &sg) {
   if (sg->kind != Kind::Sigmoid) return false;
@@ -369,7 +397,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseSilu};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

@@ -390,6 +390,24 @@ private:
   bool has_mask_;
 };
 
+// matmul.cpp:5-44 -> softmax.cpp:22-139 -> matmul.cpp:5-44 of one attention head group, fused
+class AttentionKernel : public Kernel {
+public:
+  AttentionKernel(float divisor, bool has_mask) : divisor_(divisor), has_mask_(has_mask) {}
+  std::string GetKernelName() const override { return "FusedAttentionKernel"; }
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output,
+              const Buffer &) const override {
+    const fml_tensor q = in.at(0), kt = in.at(1), v = in.at(2), mask = has_mask_ ? in.at(3) : fml_tensor{};
+    const bool hm = has_mask_;
+    const float d = divisor_;
+    rec.Add(GetKernelName(), [=](void *s) { return fml_attention(&q, &kt, &v, hm ? &mask : nullptr, d, &output, s); });
+  }
+
+private:
+  float divisor_;
+  bool has_mask_;
+};
+
 // layer_normalization.cpp:33-220 (+ the fused residual variant)
 class LayerNormalizationConstantScaleBiasKernel : public Kernel {
 public:
@@ -455,6 +473,18 @@ public:
   };
   explicit GemmLikeKernel(Config c) : c_(c) {}
   std::string GetKernelName() const override { return c_.name; }
+  bool StreamedConstant(const void **ptr, size_t *bytes) const override {
+    if (!c_.has_const_b) return false;
+    size_t n = 4;
+    for (int i = 0; i < c_.const_b.rank; ++i) n *= (size_t)c_.const_b.shape[i];
+    *ptr = c_.const_b.data;
+    *bytes = n;
+    return true;
+  }
+  void SetPrefetch(const void *ptr, size_t bytes) override {
+    c_.params.l2_prefetch = ptr;
+    c_.params.l2_prefetch_bytes = bytes;
+  }
 
   void Resolve(const std::vector<fml_tensor> &in, fml_tensor &a, fml_tensor &b, fml_tensor &bias,
                fml_tensor &res) const {
@@ -589,6 +619,7 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
     return std::make_unique<GatherConstantDataTensorAddTensorLhsAddTensorLhsKernel>(C(0), C(1), C(2));
   case Kind::Softmax: return std::make_unique<SoftmaxKernel>(n.axis, 1.0f, false);
   case Kind::FusedSoftmax: return std::make_unique<SoftmaxKernel>(n.axis, n.divisor, n.has_mask);
+  case Kind::FusedAttention: return std::make_unique<AttentionKernel>(n.divisor, n.has_mask);
   case Kind::LayerNormalizationConstantScaleBias:
     return std::make_unique<LayerNormalizationConstantScaleBiasKernel>(C(0), C(1), n.axis, n.epsilon, false);
   case Kind::FusedLayerNorm:
@@ -675,7 +706,7 @@ const char *KindName(Kind k) {
       "Not", "Pad", "Pow", "ReduceMean", "Relu", "Reshape", "Slice", "Softmax", "Sqrt", "Squeeze", "SubConstantLhs",
       "SubCommon", "Tanh", "Transpose", "Unsqueeze", "UnsqueezeSubLhsScalarMulRhsScalar",
       "WhereConstantCondConstantScalarY", "WhereConstantCondConstantTensorY", "Sigmoid", "Identity", "FusedGemm",
-      "FusedSoftmax", "FusedLayerNorm", "Silu"};
+      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention"};
   return names[(int)k];
 }
 }  // namespace flow

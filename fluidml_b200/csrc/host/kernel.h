@@ -61,6 +61,14 @@ public:
     return false;
   }
 
+  // Constant device bytes this kernel streams on every launch (its weights), if any; and the
+  // hint that a later kernel's such bytes may be fetched into L2 while this one runs.
+  virtual bool StreamedConstant(const void **ptr, size_t *bytes) const {
+    (void)ptr; (void)bytes;
+    return false;
+  }
+  virtual void SetPrefetch(const void *ptr, size_t bytes) { (void)ptr; (void)bytes; }
+
 protected:
   Kernel() = default;
 };

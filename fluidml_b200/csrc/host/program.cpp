@@ -194,9 +194,31 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
   ko.gemm_precision = options.gemm_precision;
   ko.autotune = options.autotune;
   kernel::LaunchRecorder rec;
+  std::vector<std::pair<flow::NodePtr, std::unique_ptr<kernel::Kernel>>> kernels;
   for (const auto &node : sequence.nodes) {
     if (aliases.count(node->output.get())) { ++prog->aliased_nodes; continue; }
-    std::unique_ptr<kernel::Kernel> k = kernel::SelectKernel(*node, resolve, ko);
+    kernels.emplace_back(node, kernel::SelectKernel(*node, resolve, ko));
+  }
+  // Weight prefetch chain: every kernel that streams constant weights is told about the next
+  // such kernel's bytes (circularly: the last one names the first, for the next pass), so
+  // that HBM keeps streaming weights into L2 between the launches of a latency-bound pass.
+  if (options.weight_prefetch) {
+    const void *next_ptr = nullptr;
+    size_t next_bytes = 0;
+    for (const auto &kv : kernels)
+      if (kv.second->StreamedConstant(&next_ptr, &next_bytes)) break;  // the first: target of the last
+    for (size_t i = kernels.size(); i-- > 0;) {
+      const void *own = nullptr;
+      size_t own_bytes = 0;
+      if (!kernels[i].second->StreamedConstant(&own, &own_bytes)) continue;
+      if (next_ptr && next_ptr != own) kernels[i].second->SetPrefetch(next_ptr, next_bytes);
+      next_ptr = own;
+      next_bytes = own_bytes;
+    }
+  }
+  for (const auto &kv : kernels) {
+    const flow::NodePtr &node = kv.first;
+    const std::unique_ptr<kernel::Kernel> &k = kv.second;
     std::vector<fml_tensor> ins;
     for (const auto &r : node->inputs) ins.push_back(tensor_of(r));
     const fml_tensor out = tensor_of(node->output);

@@ -26,6 +26,7 @@ struct Options {
   size_t alignment = 256;
   bool dp_constant_cost = false;
   bool autotune = true;  // tune GEMM tile / split-K choices on the device at Compile
+  bool weight_prefetch = true;  // GEMMs ask L2 to fetch the next GEMM's weights while they run
 };
 
 // region -> the region whose memory it shares (itself when it owns memory).

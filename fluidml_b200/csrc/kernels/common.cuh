@@ -133,7 +133,37 @@ __device__ __forceinline__ void offsets_of(const Iter<NOPS> &it, int64_t lin, in
 bool pdl_enabled();
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#ifdef FML_KERNEL_TRACE
+// Debug builds only (-DFML_KERNEL_TRACE): the first thread of every kernel writes %globaltimer
+// when its dependency wait returns, so consecutive stamps give each kernel's period inside a
+// stream or graph (its run time plus the gap to the next start).  Each translation unit has
+// its own copy of the pointers; fml_debug_set_kernel_trace sets them all.
+static __device__ unsigned long long *g_trace_buf;
+static __device__ unsigned *g_trace_cursor;
+static __device__ unsigned g_trace_cap;
+void register_trace_setter(cudaError_t (*setter)(unsigned long long *, unsigned *, unsigned));
+static cudaError_t set_trace_this_unit(unsigned long long *buf, unsigned *cursor, unsigned cap) {
+  cudaError_t e = cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof(buf));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_cursor, &cursor, sizeof(cursor));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof(cap));
+  return e;
+}
+static struct TraceRegistrar { TraceRegistrar() { register_trace_setter(&set_trace_this_unit); } } g_trace_registrar;
+__device__ __forceinline__ void trace_stamp() {
+  if ((threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && g_trace_buf) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    const unsigned i = atomicAdd(g_trace_cursor, 1u);
+    if (i < g_trace_cap) g_trace_buf[i] = t;
+  }
+}
+#else
+__device__ __forceinline__ void trace_stamp() {}
+#endif
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  trace_stamp();
+}
 __device__ __forceinline__ void pdl_prologue() {
   pdl_launch_dependents();
   pdl_wait();

@@ -16,6 +16,8 @@ int analyse_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
   FML_REQUIRE(a->rank >= 2 && b->rank >= 2 && c->rank >= 2 && a->rank <= c->rank && b->rank <= c->rank,
               FML_BAD_ARG, "fml_gemm: operand ranks");
   const int r = c->rank;
+  p.prefetch = nullptr;
+  p.prefetch_bytes = 0;
   p.M = c->shape[r - 2];
   p.N = c->shape[r - 1];
   p.K = a->shape[a->rank - 1];
@@ -235,6 +237,12 @@ extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tens
   if (st != FML_OK) return st;
   if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
   GemmEpilogue e = make_epilogue(*gp, bias != nullptr, residual != nullptr);
+  if (gp->l2_prefetch && gp->l2_prefetch_bytes) {
+    FML_REQUIRE((reinterpret_cast<uintptr_t>(gp->l2_prefetch) & 15) == 0, FML_MISALIGNED,
+                "fml_gemm: the L2 prefetch hint must be 16-byte aligned");
+    p.prefetch = static_cast<const char *>(gp->l2_prefetch);
+    p.prefetch_bytes = gp->l2_prefetch_bytes;
+  }
   if (use_tc) return launch_gemm_tc(p, e, plan, as_stream(stream));
   if (skinny_eligible(p)) return launch_gemm_skinny(p, e, as_stream(stream));
   return launch_gemm_simt(p, e, as_stream(stream));

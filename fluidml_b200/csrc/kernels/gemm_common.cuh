@@ -16,6 +16,8 @@ struct GemmProblem {
   int64_t res_sm, res_sn, res_b0, res_b1;
   const float *a, *b, *bias, *res;
   float *c;
+  const char *prefetch;  // optional L2 prefetch hint (fml_gemm_params::l2_prefetch)
+  unsigned long long prefetch_bytes;
 };
 
 struct GemmEpilogue {

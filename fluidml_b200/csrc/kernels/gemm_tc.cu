@@ -246,6 +246,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   while ((int)tmem_cols < BN) tmem_cols <<= 1;
 
   pdl_launch_dependents();  // the next kernel may start its own set-up while this one runs
+  if (a.p.prefetch_bytes && threadIdx.x == 64) {
+    // Constant bytes a later launch will stream (the next weights): each CTA asks L2 to fetch
+    // its share now, before this kernel even waits for its own inputs.  Fire and forget.
+    const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    const unsigned long long cta = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    const unsigned long long share = ((a.p.prefetch_bytes + ctas - 1) / ctas + 127ull) & ~127ull;
+    const unsigned long long lo = cta * share, hi = min(a.p.prefetch_bytes & ~15ull, lo + share);
+    for (unsigned long long off = lo; off < hi; off += 16384ull) {
+      const unsigned n = (unsigned)min(16384ull, hi - off);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.p.prefetch + off), "r"(n) : "memory");
+    }
+  }
   if (threadIdx.x == 0) {
     TRACE(0);
     TRACE(8);

@@ -179,6 +179,18 @@ int fml_pad(const fml_tensor *in, const fml_tensor *out, const int64_t *pads_beg
 int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
                 const fml_tensor *out, int axis, void *stream);
 
+/* The attention core in one launch: out = softmax(Q K^T / divisor + mask) V, replacing the
+ * reference's MatMulKernel -> (Div, Add) -> SoftmaxKernel -> MatMulKernel sequence
+ * (matmul.cpp:5-44, softmax.cpp:22-139).  q [.., S_q, D], kt [.., D, S_k] (the transposed
+ * keys, as the MatMul receives them), v [.., S_k, D_v], out [.., S_q, D_v], ranks 2 to 4 with
+ * equal leading dims; mask (may be NULL) broadcasts to [.., S_q, S_k].  Any strides: the
+ * head-split transposes can stay views.  fp32 FMA throughout; the scores never leave the SM.
+ * fml_attention_supported tells whether a shape fits (head sizes multiples of 4 up to 128,
+ * K and V of one head in shared memory); fml_attention returns FML_UNSUPPORTED otherwise. */
+int fml_attention_supported(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v);
+int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fml_tensor *v,
+                  const fml_tensor *mask, float divisor, const fml_tensor *out, void *stream);
+
 /* LayerNormalizationConstantScaleBiasKernel (layer_normalization.cpp:33-220) in one pass:
  * mean, biased variance about the mean, y = (x-mean) * (1/sqrtf(var+eps)) * scale + bias.
  * With `residual` != NULL the input is in + residual (Add + LayerNorm fused).  No scratch
@@ -226,6 +238,13 @@ typedef struct fml_gemm_params {
   float act_param[3];
   int32_t split_k;     /* 0 = let the library choose; at most 8 (one cluster per tile)    */
   int32_t tile_n;      /* 0 = let the library choose; a multiple of 16 up to 256          */
+  /* Optional hint: constant device bytes (16-byte aligned) that a LATER launch on this stream
+   * will stream, typically the next layer's weights.  The tensor-core kernel asks L2 to fetch
+   * them while it runs, so the later launch finds them on chip instead of waiting on HBM,
+   * which is otherwise idle between the kernels of a batch-1 pass.  NULL / 0 = none.  The
+   * bytes must stay valid and unchanged; they are only read. */
+  const void *l2_prefetch;
+  uint64_t l2_prefetch_bytes;
 } fml_gemm_params;
 
 void fml_gemm_default_params(fml_gemm_params *p);

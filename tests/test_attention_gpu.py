@@ -1,0 +1,89 @@
+"""GPU parity of the fused attention core (`fml_attention`) against the oracle's unfused
+MatMul -> Div -> Add -> Softmax -> MatMul chain, through the C ABI.
+
+Tolerance: max|gpu - ref| / max|ref| <= 2e-5 (fp32 FMA on both sides; the summation order
+differs and the softmax goes through expf).
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from fluidml_b200 import cabi
+from fluidml_b200.cabi import DeviceTensor as DT
+from oracle import oracle as orc
+
+RNG = np.random.Generator(np.random.PCG64(314))
+TOL = 2e-5
+
+
+def rnd(*shape):
+    return RNG.standard_normal(shape).astype(np.float32)
+
+
+def oracle_attention(q, kt, v, mask, divisor):
+    sh = (*q.shape[:-1], kt.shape[-1])
+    s = orc.matmul(q, kt, np.empty(sh, np.float32))
+    s = (s / np.float32(divisor)).astype(np.float32)
+    if mask is not None:
+        s = (s + mask).astype(np.float32)
+    p = orc.softmax(np.ascontiguousarray(s), np.empty(sh, np.float32), axis=-1)
+    return orc.matmul(p, v, np.empty((*q.shape[:-1], v.shape[-1]), np.float32))
+
+
+def relerr(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(1e-30, np.abs(ref).max()))
+
+
+@pytest.mark.parametrize("shape", [  # (batch dims, S_q, S_k, D, D_v)
+    ((1, 12), 128, 128, 64, 64), ((2, 3), 37, 50, 8, 12), ((4,), 16, 160, 32, 128), ((), 5, 7, 4, 4),
+    ((1, 2), 130, 129, 128, 64),
+])
+@pytest.mark.parametrize("with_mask", [False, True])
+def test_attention_contiguous(shape, with_mask):
+    lead, sq, sk, d, dv = shape
+    q, kt, v = rnd(*lead, sq, d), rnd(*lead, d, sk), rnd(*lead, sk, dv)
+    mask = None
+    if with_mask:  # additive key mask, broadcast over heads and query rows
+        mask = np.where(RNG.random((*([1] * len(lead)), 1, sk)) < 0.2, -10000.0, 0.0).astype(np.float32)
+    assert cabi.attention_supported(sq, sk, d, dv)
+    out = DT((*lead, sq, dv), np.float32)
+    cabi.attention(DT.from_numpy(q), DT.from_numpy(kt), DT.from_numpy(v),
+                   DT.from_numpy(mask) if mask is not None else None, float(np.sqrt(d)), out)
+    cabi.check_device()
+    assert relerr(out.numpy(), oracle_attention(q, kt, v, mask, np.sqrt(d))) <= TOL
+
+
+def test_attention_on_head_strided_views():
+    """Q, K^T, V as views of the merged [S, 3H] projection; the context written head-interleaved
+    into [S, H], as the executor calls it for BERT."""
+    S, H, nh, hd = 128, 768, 12, 64
+    qkv = rnd(S, 3 * H)
+    src = DT.from_numpy(qkv)
+    q = src.view((1, nh, S, hd), [0, hd, 3 * H, 1], 0)
+    k_t = src.view((1, nh, hd, S), [0, hd, 1, 3 * H], H)
+    v = src.view((1, nh, S, hd), [0, hd, 3 * H, 1], 2 * H)
+    mask = np.where(RNG.random((1, 1, 1, S)) < 0.1, -10000.0, 0.0).astype(np.float32)
+    ctx = DT((S, H), np.float32)
+    cabi.attention(q, k_t, v, DT.from_numpy(mask), 8.0, ctx.view((1, nh, S, hd), [0, hd, H, 1], 0))
+    cabi.check_device()
+    qn = qkv[:, :H].reshape(S, nh, hd).transpose(1, 0, 2)[None]
+    kn = qkv[:, H:2 * H].reshape(S, nh, hd).transpose(1, 2, 0)[None]
+    vn = qkv[:, 2 * H:].reshape(S, nh, hd).transpose(1, 0, 2)[None]
+    ref = oracle_attention(*(np.ascontiguousarray(x) for x in (qn, kn, vn)), mask, 8.0)
+    assert relerr(ctx.numpy(), ref[0].transpose(1, 0, 2).reshape(S, H)) <= TOL
+
+
+def test_attention_generic_strides_and_limits():
+    # every operand stored with a permuted layout: no unit-stride fast path applies to Q and V
+    q, kt, v = rnd(2, 20, 16), rnd(2, 16, 24), rnd(2, 24, 8)
+    out = DT((2, 20, 8), np.float32, [2, 0, 1])
+    cabi.attention(DT.from_numpy(q, [1, 0, 2]), DT.from_numpy(kt, [2, 1, 0]), DT.from_numpy(v, [1, 0, 2]), None, 4.0, out)
+    cabi.check_device()
+    assert relerr(out.numpy(), oracle_attention(q, kt, v, None, 4.0)) <= TOL
+    assert not cabi.attention_supported(128, 128, 66, 64)      # head size not a multiple of 4
+    assert not cabi.attention_supported(128, 4096, 64, 64)     # K and V of a head exceed shared memory
+    with pytest.raises(cabi.FmlError) as e:
+        cabi.attention(DT.from_numpy(rnd(8, 6)), DT.from_numpy(rnd(6, 8)), DT.from_numpy(rnd(8, 4)), None, 1.0,
+                       DT((8, 4), np.float32))
+    assert e.value.status == 2

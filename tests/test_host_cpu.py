@@ -206,7 +206,9 @@ def test_fusion_passes_on_bert(bert_bytes):
     assert len(fused) < len(unfused)
     assert fused.count("FusedGemm") == 2 * 4 + 1          # merged qkv, o, ffn1, ffn2 per layer + pooler
     assert fused.count("Slice") == 2 * 3                  # q, k, v handed back as column slices
-    assert fused.count("FusedSoftmax") == 2 and "Softmax" not in fused
+    # scores MatMul + scaled masked softmax + context MatMul collapse into one node per layer
+    assert fused.count("FusedAttention") == 2 and "MatMul" not in fused
+    assert "FusedSoftmax" not in fused and "Softmax" not in fused
     assert "GatherConstantDataTensorAddTensorLhsAddTensorLhs" in fused and "UnsqueezeSubLhsScalarMulRhsScalar" in fused
     for gone in ("Erf", "DivConstantRhs", "AddCommon", "Tanh", "MulConstant"):
         assert gone not in fused, gone
