@@ -266,6 +266,13 @@ def gemm(a, b, c, bias=None, residual=None, params=None, stream=None):
     check(lib().fml_gemm(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual), ctypes.byref(params), stream))
 
 
+def gemm_skinny_noalloc(a, b, c, bias=None, residual=None, params=None, stream=None):
+    """fml_gemm_skinny_noalloc: at most 32 rows, scratch inside the module, nothing allocated."""
+    params = params or gemm_params()
+    check(lib().fml_gemm_skinny_noalloc(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual),
+                                        ctypes.byref(params), stream))
+
+
 def conv(x, w, bias, y, pads_begin, strides, dilations, group=1, act=ACT_NONE, stream=None):
     p = ConvParams()
     nd = len(pads_begin)

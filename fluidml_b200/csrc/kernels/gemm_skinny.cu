@@ -254,4 +254,73 @@ int launch_gemm_skinny(const GemmProblem &p, const GemmEpilogue &e, cudaStream_t
 
 size_t gemm_skinny_scratch_bytes(const GemmProblem &p) { return plan_skinny(p).scratch_bytes; }
 
+
+// ---- the same product for callers that cannot let the library allocate ---------------------
+//
+// Some hosts may not have device memory allocated on their behalf while they call in: a
+// serving loop that has handed all of HBM to its own pool, code that runs inside a section
+// where cudaMalloc's implicit device synchronisation is not acceptable, or an embedding that
+// audits every allocation.  fml_gemm's skinny path grows a cudaMalloc'ed scratch buffer on
+// demand; the entry point below keeps its split-K counters and partial sums in an array that
+// is part of the loaded module instead, so it never calls an allocating routine -- at the
+// price of a fixed capacity.
+constexpr size_t kStaticScratchBytes = 1 << 20;  // 64 KiB of tile counters + 960 KiB of partial sums
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices] = {nullptr};  // per device: where the array lives
+std::mutex g_static_mu;
+}  // namespace
+
 }  // namespace fml
+
+using namespace fml;
+
+// Declared in fluidml_cuda.h.  The first call on each device does the set-up: it asks the
+// runtime where this device's copy of the array is (a host-side symbol is not a device
+// address) and clears the counter region, which has to read zero when a launch starts
+// (every launch leaves it zero again).  That first call enqueues a memset and waits for it,
+// so make it before any stream capture.  All calls on one device share the one array: two
+// calls whose kernels can overlap (different streams, no ordering between them) race on it.
+extern "C" int fml_gemm_skinny_noalloc(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                                       const fml_tensor *bias, const fml_tensor *residual,
+                                       const fml_gemm_params *gp, void *stream) {
+  FML_REQUIRE(gp, FML_BAD_ARG, "fml_gemm_skinny_noalloc: null params");
+  FML_REQUIRE(gp->precision == FML_GEMM_AUTO || gp->precision == FML_GEMM_FP32, FML_UNSUPPORTED,
+              "fml_gemm_skinny_noalloc: computes in fp32 FMA only");
+  GemmProblem p;
+  int st = analyse_gemm(a, b, c, bias, residual, p);
+  if (st != FML_OK) return st;
+  if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
+  FML_REQUIRE(skinny_eligible(p), FML_UNSUPPORTED,
+              "fml_gemm_skinny_noalloc: needs 1 <= M <= %d rows and K >= 1 (M = %lld, K = %lld)", kMaxM,
+              (long long)p.M, (long long)p.K);
+  const SkinnyPlan pl = plan_skinny(p);
+  FML_REQUIRE(pl.scratch_bytes <= kStaticScratchBytes, FML_OUT_OF_MEMORY,
+              "fml_gemm_skinny_noalloc: this product needs %zu bytes of split-K scratch, the built-in "
+              "buffer holds %zu; use fml_gemm", pl.scratch_bytes, kStaticScratchBytes);
+  GemmEpilogue e;
+  e.divisor = gp->divisor == 0.0f ? 1.0f : gp->divisor;
+  e.alpha = gp->alpha; e.beta = gp->beta; e.act = gp->act;
+  e.c0 = gp->act_param[0]; e.c1 = gp->act_param[1]; e.c2 = gp->act_param[2];
+  e.has_bias = bias != nullptr; e.has_res = residual != nullptr;
+  cudaStream_t s = as_stream(stream);
+  int dev = 0;
+  FML_CUDA(cudaGetDevice(&dev));
+  FML_REQUIRE(dev >= 0 && dev < kMaxDevices, FML_BAD_ARG, "fml_gemm_skinny_noalloc: device ordinal %d out of range", dev);
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_scratch_addr[dev]) {
+      void *addr = nullptr;
+      FML_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
+      FML_REQUIRE(addr != nullptr, FML_CUDA_ERROR, "fml_gemm_skinny_noalloc: no device address for the scratch array");
+      FML_CUDA(cudaMemsetAsync(addr, 0, kCounterBytes, s));
+      FML_CUDA(cudaStreamSynchronize(s));  // set-up is complete when this call returns
+      g_static_scratch_addr[dev] = addr;
+    }
+    scratch = g_static_scratch_addr[dev];
+  }
+  return launch_skinny(p, e, pl, scratch, s);
+}

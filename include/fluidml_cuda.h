@@ -276,6 +276,20 @@ int fml_gemm_autotune(const fml_tensor *a, const fml_tensor *b, const fml_tensor
                       const fml_tensor *bias, const fml_tensor *residual, const fml_gemm_params *p,
                       void *stream, fml_gemm_params *tuned);
 
+/* fml_gemm for products with 1 <= M <= 32 rows, for callers that cannot let the library
+ * allocate device memory (no counterpart in the reference, which has no device side).  Same
+ * arguments and results as fml_gemm with precision FP32 (AUTO is accepted and means FP32).
+ * The split-K scratch is an array inside the loaded module: 1 MiB per device, of which
+ * 960 KiB hold partial sums; a product that needs more (roughly splits * M * N * 4 bytes with
+ * N rounded up to 32) fails with FML_OUT_OF_MEMORY and a message -- use fml_gemm then.  No
+ * allocating CUDA routine is called.  The first call on each device looks up the array's
+ * device address and clears its counters; make that call outside any stream capture.  Calls
+ * on one device share the array: calls whose kernels may overlap (different streams without
+ * ordering, several threads) race on it and must be serialised by the caller. */
+int fml_gemm_skinny_noalloc(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
+                            const fml_tensor *bias, const fml_tensor *residual,
+                            const fml_gemm_params *p, void *stream);
+
 /* Reports which path fml_gemm would take for these operands: 0 = fp32 FMA, 1 = tcgen05. */
 int fml_gemm_uses_tensor_cores(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
                                const fml_gemm_params *p, int *uses);
