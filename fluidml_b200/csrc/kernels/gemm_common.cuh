@@ -63,6 +63,7 @@ struct TcPlan {
   int stages;
   int b_mn_major; // 0: B tile is K-major (b_sk == 1), 1: MN-major (b_sn == 1)
   int three_pass; // 1: 3xTF32, 0: single TF32
+  int a_tmem;     // 3xTF32 only: A's hi / lo parts live in tensor memory instead of shared memory
   size_t smem_bytes;
   size_t partial_bytes, counter_bytes;
 };

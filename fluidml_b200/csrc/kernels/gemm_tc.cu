@@ -51,7 +51,7 @@ constexpr size_t kSmemBudget = 200 * 1024;
 struct TcArgs {
   GemmProblem p;
   GemmEpilogue e;
-  int tile_n, split_k, stages, b_mn_major, three_pass;
+  int tile_n, split_k, stages, b_mn_major, three_pass, a_tmem;
   int tiles_m, tiles_n, kb_total, kb_per_split;
   int *status;
   unsigned long long *trace;  // optional: 16 stamps per CTA (fml_debug_set_gemm_trace)
@@ -129,6 +129,28 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Same with the A operand read from tensor memory (lane = row, one 32-bit column per k value).
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane, written from registers.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                ::"r"(bar) : "memory");
@@ -207,7 +229,7 @@ __device__ __forceinline__ float act_op(const GemmEpilogue &e, float v) {
 // ---------------------------------------------------------------- kernel
 // THREE_PASS / B_MN are compile-time so that each variant carries only its own code: the kernel
 // runs every phase once per CTA, and instruction fetch of cold code is a first-order cost.
-template <bool THREE_PASS, bool B_MN, int ACT>
+template <bool THREE_PASS, bool B_MN, int ACT, bool A_TMEM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcArgs a) {
@@ -220,7 +242,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int pitch = BN + 4;  // staging row pitch in floats: rows 16 bytes apart modulo 128, so the
                              // 16-byte row-wise writes of a quarter-warp hit distinct banks
   const uint32_t b_bytes = (uint32_t)BN * kBK * 4;
-  const uint32_t stage_bytes = (kABytes + b_bytes) * (THREE_PASS ? 2 : 1);
+  // A_TMEM (3xTF32 only): the converter puts A's hi and lo parts into tensor memory instead of
+  // writing a lo copy to shared memory, and the MMAs read A from there: shared-memory traffic
+  // per k block drops from (TMA 24 + split 48 + MMA 72) KiB to (24 + 32 + 24) KiB at tile_n 64,
+  // and a stage shrinks to A | B | B_lo, so more stages fit.
+  const uint32_t stage_bytes = A_TMEM ? kABytes + 2 * b_bytes : (kABytes + b_bytes) * (THREE_PASS ? 2 : 1);
   // [ pipeline stages (reused as the epilogue staging tile) | barriers | flags ]
   const size_t ring_bytes = (size_t)a.stages * stage_bytes;
   const size_t staging_bytes = ((size_t)kBM * pitch * 4 + 1023) / 1024 * 1024;
@@ -242,8 +268,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int kb0 = min(a.kb_total, split * a.kb_per_split);
   const int kb1 = min(a.kb_total, kb0 + a.kb_per_split);
   const int nkb = kb1 - kb0;  // may be 0 for the last ranks of a cluster
+  // TMEM columns: the accumulator tile, then (A_TMEM) 64 per stage: 32 of A hi, 32 of A lo
+  const uint32_t a_col0 = ((uint32_t)BN + 31u) & ~31u;
+  const uint32_t tmem_need = A_TMEM ? a_col0 + 64u * (uint32_t)a.stages : (uint32_t)BN;
   uint32_t tmem_cols = 32;
-  while ((int)tmem_cols < BN) tmem_cols <<= 1;
+  while (tmem_cols < tmem_need) tmem_cols <<= 1;
 
   pdl_launch_dependents();  // the next kernel may start its own set-up while this one runs
   if (a.p.prefetch_bytes && threadIdx.x == 64) {
@@ -327,7 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint64_t desc_a = smem_desc(tiles_base, 16u, 1024u);
       const uint64_t desc_b = smem_desc(tiles_base + kABytes, b_lbo, b_sbo, b_type);
       const uint64_t desc_al = smem_desc(tiles_base + kABytes + b_bytes, 16u, 1024u);
-      const uint64_t desc_bl = smem_desc(tiles_base + 2 * kABytes + b_bytes, b_lbo, b_sbo, b_type);
+      const uint64_t desc_bl = smem_desc(tiles_base + (A_TMEM ? kABytes + b_bytes : 2 * kABytes + b_bytes), b_lbo, b_sbo, b_type);
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         const int s = it % a.stages;
@@ -348,7 +377,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t bj = soff + (B_MN ? (uint32_t)j * 64u : (uint32_t)j * 2u);
           const uint64_t da = desc_a + aj, db = desc_b + bj;
           const uint32_t first = (it == 0 && j == 0) ? 0u : 1u;
-          if (THREE_PASS) {
+          if (A_TMEM) {
+            const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)s * 64u + (uint32_t)j * 8u, a_lo = a_hi + 32u;
+            const uint64_t dbl = desc_bl + bj;
+            umma_tf32_ts(tmem_base, a_lo, db, idesc, first);
+            umma_tf32_ts(tmem_base, a_hi, dbl, idesc, 1u);
+            umma_tf32_ts(tmem_base, a_hi, db, idesc, 1u);
+          } else if (THREE_PASS) {
             const uint64_t dal = desc_al + aj, dbl = desc_bl + bj;
             umma_tf32(tmem_base, dal, db, idesc, first);
             umma_tf32(tmem_base, da, dbl, idesc, 1u);
@@ -382,7 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint4 *hi_a = reinterpret_cast<uint4 *>(st);
         uint4 *hi_b = reinterpret_cast<uint4 *>(st + kABytes);
         uint4 *lo_a = reinterpret_cast<uint4 *>(st + kABytes + b_bytes);
-        uint4 *lo_b = reinterpret_cast<uint4 *>(st + 2 * kABytes + b_bytes);
+        uint4 *lo_b = reinterpret_cast<uint4 *>(st + (A_TMEM ? kABytes + b_bytes : 2 * kABytes + b_bytes));
         // kind::tf32 reads the upper 19 bits of each fp32 operand and ignores the rest
         // (checked on the device: masking the low 13 bits beforehand changes no output bit), so
         // the tile TMA delivered already is the "hi" operand; only lo = x - hi is written.
@@ -394,7 +429,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           lo.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xffffe000u));
           return lo;
         };
-        {  // A: 1024 16-byte units over 128 threads = 8 each; loads first so latencies overlap
+        if (A_TMEM) {
+          // This thread owns row (warp & 3) * 32 + lane of the A tile = the TMEM lane its warp may
+          // write.  The row is 128 bytes whose 16-byte chunks TMA swizzled by (row & 7).
+          const int q = warp & 3, row = q * 32 + lane, swz = row & 7;
+          const uint4 *src = reinterpret_cast<const uint4 *>(st + row * 128);
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 x = src[c ^ swz];
+            const uint4 l = lo4(x);
+            hi[4 * c + 0] = x.x & 0xffffe000u; hi[4 * c + 1] = x.y & 0xffffe000u;
+            hi[4 * c + 2] = x.z & 0xffffe000u; hi[4 * c + 3] = x.w & 0xffffe000u;
+            lo[4 * c + 0] = l.x; lo[4 * c + 1] = l.y; lo[4 * c + 2] = l.z; lo[4 * c + 3] = l.w;
+          }
+          const uint32_t t_hi = tmem_base + ((uint32_t)(q * 32) << 16) + a_col0 + (uint32_t)s * 64u;
+          tmem_st32(t_hi, hi);
+          tmem_st32(t_hi + 32u, lo);
+        } else {  // A: 1024 16-byte units over 128 threads = 8 each; loads first so latencies overlap
           uint4 x[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) x[j] = hi_a[et + 128 * j];
@@ -409,6 +461,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             if (base + et + 128 * j < b_vec) lo_b[base + et + 128 * j] = lo4(x[j]);
+        }
+        if (A_TMEM) {
+          tmem_wait_st();
+          tc_fence_before();
         }
         fence_async_smem();  // make the generic-proxy writes visible to the tensor core
         __syncwarp();
@@ -623,8 +679,19 @@ int make_map(CUtensorMap *map, const float *base, int64_t inner, int64_t rows, i
 
 bool stride_ok(int64_t s) { return s == 0 || (s > 0 && s % 4 == 0); }
 
-size_t smem_for(int tile_n, int stages, int three_pass) {
-  const size_t stage = (size_t)(kABytes + tile_n * kBK * 4) * (three_pass ? 2 : 1);
+size_t stage_bytes_for(int tile_n, int three_pass, int a_tmem) {
+  const size_t b = (size_t)tile_n * kBK * 4;
+  return a_tmem ? kABytes + 2 * b : (kABytes + b) * (three_pass ? 2 : 1);
+}
+
+// 3xTF32 keeps A's hi / lo parts in tensor memory unless FLUIDML_GEMM_A_TMEM=0.
+bool a_tmem_default() {
+  static const bool on = [] { const char *e = getenv("FLUIDML_GEMM_A_TMEM"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+size_t smem_for(int tile_n, int stages, int three_pass, int a_tmem) {
+  const size_t stage = stage_bytes_for(tile_n, three_pass, a_tmem);
   const size_t staging = ((size_t)kBM * (tile_n + 4) * 4 + 1023) / 1024 * 1024;
   const size_t data = std::max(stage * stages, staging);
   return data + (3 * stages + 1) * 8 + 16 + 1024;
@@ -652,6 +719,7 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
 
   plan.b_mn_major = mn;
   plan.three_pass = gp.precision == FML_GEMM_TF32 ? 0 : 1;
+  plan.a_tmem = plan.three_pass && a_tmem_default() ? 1 : 0;
   const int kb_total = (int)((p.K + kBK - 1) / kBK);
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
 
@@ -672,7 +740,7 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
     for (int si = 0; si < 4; ++si) {
       int sk = gp.split_k ? gp.split_k : sk_opts[si];
       if (sk > kb_total) continue;
-      if (smem_for(tn, 1, plan.three_pass) > kSmemBudget + 8192) continue;
+      if (smem_for(tn, 1, plan.three_pass, plan.a_tmem) > kSmemBudget + 8192) continue;
       const int64_t tiles = tiles_m * ((p.N + tn - 1) / tn) * batch;
       const int64_t ctas = tiles * sk;
       const int cap = sk <= 1 ? 148 : sk <= 2 ? sk_cap[1] : sk <= 4 ? sk_cap[2] : sk_cap[3];
@@ -696,11 +764,23 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
   plan.split_k = best_sk;
   if (plan.split_k > 8) return false;  // one cluster holds a tile's splits
   const int per = (kb_total + plan.split_k - 1) / plan.split_k;
-  const size_t stage = (size_t)(kABytes + plan.tile_n * kBK * 4) * (plan.three_pass ? 2 : 1);
+  const size_t stage = stage_bytes_for(plan.tile_n, plan.three_pass, plan.a_tmem);
   int stages = (int)(kSmemBudget / stage);
   stages = std::max(1, std::min(std::min(stages, 8), per));
+  if (plan.a_tmem)  // 64 TMEM columns per stage beside the accumulator tile, 512 in all
+    stages = std::max(1, std::min(stages, (512 - ((plan.tile_n + 31) / 32 * 32)) / 64));
   plan.stages = stages;
-  plan.smem_bytes = smem_for(plan.tile_n, stages, plan.three_pass);
+  plan.smem_bytes = smem_for(plan.tile_n, stages, plan.three_pass, plan.a_tmem);
+  {
+    // Never let more CTAs share an SM than its 512 TMEM columns can serve at once: a CTA that
+    // had to wait inside tcgen05.alloc for a neighbour could hold up its whole cluster.  The
+    // shared-memory request is what limits co-residency, so it is padded where needed.
+    unsigned need = plan.a_tmem ? (unsigned)((plan.tile_n + 31) / 32 * 32 + 64 * stages) : (unsigned)plan.tile_n, cols = 32;
+    while (cols < need) cols <<= 1;
+    const size_t fit = 512 / cols;  // CTAs whose TMEM fits together
+    const size_t floor_bytes = (size_t)(228 * 1024) / (fit + 1) + 1024;
+    if (plan.smem_bytes < floor_bytes) plan.smem_bytes = floor_bytes;
+  }
   if (plan.smem_bytes > 227 * 1024) return false;
   plan.partial_bytes = 0;
   plan.counter_bytes = 0;
@@ -711,7 +791,7 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
   TcArgs a;
   a.p = p; a.e = e;
   a.tile_n = plan.tile_n; a.split_k = plan.split_k; a.stages = plan.stages;
-  a.b_mn_major = plan.b_mn_major; a.three_pass = plan.three_pass;
+  a.b_mn_major = plan.b_mn_major; a.three_pass = plan.three_pass; a.a_tmem = plan.a_tmem;
   a.tiles_m = (int)((p.M + kBM - 1) / kBM);
   a.tiles_n = (int)((p.N + plan.tile_n - 1) / plan.tile_n);
   a.kb_total = (int)((p.K + kBK - 1) / kBK);
@@ -731,15 +811,17 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (st != FML_OK) return st;
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const TcArgs);
-#define FML_TC_ROW(T, M)                                                                  \
-  gemm_tc_kernel<T, M, FML_ACT_NONE>, gemm_tc_kernel<T, M, FML_ACT_GELU_ERF>,             \
-  gemm_tc_kernel<T, M, FML_ACT_RELU>, gemm_tc_kernel<T, M, FML_ACT_TANH>,                 \
-  gemm_tc_kernel<T, M, FML_ACT_SIGMOID>
-  static const KernelFn kernels[20] = {FML_TC_ROW(false, false), FML_TC_ROW(false, true),
-                                       FML_TC_ROW(true, false), FML_TC_ROW(true, true)};
+#define FML_TC_ROW(T, M, A)                                                               \
+  gemm_tc_kernel<T, M, FML_ACT_NONE, A>, gemm_tc_kernel<T, M, FML_ACT_GELU_ERF, A>,       \
+  gemm_tc_kernel<T, M, FML_ACT_RELU, A>, gemm_tc_kernel<T, M, FML_ACT_TANH, A>,           \
+  gemm_tc_kernel<T, M, FML_ACT_SIGMOID, A>
+  static const KernelFn kernels[30] = {FML_TC_ROW(false, false, false), FML_TC_ROW(false, true, false),
+                                       FML_TC_ROW(true, false, false),  FML_TC_ROW(true, true, false),
+                                       FML_TC_ROW(true, false, true),   FML_TC_ROW(true, true, true)};
 #undef FML_TC_ROW
   const int act = (e.act >= 0 && e.act <= FML_ACT_SIGMOID) ? e.act : 0;
-  const KernelFn kernel = kernels[((plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0)) * 5 + act];
+  const int row = plan.a_tmem ? 4 + (plan.b_mn_major ? 1 : 0) : (plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0);
+  const KernelFn kernel = kernels[row * 5 + act];
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
