@@ -46,7 +46,7 @@ class GemmParams(ctypes.Structure):
     _fields_ = [("precision", ctypes.c_int32), ("act", ctypes.c_int32),
                 ("divisor", ctypes.c_float), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("act_param", ctypes.c_float * 3), ("split_k", ctypes.c_int32),
-                ("tile_n", ctypes.c_int32), ("l2_prefetch", ctypes.c_void_p),
+                ("tile_n", ctypes.c_int32), ("b_constant", ctypes.c_int32), ("l2_prefetch", ctypes.c_void_p),
                 ("l2_prefetch_bytes", ctypes.c_uint64)]
 
 

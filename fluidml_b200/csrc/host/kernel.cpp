@@ -502,6 +502,7 @@ public:
     fml_tensor a, b, bias{}, res{};
     Resolve(in, a, b, bias, res);
     Config c = c_;
+    c.params.b_constant = c.has_const_b ? 1 : 0;
     if (c.autotune) {  // device buffers are live while the builder records: try the candidates now
       fml_gemm_params tuned;
       if (fml_gemm_autotune(&a, &b, &output, c.has_bias ? &bias : nullptr, c.has_residual ? &res : nullptr,

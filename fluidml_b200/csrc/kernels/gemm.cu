@@ -18,6 +18,7 @@ int analyse_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c,
   const int r = c->rank;
   p.prefetch = nullptr;
   p.prefetch_bytes = 0;
+  p.b_constant = 0;
   p.M = c->shape[r - 2];
   p.N = c->shape[r - 1];
   p.K = a->shape[a->rank - 1];
@@ -237,6 +238,7 @@ extern "C" int fml_gemm(const fml_tensor *a, const fml_tensor *b, const fml_tens
   if (st != FML_OK) return st;
   if (p.M == 0 || p.N == 0 || p.nb0 * p.nb1 == 0) return FML_OK;
   GemmEpilogue e = make_epilogue(*gp, bias != nullptr, residual != nullptr);
+  p.b_constant = gp->b_constant ? 1 : 0;
   if (gp->l2_prefetch && gp->l2_prefetch_bytes) {
     FML_REQUIRE((reinterpret_cast<uintptr_t>(gp->l2_prefetch) & 15) == 0, FML_MISALIGNED,
                 "fml_gemm: the L2 prefetch hint must be 16-byte aligned");

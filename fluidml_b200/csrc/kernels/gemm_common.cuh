@@ -18,6 +18,7 @@ struct GemmProblem {
   float *c;
   const char *prefetch;  // optional L2 prefetch hint (fml_gemm_params::l2_prefetch)
   unsigned long long prefetch_bytes;
+  int b_constant;  // B is not written by earlier launches on the stream (fml_gemm_params::b_constant)
 };
 
 struct GemmEpilogue {

@@ -304,8 +304,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Barriers, TMEM and descriptors are ready; nothing has touched global memory yet.  From here
-  // on the preceding kernel's results are needed (and its inputs may be overwritten).
+  // Barriers, TMEM and descriptors are ready.  Weights do not depend on the preceding kernel:
+  // with a constant B the producer fills the B half of the first stages right away, so that
+  // HBM latency overlaps the tail of that kernel; the A halves follow after the wait.
+  int pre_b = 0;
+  if (a.p.b_constant && warp == 0 && lane == 0) {
+    const int cb2 = a.p.b_b0 ? z0 : 0, cb3 = a.p.b_b1 ? z1 : 0;
+    pre_b = min(a.stages, nkb);
+    for (int it = 0; it < pre_b; ++it) {
+      const uint32_t sb = tiles_base + (uint32_t)it * stage_bytes + kABytes;
+      const int k = (kb0 + it) * kBK;
+      mbar_expect_tx(bar_full + 8u * it, kABytes + b_bytes);
+      if (!B_MN) {
+        tma_load_4d(sb, &map_b, bar_full + 8u * it, k, tile_n * BN, cb2, cb3);
+      } else {
+        for (int g = 0; g < BN / 32; ++g)
+          tma_load_4d(sb + (uint32_t)g * (kBK * 128), &map_b, bar_full + 8u * it, tile_n * BN + g * 32, k, cb2, cb3);
+      }
+    }
+  }
+  // From here on the preceding kernel's results are needed (and its inputs may be overwritten).
   pdl_wait();
   if (threadIdx.x == 0) TRACE(1);
 
@@ -319,10 +337,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int it = 0; it < nkb && ok; ++it) {
         const int s = it % a.stages;
         const uint32_t ph = (uint32_t)(it / a.stages) & 1u;
-        ok = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag);
-        if (!ok) break;
         const uint32_t sa = tiles_base + (uint32_t)s * stage_bytes, sb = sa + kABytes;
         const int k = (kb0 + it) * kBK;
+        if (it < pre_b) {  // B of this stage is already on its way, the byte count already posted
+          tma_load_4d(sa, &map_a, bar_full + 8u * s, k, tile_m * kBM, ca2, ca3);
+          ++issued;
+          continue;
+        }
+        ok = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag);
+        if (!ok) break;
         mbar_expect_tx(bar_full + 8u * s, kABytes + b_bytes);
         tma_load_4d(sa, &map_a, bar_full + 8u * s, k, tile_m * kBM, ca2, ca3);
         if (!B_MN) {

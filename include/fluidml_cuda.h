@@ -238,6 +238,9 @@ typedef struct fml_gemm_params {
   float act_param[3];
   int32_t split_k;     /* 0 = let the library choose; at most 8 (one cluster per tile)    */
   int32_t tile_n;      /* 0 = let the library choose; a multiple of 16 up to 256          */
+  int32_t b_constant;  /* non-zero: B holds weights that no earlier launch on the stream
+                        * writes, so the kernel may load its first B tiles while the
+                        * preceding kernel is still finishing                              */
   /* Optional hint: constant device bytes (16-byte aligned) that a LATER launch on this stream
    * will stream, typically the next layer's weights.  The tensor-core kernel asks L2 to fetch
    * them while it runs, so the later launch finds them on chip instead of waiting on HBM,
