@@ -273,15 +273,25 @@ def gemm_skinny_noalloc(a, b, c, bias=None, residual=None, params=None, stream=N
                                         ctypes.byref(params), stream))
 
 
-def conv(x, w, bias, y, pads_begin, strides, dilations, group=1, act=ACT_NONE, stream=None):
+def conv(x, w, bias, y, pads_begin, strides, dilations, group=1, act=ACT_NONE, stream=None, precision=None):
     p = ConvParams()
     nd = len(pads_begin)
     for i in range(2):
         p.pads_begin[i] = pads_begin[i] if i < nd else 0
         p.strides[i] = strides[i] if i < nd else 1
         p.dilations[i] = dilations[i] if i < nd else 1
-    p.group, p.act, p.precision = group, act, GEMM_AUTO
+    p.group, p.act, p.precision = group, act, GEMM_AUTO if precision is None else precision
     check(lib().fml_conv(_ref(x), _ref(w), _ref(bias), _ref(y), ctypes.byref(p), stream))
+
+
+def conv_uses_tensor_cores(x, w, y, pads_begin, precision=None) -> bool:
+    p = ConvParams()
+    for i in range(2):
+        p.pads_begin[i], p.strides[i], p.dilations[i] = pads_begin[i], 1, 1
+    p.group, p.precision = 1, GEMM_AUTO if precision is None else precision
+    uses = ctypes.c_int()
+    check(lib().fml_conv_uses_tensor_cores(_ref(x), _ref(w), _ref(y), ctypes.byref(p), ctypes.byref(uses)))
+    return bool(uses.value)
 
 
 def pool2d(x, y, mode, kernel, strides, stream=None):

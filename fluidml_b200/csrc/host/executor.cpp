@@ -2,6 +2,7 @@
 // (include/fluidml_executor.h).  Compile = Parser -> Converter -> fusion passes ->
 // TopologicalSort -> (DP layout search) -> lowering -> memory plan -> Builder -> Runner,
 // the same stage order as src/worker/executor.cpp:91-133.
+#include <algorithm>
 #include "worker/executor.h"
 #include "converter.h"
 #include "dp.h"
@@ -135,6 +136,17 @@ private:
         if (plan.HasLayout(r->name)) r->layout = plan.GetLayout(r->name);
       dp_json = table.ToJson();
       plan_json = plan.ToJson();
+    }
+
+    // Convolution weights the tensor-core kernel can take are baked tap-major with the output
+    // channel innermost ([KH][KW][IC][OC]): layout (3, 2, 0, 1) of the OIHW constant.  The
+    // CUDA-core kernel reads any strides, so the choice is safe whichever path runs.
+    for (const auto &n : sequence.nodes) {
+      if (n->kind != flow::Kind::ConvWithPadding && n->kind != flow::Kind::ConvWithoutPadding) continue;
+      if (n->group != 1 || n->consts.empty() || n->consts[0]->meta.GetRank() != 4) continue;
+      const auto unit = [](const std::vector<int64_t> &v) { return std::all_of(v.begin(), v.end(), [](int64_t x) { return x == 1; }); };
+      if (!unit(n->strides) || !unit(n->dilations)) continue;
+      n->consts[0]->layout = {3, 2, 0, 1};
     }
 
     kernel::KernelOptions ko;

@@ -186,6 +186,7 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
   const int64_t M = a.N * a.OH * a.OW;
   if (M == 0 || a.OC == 0) return FML_OK;
   cudaStream_t s = as_stream(stream);
+  if (group == 1 && nd == 2 && conv_tc_eligible(x, w, y, p)) return launch_conv_tc(x, w, bias, y, p, s);
   if (group == 1) {
     FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");
     dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));
@@ -195,6 +196,16 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     FML_LAUNCH((conv_depthwise_kernel), grid_for(M * a.OC, 256), 256, 0, s, a);
   }
   FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_conv_uses_tensor_cores(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y,
+                                          const fml_conv_params *p, int *uses) {
+  FML_REQUIRE(valid_tensor(x) && valid_tensor(w) && valid_tensor(y) && p && uses, FML_BAD_ARG,
+              "fml_conv_uses_tensor_cores: bad argument");
+  *uses = x->rank == 4 && w->rank == 4 && y->rank == 4 && x->dtype == FML_F32 && w->dtype == FML_F32 &&
+                  y->dtype == FML_F32 && p->group <= 1 && conv_tc_eligible(x, w, y, p)
+              ? 1 : 0;
   return FML_OK;
 }
 

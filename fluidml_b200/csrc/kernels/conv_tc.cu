@@ -1,0 +1,446 @@
+// Implicit-GEMM convolution on tcgen05 for sm_100a: M = output positions (a TH x TW patch of
+// one image = 128 rows), N = output channels, K = (tap, input channel).  Replaces the loop
+// nest the reference generates for ConvWithoutPaddingKernel / ConvWithPaddingKernel
+// (src/structure/kernel/kernel/conv.cpp:27-280) for unit-stride, undilated, group-1 2-D
+// convolutions in NCHW; everything else stays on the CUDA-core kernels of conv.cu.
+//
+// What makes it "implicit": the input is read once per input-channel block as a raw patch
+// of (TH + KH - 1) x (TW + KW - 1, widened to 16-byte steps) pixels x ICB channels by ONE TMA
+// box load -- out-of-range rows and columns come back as zeros, which is the padding -- and
+// the KH*KW shifted A tiles are cut out of that patch on chip: each converter thread owns one
+// output position (= one TMEM lane), gathers its ICB channel values for the tap from shared
+// memory and writes them (split into TF32 hi / lo parts) into tensor memory, from where the
+// MMAs read A.  A shifted window can not be loaded by TMA directly: the innermost coordinate
+// of a tile load must be a multiple of 16 bytes and the taps shift by single pixels.
+//
+// When the image rows are not a multiple of 16 bytes long (14 x 14 feature maps) no box with
+// the row as its second dimension can be described to TMA; if the tile spans the full width the
+// patch is then loaded as one run of the flattened H*W plane ("flat mode": whole rows, start
+// rounded down to a 16-byte step, rows above and below the image still zero-filled by TMA) and
+// the missing left / right padding columns are masked in the gather.
+//
+// Weights are expected tap-major with the output channel innermost ([KH][KW][IC][OC], i.e.
+// the OIHW tensor stored with layout permutation (3, 2, 0, 1)): the B tile of a (tap, channel
+// block) is then an MN-major box, loaded exactly like the GEMM's MN-major B.
+//
+// Roles (192 threads) and the bounded waits are those of the GEMM kernel (gemm_tc.cu).
+#include "gemm_common.cuh"
+#include "tc_common.cuh"
+#include <algorithm>
+
+namespace fml {
+namespace {
+
+constexpr int kThreads = 192;
+constexpr size_t kSmemBudget = 200 * 1024;
+
+struct ConvTcArgs {
+  int N, IC, OC, OH, OW, KH, KW, ph, pw;
+  int TW, TH, PWD, PHT, xoff;  // tile geometry: patch PHT rows x PWD columns per channel
+  int flat, IW, plane, raw_elems;  // flat mode: the patch is a run of whole image rows (see below)
+  int n_icb, taps, tile_n, stages, raw_stages;
+  int tiles_w, tiles_h;
+  int64_t ys[4];
+  float *y;
+  const float *bias;
+  int64_t bias_stride;
+  int act;
+  int *status;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t *r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+__device__ __forceinline__ float conv_act(int act, float v) {
+  switch (act) {
+  case FML_ACT_RELU: return fmaxf(v, 0.0f);
+  case FML_ACT_TANH: return tanhf(v);
+  case FML_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+  default: return v;
+  }
+}
+
+// ICB: input channels per k block (32, or 8 for the first layer's few channels).
+template <bool THREE_PASS, int ICB, bool FLAT>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const ConvTcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int BN = a.tile_n, NS = a.stages, RS = a.raw_stages;
+  const uint32_t b_bytes = (uint32_t)ICB * BN * 4;
+  const uint32_t stage_bytes = b_bytes * (THREE_PASS ? 2 : 1);
+  const uint32_t raw_bytes = (uint32_t)(a.raw_elems * ICB) * 4;
+  const uint32_t raw_pitch = (raw_bytes + 127u) & ~127u;
+  // [ B stages | raw patches | barriers | flags ]
+  const uint32_t b_base = smem_u32(smem);
+  uint8_t *raw_ptr = smem + (size_t)NS * stage_bytes;
+  const uint32_t raw_base = smem_u32(raw_ptr);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ptr + (size_t)RS * raw_pitch);
+  const uint32_t bar_bfull = smem_u32(bars);
+  const uint32_t bar_ready = bar_bfull + 8u * NS;
+  const uint32_t bar_empty = bar_ready + 8u * NS;
+  const uint32_t bar_rfull = bar_empty + 8u * NS;
+  const uint32_t bar_rempty = bar_rfull + 8u * RS;
+  const uint32_t bar_accum = bar_rempty + 8u * RS;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * NS + 2 * RS + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int t = blockIdx.x;
+  const int tw = t % a.tiles_w; t /= a.tiles_w;
+  const int th = t % a.tiles_h; t /= a.tiles_h;
+  const int n = t;
+  const int oc0 = blockIdx.y * BN;
+  const int oh0 = th * a.TH, ow0 = tw * a.TW;
+  const int total_kb = a.n_icb * a.taps;
+  const uint32_t a_col0 = ((uint32_t)BN + 31u) & ~31u;
+  const uint32_t a_cols = THREE_PASS ? 2u * ICB : (uint32_t)ICB;  // per stage: hi [, lo]
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < a_col0 + a_cols * (uint32_t)NS) tmem_cols <<= 1;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar_bfull + 8u * s, 1);
+      mbar_init(bar_ready + 8u * s, 4);
+      mbar_init(bar_empty + 8u * s, 1);
+    }
+    for (int s = 0; s < RS; ++s) {
+      mbar_init(bar_rfull + 8u * s, 1);
+      mbar_init(bar_rempty + 8u * s, 4);
+    }
+    mbar_init(bar_accum, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      int kb = 0;
+      for (int icb = 0; icb < a.n_icb && ok; ++icb) {
+        const int rs = icb % RS;
+        ok = mbar_wait(bar_rempty + 8u * rs, (((uint32_t)(icb / RS)) & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bar_rfull + 8u * rs, raw_bytes);
+        // x = ow0 - pw - xoff is a multiple of 4 by construction; rows / columns / channels outside
+        // the image are filled with zeros: the padding, and the channel tail of the last block
+        if (!FLAT)
+          tma_load_4d(raw_base + (uint32_t)rs * raw_pitch, &map_x, bar_rfull + 8u * rs, ow0 - a.pw - a.xoff,
+                      oh0 - a.ph, icb * ICB, n);
+        else  // whole rows from (oh0 - ph) on, as one run of the flattened H*W plane
+          tma_load_3d(raw_base + (uint32_t)rs * raw_pitch, &map_x, bar_rfull + 8u * rs,
+                      (oh0 - a.ph) * a.IW - a.pw - a.xoff, icb * ICB, n);
+        for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
+          const int s = kb % NS;
+          ok = mbar_wait(bar_empty + 8u * s, (((uint32_t)(kb / NS)) & 1u) ^ 1u, abort_flag);
+          if (!ok) break;
+          const uint32_t sb = b_base + (uint32_t)s * stage_bytes;
+          mbar_expect_tx(bar_bfull + 8u * s, b_bytes);
+          for (int g = 0; g < BN / 32; ++g)
+            tma_load_3d(sb + (uint32_t)g * (ICB * 128), &map_w, bar_bfull + 8u * s, oc0 + g * 32, icb * ICB, tap);
+        }
+      }
+      if (!ok) {
+        atomicOr(a.status, kStatusTimeout);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(BN, 1);
+      const uint64_t desc_b = smem_desc(b_base, (uint32_t)(ICB * 128), 512u, 1u);
+      const uint64_t desc_bl = smem_desc(b_base + b_bytes, (uint32_t)(ICB * 128), 512u, 1u);
+      bool ok = true;
+      for (int kb = 0; kb < total_kb; ++kb) {
+        const int s = kb % NS;
+        ok = mbar_wait(bar_ready + 8u * s, ((uint32_t)(kb / NS)) & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t soff = ((uint32_t)s * stage_bytes) >> 4;
+#pragma unroll
+        for (int j = 0; j < ICB / 8; ++j) {
+          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)s * a_cols + (uint32_t)j * 8u;
+          const uint64_t db = desc_b + soff + (uint32_t)j * 64u;  // 8 k rows = 1024 bytes further down
+          const uint32_t first = (kb == 0 && j == 0) ? 0u : 1u;
+          if (THREE_PASS) {
+            const uint64_t dbl = desc_bl + soff + (uint32_t)j * 64u;
+            umma_tf32_ts(tmem_base, a_hi + ICB, db, idesc, first);
+            umma_tf32_ts(tmem_base, a_hi, dbl, idesc, 1u);
+            umma_tf32_ts(tmem_base, a_hi, db, idesc, 1u);
+          } else {
+            umma_tf32_ts(tmem_base, a_hi, db, idesc, first);
+          }
+        }
+        umma_commit(bar_empty + 8u * s);
+      }
+      if (ok) umma_commit(bar_accum);
+      else {
+        atomicOr(a.status, kStatusTimeout);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ A gather + operand split, then epilogue
+    const int et = threadIdx.x - 64;
+    const int q = warp & 3, m = q * 32 + lane;  // output position = TMEM lane
+    const int r = m / a.TW, c = m - r * a.TW;
+    const int plane = a.plane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    bool ok = true;
+    int kb = 0;
+    auto lo1 = [](uint32_t x) { return __float_as_uint(__uint_as_float(x) - __uint_as_float(x & 0xffffe000u)); };
+    for (int icb = 0; icb < a.n_icb && ok; ++icb) {
+      const int rs = icb % RS;
+      ok = mbar_wait(bar_rfull + 8u * rs, ((uint32_t)(icb / RS)) & 1u, abort_flag);
+      if (!ok) break;
+      const uint32_t *rawp = reinterpret_cast<const uint32_t *>(raw_ptr + (size_t)rs * raw_pitch);
+      for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
+        const int kh = tap / a.KW, kw = tap - kh * a.KW;
+        const int s = kb % NS;
+        const uint32_t phs = ((uint32_t)(kb / NS)) & 1u;
+        ok = mbar_wait(bar_empty + 8u * s, phs ^ 1u, abort_flag);  // the MMAs that read this A slot are done
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t *src = rawp + (r + kh) * a.PWD + c + kw + a.xoff;
+        // flat mode has no zero columns left and right of the image rows: mask them here
+        const bool col_ok = !FLAT || ((unsigned)(c + kw - a.pw) < (unsigned)a.IW);
+        uint32_t hi[ICB], lo[ICB];
+#pragma unroll
+        for (int ic = 0; ic < ICB; ++ic) {
+          const uint32_t x = (!FLAT || col_ok) ? src[ic * plane] : 0u;
+          hi[ic] = x & 0xffffe000u;
+          if (THREE_PASS) lo[ic] = lo1(x);
+        }
+        const uint32_t t_hi = lane_addr + a_col0 + (uint32_t)s * a_cols;
+        if (ICB == 32) {
+          tmem_st32(t_hi, hi);
+          if (THREE_PASS) tmem_st32(t_hi + 32u, lo);
+        } else {
+          tmem_st8(t_hi, hi);
+          if (THREE_PASS) tmem_st8(t_hi + 8u, lo);
+        }
+        ok = mbar_wait(bar_bfull + 8u * s, phs, abort_flag);
+        if (!ok) break;
+        if (THREE_PASS) {
+          uint4 *hi_b = reinterpret_cast<uint4 *>(smem + (size_t)s * stage_bytes);
+          uint4 *lo_b = reinterpret_cast<uint4 *>(smem + (size_t)s * stage_bytes + b_bytes);
+          const int b_vec = (int)b_bytes / 16;
+          for (int base = 0; base < b_vec; base += 512) {
+            uint4 x[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (base + et + 128 * j < b_vec) x[j] = hi_b[base + et + 128 * j];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (base + et + 128 * j < b_vec) {
+                uint4 l;
+                l.x = lo1(x[j].x); l.y = lo1(x[j].y); l.z = lo1(x[j].z); l.w = lo1(x[j].w);
+                lo_b[base + et + 128 * j] = l;
+              }
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ready + 8u * s);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_rempty + 8u * rs);  // the patch may be overwritten
+    }
+    if (ok) ok = mbar_wait(bar_accum, 0u, abort_flag);
+    if (!ok) {
+      atomicOr(a.status, kStatusTimeout);
+      *abort_flag = 1;
+    }
+    tc_fence_after();
+    // ---- epilogue: this thread's output position, all channels of the tile; for a fixed channel
+    // the lanes of a warp write consecutive pixels of a row
+    const int oh = oh0 + r, ow = ow0 + c;
+    const bool inside = oh < a.OH && ow < a.OW;  // lanes outside the image still take part in the
+                                                 // warp-wide TMEM loads
+    float *yp = a.y + (int64_t)n * a.ys[0] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3];
+    if (ok) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(lane_addr + (uint32_t)c0, v);
+        if (inside) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int oc = oc0 + c0 + i;
+            if (oc < a.OC) {
+              float acc = v[i];
+              if (a.bias) acc += a.bias[(int64_t)oc * a.bias_stride];
+              yp[(int64_t)oc * a.ys[1]] = conv_act(a.act, acc);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+int make_map_nd(CUtensorMap *map, const float *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
+                const cuuint32_t *box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  FML_REQUIRE(fn, FML_CUDA_ERROR, "fml_conv: cuTensorMapEncodeTiled is not available");
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float *>(base), dims,
+                  strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FML_REQUIRE(r == CUDA_SUCCESS, FML_CUDA_ERROR, "fml_conv: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return FML_OK;
+}
+
+}  // namespace
+
+// Whether the tensor-core path takes this convolution (see the header of this file).
+bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y, const fml_conv_params *p) {
+  if (x->rank != 4 || p->precision == FML_GEMM_FP32) return false;
+  if ((p->group > 1) || p->strides[0] != 1 || p->strides[1] != 1 || p->dilations[0] != 1 || p->dilations[1] != 1) return false;
+  const int64_t N = x->shape[0], IC = x->shape[1], IH = x->shape[2], IW = x->shape[3];
+  const int64_t OC = w->shape[0], KH = w->shape[2], KW = w->shape[3];
+  if (N < 1 || IC < 1 || OC < 16 || (OC & 3) || KH * KW > 49 || KH > 7 || KW > 7) return false;
+  if (IW & 3) {  // flat mode: the tile must span the width, planes must start on 16-byte steps
+    const int64_t OW = y->shape[3], TW = OW <= 8 ? 8 : OW <= 16 ? 16 : 32;
+    if (OW > TW || ((IH * IW) & 3) || (128 / TW + KH - 1) * IW + KW + 6 > 256) return false;
+  }
+  if (p->pads_begin[0] < 0 || p->pads_begin[1] < 0 || p->pads_begin[0] > 8 || p->pads_begin[1] > 8) return false;
+  // x: dense NCHW; w: [KH][KW][IC][OC] in memory
+  if (x->stride[3] != 1 || x->stride[2] != IW || x->stride[1] != IH * IW || (N > 1 && x->stride[0] != IC * IH * IW)) return false;
+  if (w->stride[0] != 1 || (IC > 1 && w->stride[1] != OC) || (KW > 1 && w->stride[3] != IC * OC) ||
+      (KH > 1 && w->stride[2] != KW * IC * OC)) return false;
+  if (!aligned16(x->data) || !aligned16(w->data)) return false;
+  if (N * IC * IH * IW >= (1ll << 31) || y->shape[2] * y->shape[3] < 64) return false;
+  return true;
+}
+
+int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,
+                   const fml_conv_params *p, cudaStream_t s) {
+  ConvTcArgs a;
+  a.N = (int)x->shape[0]; a.IC = (int)x->shape[1]; a.OC = (int)w->shape[0];
+  const int IH = (int)x->shape[2], IW = (int)x->shape[3];
+  a.OH = (int)y->shape[2]; a.OW = (int)y->shape[3];
+  a.KH = (int)w->shape[2]; a.KW = (int)w->shape[3];
+  a.ph = (int)p->pads_begin[0]; a.pw = (int)p->pads_begin[1];
+  a.flat = (IW & 3) ? 1 : 0;
+  a.TW = a.flat ? (a.OW <= 8 ? 8 : a.OW <= 16 ? 16 : 32) : (a.OW >= 32 ? 32 : a.OW >= 16 ? 16 : 8);
+  a.TH = kBM / a.TW;
+  a.PHT = a.TH + a.KH - 1;
+  a.IW = IW;
+  if (!a.flat) {
+    a.xoff = (4 - a.pw % 4) % 4;
+    a.PWD = (a.TW + a.KW - 1 + a.xoff + 3) / 4 * 4;
+    a.plane = a.PHT * a.PWD;
+  } else {
+    // the run starts at flat index (oh0 - ph) * IW - pw; oh0 is a multiple of TH (even), so its
+    // remainder modulo 4 is that of -(ph * IW + pw), the same for every tile
+    const int start = -(a.ph * IW + a.pw);
+    a.xoff = ((start % 4) + 4) % 4;
+    a.PWD = IW;  // row pitch of the gather
+    a.plane = (a.PHT * IW + a.KW + a.xoff + 3) / 4 * 4;
+  }
+  a.raw_elems = a.plane;
+  const int icb = a.IC > 8 ? 32 : 8;
+  a.n_icb = (a.IC + icb - 1) / icb;
+  a.taps = a.KH * a.KW;
+  const bool three = p->precision != FML_GEMM_TF32;
+  a.tile_n = a.OC >= 128 ? 128 : (a.OC + 31) / 32 * 32;
+  if (a.tile_n > 128) a.tile_n = 128;
+  a.raw_stages = 2;
+  const size_t raw_pitch = ((size_t)a.raw_elems * icb * 4 + 127) / 128 * 128;
+  const size_t stage = (size_t)icb * a.tile_n * 4 * (three ? 2 : 1);
+  FML_REQUIRE(a.raw_stages * raw_pitch + 2 * stage <= kSmemBudget, FML_UNSUPPORTED, "fml_conv: patch does not fit in shared memory");
+  int stages = (int)((kSmemBudget - a.raw_stages * raw_pitch) / stage);
+  const int a_cols = (three ? 2 : 1) * icb;
+  stages = std::min(stages, (512 - (a.tile_n + 31) / 32 * 32) / a_cols);
+  stages = std::max(2, std::min(stages, 8));
+  a.stages = stages;
+  a.tiles_w = (a.OW + a.TW - 1) / a.TW;
+  a.tiles_h = (a.OH + a.TH - 1) / a.TH;
+  for (int i = 0; i < 4; ++i) a.ys[i] = y->stride[i];
+  a.y = (float *)y->data;
+  a.bias = nullptr; a.bias_stride = 0;
+  if (bias) {
+    a.bias = (const float *)bias->data;
+    for (int i = 0; i < bias->rank; ++i) if (bias->shape[i] != 1) a.bias_stride = bias->stride[i];
+  }
+  a.act = p->act;
+  a.status = device_status_word();
+  FML_REQUIRE(a.status, FML_CUDA_ERROR, "fml_conv: no device status word");
+  const int64_t m_tiles = (int64_t)a.tiles_w * a.tiles_h * a.N;
+  FML_REQUIRE(m_tiles <= 0x7fffffff && (a.OC + a.tile_n - 1) / a.tile_n <= 65535, FML_UNSUPPORTED, "fml_conv: grid too large");
+
+  CUtensorMap map_x, map_w;
+  if (a.flat) {
+    const cuuint64_t dims[3] = {(cuuint64_t)IH * IW, (cuuint64_t)a.IC, (cuuint64_t)a.N};
+    const cuuint64_t str[2] = {(cuuint64_t)IH * IW * 4, (cuuint64_t)a.IC * IH * IW * 4};
+    const cuuint32_t box[3] = {(cuuint32_t)a.plane, (cuuint32_t)icb, 1};
+    int st = make_map_nd(&map_x, (const float *)x->data, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st != FML_OK) return st;
+  } else {
+    const cuuint64_t dims[4] = {(cuuint64_t)IW, (cuuint64_t)IH, (cuuint64_t)a.IC, (cuuint64_t)a.N};
+    const cuuint64_t str[3] = {(cuuint64_t)IW * 4, (cuuint64_t)IH * IW * 4, (cuuint64_t)a.IC * IH * IW * 4};
+    const cuuint32_t box[4] = {(cuuint32_t)a.PWD, (cuuint32_t)a.PHT, (cuuint32_t)icb, 1};
+    int st = make_map_nd(&map_x, (const float *)x->data, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st != FML_OK) return st;
+  }
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)a.OC, (cuuint64_t)a.IC, (cuuint64_t)a.taps};
+    const cuuint64_t str[2] = {(cuuint64_t)a.OC * 4, (cuuint64_t)a.IC * a.OC * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)icb, 1};
+    int st = make_map_nd(&map_w, (const float *)w->data, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (st != FML_OK) return st;
+  }
+  size_t smem = (size_t)stages * stage + a.raw_stages * raw_pitch + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 1024;
+  {  // co-residency capped by TMEM columns, as in the GEMM
+    unsigned need = (unsigned)((a.tile_n + 31) / 32 * 32 + a_cols * stages), cols = 32;
+    while (cols < need) cols <<= 1;
+    const size_t fit = 512 / cols, floor_bytes = (size_t)(228 * 1024) / (fit + 1) + 1024;
+    if (smem < floor_bytes) smem = floor_bytes;
+  }
+  FML_REQUIRE(smem <= 227 * 1024, FML_UNSUPPORTED, "fml_conv: shared memory");
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const ConvTcArgs);
+  static const KernelFn kernels[8] = {conv_tc_kernel<false, 8, false>, conv_tc_kernel<false, 32, false>,
+                                      conv_tc_kernel<true, 8, false>,  conv_tc_kernel<true, 32, false>,
+                                      conv_tc_kernel<false, 8, true>,  conv_tc_kernel<false, 32, true>,
+                                      conv_tc_kernel<true, 8, true>,   conv_tc_kernel<true, 32, true>};
+  const KernelFn kernel = kernels[(a.flat ? 4 : 0) + (three ? 2 : 0) + (icb == 32 ? 1 : 0)];
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FML_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    for (KernelFn k : kernels) FML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set[dev & 63] = true;
+  }
+  const dim3 grid((unsigned)m_tiles, (unsigned)((a.OC + a.tile_n - 1) / a.tile_n));
+  FML_CUDA(launch_kernel(kernel, grid, dim3(kThreads), smem, s, map_x, map_w, a));
+  return FML_OK;
+}
+
+}  // namespace fml

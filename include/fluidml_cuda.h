@@ -313,6 +313,13 @@ typedef struct fml_conv_params {
 int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
              const fml_tensor *y, const fml_conv_params *p, void *stream);
 
+/* Reports which path fml_conv takes: 1 = the tcgen05 implicit GEMM (2-D, group 1, unit stride
+ * and dilation, dense NCHW input whose row length is a multiple of 4, weights stored
+ * [KH][KW][IC][OC] -- the OIHW tensor with layout permutation (3, 2, 0, 1) -- with OC a
+ * multiple of 4, precision not FP32), 0 = the CUDA-core kernels. */
+int fml_conv_uses_tensor_cores(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y,
+                               const fml_conv_params *p, int *uses);
+
 /* MaxPoolWithoutPaddingKernel / AveragePoolWithoutPaddingKernel (maxpool.cpp:17-82,
  * averagepool.cpp:19-87): 2-D windows, no padding.  mode 0 = max, 1 = average. */
 int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t *kernel,
