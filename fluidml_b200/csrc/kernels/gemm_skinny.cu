@@ -64,8 +64,29 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
         const float *brow = B + n * a.p.b_sn;
         if (vec) {
           const int64_t kv = k0 + ((k1 - k0) & ~(int64_t)3);
-          for (int64_t k = k0 + lane * 4; k < kv; k += 128) {
-            const float4 bv = *reinterpret_cast<const float4 *>(brow + k);
+          int64_t k = k0 + lane * 4;
+          // four independent 16-byte weight loads per lane and step: the kernel lives on memory-
+          // level parallelism (weights are read once: streaming loads that do not pollute L1)
+          for (; k + 384 < kv; k += 512) {
+            const float4 b0 = __ldcs(reinterpret_cast<const float4 *>(brow + k));
+            const float4 b1 = __ldcs(reinterpret_cast<const float4 *>(brow + k + 128));
+            const float4 b2 = __ldcs(reinterpret_cast<const float4 *>(brow + k + 256));
+            const float4 b3 = __ldcs(reinterpret_cast<const float4 *>(brow + k + 384));
+#pragma unroll
+            for (int m = 0; m < kMaxM; ++m)
+              if (m < M) {
+                const float *ap = A + m * a.p.a_sm + k;
+                const float4 a0 = *reinterpret_cast<const float4 *>(ap), a1 = *reinterpret_cast<const float4 *>(ap + 128);
+                const float4 a2 = *reinterpret_cast<const float4 *>(ap + 256), a3 = *reinterpret_cast<const float4 *>(ap + 384);
+                float t = acc[m];
+                t = fmaf(a0.x, b0.x, fmaf(a0.y, b0.y, fmaf(a0.z, b0.z, fmaf(a0.w, b0.w, t))));
+                t = fmaf(a1.x, b1.x, fmaf(a1.y, b1.y, fmaf(a1.z, b1.z, fmaf(a1.w, b1.w, t))));
+                t = fmaf(a2.x, b2.x, fmaf(a2.y, b2.y, fmaf(a2.z, b2.z, fmaf(a2.w, b2.w, t))));
+                acc[m] = fmaf(a3.x, b3.x, fmaf(a3.y, b3.y, fmaf(a3.z, b3.z, fmaf(a3.w, b3.w, t))));
+              }
+          }
+          for (; k < kv; k += 128) {
+            const float4 bv = __ldcs(reinterpret_cast<const float4 *>(brow + k));
 #pragma unroll
             for (int m = 0; m < kMaxM; ++m)
               if (m < M) {
@@ -114,8 +135,9 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
       }
       __syncthreads();
       if (n < a.p.N)
+#pragma unroll 4
         for (int kk = kq; kk < len; kk += kThreads / 32) {
-          const float bv = B[(kc + kk) * a.p.b_sk + n * a.p.b_sn];
+          const float bv = __ldcs(B + (kc + kk) * a.p.b_sk + n * a.p.b_sn);
 #pragma unroll
           for (int m = 0; m < kMaxM; ++m)
             if (m < M) acc[m] = fmaf(a_sh[m * 128 + kk], bv, acc[m]);
@@ -176,8 +198,8 @@ SkinnyPlan plan_skinny(const GemmProblem &p) {
   SkinnyPlan pl;
   pl.tiles_n = (int)((p.N + kColsPerCta - 1) / kColsPerCta);
   const int64_t tiles = (int64_t)pl.tiles_n * p.nb0 * p.nb1;
-  // enough CTAs for ~4 per SM, each split at least 256 k values long
-  int64_t s = (148 * 4 + tiles - 1) / tiles;
+  // enough CTAs for ~8 per SM, each split at least 256 k values long
+  int64_t s = (148 * 8 + tiles - 1) / tiles;
   s = std::min<int64_t>(s, std::max<int64_t>(1, p.K / 256));
   s = std::max<int64_t>(1, std::min<int64_t>(s, 64));
   int64_t per = (p.K + s - 1) / s;
