@@ -78,6 +78,18 @@ def build_kernels(verbose: bool = False, ptxas_info: bool = False) -> str:
     return KERNELS_SO
 
 
+def build_cli(verbose: bool = False) -> str:
+    """fluidml-compiler, the counterpart of the reference's bin/compiler."""
+    bindir = os.path.join(PKG, "bin")
+    os.makedirs(bindir, exist_ok=True)
+    src = os.path.join(CSRC, "cli", "compiler.cpp")
+    exe = os.path.join(bindir, "fluidml-compiler")
+    if _newer(exe, [src, HOST_SO, KERNELS_SO]):
+        _run([CXX, *CXX_FLAGS, src, "-o", exe, "-L", LIBDIR, "-lfluidml_b200", "-lfluidml_b200_kernels",
+              "-Wl,-rpath,$ORIGIN/../lib"], verbose)
+    return exe
+
+
 def build_host(verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
@@ -103,6 +115,7 @@ def build_host(verbose: bool = False) -> str:
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose)
     build_host(verbose)
+    build_cli(verbose)
 
 
 if __name__ == "__main__":

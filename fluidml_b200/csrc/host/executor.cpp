@@ -3,6 +3,9 @@
 // TopologicalSort -> (DP layout search) -> lowering -> memory plan -> Builder -> Runner,
 // the same stage order as src/worker/executor.cpp:91-133.
 #include <algorithm>
+#include <iterator>
+#include <cstdio>
+#include <fstream>
 #include "worker/executor.h"
 #include "converter.h"
 #include "dp.h"
@@ -46,6 +49,7 @@ public:
     SetOption("dp_cost", EnvOr("FLUIDML_DP_COST", "model"));
     SetOption("autotune", EnvOr("FLUIDML_AUTOTUNE", "1"));
     SetOption("weight_prefetch", EnvOr("FLUIDML_WEIGHT_PREFETCH", "1"));
+    SetOption("plan_cache", EnvOr("FLUIDML_PLAN_CACHE", ""));
   }
 
   void SetOption(const std::string &key, const std::string &value) override {
@@ -55,6 +59,7 @@ public:
     else if (key == "cuda_graph") options_.cuda_graph = value != "0";
     else if (key == "autotune") options_.autotune = value != "0";
     else if (key == "weight_prefetch") options_.weight_prefetch = value != "0";
+    else if (key == "plan_cache") options_.plan_cache = value;
     else if (key == "alignment") {
       options_.alignment = (size_t)std::stoul(value);
       if (options_.alignment < 16 || (options_.alignment & (options_.alignment - 1)))
@@ -66,7 +71,8 @@ public:
   }
 
   void Compile(std::istream &input, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json) override {
-    CompileGraph(Parser::Run(input), mlir, llvm, json);
+    const std::string bytes((std::istreambuf_iterator<char>(input)), std::istreambuf_iterator<char>());
+    CompileBuffer(bytes.data(), bytes.size(), mlir, llvm, json);
   }
 
   void Compile(std::string_view input, std::optional<std::string_view> mlir,
@@ -79,11 +85,17 @@ public:
       return &f;
     };
     std::ofstream *pm = open(fm, mlir), *pl = open(fl, llvm), *pj = open(fj, json);
-    CompileGraph(Parser::Run(std::string(input)), pm, pl, pj);
+    std::ifstream in{std::string(input), std::ios::binary};
+    if (!in) throw Error("cannot open '" + std::string(input) + "'");
+    Compile(in, pm, pl, pj);
   }
 
   void CompileBuffer(const void *data, size_t size, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json,
                      bool dry_run = false) {
+    // FNV-1a over the model bytes: the key of the plan cache
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < size; ++i) h = (h ^ ((const uint8_t *)data)[i]) * 1099511628211ull;
+    model_hash_ = h;
     CompileGraph(Parser::Run((const uint8_t *)data, size), mlir, llvm, json, dry_run);
   }
 
@@ -107,6 +119,63 @@ public:
   }
 
 private:
+  // One file per (model bytes, mode, options that shape the plan): text lines
+  //   layout <tensor> <p0> <p1> ...      physical position of every logical dim
+  //   tiles <node> <tile_n> <split_k>    tuned GEMM tiles
+  struct PlanCacheEntry {
+    std::map<std::string, std::vector<size_t>> layouts;
+    std::map<std::string, std::pair<int, int>> tiles;
+    bool Load(const std::string &path) {
+      std::ifstream in(path);
+      if (!in) return false;
+      std::string line;
+      bool complete = false;
+      while (std::getline(in, line)) {
+        std::istringstream ls(line);
+        std::string tag, name;
+        ls >> tag;
+        if (tag == "end") { complete = true; break; }
+        ls >> name;
+        if (tag == "layout") {
+          std::vector<size_t> l;
+          size_t v;
+          while (ls >> v) l.push_back(v);
+          layouts[name] = l;
+        } else if (tag == "tiles") {
+          int tn = 0, sk = 0;
+          ls >> tn >> sk;
+          if (tn > 0 && sk > 0) tiles[name] = {tn, sk};
+        }
+      }
+      return complete;  // a truncated file (interrupted writer) is a miss
+    }
+    void Store(const std::string &path) const {
+      const std::string tmp = path + ".tmp";
+      {
+        std::ofstream out(tmp);
+        if (!out) return;
+        for (const auto &kv : layouts) {
+          out << "layout " << kv.first;
+          for (size_t v : kv.second) out << " " << v;
+          out << "\n";
+        }
+        for (const auto &kv : tiles) out << "tiles " << kv.first << " " << kv.second.first << " " << kv.second.second << "\n";
+        out << "end\n";
+      }
+      std::rename(tmp.c_str(), path.c_str());
+    }
+  };
+
+  std::string PlanCachePath() const {
+    if (options_.plan_cache.empty() || model_hash_ == 0) return std::string();
+    char buf[160];
+    snprintf(buf, sizeof(buf), "/%016llx-%s-%s-p%d-f%d-c%d-a%d-t%d.plan", (unsigned long long)model_hash_,
+             layout_ == LayoutMode::kDP ? "dp" : "plain", plan_ == MemoryPlanKind::kGreedy ? "greedy" : "linear",
+             options_.gemm_precision, options_.fusion ? 1 : 0, options_.dp_constant_cost ? 1 : 0, (int)options_.alignment,
+             options_.autotune ? 1 : 0);
+    return options_.plan_cache + buf;
+  }
+
   // `dry_run`: stop before anything touches the device (planning only).
   void CompileGraph(graph::Graph graph, std::ofstream *mlir, std::ofstream *llvm, std::ofstream *json,
                     bool dry_run = false) {
@@ -129,7 +198,19 @@ private:
     flow::Sequence sequence = Planner::TopologicalSort(flow);
     json::Value dp_json = json::Value::Object();
     json::Value plan_json = json::Value::Object();
-    if (layout_ == LayoutMode::kDP) {
+    // Plan cache: layouts and GEMM tiles of an earlier Compile of the same bytes and options.
+    PlanCacheEntry cached;
+    const std::string cache_path = dry_run ? std::string() : PlanCachePath();
+    const bool cache_hit = !cache_path.empty() && cached.Load(cache_path);
+    options_.gemm_tiles = std::make_shared<std::map<std::string, std::pair<int, int>>>();
+    if (cache_hit) {
+      for (const auto &r : sequence.regions) {
+        auto it = cached.layouts.find(r->name);
+        if (it != cached.layouts.end() && it->second.size() == r->meta.GetRank()) r->layout = it->second;
+      }
+      *options_.gemm_tiles = cached.tiles;
+      dp_json.Set("plan_cache", json::Value(cache_path));
+    } else if (layout_ == LayoutMode::kDP) {
       evaluation::DynamicProgrammingTable table(options_.dp_constant_cost, options_.gemm_precision);
       evaluation::DynamicProgrammingPlan plan = table.Run(flow);
       for (const auto &r : sequence.regions)
@@ -159,6 +240,12 @@ private:
 
     std::unique_ptr<Program> program;
     if (!dry_run) program = Builder::Run(flow, sequence, index, aliases, options_);
+    if (program && !cache_path.empty() && !cache_hit) {
+      PlanCacheEntry fresh;
+      for (const auto &r : sequence.regions) fresh.layouts[r->name] = r->layout;
+      fresh.tiles = *options_.gemm_tiles;
+      fresh.Store(cache_path);  // best effort: an unwritable directory only costs the next Compile its time
+    }
 
     stats_ = json::Value::Object();
     stats_.Set("name", json::Value(name_));
@@ -171,6 +258,7 @@ private:
     stats_.Set("graph_nodes", json::Value((double)nodes_before_fusion));
     stats_.Set("flow_nodes", json::Value((double)flow.nodes.size()));
     stats_.Set("aliased_nodes", json::Value((double)aliases.size()));
+    stats_.Set("plan_cache", json::Value(std::string(cache_path.empty() ? "off" : cache_hit ? "hit" : "miss")));
     json::Value seq = json::Value::Array();
     for (const auto &n : sequence.nodes) {
       json::Value e = json::Value::Object();
@@ -186,6 +274,10 @@ private:
       stats_.Set("weight_bytes", json::Value((double)program->weight_bytes));
       stats_.Set("interface_bytes", json::Value((double)program->io_bytes));
       stats_.Set("launches", json::Value((double)program->launches.size()));
+      json::Value iface = json::Value::Object();  // host buffer size of every argument of Invoke
+      for (const auto &b : program->inputs) iface.Set(b.name, json::Value((double)b.bytes));
+      for (const auto &b : program->outputs) iface.Set(b.name, json::Value((double)b.bytes));
+      stats_.Set("interface", iface);
       json::Value hist = json::Value::Object();
       for (const auto &kv : program->kernel_histogram) hist.Set(kv.first, json::Value((double)kv.second));
       stats_.Set("kernels", hist);
@@ -244,6 +336,7 @@ private:
   Options options_;
   std::unique_ptr<Runner> runner_;
   json::Value stats_ = json::Value::Object();
+  uint64_t model_hash_ = 0;
 
 };
 

@@ -485,6 +485,17 @@ public:
     c_.params.l2_prefetch = ptr;
     c_.params.l2_prefetch_bytes = bytes;
   }
+  void PresetTiles(int tile_n, int split_k) override {
+    c_.params.tile_n = tile_n;
+    c_.params.split_k = split_k;
+    c_.autotune = false;
+  }
+  bool TunedTiles(int *tile_n, int *split_k) const override {
+    if (tuned_tn_ <= 0) return false;
+    *tile_n = tuned_tn_;
+    *split_k = tuned_sk_;
+    return true;
+  }
 
   void Resolve(const std::vector<fml_tensor> &in, fml_tensor &a, fml_tensor &b, fml_tensor &bias,
                fml_tensor &res) const {
@@ -509,6 +520,8 @@ public:
                             &c.params, nullptr, &tuned) != FML_OK)
         throw Error(std::string(c.name) + ": " + fml_last_error());
       c.params = tuned;
+      tuned_tn_ = tuned.tile_n;
+      tuned_sk_ = tuned.split_k;
     }
     rec.Add(c.name, [=](void *s) {
       return fml_gemm(&a, &b, &output, c.has_bias ? &bias : nullptr, c.has_residual ? &res : nullptr, &c.params, s);
@@ -517,6 +530,7 @@ public:
 
 private:
   Config c_;
+  mutable int tuned_tn_ = 0, tuned_sk_ = 0;
 };
 
 // conv.cpp:27-280

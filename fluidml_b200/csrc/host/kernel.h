@@ -68,6 +68,10 @@ public:
     return false;
   }
   virtual void SetPrefetch(const void *ptr, size_t bytes) { (void)ptr; (void)bytes; }
+  // Tile choices that can be carried from one Compile to the next (GEMM tile_n / split_k): a
+  // preset replaces the on-device tuning; TunedTiles reports what Launch ended up using.
+  virtual void PresetTiles(int tile_n, int split_k) { (void)tile_n; (void)split_k; }
+  virtual bool TunedTiles(int *tile_n, int *split_k) const { (void)tile_n; (void)split_k; return false; }
 
 protected:
   Kernel() = default;

@@ -230,8 +230,14 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
       buf.data = (char *)prog->arena + index.Get(node->name);
       buf.bytes = node->buffer_size;
     }
+    if (options.gemm_tiles) {
+      auto it = options.gemm_tiles->find(node->name);
+      if (it != options.gemm_tiles->end()) k->PresetTiles(it->second.first, it->second.second);
+    }
     rec.SetNode(node->name);
     k->Launch(rec, ins, out, buf);
+    int tn = 0, sk = 0;
+    if (options.gemm_tiles && k->TunedTiles(&tn, &sk)) (*options.gemm_tiles)[node->name] = {tn, sk};
   }
   prog->launches = rec.Launches();
   for (const auto &l : prog->launches) ++prog->kernel_histogram[l.kernel];

@@ -13,6 +13,8 @@
 #include "kernel.h"
 #include "memory.h"
 #include <map>
+#include <memory>
+#include <string>
 #include <unordered_map>
 
 namespace fluidml {
@@ -27,6 +29,12 @@ struct Options {
   bool dp_constant_cost = false;
   bool autotune = true;  // tune GEMM tile / split-K choices on the device at Compile
   bool weight_prefetch = true;  // GEMMs ask L2 to fetch the next GEMM's weights while they run
+  // Directory of the plan cache (empty: none).  A compiled model leaves its DP layouts and the
+  // tuned GEMM tiles there, keyed by a hash of the model bytes and the options that shape the
+  // plan, so that compiling the same model again skips the layout search and the on-device tuning.
+  std::string plan_cache;
+  // node name -> (tile_n, split_k): read by the Builder as presets, filled with what it tuned
+  std::shared_ptr<std::map<std::string, std::pair<int, int>>> gemm_tiles;
 };
 
 // region -> the region whose memory it shares (itself when it owns memory).

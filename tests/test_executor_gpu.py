@@ -4,6 +4,8 @@ Final fp32 outputs must agree within max|gpu - ref| / max|ref| <= 1e-3, the tole
 hot-path specification states; the indexing operators underneath are covered bit-exactly in
 test_kernels_gpu.py.
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -128,3 +130,35 @@ def test_vgg_small_and_gpt_neox_small():
     for factory in (Executor.make_plain_greedy, Executor.make_dp_greedy):
         outs, _ = run(g, xg, factory)
         assert relerr(outs["last_hidden_state"], ref["last_hidden_state"]) <= TOL
+
+
+def test_plan_cache_and_cli_run(tmp_path):
+    """A second Compile of the same bytes with the same options takes layouts and GEMM tiles from
+    the plan cache and produces the same outputs; the CLI compiles and runs a model."""
+    import subprocess
+    import fluidml_b200.build as b
+    m = models.build_bert(layers=2, vocab=500)
+    x = models.bert_inputs(vocab=500)
+    outs, states = [], []
+    for _ in range(2):
+        ex = Executor.make_dp_greedy("bert", 1)
+        ex.set_option("plan_cache", str(tmp_path))
+        ex.compile(m.to_bytes())
+        states.append(ex.stats()["plan_cache"])
+        host = {vi.name: np.zeros(vi.shape, {1: np.float32, 7: np.int64}[vi.dtype]) for vi in (*m.inputs, *m.outputs)}
+        for k, v in x.items():
+            host[k][...] = v
+        ex.invoke(host)
+        outs.append({k: host[k].copy() for k in ("last_hidden_state", "pooler_output")})
+    assert states == ["miss", "hit"]
+    assert len(list(tmp_path.glob("*.plan"))) == 1
+    for k in outs[0]:
+        assert np.array_equal(outs[0][k], outs[1][k])
+    path = tmp_path / "m.onnx"
+    path.write_bytes(m.to_bytes())
+    exe = os.path.join(os.path.dirname(b.HOST_SO), "..", "bin", "fluidml-compiler")
+    r = subprocess.run([exe, "-n", "bert", "-i", str(path), "-m", "dp_greedy", "-e", "3", "--run",
+                        "--mlir", str(tmp_path / "launches.txt")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert "ns per pass" in r.stdout
+    assert "FusedGemmKernel" in (tmp_path / "launches.txt").read_text()

@@ -272,3 +272,37 @@ def test_options_are_validated():
     for k, v in (("gemm_precision", "fp64"), ("alignment", "24"), ("dp_cost", "measured"), ("nonsense", "1")):
         with pytest.raises(RuntimeError):
             ex.set_option(k, v)
+
+
+# ------------------------------------------------------------------ command-line front end
+def _cli():
+    import fluidml_b200.build as b
+    exe = os.path.join(os.path.dirname(b.HOST_SO), "..", "bin", "fluidml-compiler")
+    assert os.path.exists(exe), "fluidml-compiler has not been built"
+    return exe
+
+
+def test_cli_options_follow_the_reference(bert_bytes):
+    """Same options as the reference's bin/compiler.cpp; --mode is honoured, required options
+    and bad modes exit 1 with a message, --plan-only runs without a device."""
+    import subprocess
+    exe = _cli()
+    assert "--mode" in subprocess.run([exe, "--help"], capture_output=True, text=True).stdout
+    r = subprocess.run([exe, "-n", "x"], capture_output=True, text=True)
+    assert r.returncode == 1 and "--input" in r.stderr
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "m.onnx")
+        with open(path, "wb") as f:
+            f.write(bert_bytes)
+        r = subprocess.run([exe, "-n", "bert", "-i", path, "-m", "fastest"], capture_output=True, text=True)
+        assert r.returncode == 1 and "invalid mode" in r.stderr
+        arenas = {}
+        for mode in ("plain_linear", "dp_greedy"):
+            r = subprocess.run([exe, "-n", "bert", "-i", path, "-m", mode, "--plan-only", "--json", os.path.join(d, mode)],
+                               capture_output=True, text=True)
+            assert r.returncode == 0, r.stderr
+            st = json.loads(r.stdout)
+            assert st["mode"] == mode
+            arenas[mode] = st["peak_arena_bytes"]
+            assert set(json.load(open(os.path.join(d, mode)))) == {"dp_table", "plan", "arena"}
+        assert arenas["dp_greedy"] < arenas["plain_linear"]
