@@ -27,7 +27,7 @@ ADD_SCALAR, MUL_SCALAR, DIV_SCALAR, RSUB_SCALAR, POW_SCALAR, EQUAL_SCALAR, CLIP,
     RSUB_MUL_SCALAR = 16, 17, 18, 19, 20, 21, 22, 23
 ERF, TANH, SQRT, NEG, RELU, SIGMOID, NOT, COPY, CAST, EXP, SILU = range(32, 43)
 # fml_gemm_act / precision
-ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_TANH, ACT_SIGMOID = range(5)
+ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_TANH, ACT_SIGMOID, ACT_SILU = range(6)
 GEMM_AUTO, GEMM_FP32, GEMM_3XTF32, GEMM_TF32 = range(4)
 
 

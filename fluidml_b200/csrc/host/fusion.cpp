@@ -294,6 +294,17 @@ bool FuseSilu(Rewriter &rw, const NodePtr &sg) {
   return true;
 }
 
+// ---- Conv -> SiLU: the activation rides in the convolution's epilogue
+bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
+  if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
+  NodePtr silu = rw.SoleOfKind(cv->output, Kind::Silu);
+  if (!silu) return false;
+  cv->act = FML_ACT_SILU;
+  cv->output = silu->output;
+  rw.Kill(silu);
+  return true;
+}
+
 // ---- GEMMs that read the same activations with constant weights (the Q, K, V projections):
 // one GEMM over the concatenated weights, the original outputs become column slices of its
 // result (views, no copy).  Fewer launches and one pass over the shared A operand.
@@ -397,7 +408,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

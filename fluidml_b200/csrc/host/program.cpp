@@ -341,6 +341,13 @@ std::map<std::string, Runner::KernelTime> Runner::Profile(const std::unordered_m
       KernelTime &k = out[i < n ? program_->launches[i].kernel : std::string("(empty event pair)")];
       k.us += (double)ms * 1e3;
       k.launches += 1;
+      // FLUIDML_PROFILE_NODES=1: one more entry per launch, keyed "node <name>"
+      static const bool per_node = [] { const char *e = getenv("FLUIDML_PROFILE_NODES"); return e && e[0] == '1'; }();
+      if (per_node && i < n) {
+        KernelTime &pn = out["node " + program_->launches[i].node];
+        pn.us += (double)ms * 1e3;
+        pn.launches += 1;
+      }
     }
   }
   for (auto &e : events) fml_event_destroy(e);

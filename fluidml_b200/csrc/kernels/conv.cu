@@ -25,6 +25,7 @@ __device__ __forceinline__ float conv_act(int act, float v) {
   case FML_ACT_RELU: return fmaxf(v, 0.0f);
   case FML_ACT_TANH: return tanhf(v);
   case FML_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+  case FML_ACT_SILU: return v * (1.0f / (1.0f + expf(-v)));
   default: return v;
   }
 }
@@ -186,6 +187,24 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
   const int64_t M = a.N * a.OH * a.OW;
   if (M == 0 || a.OC == 0) return FML_OK;
   cudaStream_t s = as_stream(stream);
+  if (group == 1 && a.IH == 1 && a.IW == 1 && a.OH == 1 && a.OW == 1 && a.ph < a.KH && a.pw < a.KW) {
+    // One pixel in, one pixel out (the squeeze-and-excite convolutions): only the tap under the
+    // pixel contributes, and the convolution is the product [N, IC] x [IC, OC] -- rows = images,
+    // so the weight-streaming kernel takes it (up to 32 images), with the bias and activation in
+    // its epilogue.
+    GemmProblem g;
+    memset(&g, 0, sizeof(g));
+    g.M = a.N; g.N = a.OC; g.K = a.IC; g.nb0 = g.nb1 = 1;
+    g.a = a.x; g.a_sm = a.xs[0]; g.a_sk = a.xs[1];
+    g.b = a.w + a.ph * a.ws[2] + a.pw * a.ws[3]; g.b_sk = a.ws[1]; g.b_sn = a.ws[0];
+    g.c = a.y; g.c_sm = a.ys[0]; g.c_sn = a.ys[1];
+    g.bias = a.bias; g.bias_sm = 0; g.bias_sn = a.bias_stride;
+    GemmEpilogue e;
+    e.divisor = 1.0f; e.alpha = 1.0f; e.beta = 1.0f; e.act = a.act;
+    e.c0 = 1.4142135381698608f; e.c1 = 1.0f; e.c2 = 0.5f;
+    e.has_bias = a.bias != nullptr; e.has_res = 0;
+    return skinny_eligible(g) ? launch_gemm_skinny(g, e, s) : launch_gemm_simt(g, e, s);
+  }
   if (group == 1 && nd == 2 && conv_tc_eligible(x, w, y, p)) return launch_conv_tc(x, w, bias, y, p, s);
   if (group == 1) {
     FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");

@@ -19,6 +19,10 @@
 // rounded down to a 16-byte step, rows above and below the image still zero-filled by TMA) and
 // the missing left / right padding columns are masked in the gather.
 //
+// 1x1 convolutions over planes of at most 128 pixels whose size is not a multiple of 4 either
+// (7 x 7) need no halo at all: 32 whole planes of one image are one contiguous run, fetched with
+// a plain bulk copy ("linear mode"; the channel count must be a multiple of 32).
+//
 // Weights are expected tap-major with the output channel innermost ([KH][KW][IC][OC], i.e.
 // the OIHW tensor stored with layout permutation (3, 2, 0, 1)): the B tile of a (tap, channel
 // block) is then an MN-major box, loaded exactly like the GEMM's MN-major B.
@@ -37,7 +41,8 @@ constexpr size_t kSmemBudget = 200 * 1024;
 struct ConvTcArgs {
   int N, IC, OC, OH, OW, KH, KW, ph, pw;
   int TW, TH, PWD, PHT, xoff;  // tile geometry: patch PHT rows x PWD columns per channel
-  int flat, IW, plane, raw_elems;  // flat mode: the patch is a run of whole image rows (see below)
+  int flat, IW, plane, raw_elems;  // flat: 1 = the patch is a run of whole image rows, 2 = whole planes
+  const float *x;                  // input base (linear mode copies without a tensor map)
   int n_icb, taps, tile_n, stages, raw_stages;
   int tiles_w, tiles_h;
   int64_t ys[4];
@@ -65,12 +70,14 @@ __device__ __forceinline__ float conv_act(int act, float v) {
   case FML_ACT_RELU: return fmaxf(v, 0.0f);
   case FML_ACT_TANH: return tanhf(v);
   case FML_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+  case FML_ACT_SILU: return v * (1.0f / (1.0f + expf(-v)));
   default: return v;
   }
 }
 
 // ICB: input channels per k block (32, or 8 for the first layer's few channels).
-template <bool THREE_PASS, int ICB, bool FLAT>
+// MODE: 0 = box patch, 1 = flat rows, 2 = linear (whole planes), see the header.
+template <bool THREE_PASS, int ICB, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const ConvTcArgs a) {
@@ -142,12 +149,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         mbar_expect_tx(bar_rfull + 8u * rs, raw_bytes);
         // x = ow0 - pw - xoff is a multiple of 4 by construction; rows / columns / channels outside
         // the image are filled with zeros: the padding, and the channel tail of the last block
-        if (!FLAT)
+        if (MODE == 0)
           tma_load_4d(raw_base + (uint32_t)rs * raw_pitch, &map_x, bar_rfull + 8u * rs, ow0 - a.pw - a.xoff,
                       oh0 - a.ph, icb * ICB, n);
-        else  // whole rows from (oh0 - ph) on, as one run of the flattened H*W plane
+        else if (MODE == 1)  // whole rows from (oh0 - ph) on, as one run of the flattened H*W plane
           tma_load_3d(raw_base + (uint32_t)rs * raw_pitch, &map_x, bar_rfull + 8u * rs,
                       (oh0 - a.ph) * a.IW - a.pw - a.xoff, icb * ICB, n);
+        else  // ICB whole planes of this image: one contiguous run, a plain bulk copy
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(raw_base + (uint32_t)rs * raw_pitch),
+                         "l"(a.x + ((size_t)n * a.IC + (size_t)icb * ICB) * a.plane), "r"(raw_bytes),
+                         "r"(bar_rfull + 8u * rs) : "memory");
         for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
           const int s = kb % NS;
           ok = mbar_wait(bar_empty + 8u * s, (((uint32_t)(kb / NS)) & 1u) ^ 1u, abort_flag);
@@ -222,11 +234,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc_fence_after();
         const uint32_t *src = rawp + (r + kh) * a.PWD + c + kw + a.xoff;
         // flat mode has no zero columns left and right of the image rows: mask them here
-        const bool col_ok = !FLAT || ((unsigned)(c + kw - a.pw) < (unsigned)a.IW);
+        const bool col_ok = MODE == 0 || (MODE == 1 ? ((unsigned)(c + kw - a.pw) < (unsigned)a.IW) : m < a.plane);
         uint32_t hi[ICB], lo[ICB];
 #pragma unroll
         for (int ic = 0; ic < ICB; ++ic) {
-          const uint32_t x = (!FLAT || col_ok) ? src[ic * plane] : 0u;
+          const uint32_t x = (MODE == 0 || col_ok) ? src[ic * plane] : 0u;
           hi[ic] = x & 0xffffe000u;
           if (THREE_PASS) lo[ic] = lo1(x);
         }
@@ -326,9 +338,13 @@ bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor
   const int64_t N = x->shape[0], IC = x->shape[1], IH = x->shape[2], IW = x->shape[3];
   const int64_t OC = w->shape[0], KH = w->shape[2], KW = w->shape[3];
   if (N < 1 || IC < 1 || OC < 16 || (OC & 3) || KH * KW > 49 || KH > 7 || KW > 7) return false;
-  if (IW & 3) {  // flat mode: the tile must span the width, planes must start on 16-byte steps
+  if (IW & 3) {
     const int64_t OW = y->shape[3], TW = OW <= 8 ? 8 : OW <= 16 ? 16 : 32;
-    if (OW > TW || ((IH * IW) & 3) || (128 / TW + KH - 1) * IW + KW + 6 > 256) return false;
+    const bool linear = KH == 1 && KW == 1 && p->pads_begin[0] == 0 && p->pads_begin[1] == 0 && IH * IW <= 128 &&
+                        (IC & 31) == 0;
+    // flat mode: the tile must span the width, planes must start on 16-byte steps
+    const bool flat = OW <= TW && ((IH * IW) & 3) == 0 && (128 / TW + KH - 1) * IW + KW + 6 <= 256;
+    if (!linear && !flat) return false;
   }
   if (p->pads_begin[0] < 0 || p->pads_begin[1] < 0 || p->pads_begin[0] > 8 || p->pads_begin[1] > 8) return false;
   // x: dense NCHW; w: [KH][KW][IC][OC] in memory
@@ -336,7 +352,7 @@ bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor
   if (w->stride[0] != 1 || (IC > 1 && w->stride[1] != OC) || (KW > 1 && w->stride[3] != IC * OC) ||
       (KH > 1 && w->stride[2] != KW * IC * OC)) return false;
   if (!aligned16(x->data) || !aligned16(w->data)) return false;
-  if (N * IC * IH * IW >= (1ll << 31) || y->shape[2] * y->shape[3] < 64) return false;
+  if (N * IC * IH * IW >= (1ll << 31) || y->shape[2] * y->shape[3] < 32) return false;
   return true;
 }
 
@@ -349,11 +365,19 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   a.KH = (int)w->shape[2]; a.KW = (int)w->shape[3];
   a.ph = (int)p->pads_begin[0]; a.pw = (int)p->pads_begin[1];
   a.flat = (IW & 3) ? 1 : 0;
+  if (a.flat && a.KH == 1 && a.KW == 1 && a.ph == 0 && a.pw == 0 && IH * IW <= 128 && (a.IC & 31) == 0 && ((IH * IW) & 3))
+    a.flat = 2;
+  a.x = (const float *)x->data;
   a.TW = a.flat ? (a.OW <= 8 ? 8 : a.OW <= 16 ? 16 : 32) : (a.OW >= 32 ? 32 : a.OW >= 16 ? 16 : 8);
-  a.TH = kBM / a.TW;
+  if (a.flat == 2) a.TW = a.OW;  // position m = oh * OW + ow
+  a.TH = a.flat == 2 ? a.OH : kBM / a.TW;
   a.PHT = a.TH + a.KH - 1;
   a.IW = IW;
-  if (!a.flat) {
+  if (a.flat == 2) {
+    a.xoff = 0;
+    a.PWD = IW;
+    a.plane = IH * IW;
+  } else if (!a.flat) {
     a.xoff = (4 - a.pw % 4) % 4;
     a.PWD = (a.TW + a.KW - 1 + a.xoff + 3) / 4 * 4;
     a.plane = a.PHT * a.PWD;
@@ -372,7 +396,9 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   const bool three = p->precision != FML_GEMM_TF32;
   a.tile_n = a.OC >= 128 ? 128 : (a.OC + 31) / 32 * 32;
   if (a.tile_n > 128) a.tile_n = 128;
-  a.raw_stages = 2;
+  // a patch feeds `taps` k blocks: with a single tap every k block waits for its own patch, so the
+  // patch ring must be as deep as the operand ring to cover the load latency
+  a.raw_stages = a.taps == 1 ? 6 : a.taps <= 4 ? 3 : 2;
   const size_t raw_pitch = ((size_t)a.raw_elems * icb * 4 + 127) / 128 * 128;
   const size_t stage = (size_t)icb * a.tile_n * 4 * (three ? 2 : 1);
   FML_REQUIRE(a.raw_stages * raw_pitch + 2 * stage <= kSmemBudget, FML_UNSUPPORTED, "fml_conv: patch does not fit in shared memory");
@@ -397,7 +423,9 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   FML_REQUIRE(m_tiles <= 0x7fffffff && (a.OC + a.tile_n - 1) / a.tile_n <= 65535, FML_UNSUPPORTED, "fml_conv: grid too large");
 
   CUtensorMap map_x, map_w;
-  if (a.flat) {
+  if (a.flat == 2) {
+    map_x = CUtensorMap{};  // unused
+  } else if (a.flat) {
     const cuuint64_t dims[3] = {(cuuint64_t)IH * IW, (cuuint64_t)a.IC, (cuuint64_t)a.N};
     const cuuint64_t str[2] = {(cuuint64_t)IH * IW * 4, (cuuint64_t)a.IC * IH * IW * 4};
     const cuuint32_t box[3] = {(cuuint32_t)a.plane, (cuuint32_t)icb, 1};
@@ -426,11 +454,13 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   }
   FML_REQUIRE(smem <= 227 * 1024, FML_UNSUPPORTED, "fml_conv: shared memory");
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const ConvTcArgs);
-  static const KernelFn kernels[8] = {conv_tc_kernel<false, 8, false>, conv_tc_kernel<false, 32, false>,
-                                      conv_tc_kernel<true, 8, false>,  conv_tc_kernel<true, 32, false>,
-                                      conv_tc_kernel<false, 8, true>,  conv_tc_kernel<false, 32, true>,
-                                      conv_tc_kernel<true, 8, true>,   conv_tc_kernel<true, 32, true>};
-  const KernelFn kernel = kernels[(a.flat ? 4 : 0) + (three ? 2 : 0) + (icb == 32 ? 1 : 0)];
+  static const KernelFn kernels[12] = {conv_tc_kernel<false, 8, 0>, conv_tc_kernel<false, 32, 0>,
+                                       conv_tc_kernel<true, 8, 0>,  conv_tc_kernel<true, 32, 0>,
+                                       conv_tc_kernel<false, 8, 1>, conv_tc_kernel<false, 32, 1>,
+                                       conv_tc_kernel<true, 8, 1>,  conv_tc_kernel<true, 32, 1>,
+                                       conv_tc_kernel<false, 8, 2>, conv_tc_kernel<false, 32, 2>,
+                                       conv_tc_kernel<true, 8, 2>,  conv_tc_kernel<true, 32, 2>};
+  const KernelFn kernel = kernels[a.flat * 4 + (three ? 2 : 0) + (icb == 32 ? 1 : 0)];
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));

@@ -39,6 +39,7 @@ __device__ __forceinline__ float gemm_epilogue(const GemmEpilogue &e, float acc,
   case FML_ACT_RELU: v = fmaxf(v, 0.0f); break;
   case FML_ACT_TANH: v = tanhf(v); break;
   case FML_ACT_SIGMOID: v = 1.0f / (1.0f + expf(-v)); break;
+  case FML_ACT_SILU: v = v * (1.0f / (1.0f + expf(-v))); break;
   default: break;
   }
   if (e.has_res) v += res;

@@ -205,6 +205,38 @@ __global__ void reduce_mean_kernel(ReduceArgs a, float *out, const float *in) {
   if (lane == 0) out[off[0]] = s / (float)a.count;
 }
 
+// The reduced dims form one contiguous run of `count` floats (a global average pool over
+// H x W in NCHW): one CTA per output, 16-byte loads when the run is aligned, shuffle + shared
+// memory reduction in a fixed order.
+__global__ void __launch_bounds__(256) reduce_mean_contig_kernel(ReduceArgs a, float *out, const float *in) {
+  pdl_prologue();
+  __shared__ float part[8];
+  const int64_t o = blockIdx.x;
+  int64_t off[2];
+  offsets_of(a.keep, o, off);
+  const float *src = in + off[1];
+  float s = 0.0f;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const int64_t n4 = a.count >> 2;
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    for (int64_t i = threadIdx.x; i < n4; i += 256) {
+      const float4 v = s4[i];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    for (int64_t i = (n4 << 2) + threadIdx.x; i < a.count; i += 256) s += src[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < a.count; i += 256) s += src[i];
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int w = 0; w < 8; ++w) t += part[w];
+    out[off[0]] = t / (float)a.count;
+  }
+}
+
 __global__ void cumsum_kernel(RowArgs a, int64_t *out, const int64_t *in) {
   pdl_prologue();
   const int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -356,6 +388,20 @@ extern "C" int fml_reduce_mean(const fml_tensor *in, const fml_tensor *out, cons
   }
   collapse(a.keep);
   if (a.keep.total == 0 || a.count == 0) return FML_OK;
+  // contiguous run? (reduced dims in memory order, each stride = the product of the later extents)
+  bool contig = a.rrank > 0;
+  {
+    int64_t expect = 1;
+    for (int d = a.rrank - 1; d >= 0 && contig; --d) {
+      if (a.rshape[d] != 1 && a.rstride[d] != expect) contig = false;
+      expect *= a.rshape[d];
+    }
+  }
+  if (contig && a.count >= 256 && a.keep.total <= 0x7fffffff) {
+    FML_LAUNCH((reduce_mean_contig_kernel), (unsigned)a.keep.total, 256, 0, as_stream(stream), a, (float *)out->data,
+               (const float *)in->data);
+    return FML_OK;
+  }
   FML_LAUNCH((reduce_mean_kernel), (unsigned)((a.keep.total * 32 + 255) / 256), 256, 0, as_stream(stream), 
       a, (float *)out->data, (const float *)in->data);
   FML_CUDA(cudaGetLastError());

@@ -341,6 +341,71 @@ def vgg_inputs(seed: int = 1, batch: int = 1, image: int = 224):
     return {"input": rng.normal(0, 1, (batch, 3, image, image)).astype(np.float32)}
 
 
+# ------------------------------------------------------------------------------ EfficientNet-B0
+# (expand ratio, depthwise kernel, stride, output channels, repeats) of the seven stages
+_EFFNET_B0_STAGES = ((1, 3, 1, 16, 1), (6, 3, 2, 24, 2), (6, 5, 2, 40, 2), (6, 3, 2, 80, 3),
+                     (6, 5, 1, 112, 3), (6, 5, 2, 192, 4), (6, 3, 1, 320, 1))
+
+
+def build_efficientnet_b0(seed: int = 0, batch: int = 1, image: int = 224, classes: int = 1000,
+                          width: float = 1.0, stages=_EFFNET_B0_STAGES, std: float = 0.02) -> Model:
+    """EfficientNet-B0 with batch norm folded into the convolutions (every conv carries a bias):
+    stem conv3x3 stride 2 (32 channels), 16 MBConv blocks (1x1 expansion, depthwise 3x3 / 5x5,
+    squeeze-and-excite with ratio 0.25 of the block input, 1x1 projection, residual when the
+    shape is kept), head conv1x1 (1280), global average pool, FC.  SiLU is written Sigmoid x Mul,
+    the SE gate Sigmoid.  Weights N(0, std) (0.02 as configured; tests widen it so that the
+    logits are not all bias), biases N(0, 0.02), from PCG64(seed), drawn in graph order.
+    `width` scales the channel counts (tests use a narrow copy); `image` must make the final
+    feature map square with an integral size (multiples of 32)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    g = GraphBuilder("efficientnet_b0")
+    ch = lambda c: max(8, int(round(c * width / 8)) * 8)
+    counter = [0]
+
+    def conv(x, cout, k, stride=1, group=1, act=None):
+        counter[0] += 1
+        cin = g.shapes[x][1]
+        w = g.const(f"conv{counter[0]}.w", (rng.standard_normal((cout, cin // group, k, k)) * std).astype(np.float32))
+        b = g.const(f"conv{counter[0]}.b", (rng.standard_normal(cout) * 0.02).astype(np.float32))
+        y = g.conv(x, w, b, pads=[k // 2] * 4, strides=[stride, stride], dilations=[1, 1], group=group)
+        if act == "silu":
+            y = g.mul(y, g.sigmoid(y))
+        elif act == "sigmoid":
+            y = g.sigmoid(y)
+        return y
+
+    x = g.input("input", 1, (batch, 3, image, image))
+    y = conv(x, ch(32), 3, stride=2, act="silu")
+    for expand, k, stride, cout, repeats in stages:
+        for r in range(repeats):
+            cin = g.shapes[y][1]
+            s = stride if r == 0 else 1
+            t = y
+            if expand != 1:
+                t = conv(t, cin * expand, 1, act="silu")
+            mid = g.shapes[t][1]
+            t = conv(t, mid, k, stride=s, group=mid, act="silu")
+            gate = g.reduce_mean(t, [2, 3])
+            gate = conv(gate, max(1, cin // 4), 1, act="silu")
+            gate = conv(gate, mid, 1, act="sigmoid")
+            t = g.mul(t, gate)
+            t = conv(t, ch(cout), 1)
+            y = g.add(y, t) if s == 1 and cin == ch(cout) else t
+    y = conv(y, ch(1280), 1, act="silu")
+    hw = g.shapes[y][2]
+    y = g.avgpool(y, [hw, hw])
+    y = g.flatten(y, 1)
+    fc_w = g.const("fc.w", (rng.standard_normal((classes, g.shapes[y][1])) * 0.02).astype(np.float32))
+    fc_b = g.const("fc.b", (rng.standard_normal(classes) * 0.02).astype(np.float32))
+    g.output(g.gemm(y, fc_w, fc_b, transB=1, out="logits"))
+    return g.finish()
+
+
+def efficientnet_inputs(seed: int = 1, batch: int = 1, image: int = 224):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return {"input": rng.standard_normal((batch, 3, image, image)).astype(np.float32)}
+
+
 # ------------------------------------------------------------------------------ GPT-NeoX
 def build_gpt_neox(seed: int = 0, layers: int = 24, hidden: int = 1024, heads: int = 16,
                    ffn: int = 4096, vocab: int = 50304, batch: int = 4, seq: int = 512,

@@ -220,7 +220,8 @@ typedef enum fml_gemm_act {
   FML_ACT_GELU_ERF = 1, /* v * (erf(v / c0) + c1) * c2, constants in act_param[3]         */
   FML_ACT_RELU = 2,
   FML_ACT_TANH = 3,
-  FML_ACT_SIGMOID = 4
+  FML_ACT_SIGMOID = 4,
+  FML_ACT_SILU = 5 /* x * sigmoid(x); fml_conv only */
 } fml_gemm_act;
 
 typedef enum fml_gemm_precision {

@@ -41,6 +41,9 @@ CASES = [  # (x shape, w shape, pads) -- VGG blocks, ragged tiles, 1x1, 5x5, few
     ((1, 512, 14, 14), (64, 512, 3, 3), (1, 1)),
     ((2, 48, 18, 10), (32, 48, 3, 3), (1, 1)),
     ((1, 24, 22, 14), (32, 24, 5, 5), (2, 2)),
+    # 1x1 kernels over 7 x 7 planes: whole planes fetched with a plain bulk copy
+    ((1, 64, 7, 7), (96, 64, 1, 1), (0, 0)),
+    ((3, 1152, 7, 7), (192, 1152, 1, 1), (0, 0)),
 ]
 
 
@@ -76,10 +79,26 @@ def test_conv_paths_agree_and_repeat():
     assert relerr(outs[0], outs[2]) <= 2e-5
 
 
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("act", [cabi.ACT_SIGMOID, cabi.ACT_SILU])
+def test_single_pixel_convolution_is_a_skinny_gemm(packed, act):
+    """Squeeze-and-excite convolutions (1 x 1 images): the product [N, IC] x [IC, OC] with bias and
+    gate in the epilogue, on the weight-streaming kernel."""
+    x, w, b = rnd(4, 1152, 1, 1), rnd(48, 1152, 1, 1) * 0.05, rnd(48)
+    t = orc.conv(x, w, b, np.empty((4, 48, 1, 1), np.float32), [0, 0], [1, 1], [1, 1], 1, acc64=True).astype(np.float64)
+    sig = 1.0 / (1.0 + np.exp(-t))
+    ref = sig if act == cabi.ACT_SIGMOID else t * sig
+    out = DT((4, 48, 1, 1), np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w, PACKED if packed else None), DT.from_numpy(b), out, [0, 0], [1, 1],
+              [1, 1], 1, act=act)
+    cabi.check_device()
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
 def test_conv_shapes_left_to_the_cuda_cores():
     w = DT.from_numpy(rnd(32, 16, 3, 3), PACKED)
     # 7 x 7 planes do not start on 16-byte steps; 50 columns neither fit a box nor one tile
-    for hw in ((7, 7), (9, 50)):
+    for hw in ((7, 7), (9, 50)):  # (3 x 3 kernels: the 7 x 7 case needs a halo, unlike 1 x 1 kernels)
         x, y = DT.from_numpy(rnd(1, 16, *hw)), DT((1, 32, *hw), np.float32)
         assert not cabi.conv_uses_tensor_cores(x, w, y, [1, 1])
         cabi.conv(x, w, None, y, [1, 1], [1, 1], [1, 1], 1)

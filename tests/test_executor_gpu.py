@@ -162,3 +162,23 @@ def test_plan_cache_and_cli_run(tmp_path):
     assert r.returncode == 0, r.stderr
     assert "ns per pass" in r.stdout
     assert "FusedGemmKernel" in (tmp_path / "launches.txt").read_text()
+
+
+def test_efficientnet_b0_and_full_size_vgg():
+    """EfficientNet-B0 (strided and depthwise convolutions, SiLU, squeeze-and-excite: operators
+    the reference cannot run) against the oracle on a narrow low-resolution copy whose weights
+    are wide enough for the logits not to be all bias; then the full-size models run and repeat
+    bit for bit (the oracle needs minutes for those)."""
+    e = models.build_efficientnet_b0(image=64, width=0.5, std=0.25, classes=100)
+    xe = models.efficientnet_inputs(image=64)
+    ref = orc.run_model(e, xe, acc64=True)
+    assert float(np.abs(ref["logits"]).max()) > 0.2
+    for factory in (Executor.make_plain_greedy, Executor.make_dp_greedy):
+        outs, ex = run(e, xe, factory)
+        assert relerr(outs["logits"], ref["logits"]) <= TOL
+        assert "SiluKernel" not in ex.stats()["kernels"]  # every SiLU rides in a convolution epilogue
+    for model, x, out in ((models.build_efficientnet_b0(), models.efficientnet_inputs(), "logits"),
+                          (models.build_vgg16(), models.vgg_inputs(), "output")):
+        a, _ = run(model, x, Executor.make_dp_greedy)
+        b, _ = run(model, x, Executor.make_dp_greedy)
+        assert np.isfinite(a[out]).all() and np.array_equal(a[out], b[out])
