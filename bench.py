@@ -257,6 +257,8 @@ def run_ours(args):
     dist_barrier(ctx)
     clocks = sampler.stop() if sampler else None
 
+    if ctx is not None:
+        ctx[0].destroy_process_group()
     if rank != 0:
         return
     value = args.gpus / dev_s
