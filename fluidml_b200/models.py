@@ -197,6 +197,14 @@ class GraphBuilder:
                self.const(f"steps{n}", np.ones(len(axes), dtype=np.int64))]
         return self._emit("Slice", ins, s, None, out)
 
+    def pad(self, x, pads: Sequence[int], out=None):
+        """Constant (zero) padding; `pads` = begins of every dim then ends, as in ONNX."""
+        self._n += 1
+        pc = self.const(f"pads{self._n}", np.asarray(pads, dtype=np.int64))
+        r = len(self.shapes[x])
+        s = [d + pads[i] + pads[r + i] for i, d in enumerate(self.shapes[x])]
+        return self._emit("Pad", [x, pc], s, None, out)
+
     def concat(self, a, b, axis, out=None):
         s = list(self.shapes[a])
         s[axis] += self.shapes[b][axis]
@@ -339,6 +347,86 @@ def build_vgg16(seed: int = 0, batch: int = 1, image: int = 224, classes: int = 
 def vgg_inputs(seed: int = 1, batch: int = 1, image: int = 224):
     rng = np.random.Generator(np.random.PCG64(seed))
     return {"input": rng.normal(0, 1, (batch, 3, image, image)).astype(np.float32)}
+
+
+# ------------------------------------------------------------------------------ ConvBERT
+def build_convbert(seed: int = 0, layers: int = 12, hidden: int = 768, heads: int = 12, head_ratio: int = 2,
+                   conv_kernel: int = 9, ffn: int = 3072, vocab: int = 30522, max_pos: int = 512,
+                   batch: int = 8, seq: int = 128, eps: float = 1e-12, name: str = "convbert") -> Model:
+    """ConvBERT encoder: per layer `heads / head_ratio` self-attention heads plus a span-based
+    dynamic convolution branch of the same width, concatenated before the output projection;
+    then the BERT feed-forward block.  The dynamic convolution is written with the operators
+    the reference converts: a depthwise Conv (1-D, kernel 9) + pointwise Conv over the
+    transposed hidden states make the span-aware key, key x query goes through a Linear to
+    `conv_kernel` logits per head and a Softmax, and the "unfold + matmul" over the value
+    projection is a zero Pad along the sequence followed by `conv_kernel` (Slice, Slice, Mul,
+    Add) steps.  Weights N(0, 0.02) from PCG64(seed) in graph order, LayerNorm gamma 1 beta 0."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    nrm = lambda *s: rng.normal(0.0, 0.02, size=s).astype(np.float32)
+    nh = heads // head_ratio
+    hd = hidden // heads
+    width = nh * hd  # of each branch
+    half = conv_kernel // 2
+    g = GraphBuilder(name)
+    ids = g.input("input_ids", INT64, (batch, seq))
+    am = g.input("attention_mask", FLOAT, (batch, seq))
+    word = g.const("embeddings.word", nrm(vocab, hidden))
+    pos = g.const("embeddings.position", nrm(max_pos, hidden)[:seq].reshape(1, seq, hidden).copy())
+    typ = g.const("embeddings.token_type", nrm(2, hidden)[0].copy())
+    ones, zeros = np.ones(hidden, np.float32), np.zeros(hidden, np.float32)
+    x = g.add(g.add(g.gather(word, ids, axis=0), pos), typ)
+    x = g.layernorm(x, g.const("embeddings.ln.g", ones), g.const("embeddings.ln.b", zeros), axis=-1, eps=eps)
+    m = g.unsqueeze(g.unsqueeze(am, [1]), [2])
+    mask = g.mul(g.sub(g.scalar(1.0), m), g.scalar(F32_LOWEST))
+
+    for l in range(layers):
+        p = f"layer{l}."
+
+        def linear(t, key, n_in, n_out):
+            w = g.const(p + key + ".w", nrm(n_in, n_out))
+            b = g.const(p + key + ".b", nrm(n_out))
+            return g.add(b, g.matmul(t, w))
+
+        q = linear(x, "q", hidden, width)
+        k = linear(x, "k", hidden, width)
+        v = linear(x, "v", hidden, width)
+        # span-aware key: depthwise conv over the sequence, then a pointwise conv (+ bias)
+        xt = g.transpose(x, (0, 2, 1))
+        dw = g.conv(xt, g.const(p + "kconv.dw", nrm(hidden, 1, conv_kernel)), None, pads=[half, half], strides=[1],
+                    dilations=[1], group=hidden)
+        pw = g.conv(dw, g.const(p + "kconv.pw", nrm(width, hidden, 1)), g.const(p + "kconv.b", nrm(width)),
+                    pads=[0, 0], strides=[1], dilations=[1])
+        kc = g.transpose(pw, (0, 2, 1))
+        ck = linear(g.mul(kc, q), "ck", width, nh * conv_kernel)
+        ck = g.softmax(g.reshape(ck, (batch, seq, nh, conv_kernel)), axis=-1)
+        co = g.reshape(linear(x, "co", hidden, width), (batch, seq, nh, hd))
+        co = g.pad(co, [0, half, 0, 0, 0, half, 0, 0])
+        acc = None
+        for j in range(conv_kernel):
+            term = g.mul(g.slice(co, [j], [j + seq], [1]), g.slice(ck, [j], [j + 1], [3]))
+            acc = term if acc is None else g.add(acc, term)
+        conv_out = g.reshape(acc, (batch, seq, width))
+        # self-attention over the other half of the heads
+        qh = g.transpose(g.reshape(q, (batch, seq, nh, hd)), (0, 2, 1, 3))
+        kt = g.transpose(g.reshape(k, (batch, seq, nh, hd)), (0, 2, 3, 1))
+        vh = g.transpose(g.reshape(v, (batch, seq, nh, hd)), (0, 2, 1, 3))
+        s = g.softmax(g.add(g.div(g.matmul(qh, kt), g.scalar(math.sqrt(hd))), mask), axis=-1)
+        ctx = g.reshape(g.transpose(g.matmul(s, vh), (0, 2, 1, 3)), (batch, seq, width))
+        cat = g.concat(ctx, conv_out, axis=2)
+        a = g.add(linear(cat, "o", hidden, hidden), x)
+        x = g.layernorm(a, g.const(p + "ln1.g", ones), g.const(p + "ln1.b", zeros), axis=-1, eps=eps)
+        h = linear(x, "f1", hidden, ffn)
+        e = g.erf(g.div(h, g.scalar(math.sqrt(2.0))))
+        h = g.mul(g.mul(h, g.add(e, g.scalar(1.0))), g.scalar(0.5))
+        a = g.add(linear(h, "f2", ffn, hidden), x)
+        x = g.layernorm(a, g.const(p + "ln2.g", ones), g.const(p + "ln2.b", zeros), axis=-1, eps=eps,
+                        out="last_hidden_state" if l == layers - 1 else None)
+    g.output("last_hidden_state")
+    return g.finish()
+
+
+def convbert_inputs(seed: int = 1, batch: int = 8, seq: int = 128, vocab: int = 30522):
+    return bert_inputs(seed, batch, seq, vocab)
 
 
 # ------------------------------------------------------------------------------ EfficientNet-B0

@@ -182,3 +182,16 @@ def test_efficientnet_b0_and_full_size_vgg():
         a, _ = run(model, x, Executor.make_dp_greedy)
         b, _ = run(model, x, Executor.make_dp_greedy)
         assert np.isfinite(a[out]).all() and np.array_equal(a[out], b[out])
+
+
+def test_convbert_small():
+    """ConvBERT: the span-based dynamic convolution branch (1-D depthwise + pointwise Conv over
+    the transposed hidden states, Softmax over the 9 kernel taps, Pad + sliding Slices) beside
+    the attention heads, Concat of the two; the Slices must stay views."""
+    m = models.build_convbert(layers=2, hidden=256, heads=8, ffn=512, vocab=400, batch=3, seq=48)
+    x = models.convbert_inputs(batch=3, seq=48, vocab=400)
+    ref = orc.run_model(m, x, acc64=True)
+    for factory in (Executor.make_plain_greedy, Executor.make_dp_greedy):
+        outs, ex = run(m, x, factory)
+        assert relerr(outs["last_hidden_state"], ref["last_hidden_state"]) <= TOL
+        assert "SliceKernel" not in ex.stats()["kernels"]
