@@ -321,12 +321,18 @@ class GatherConstantIndexScalarKernel : public SingleInputWithoutBufferKernel {
 public:
   GatherConstantIndexScalarKernel(int64_t axis, int64_t index) : axis_(axis), index_(index) {}
   std::string GetKernelName() const override { return "GatherConstantIndexScalarKernel"; }
-  void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
+  // One index along one axis is a view: the input without that axis, starting `index` steps in.
+  bool GetView(const fml_tensor &input, const fml_tensor &output, fml_tensor *view) const override {
     if (index_ < 0 || index_ >= input.shape[axis_]) throw Error("Gather: constant index is outside the gathered axis");
-    fml_tensor view = output;
-    view.data = Offset(input, index_ * input.stride[axis_]);
+    *view = output;
+    view->data = Offset(input, index_ * input.stride[axis_]);
     for (int i = 0, j = 0; i < input.rank; ++i)
-      if (i != axis_) view.stride[j++] = input.stride[i];
+      if (i != axis_) view->stride[j++] = input.stride[i];
+    return true;
+  }
+  void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
+    fml_tensor view;
+    GetView(input, output, &view);
     rec.Add(GetKernelName(), [=](void *s) { return fml_copy_strided(&view, &output, s); });
   }
 
