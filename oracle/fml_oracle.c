@@ -188,6 +188,12 @@ int orc_cast(const orc_tensor *in, orc_tensor *out) {
  * generator/matmul.cpp:88-131).  Both accumulate every c[i][j] sequentially in k, so
  * they give the same bits; i-k-j is only faster.  `acc64` accumulates in double, giving a
  * summation-order-independent target. */
+/* Rows of the product are independent, so they may be spread over host threads without
+ * changing a single bit (each row keeps its k order); orc_set_threads(n) sets how many
+ * (default 1: the reference executes single-threaded; the benchmark's CPU arm uses them all). */
+static int orc_threads = 1;
+void orc_set_threads(int n) { orc_threads = n < 1 ? 1 : n; }
+
 int orc_matmul(const orc_tensor *a, const orc_tensor *b, orc_tensor *c, int order, int acc64) {
   int r = c->rank;
   int64_t M = c->shape[r - 2], N = c->shape[r - 1], K = a->shape[a->rank - 1];
@@ -196,7 +202,6 @@ int orc_matmul(const orc_tensor *a, const orc_tensor *b, orc_tensor *c, int orde
   int64_t sam = a->stride[a->rank - 2], sak = a->stride[a->rank - 1];
   int64_t sbk = b->stride[b->rank - 2], sbn = b->stride[b->rank - 1];
   int64_t scm = c->stride[r - 2], scn = c->stride[r - 1];
-  double *acc = acc64 ? (double *)malloc(sizeof(double) * (size_t)N) : NULL;
   for (int64_t bi = 0; bi < batch; ++bi) {
     unravel(bi, c->shape, r - 2, idx);
     int64_t oa = 0, ob = 0, oc = 0;
@@ -208,6 +213,10 @@ int orc_matmul(const orc_tensor *a, const orc_tensor *b, orc_tensor *c, int orde
     }
     const float *A = (const float *)a->data + oa, *B = (const float *)b->data + ob;
     float *C = (float *)c->data + oc;
+#pragma omp parallel num_threads(orc_threads) if (orc_threads > 1)
+    {
+    double *acc = acc64 ? (double *)malloc(sizeof(double) * (size_t)N) : NULL;
+#pragma omp for schedule(static)
     for (int64_t i = 0; i < M; ++i) {
       if (acc64) {
         for (int64_t j = 0; j < N; ++j) acc[j] = 0.0;
@@ -230,8 +239,9 @@ int orc_matmul(const orc_tensor *a, const orc_tensor *b, orc_tensor *c, int orde
         }
       }
     }
+    free(acc);
+    }
   }
-  free(acc);
   return 0;
 }
 

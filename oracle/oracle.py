@@ -28,7 +28,7 @@ def build(force: bool = False) -> str:
     """Compile fml_oracle.c.  -ffp-contract=off keeps a*b+c as two rounded operations, as
     the reference's separate arith.mulf / arith.addf ops are."""
     if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(_SRC):
-        subprocess.check_call(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fPIC",
+        subprocess.check_call(["gcc", "-O3", "-march=native", "-ffp-contract=off", "-fopenmp", "-fPIC",
                                "-shared", "-o", _SO, _SRC, "-lm"])
     return _SO
 
@@ -86,6 +86,11 @@ def unary(op: str, x, out, p0=0.0, p1=0.0):
     assert lib().orc_unary(UN[op], _p(T(x)), _p(T(out)), ctypes.c_float(p0),
                            ctypes.c_float(p1)) == 0
     return out
+
+
+def set_threads(n: int) -> None:
+    """Host threads the matrix products may use (rows are independent: the bits do not change)."""
+    lib().orc_set_threads(int(n))
 
 
 def matmul(a, b, out, order=1, acc64=False):
