@@ -27,7 +27,10 @@
 // the OIHW tensor stored with layout permutation (3, 2, 0, 1)): the B tile of a (tap, channel
 // block) is then an MN-major box, loaded exactly like the GEMM's MN-major B.
 //
-// Roles (192 threads) and the bounded waits are those of the GEMM kernel (gemm_tc.cu).
+// Roles and bounded waits follow the GEMM kernel (gemm_tc.cu), with one difference: cutting a tap
+// out of the patch and splitting it is the longest stage of a k block here (the tensor pipe was
+// 27 % busy with one set of converter warps), so two sets of four converter warps take the k
+// blocks alternately, and share the epilogue's columns.
 #include "gemm_common.cuh"
 #include "tc_common.cuh"
 #include <algorithm>
@@ -35,7 +38,7 @@
 namespace fml {
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // producer warp, MMA warp, two sets of four converter / epilogue warps
 constexpr size_t kSmemBudget = 200 * 1024;
 
 struct ConvTcArgs {
@@ -124,7 +127,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int s = 0; s < RS; ++s) {
       mbar_init(bar_rfull + 8u * s, 1);
-      mbar_init(bar_rempty + 8u * s, 4);
+      mbar_init(bar_rempty + 8u * s, 8);  // both converter sets must have left the patch
     }
     mbar_init(bar_accum, 1);
     *abort_flag = 0;
@@ -212,7 +215,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ A gather + operand split, then epilogue
-    const int et = threadIdx.x - 64;
+    const int set = (warp - 2) >> 2;          // converter set 0 takes the even k blocks, set 1 the odd ones
+    const int et = (threadIdx.x - 64) & 127;  // thread within the set
     const int q = warp & 3, m = q * 32 + lane;  // output position = TMEM lane
     const int r = m / a.TW, c = m - r * a.TW;
     const int plane = a.plane;
@@ -226,6 +230,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (!ok) break;
       const uint32_t *rawp = reinterpret_cast<const uint32_t *>(raw_ptr + (size_t)rs * raw_pitch);
       for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
+        if ((kb & 1) != set) continue;
         const int kh = tap / a.KW, kw = tap - kh * a.KW;
         const int s = kb % NS;
         const uint32_t phs = ((uint32_t)(kb / NS)) & 1u;
@@ -292,7 +297,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                                  // warp-wide TMEM loads
     float *yp = a.y + (int64_t)n * a.ys[0] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3];
     if (ok) {
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      // the two sets share the tile's columns: set 0 the first half of the 32-column groups
+      const int groups = BN / 32, half = (groups + 1) / 2;
+      const int c_lo = set == 0 ? 0 : half * 32, c_hi = set == 0 ? half * 32 : BN;
+      for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
         float v[32];
         tmem_ld32(lane_addr + (uint32_t)c0, v);
         if (inside) {
