@@ -177,6 +177,13 @@ def test_efficientnet_b0_and_full_size_vgg():
         outs, ex = run(e, xe, factory)
         assert relerr(outs["logits"], ref["logits"]) <= TOL
         assert "SiluKernel" not in ex.stats()["kernels"]  # every SiLU rides in a convolution epilogue
+    # full-size EfficientNet-B0 (224 x 224: every map size from 112 down to 7 and 1) against the
+    # oracle, again with weights wide enough for the logits to carry signal
+    full = models.build_efficientnet_b0(std=0.16)
+    xf = models.efficientnet_inputs()
+    ref = orc.run_model(full, xf, acc64=True)
+    outs, _ = run(full, xf, Executor.make_dp_greedy)
+    assert float(np.abs(ref["logits"]).max()) > 0.2 and relerr(outs["logits"], ref["logits"]) <= TOL
     for model, x, out in ((models.build_efficientnet_b0(), models.efficientnet_inputs(), "logits"),
                           (models.build_vgg16(), models.vgg_inputs(), "output")):
         a, _ = run(model, x, Executor.make_dp_greedy)
