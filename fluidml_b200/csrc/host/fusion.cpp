@@ -229,20 +229,47 @@ bool FuseAddLayerNorm(Rewriter &rw, const NodePtr &add) {
   return true;
 }
 
-// ---- x / c -> + mask -> Softmax  (attention scores)
+// ---- x / c -> + mask -> Softmax  (attention scores); the mask may also be a constant-condition
+// Where that replaces masked scores by a scalar (a causal mask): Where(cond, s, y) feeds the
+// softmax the same values as s + m with m = cond ? 0 : y whenever y is so negative that
+// s + y rounds to y (the usual float lowest), so it becomes a baked additive mask.
 bool FuseScaledMaskedSoftmax(Rewriter &rw, const NodePtr &div) {
   if (div->kind != Kind::DivConstantRhs) return false;
   NodePtr nx = rw.Sole(div->output);
   if (!nx) return false;
-  NodePtr add = nullptr, sm = nullptr;
+  NodePtr add = nullptr, where = nullptr, sm = nullptr;
   if (nx->kind == Kind::AddCommon) {
     add = nx;
     if (add->output->meta != div->output->meta) return false;
     sm = rw.SoleOfKind(add->output, Kind::Softmax);
+  } else if (nx->kind == Kind::WhereConstantCondConstantScalarY) {
+    where = nx;
+    // s + y == y needs |y| >= 2^25 |s|: accept the float lowest and anything within 2^-40 of it
+    if (where->output->meta != div->output->meta || !(where->value <= -3.0e26) ||
+        where->consts.empty() || !where->consts[0]->constant)
+      return false;
+    sm = rw.SoleOfKind(where->output, Kind::Softmax);
   } else if (nx->kind == Kind::Softmax) {
     sm = nx;
   }
   if (!sm || sm->axis != (int64_t)sm->output->meta.GetRank() - 1) return false;
+  RegionPtr mask = nullptr;
+  if (where) {
+    const RegionPtr &cond = where->consts[0];
+    const int64_t n = (int64_t)cond->meta.GetElementsNum();
+    std::vector<uint8_t> bytes((size_t)n * 4);
+    float *m = reinterpret_cast<float *>(bytes.data());
+    const float y = (float)where->value;
+    for (int64_t i = 0; i < n; ++i) m[i] = cond->constant->AsInt(i) ? 0.0f : y;
+    mask = std::make_shared<flow::Region>();
+    mask->kind = flow::Region::kConstant;
+    mask->name = where->name + "_additive_mask";
+    mask->meta = Meta(Type::kFloat32, cond->meta.GetShape());
+    mask->layout = utils::GenDefaultLayout(cond->meta.GetRank());
+    mask->constant = std::make_shared<Tensor>(mask->meta, std::move(bytes));
+    rw.f.regions.push_back(mask);
+    rw.f.by_name[mask->name] = mask;
+  }
   sm->kind = Kind::FusedSoftmax;
   sm->divisor = (float)div->value;
   sm->inputs = {div->inputs[0]};
@@ -250,6 +277,10 @@ bool FuseScaledMaskedSoftmax(Rewriter &rw, const NodePtr &div) {
     sm->inputs.push_back(Other(add, div->output));
     sm->has_mask = true;
     rw.Kill(add);
+  } else if (where) {
+    sm->inputs.push_back(mask);
+    sm->has_mask = true;
+    rw.Kill(where);
   }
   rw.Kill(div);
   return true;

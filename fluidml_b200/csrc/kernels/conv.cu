@@ -206,6 +206,31 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     return skinny_eligible(g) ? launch_gemm_skinny(g, e, s) : launch_gemm_simt(g, e, s);
   }
   if (group == 1 && nd == 2 && conv_tc_eligible(x, w, y, p)) return launch_conv_tc(x, w, bias, y, p, s);
+  if (group == 1 && a.KH == 1 && a.KW == 1 && a.ph == 0 && a.pw == 0 && a.sh == 1 && a.sw == 1 && a.ws[1] == 1 &&
+      a.xs[3] == 1 && (nd == 1 || a.xs[2] == a.IW) && a.ys[3] == 1 && (nd == 1 || a.ys[2] == a.OW) &&
+      a.act <= FML_ACT_SIGMOID && a.OH == a.IH && a.OW == a.IW) {
+    // A pointwise convolution with channel-contiguous weights is, per image, the product
+    // W [OC, IC] x X [IC, H*W] (pixels contiguous: an MN-major B operand): fml_gemm takes it, on
+    // tensor cores when the pixel count is a multiple of 4, with the bias per output row.
+    fml_tensor A, B, C, bias_t;
+    memset(&A, 0, sizeof(A)); memset(&B, 0, sizeof(B)); memset(&C, 0, sizeof(C)); memset(&bias_t, 0, sizeof(bias_t));
+    const int64_t HW = a.IH * a.IW;
+    A.data = const_cast<float *>(a.w); A.dtype = FML_F32; A.rank = 2;
+    A.shape[0] = a.OC; A.shape[1] = a.IC; A.stride[0] = a.ws[0]; A.stride[1] = 1;
+    B.data = const_cast<float *>(a.x); B.dtype = FML_F32; B.rank = 3;
+    B.shape[0] = a.N; B.shape[1] = a.IC; B.shape[2] = HW; B.stride[0] = a.xs[0]; B.stride[1] = a.xs[1]; B.stride[2] = 1;
+    C.data = a.y; C.dtype = FML_F32; C.rank = 3;
+    C.shape[0] = a.N; C.shape[1] = a.OC; C.shape[2] = HW; C.stride[0] = a.ys[0]; C.stride[1] = a.ys[1]; C.stride[2] = 1;
+    bias_t.data = const_cast<float *>(a.bias); bias_t.dtype = FML_F32; bias_t.rank = 2;
+    bias_t.shape[0] = a.OC; bias_t.shape[1] = 1; bias_t.stride[0] = a.bias_stride; bias_t.stride[1] = 0;
+    fml_gemm_params gp;
+    fml_gemm_default_params(&gp);
+    gp.precision = p->precision;
+    gp.act = a.act;
+    gp.b_constant = 0;
+    const int st = fml_gemm(&A, &B, &C, a.bias ? &bias_t : nullptr, nullptr, &gp, stream);
+    if (st != FML_MISALIGNED) return st;  // a forced tensor-core precision on unaligned planes: CUDA cores below
+  }
   if (group == 1) {
     FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");
     dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));

@@ -103,3 +103,17 @@ def test_conv_shapes_left_to_the_cuda_cores():
         assert not cabi.conv_uses_tensor_cores(x, w, y, [1, 1])
         cabi.conv(x, w, None, y, [1, 1], [1, 1], [1, 1], 1)
     cabi.check_device()
+
+
+@pytest.mark.parametrize("xs,oc", [((8, 768, 128), 384), ((2, 96, 50), 40), ((1, 64, 12, 20), 32)])
+def test_pointwise_convolution_with_row_major_weights_is_a_gemm(xs, oc):
+    """1 x 1 kernels over dense planes with OIHW weights (the 1-D pointwise convolution of
+    ConvBERT's separable convolution): W [OC, IC] x X [IC, pixels] per image through fml_gemm."""
+    nd = len(xs) - 2
+    x, w, b = rnd(*xs), rnd(oc, xs[1], *([1] * nd)) * 0.05, rnd(oc)
+    oshape = (xs[0], oc, *xs[2:])
+    ref = orc.conv(x, w, b, np.empty(oshape, np.float32), [0] * nd, [1] * nd, [1] * nd, 1, acc64=True)
+    out = DT(oshape, np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), out, [0] * nd, [1] * nd, [1] * nd, 1)
+    cabi.check_device()
+    assert relerr(out.numpy(), ref) <= 2e-5

@@ -306,3 +306,13 @@ def test_cli_options_follow_the_reference(bert_bytes):
             arenas[mode] = st["peak_arena_bytes"]
             assert set(json.load(open(os.path.join(d, mode)))) == {"dp_table", "plan", "arena"}
         assert arenas["dp_greedy"] < arenas["plain_linear"]
+
+
+def test_causal_where_becomes_an_additive_mask():
+    """GPT-NeoX: Div -> Where(constant causal condition, s, lowest) -> Softmax turns into one scaled
+    masked softmax with a baked additive mask (and, at this size, into the attention kernel)."""
+    g = models.build_gpt_neox(layers=1, hidden=128, heads=2, ffn=256, vocab=200, batch=1, seq=32).to_bytes()
+    unfused, fused = kinds_of(g, fusion=0), kinds_of(g, fusion=1)
+    assert "WhereConstantCondConstantScalarY" in unfused and "DivConstantRhs" in unfused
+    assert "WhereConstantCondConstantScalarY" not in fused and "DivConstantRhs" not in fused
+    assert ("FusedAttention" in fused) or ("FusedSoftmax" in fused)
