@@ -252,6 +252,217 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
   trace_stamp();
 }
 
+// Keys and values that do not fit in shared memory at once (long sequences) stream through it in
+// chunks of 128 keys with the running-maximum ("online") softmax: per chunk the scores, their
+// maximum m' = max(m, chunk max), the weights e = exp(s - m'), and the context accumulator and
+// the normaliser l rescaled by exp(m - m') before the chunk's contribution is added; the output
+// is accumulator / l.  The arithmetic is that of softmax followed by the product, in another
+// order (within a few ulp per element).  Tiles, thread mappings and the warp-ordered reduction
+// are those of attention_kernel.
+constexpr int kChunk = 128;
+
+__global__ void __launch_bounds__(kThreads) attention_flash_kernel(AttnArgs a) {
+  pdl_prologue();
+  extern __shared__ __align__(16) float smem[];
+  const int D = (int)a.D, Dv = (int)a.Dv, Sk = (int)a.Sk;
+  const int pk = D + 4, pp = kChunk | 1;
+  float *Qs = smem;                        // [kRows][pk]
+  float *Ks = Qs + kRows * pk;             // [kChunk][pk]
+  float *Vs = Ks + (size_t)kChunk * pk;    // [kChunk][Dv]
+  float *Red = Vs + (size_t)kChunk * Dv;   // [8][kRows][Dv]
+  float *Ps = Red + 8 * kRows * Dv;        // [kRows][pp]
+  float *Ms = Ps + kRows * pp;             // [kRows or 1][kChunk]
+  float *row_m = Ms + kRows * kChunk;      // [kRows] running maximum
+  float *row_l = row_m + kRows;            // [kRows] running normaliser
+  float *row_scale = row_l + kRows;        // [kRows] exp(old maximum - new maximum) of the current chunk
+  const int64_t z0 = blockIdx.y % a.nb0, z1 = blockIdx.y / a.nb0;
+  const int64_t row0 = (int64_t)blockIdx.x * kRows;
+  const int rows = (int)min((int64_t)kRows, a.Sq - row0);
+  const float *q = a.q + z1 * a.q_s[0] + z0 * a.q_s[1] + row0 * a.q_s[2];
+  const float *k = a.k + z1 * a.k_s[0] + z0 * a.k_s[1];
+  const float *v = a.v + z1 * a.v_s[0] + z0 * a.v_s[1];
+  float *o = a.out + z1 * a.o_s[0] + z0 * a.o_s[1] + row0 * a.o_s[2];
+  const float *m = a.mask ? a.mask + z1 * a.m_s[0] + z0 * a.m_s[1] + row0 * a.m_s[2] : nullptr;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mrows = m ? (a.m_s[2] == 0 ? 1 : rows) : 0;
+
+  if (rows < kRows)
+    for (int i = threadIdx.x; i < (kRows - rows) * pk; i += kThreads) Qs[rows * pk + i] = 0.0f;
+  if (threadIdx.x < kRows) { row_m[threadIdx.x] = -3.402823466e+38f; row_l[threadIdx.x] = 0.0f; }
+  load_tile(Qs, pk, q, rows, D, a.q_s[2], a.q_s[3]);
+  // context accumulators of the threads that combine the partial tiles: 16 rows x Dv / 4 quads over
+  // 256 threads = at most two per thread (Dv <= 128)
+  float4 acc_out0 = make_float4(0.f, 0.f, 0.f, 0.f), acc_out1 = acc_out0;
+
+  for (int j0 = 0; j0 < Sk; j0 += kChunk) {
+    const int kc = min(kChunk, Sk - j0);
+    __syncthreads();  // the previous chunk's K, V, P and partial tiles are no longer read
+    load_tile(Ks, pk, k + (int64_t)j0 * a.k_s[3], kc, D, a.k_s[3], a.k_s[2]);
+    if (mrows) load_tile(Ms, kChunk, m + (int64_t)j0 * a.m_s[3], mrows, kc, a.m_s[2], a.m_s[3]);
+    cp_async_commit();
+    load_tile(Vs, Dv, v + (int64_t)j0 * a.v_s[2], kc, Dv, a.v_s[2], a.v_s[3]);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    // ---- scores of the chunk
+    {
+      const int half = warp >> 2, rq = warp & 3, cq = lane;
+      const int n4 = D >> 2, d_lo = half ? n4 >> 1 : 0, d_hi = half ? n4 : n4 >> 1;
+      float acc[4][4];
+      const float4 *k4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[x][u] = 0.0f;
+        k4[u] = reinterpret_cast<const float4 *>(Ks + (size_t)min(cq + 32 * u, kc - 1) * pk);
+      }
+      const float4 *q4 = reinterpret_cast<const float4 *>(Qs + rq * pk);
+#pragma unroll 2
+      for (int d = d_lo; d < d_hi; ++d) {
+        float4 qv[4], kv[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) qv[x] = q4[x * pk + d];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) kv[u] = k4[u][d];
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            acc[x][u] = fmaf(qv[x].x, kv[u].x, acc[x][u]);
+            acc[x][u] = fmaf(qv[x].y, kv[u].y, acc[x][u]);
+            acc[x][u] = fmaf(qv[x].z, kv[u].z, acc[x][u]);
+            acc[x][u] = fmaf(qv[x].w, kv[u].w, acc[x][u]);
+          }
+      }
+      for (int turn = 0; turn < 2; ++turn) {
+        if (turn == half) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int j = cq + 32 * u;
+              if (j < kc) {
+                float *dst = Ps + (rq + 4 * x) * pp + j;
+                *dst = turn ? *dst + acc[x][u] : acc[x][u];
+              }
+            }
+        }
+        __syncthreads();
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    // ---- running softmax of the chunk
+    {
+      const int r = threadIdx.x >> 4, cg = threadIdx.x & 15;
+      const bool live = r < rows;
+      float *p = Ps + r * pp;
+      const float *mr = Ms + (mrows > 1 ? r * kChunk : 0);
+      const float m_old = row_m[r], l_old = row_l[r];
+      float mx = m_old;
+      if (live)
+        for (int j = cg; j < kc; j += 16) {
+          float sc = p[j];
+          if (a.divisor != 1.0f) sc = sc / a.divisor;
+          if (m) sc += mr[j];
+          p[j] = sc;
+          mx = fmaxf(mx, sc);
+        }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+      float sum = 0.0f;
+      for (int j = cg; j < kc; j += 16) {
+        const float e = live ? expf(p[j] - mx) : 0.0f;
+        p[j] = e;
+        sum += e;
+      }
+#pragma unroll
+      for (int o2 = 8; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+      __syncwarp();
+      if (cg == 0) {
+        const float sc = expf(m_old - mx);  // 0 for the first chunk (m_old is the float lowest)
+        row_scale[r] = sc;
+        row_m[r] = mx;
+        row_l[r] = l_old * sc + sum;
+      }
+    }
+    __syncthreads();
+    // ---- context contribution of the chunk, added to the rescaled accumulators
+    {
+      const int rg = lane >> 3, cgp = lane & 7;
+      const int per = (kc + 7) >> 3, j_lo = min(kc, warp * per), j_hi = min(kc, j_lo + per);
+      const float *p0 = Ps + rg * pp;
+      int pass = 0;
+      for (int dv0 = 0; dv0 < Dv; dv0 += 64, ++pass) {
+        const int ca = dv0 + cgp * 4, cb = ca + 32;
+        const bool has_a = ca < Dv, has_b = cb < Dv;
+        float4 acc[4][2];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[x][0] = acc[x][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+        for (int j = j_lo; j < j_hi; ++j) {
+          const float *vr = Vs + (size_t)j * Dv;
+          const float4 va = has_a ? *reinterpret_cast<const float4 *>(vr + ca) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 vb = has_b ? *reinterpret_cast<const float4 *>(vr + cb) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float pj = p0[4 * x * pp + j];
+            acc[x][0].x = fmaf(pj, va.x, acc[x][0].x); acc[x][0].y = fmaf(pj, va.y, acc[x][0].y);
+            acc[x][0].z = fmaf(pj, va.z, acc[x][0].z); acc[x][0].w = fmaf(pj, va.w, acc[x][0].w);
+            acc[x][1].x = fmaf(pj, vb.x, acc[x][1].x); acc[x][1].y = fmaf(pj, vb.y, acc[x][1].y);
+            acc[x][1].z = fmaf(pj, vb.z, acc[x][1].z); acc[x][1].w = fmaf(pj, vb.w, acc[x][1].w);
+          }
+        }
+        if (dv0) __syncthreads();
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float *dst = Red + ((size_t)warp * kRows + rg + 4 * x) * Dv;
+          if (has_a) *reinterpret_cast<float4 *>(dst + ca) = acc[x][0];
+          if (has_b) *reinterpret_cast<float4 *>(dst + cb) = acc[x][1];
+        }
+        __syncthreads();
+        const int w4 = min(64, Dv - dv0) >> 2;
+        const int i = threadIdx.x;  // 16 rows x at most 16 quads: one (row, quad) per thread and pass
+        if (i < kRows * w4) {
+          const int r = i / w4, c = dv0 + ((i - r * w4) << 2);
+          float4 t = *reinterpret_cast<const float4 *>(Red + (size_t)r * Dv + c);
+#pragma unroll
+          for (int w = 1; w < 8; ++w) {
+            const float4 u = *reinterpret_cast<const float4 *>(Red + ((size_t)w * kRows + r) * Dv + c);
+            t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+          }
+          const float sc = row_scale[r];
+          float4 &ao = pass == 0 ? acc_out0 : acc_out1;
+          ao.x = ao.x * sc + t.x; ao.y = ao.y * sc + t.y; ao.z = ao.z * sc + t.z; ao.w = ao.w * sc + t.w;
+        }
+      }
+    }
+  }
+  // ---- out = accumulator / normaliser
+  int pass = 0;
+  for (int dv0 = 0; dv0 < Dv; dv0 += 64, ++pass) {
+    const int w4 = min(64, Dv - dv0) >> 2;
+    const int i = threadIdx.x;
+    if (i < kRows * w4) {
+      const int r = i / w4, c = dv0 + ((i - r * w4) << 2);
+      if (r < rows) {
+        const float l = row_l[r];
+        const float4 ao = pass == 0 ? acc_out0 : acc_out1;
+        const float4 t = make_float4(ao.x / l, ao.y / l, ao.z / l, ao.w / l);
+        float *dst = o + r * a.o_s[2] + c * a.o_s[3];
+        const bool ovec = a.o_s[3] == 1 && (a.o_s[2] & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0;
+        if (ovec) *reinterpret_cast<float4 *>(dst) = t;
+        else { dst[0] = t.x; dst[a.o_s[3]] = t.y; dst[2 * a.o_s[3]] = t.z; dst[3 * a.o_s[3]] = t.w; }
+      }
+    }
+  }
+}
+
+size_t attn_flash_smem_bytes(int64_t D, int64_t Dv) {
+  return (size_t)(kRows * (D + 4) + kChunk * (D + 4) + kChunk * Dv + 8 * kRows * Dv + kRows * (kChunk | 1) +
+                  kRows * kChunk + 3 * kRows) * sizeof(float);
+}
+
 size_t attn_smem_bytes(int64_t Sk, int64_t D, int64_t Dv) {
   return (size_t)(kRows * (D + 4) + Sk * (D + 4) + Sk * Dv + 8 * kRows * Dv + kRows * (Sk | 1) + kRows * Sk) * sizeof(float);
 }
@@ -273,8 +484,9 @@ bool as4(const fml_tensor *t, int64_t shape[4], int64_t stride[4]) {
 using namespace fml;
 
 extern "C" int fml_attention_supported(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v) {
+  // any number of keys: those that do not fit in shared memory at once stream through it
   return s_q >= 1 && s_k >= 1 && d >= 4 && d_v >= 4 && d <= 128 && d_v <= 128 && (d & 3) == 0 && (d_v & 3) == 0 &&
-                 attn_smem_bytes(s_k, d, d_v) <= kSmemLimit
+                 (attn_smem_bytes(s_k, d, d_v) <= kSmemLimit || attn_flash_smem_bytes(d, d_v) <= kSmemLimit)
              ? 1 : 0;
 }
 
@@ -312,15 +524,19 @@ extern "C" int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fm
   a.mask = mask ? (const float *)mask->data : nullptr;
   a.out = (float *)out->data;
   a.divisor = divisor;
-  const size_t smem = attn_smem_bytes(a.Sk, a.D, a.Dv);
+  const bool whole = attn_smem_bytes(a.Sk, a.D, a.Dv) <= attn_flash_smem_bytes(a.D, a.Dv) ||
+                     attn_flash_smem_bytes(a.D, a.Dv) > kSmemLimit;  // K and V of a head fit at once
+  const size_t smem = whole ? attn_smem_bytes(a.Sk, a.D, a.Dv) : attn_flash_smem_bytes(a.D, a.Dv);
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     FML_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
+    FML_CUDA(cudaFuncSetAttribute(attention_flash_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
     attr_set[dev] = true;
   }
   const dim3 grid((unsigned)((a.Sq + kRows - 1) / kRows), (unsigned)(a.nb0 * a.nb1));
-  FML_LAUNCH((attention_kernel), grid, kThreads, smem, as_stream(stream), a);
+  if (whole) FML_LAUNCH((attention_kernel), grid, kThreads, smem, as_stream(stream), a);
+  else FML_LAUNCH((attention_flash_kernel), grid, kThreads, smem, as_stream(stream), a);
   return FML_OK;
 }

@@ -185,8 +185,10 @@ int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
  * keys, as the MatMul receives them), v [.., S_k, D_v], out [.., S_q, D_v], ranks 2 to 4 with
  * equal leading dims; mask (may be NULL) broadcasts to [.., S_q, S_k].  Any strides: the
  * head-split transposes can stay views.  fp32 FMA throughout; the scores never leave the SM.
- * fml_attention_supported tells whether a shape fits (head sizes multiples of 4 up to 128,
- * K and V of one head in shared memory); fml_attention returns FML_UNSUPPORTED otherwise. */
+ * K and V of a head are staged once when they fit in shared memory; longer key sequences stream
+ * through it in chunks of 128 keys with a running-maximum softmax.  fml_attention_supported
+ * tells whether a shape is taken (head sizes multiples of 4 up to 128); fml_attention returns
+ * FML_UNSUPPORTED otherwise. */
 int fml_attention_supported(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v);
 int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fml_tensor *v,
                   const fml_tensor *mask, float divisor, const fml_tensor *out, void *stream);

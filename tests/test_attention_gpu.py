@@ -38,6 +38,8 @@ def relerr(got, ref):
 @pytest.mark.parametrize("shape", [  # (batch dims, S_q, S_k, D, D_v)
     ((1, 12), 128, 128, 64, 64), ((2, 3), 37, 50, 8, 12), ((4,), 16, 160, 32, 128), ((), 5, 7, 4, 4),
     ((1, 2), 130, 129, 128, 64),
+    # more keys than fit in shared memory at once: chunks of 128 keys, running-maximum softmax
+    ((2, 4), 512, 512, 64, 64), ((3,), 40, 700, 32, 128), ((1,), 16, 129, 128, 64), ((2,), 100, 1000, 8, 4),
 ])
 @pytest.mark.parametrize("with_mask", [False, True])
 def test_attention_contiguous(shape, with_mask):
@@ -82,8 +84,22 @@ def test_attention_generic_strides_and_limits():
     cabi.check_device()
     assert relerr(out.numpy(), oracle_attention(q, kt, v, None, 4.0)) <= TOL
     assert not cabi.attention_supported(128, 128, 66, 64)      # head size not a multiple of 4
-    assert not cabi.attention_supported(128, 4096, 64, 64)     # K and V of a head exceed shared memory
+    assert not cabi.attention_supported(128, 128, 256, 64)     # head size above 128
+    assert cabi.attention_supported(128, 4096, 64, 64)         # long key sequences stream in chunks
     with pytest.raises(cabi.FmlError) as e:
         cabi.attention(DT.from_numpy(rnd(8, 6)), DT.from_numpy(rnd(6, 8)), DT.from_numpy(rnd(8, 4)), None, 1.0,
                        DT((8, 4), np.float32))
     assert e.value.status == 2
+
+
+@pytest.mark.parametrize("s", [64, 512])
+def test_attention_causal_mask(s):
+    """A causal additive mask [1, 1, S, S] (0 on and below the diagonal, the float lowest above):
+    per-row mask values, in the kernel that stages K and V whole (S = 64) and in the streaming
+    one (S = 512)."""
+    q, kt, v = rnd(2, 3, s, 64), rnd(2, 3, 64, s), rnd(2, 3, s, 64)
+    mask = np.where(np.tril(np.ones((s, s), bool)), 0.0, np.finfo(np.float32).min).astype(np.float32)[None, None]
+    out = DT((2, 3, s, 64), np.float32)
+    cabi.attention(DT.from_numpy(q), DT.from_numpy(kt), DT.from_numpy(v), DT.from_numpy(mask), 8.0, out)
+    cabi.check_device()
+    assert relerr(out.numpy(), oracle_attention(q, kt, v, mask, 8.0)) <= TOL
