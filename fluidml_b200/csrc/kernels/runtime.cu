@@ -196,11 +196,16 @@ int fml_warmup(void) {
 }
 
 int fml_check_device(void *stream) {
-  FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
   int *w = device_status_word();
   FML_REQUIRE(w, FML_CUDA_ERROR, "fml_check_device: no status word");
-  int v = 0;
-  FML_CUDA(cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost));
+  // The status word rides the stream into a pinned host word, so that one synchronisation serves
+  // both the caller's work and the check (a blocking copy after the synchronise costs a second
+  // round trip on every Invoke).  One pinned word per calling thread.
+  static thread_local int *pinned = nullptr;
+  if (!pinned) FML_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&pinned), sizeof(int), cudaHostAllocDefault));
+  FML_CUDA(cudaMemcpyAsync(pinned, w, sizeof(int), cudaMemcpyDeviceToHost, as_stream(stream)));
+  FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  const int v = *pinned;
   if (v) FML_CUDA(cudaMemset(w, 0, sizeof(int)));
   if (v & kStatusTimeout) {
     set_error("a bounded device-side wait expired");
