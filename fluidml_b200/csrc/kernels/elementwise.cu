@@ -153,6 +153,65 @@ __global__ void bias_gelu_generic(Iter<3> it, float *out, const float *x, const 
   }
 }
 
+// Offsets of the float4 with linear index i when the innermost dim is walked 4 elements at a
+// time: operand o advances 4 * c4 elements when its innermost stride is 1, nothing when it is 0.
+template <int N>
+__device__ __forceinline__ void vec4_offsets(const Iter<N> &it, int64_t i, int64_t inner4, int64_t off[N]) {
+  int64_t row = i / inner4;
+  const int64_t c4 = i - row * inner4;
+#pragma unroll
+  for (int o = 0; o < N; ++o) off[o] = it.stride[o][it.rank - 1] == 1 ? c4 * 4 : 0;
+  for (int d = it.rank - 2; d >= 0; --d) {
+    const int64_t q = row / it.shape[d], c = row - q * it.shape[d];
+    row = q;
+#pragma unroll
+    for (int o = 0; o < N; ++o) off[o] += c * it.stride[o][d];
+  }
+}
+
+// 16-byte variants of the two kernels above (innermost dim: out stride 1, inputs stride 1 or 0,
+// extent a multiple of 4, everything 16-byte aligned).
+__global__ void bias_gelu_vec4(Iter<3> it, float *out, const float *x, const float *bias, float c0, float c1, float c2) {
+  pdl_prologue();
+  const int64_t inner4 = it.shape[it.rank - 1] >> 2, total4 = it.total >> 2;
+  const bool x_vec = it.stride[1][it.rank - 1] == 1, b_vec = it.stride[2][it.rank - 1] == 1;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[3];
+    vec4_offsets<3>(it, i, inner4, off);
+    float4 xv, bv;
+    if (x_vec) xv = *reinterpret_cast<const float4 *>(x + off[1]);
+    else { const float t = x[off[1]]; xv = make_float4(t, t, t, t); }
+    if (b_vec) bv = *reinterpret_cast<const float4 *>(bias + off[2]);
+    else { const float t = bias[off[2]]; bv = make_float4(t, t, t, t); }
+    *reinterpret_cast<float4 *>(out + off[0]) =
+        make_float4(gelu_erf(xv.x + bv.x, c0, c1, c2), gelu_erf(xv.y + bv.y, c0, c1, c2),
+                    gelu_erf(xv.z + bv.z, c0, c1, c2), gelu_erf(xv.w + bv.w, c0, c1, c2));
+  }
+}
+
+__global__ void where_vec4(Iter<4> it, float *out, const uint8_t *cond, const float *x, const float *y, float y_scalar) {
+  pdl_prologue();
+  const int64_t inner4 = it.shape[it.rank - 1] >> 2, total4 = it.total >> 2;
+  const int l = it.rank - 1;
+  const bool c_vec = it.stride[1][l] == 1, x_vec = it.stride[2][l] == 1, y_vec = y && it.stride[3][l] == 1;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[4];
+    vec4_offsets<4>(it, i, inner4, off);
+    uchar4 cv;
+    if (c_vec) cv = *reinterpret_cast<const uchar4 *>(cond + off[1]);
+    else { const uint8_t t = cond[off[1]]; cv = make_uchar4(t, t, t, t); }
+    float4 xv, yv = make_float4(y_scalar, y_scalar, y_scalar, y_scalar);
+    if (x_vec) xv = *reinterpret_cast<const float4 *>(x + off[2]);
+    else { const float t = x[off[2]]; xv = make_float4(t, t, t, t); }
+    if (y) {
+      if (y_vec) yv = *reinterpret_cast<const float4 *>(y + off[3]);
+      else { const float t = y[off[3]]; yv = make_float4(t, t, t, t); }
+    }
+    *reinterpret_cast<float4 *>(out + off[0]) =
+        make_float4(cv.x ? xv.x : yv.x, cv.y ? xv.y : yv.y, cv.z ? xv.z : yv.z, cv.w ? xv.w : yv.w);
+  }
+}
+
 // operand 0 = out, 1 = cond, 2 = x, 3 = y
 __global__ void where_generic(Iter<4> it, float *out, const uint8_t *cond, const float *x,
                               const float *y, float y_scalar) {
@@ -295,8 +354,12 @@ extern "C" int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const 
   int st = make_iter(it, out, ins, "fml_bias_gelu");
   if (st != FML_OK) return st;
   if (it.total == 0) return FML_OK;
-  FML_LAUNCH((bias_gelu_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
-      it, (float *)out->data, (const float *)x->data, (const float *)bias->data, c0, c1, c2);
+  if (vec4_ok(it, out->data, x->data, (const float *)bias->data))
+    FML_LAUNCH((bias_gelu_vec4), grid_for(it.total / 4, 256), 256, 0, as_stream(stream),
+        it, (float *)out->data, (const float *)x->data, (const float *)bias->data, c0, c1, c2);
+  else
+    FML_LAUNCH((bias_gelu_generic), grid_for(it.total, 256), 256, 0, as_stream(stream),
+        it, (float *)out->data, (const float *)x->data, (const float *)bias->data, c0, c1, c2);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }
@@ -312,6 +375,23 @@ extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_
   int st = make_iter(it, out, ins, "fml_where");
   if (st != FML_OK) return st;
   if (it.total == 0) return FML_OK;
+  {
+    // the 16-byte path: out / x / y as for the binary kernels, the condition bytes on 4-byte steps
+    const int l = it.rank - 1;
+    bool ok = it.rank >= 1 && (it.shape[l] & 3) == 0 && it.stride[0][l] == 1 && aligned16(out->data) && aligned16(x->data) &&
+              (!y || aligned16(y->data)) && (reinterpret_cast<uintptr_t>(cond->data) & 3) == 0;
+    for (int o = 1; o < 4 && ok; ++o) ok = it.stride[o][l] == 1 || it.stride[o][l] == 0 || (o == 3 && !y);
+    for (int d = 0; d < l && ok; ++d)
+      for (int o = 0; o < 4; ++o)
+        if (it.stride[o][d] % 4 != 0 && !(o == 3 && !y)) ok = false;
+    if (ok) {
+      FML_LAUNCH((where_vec4), grid_for(it.total / 4, 256), 256, 0, as_stream(stream),
+          it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
+          y ? (const float *)y->data : nullptr, y_scalar);
+      FML_CUDA(cudaGetLastError());
+      return FML_OK;
+    }
+  }
   FML_LAUNCH((where_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
       y ? (const float *)y->data : nullptr, y_scalar);

@@ -52,8 +52,36 @@ def main() -> None:
     a.add_argument("--seq", type=int, default=128)
     a.add_argument("--dim", type=int, default=64)
     a.add_argument("--reps", type=int, default=3)
+    mb = sub.add_parser("membound")
+    mb.add_argument("--rows", type=int, default=131072)
+    mb.add_argument("--cols", type=int, default=768)
+    mb.add_argument("--only", default="", help="run just one of: add, bias_gelu, layernorm, softmax, transpose")
+    mb.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
     rng = np.random.Generator(np.random.PCG64(0))
+
+    if args.op == "membound":
+        # the HBM-bound kernels on tensors far larger than L2: achieved GB/s of algorithmic bytes
+        R, C = args.rows, args.cols
+        x = DT.from_numpy(rng.standard_normal((R, C)).astype(np.float32))
+        y = DT.from_numpy(rng.standard_normal((R, C)).astype(np.float32))
+        o = DT((R, C), np.float32)
+        vec = DT.from_numpy(rng.standard_normal(C).astype(np.float32))
+        ot = DT((C, R), np.float32)
+        nb = R * C * 4.0
+        cases = {
+            "add": (lambda: cabi.elementwise(cabi.ADD, x, y, o), 3 * nb),
+            "bias_gelu": (lambda: cabi.bias_gelu(x, vec, o, float(np.sqrt(2.0)), 1.0, 0.5), 2 * nb),
+            "layernorm": (lambda: cabi.layernorm(x, y, vec, vec, o, 1, 1e-5), 3 * nb),
+            "softmax": (lambda: cabi.softmax(x, None, 8.0, o, 1), 2 * nb),
+            "transpose": (lambda: cabi.copy_strided(x.view((C, R), [1, C], 0), ot), 2 * nb),
+        }
+        for name, (fn, nbytes) in cases.items():
+            if args.only and name != args.only:
+                continue
+            us = _time(fn, args.reps)
+            print(f"{name:10s} [{R} x {C}] {us:9.1f} us  {nbytes / us / 1e3:8.1f} GB/s")
+        return
 
     if args.op == "conv":
         prec = {"fp32": cabi.GEMM_FP32, "3xtf32": cabi.GEMM_3XTF32, "tf32": cabi.GEMM_TF32}[args.precision]

@@ -136,6 +136,29 @@ def test_where():
     assert np.array_equal(out.numpy(), np.where(cond, x, y))
 
 
+@pytest.mark.parametrize("shape,cshape,yshape", [((3, 5, 7), (5, 7), (7,)),       # odd inner extent: scalar kernel
+                                                 ((2, 6, 16), (2, 6, 1), (16,)),   # condition broadcast along rows
+                                                 ((4, 8, 32), (8, 32), (4, 8, 1))])  # y broadcast along rows
+def test_where_broadcast_forms(shape, cshape, yshape):
+    rng = np.random.default_rng(7)
+    cond = rng.random(cshape) < 0.5
+    x, y = rnd(*shape), rnd(*yshape)
+    out = DT(shape, np.float32)
+    cabi.where(DT.from_numpy(cond), DT.from_numpy(x), DT.from_numpy(y), 0.0, out)
+    assert np.array_equal(out.numpy(), np.where(cond, x, y))
+
+
+@pytest.mark.parametrize("xshape,bshape", [((5, 33), (33,)), ((6, 64), (6, 1)), ((2, 8, 64), (8, 64))])
+def test_bias_gelu_broadcast_forms(xshape, bshape):
+    x, b = rnd(*xshape), rnd(*bshape)
+    c0, c1, c2 = np.float32(np.sqrt(2.0)), np.float32(1.0), np.float32(0.5)
+    t = x + b
+    e = orc.unary("Erf", (t / c0).astype(np.float32), np.empty_like(t))
+    out = DT(xshape, np.float32)
+    cabi.bias_gelu(DT.from_numpy(x), DT.from_numpy(b), out, c0, c1, c2)
+    assert np.abs(out.numpy() - (t * (e + c1)) * c2).max() <= 4e-6
+
+
 # ------------------------------------------------------------------ data movement (bit-exact)
 @pytest.mark.parametrize("shape,perm", [((1, 128, 12, 64), (0, 2, 1, 3)), ((1, 128, 12, 64), (0, 2, 3, 1)),
                                         ((1, 12, 128, 64), (0, 2, 1, 3)), ((5, 7, 3), (2, 0, 1)),
