@@ -71,11 +71,13 @@ __global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const f
     }
   }
   sum = warp_sum(sum);
+  // one correctly rounded reciprocal per row, then multiplies: within 1.5 ulp of the division
+  const float inv = 1.0f / sum;
   float4 *y4 = reinterpret_cast<float4 *>(out + off[0]);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     int64_t c = lane + 32 * i;
-    if (c < n4) y4[c] = make_float4(v[i].x / sum, v[i].y / sum, v[i].z / sum, v[i].w / sum);
+    if (c < n4) y4[c] = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
   }
 }
 

@@ -162,7 +162,8 @@ def test_bias_gelu_broadcast_forms(xshape, bshape):
 # ------------------------------------------------------------------ data movement (bit-exact)
 @pytest.mark.parametrize("shape,perm", [((1, 128, 12, 64), (0, 2, 1, 3)), ((1, 128, 12, 64), (0, 2, 3, 1)),
                                         ((1, 12, 128, 64), (0, 2, 1, 3)), ((5, 7, 3), (2, 0, 1)),
-                                        ((33, 65), (1, 0)), ((2, 3, 4, 5), (3, 2, 1, 0))])
+                                        ((33, 65), (1, 0)), ((2, 3, 4, 5), (3, 2, 1, 0)),
+                                        ((260, 196), (1, 0)), ((2, 128, 3, 68), (0, 2, 3, 1))])
 @pytest.mark.parametrize("dtype", [np.float32, np.int64, np.bool_])
 def test_transpose_bit_exact(shape, perm, dtype):
     x = (RNG.integers(0, 2**31 - 1, shape)).astype(dtype)
