@@ -266,6 +266,9 @@ private:
       e.Set("kind", json::Value(flow::KindName(n->kind)));
       e.Set("alias", json::Value(aliases.count(n->output.get()) != 0));
       e.Set("output", json::Value(n->output->name));
+      json::Value ins = json::Value::Array();
+      for (const auto &r : n->inputs) ins.Push(json::Value(r->name));
+      e.Set("inputs", ins);
       e.Set("scratch", json::Value((double)n->buffer_size));
       seq.Push(e);
     }
@@ -304,6 +307,15 @@ private:
       json::Value root = json::Value::Object();
       root.Set("dp_table", dp_json);
       root.Set("plan", plan_json);
+      // logical shape of every tensor the sequence touches: what the reference's analyzer
+      // (tools/analyzer.py:96-112) reads from the ONNX file's value_info
+      json::Value shapes = json::Value::Object();
+      for (const auto &r : sequence.regions) {
+        json::Value sh = json::Value::Array();
+        for (int64_t d : r->meta.GetShape()) sh.Push(json::Value((double)d));
+        shapes.Set(r->name, sh);
+      }
+      root.Set("infos", shapes);
       json::Value arena = json::Value::Object();
       for (const auto &kv : index.All()) {
         json::Value e = json::Value::Array();

@@ -220,7 +220,7 @@ def test_plan_is_consistent(bert_bytes, factory):
         ex = factory("bert")
         st = ex.plan(bert_bytes, json=os.path.join(d, "p.json"))
         dump = json.load(open(os.path.join(d, "p.json")))
-    assert set(dump) == {"dp_table", "plan", "arena"}
+    assert set(dump) == {"dp_table", "plan", "infos", "arena"}
     lives, tenants = dump["arena"]["lifetimes"], dump["arena"]["tenants"]
     names = list(lives)
     start, end, size = ([lives[n][i] for n in names] for i in range(3))
@@ -237,6 +237,24 @@ def test_plan_is_consistent(bert_bytes, factory):
         assert st["peak_arena_bytes"] >= sum(size)
     else:
         assert st["peak_arena_bytes"] < sum(size)
+
+
+def test_analyzer_reports_default_versus_planned_cost(bert_bytes, tmp_path):
+    """The report of the reference's tools/analyzer.py, rebuilt from the dump alone."""
+    from fluidml_b200 import analyzer
+    dump_path, out_path = str(tmp_path / "p.json"), str(tmp_path / "r.json")
+    st = Executor.make_dp_greedy("b").plan(bert_bytes, json=dump_path)
+    assert analyzer.main(["--json", dump_path, "--output", out_path]) == 0
+    rep = json.load(open(out_path))
+    assert rep["unmatched"] == []
+    assert sum(r[2] for r in rep["kernels"].values()) == len(st["sequence"])
+    # what the search gains on BERT: every transpose becomes a view
+    assert rep["kernels"]["TransposeKernel"][0] > 0 and rep["kernels"]["TransposeKernel"][1] == 0
+    assert rep["total"][1] < rep["total"][0]
+    # without a layout search there is no table to look records up in
+    Executor.make_plain_greedy("b").plan(bert_bytes, json=dump_path)
+    plain = analyzer.analyze(json.load(open(dump_path)))
+    assert plain["kernels"] == {} and len(plain["unmatched"]) > 0
 
 
 def test_dp_layout_search(bert_bytes):
@@ -304,7 +322,7 @@ def test_cli_options_follow_the_reference(bert_bytes):
             st = json.loads(r.stdout)
             assert st["mode"] == mode
             arenas[mode] = st["peak_arena_bytes"]
-            assert set(json.load(open(os.path.join(d, mode)))) == {"dp_table", "plan", "arena"}
+            assert set(json.load(open(os.path.join(d, mode)))) == {"dp_table", "plan", "infos", "arena"}
         assert arenas["dp_greedy"] < arenas["plain_linear"]
 
 
