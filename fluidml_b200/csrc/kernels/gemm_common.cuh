@@ -67,7 +67,6 @@ struct TcPlan {
   int three_pass; // 1: 3xTF32, 0: single TF32
   int a_tmem;     // 3xTF32 only: A's hi / lo parts live in tensor memory instead of shared memory
   size_t smem_bytes;
-  size_t partial_bytes, counter_bytes;
 };
 
 // Whether the operands can be fed to TMA/UMMA directly, and with which plan.

@@ -649,8 +649,6 @@ bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan)
     if (plan.smem_bytes < floor_bytes) plan.smem_bytes = floor_bytes;
   }
   if (plan.smem_bytes > 227 * 1024) return false;
-  plan.partial_bytes = 0;
-  plan.counter_bytes = 0;
   return true;
 }
 
