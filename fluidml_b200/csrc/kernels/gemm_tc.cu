@@ -178,6 +178,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
+  // The per-column bias is a weight as well, cold in HBM when the epilogue asks for it: pull
+  // this tile's slice into L2 now (a prefetch moves nothing into the SM, so it is safe
+  // whoever produces the vector).
+  if (warp == 2 && a.p.bias && a.p.bias_sm == 0 && a.p.bias_sn == 1) {
+    const float *bp = a.p.bias + (int64_t)z0 * a.p.bias_b0 + (int64_t)z1 * a.p.bias_b1;
+    for (int64_t n = (int64_t)tile_n * BN + lane * 8; n < min((int64_t)(tile_n + 1) * BN, a.p.N); n += 256)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(bp + n));
+  }
   // From here on the preceding kernel's results are needed (and its inputs may be overwritten).
   pdl_wait();
   if (threadIdx.x == 0) TRACE(1);

@@ -106,19 +106,36 @@ __global__ void softmax_rows_generic(RowArgs a, float *out, const float *in, con
 }
 
 // ---- LayerNorm ---------------------------------------------------------------------
-template <int NV>
+// EARLY: for a few rows (a latency-bound launch) gamma and beta are fetched together with the
+// row instead of after the two reductions, so that their latency overlaps the row's; with many
+// rows the 8 * NV extra registers would cost occupancy and the vectors are cache hits anyway.
+template <int NV, bool EARLY>
 __global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const float *res,
                                    const float *gamma, const float *beta, float eps) {
-  pdl_prologue();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
+  const int64_t n4 = a.len >> 2;
+  const float4 *g4 = reinterpret_cast<const float4 *>(gamma), *b4 = reinterpret_cast<const float4 *>(beta);
+  // While the preceding kernel drains: pull gamma and beta (weights: cold in a pass that
+  // streams more weights than L2 holds) into L2.  A prefetch reads nothing into the SM, so it
+  // is harmless even when that kernel is still producing them.
+  if (blockIdx.x == 0 && threadIdx.x < 32) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (lane + 32 * i < n4) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(g4 + lane + 32 * i));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(b4 + lane + 32 * i));
+      }
+  }
+  pdl_wait();
   const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   if (row >= a.rows.total) return;
   int64_t off[3];
   offsets_of(a.rows, row, off);
-  const int64_t n4 = a.len >> 2;
   const float4 *x4 = reinterpret_cast<const float4 *>(in + off[1]);
   const float4 *r4 = res ? reinterpret_cast<const float4 *>(res + off[2]) : nullptr;
   float4 v[NV];
+  float4 ge[EARLY ? NV : 1], be[EARLY ? NV : 1];
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -126,6 +143,7 @@ __global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const
     if (c < n4) {
       float4 t = x4[c];
       if (r4) { float4 r = r4[c]; t.x += r.x; t.y += r.y; t.z += r.z; t.w += r.w; }
+      if (EARLY) { ge[EARLY ? i : 0] = g4[c]; be[EARLY ? i : 0] = b4[c]; }
       v[i] = t;
       s += (t.x + t.y) + (t.z + t.w);
     }
@@ -141,13 +159,12 @@ __global__ void layernorm_rows_vec(RowArgs a, float *out, const float *in, const
   }
   const float var = warp_sum(q) / (float)a.len;
   const float inv = 1.0f / sqrtf(var + eps);
-  const float4 *g4 = reinterpret_cast<const float4 *>(gamma), *b4 = reinterpret_cast<const float4 *>(beta);
   float4 *y4 = reinterpret_cast<float4 *>(out + off[0]);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     int64_t c = lane + 32 * i;
     if (c < n4) {
-      float4 g = g4[c], b = b4[c];
+      const float4 g = EARLY ? ge[EARLY ? i : 0] : g4[c], b = EARLY ? be[EARLY ? i : 0] : b4[c];
       y4[c] = make_float4(v[i].x * inv * g.x + b.x, v[i].y * inv * g.y + b.y,
                           v[i].z * inv * g.z + b.z, v[i].w * inv * g.w + b.w);
     }
@@ -308,6 +325,17 @@ using namespace fml;
     else FML_LAUNCH((KERNEL<32>), grid, 256, 0, stream, __VA_ARGS__);                      \
   } while (0)
 
+// The same ladder for a kernel family named through a macro K(NV).
+#define DISPATCH_NV_FN(per_lane, K, grid, stream, ...)                                     \
+  do {                                                                                     \
+    if ((per_lane) <= 1) FML_LAUNCH((K(1)), grid, 256, 0, stream, __VA_ARGS__);            \
+    else if ((per_lane) <= 2) FML_LAUNCH((K(2)), grid, 256, 0, stream, __VA_ARGS__);       \
+    else if ((per_lane) <= 4) FML_LAUNCH((K(4)), grid, 256, 0, stream, __VA_ARGS__);       \
+    else if ((per_lane) <= 8) FML_LAUNCH((K(8)), grid, 256, 0, stream, __VA_ARGS__);       \
+    else if ((per_lane) <= 16) FML_LAUNCH((K(16)), grid, 256, 0, stream, __VA_ARGS__);     \
+    else FML_LAUNCH((K(32)), grid, 256, 0, stream, __VA_ARGS__);                           \
+  } while (0)
+
 extern "C" int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
                            const fml_tensor *out, int axis, void *stream) {
   FML_REQUIRE(in && out, FML_BAD_ARG, "fml_softmax: null tensor");
@@ -353,7 +381,15 @@ extern "C" int fml_layernorm(const fml_tensor *in, const fml_tensor *residual,
   const bool res_vec = !residual || a.axis_stride[2] == 1;
   if (rows_vec_ok(a, out->data, in->data, rp) && res_vec && gs == 1 && bs == 1 &&
       aligned16(scale->data) && aligned16(bias->data)) {
-    DISPATCH_NV(a.len, layernorm_rows_vec, grid, s, a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps);
+#define LN_EARLY(NV) layernorm_rows_vec<NV, true>
+#define LN_LATE(NV) layernorm_rows_vec<NV, false>
+    const int64_t per_lane = (a.len / 4 + 31) / 32;
+    if (a.rows.total <= 4096 && per_lane <= 8)
+      DISPATCH_NV_FN(per_lane, LN_EARLY, grid, s, a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps);
+    else
+      DISPATCH_NV_FN(per_lane, LN_LATE, grid, s, a, (float *)out->data, (const float *)in->data, rp, (const float *)scale->data, (const float *)bias->data, eps);
+#undef LN_EARLY
+#undef LN_LATE
   } else {
     FML_LAUNCH((layernorm_rows_generic), grid, 256, 0, s, a, (float *)out->data, (const float *)in->data, rp,
                                                 (const float *)scale->data, gs,
