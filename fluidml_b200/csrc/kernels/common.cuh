@@ -128,8 +128,10 @@ __device__ __forceinline__ void offsets_of(const Iter<NOPS> &it, int64_t lin, in
 // "programmatic stream serialization" attribute and starts with pdl_prologue(), so inside a
 // stream (or a captured graph) kernel N+1 may be scheduled, and run its own set-up, while
 // kernel N drains; griddepcontrol.wait returns once kernel N has completed and its writes are
-// visible, and no kernel touches global memory before it.  FLUIDML_PDL=0 turns the attribute
-// off (the device instructions are then no-ops).
+// visible, and no kernel reads or writes global data before it.  What a kernel may do before
+// the wait: load operands the caller declared constant (the tensor-core GEMM's weights) and
+// issue L2 prefetches (they move nothing into the SM, so they are safe whoever produces the
+// bytes).  FLUIDML_PDL=0 turns the attribute off (the device instructions are then no-ops).
 bool pdl_enabled();
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

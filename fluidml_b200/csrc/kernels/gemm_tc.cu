@@ -120,6 +120,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tile = blockIdx.x, tile_m = tile / a.tiles_n, tile_n = tile % a.tiles_n;
   const int split = blockIdx.y;  // == rank inside the (1, S, 1) cluster
   const int z = blockIdx.z, z0 = z % (int)a.p.nb0, z1 = z / (int)a.p.nb0;
+  // Weights that one row of tiles reads cross L2 once per pass: mark them evict-first so that
+  // the bytes streamed by a pass (more than L2 holds) do not displace what every launch
+  // re-reads.  With several tile rows the weights are themselves re-read from L2 and keep the
+  // default policy.
+  const bool b_stream = a.p.b_constant != 0 && a.tiles_m == 1;
+  const uint64_t b_policy = b_stream ? l2_policy_evict_first() : 0ull;
+  auto load_b = [&](uint32_t dst, uint32_t bar, int c0, int c1, int c2, int c3) {
+    if (b_stream) tma_load_4d_hint(dst, &map_b, bar, c0, c1, c2, c3, b_policy);
+    else tma_load_4d(dst, &map_b, bar, c0, c1, c2, c3);
+  };
   const int kb0 = min(a.kb_total, split * a.kb_per_split);
   const int kb1 = min(a.kb_total, kb0 + a.kb_per_split);
   const int nkb = kb1 - kb0;  // may be 0 for the last ranks of a cluster
@@ -133,13 +143,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (a.p.prefetch_bytes && threadIdx.x == 64) {
     // Constant bytes a later launch will stream (the next weights): each CTA asks L2 to fetch
     // its share now, before this kernel even waits for its own inputs.  Fire and forget.
+    const uint64_t pf_policy = l2_policy_evict_first();
     const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
     const unsigned long long cta = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
     const unsigned long long share = ((a.p.prefetch_bytes + ctas - 1) / ctas + 127ull) & ~127ull;
     const unsigned long long lo = cta * share, hi = min(a.p.prefetch_bytes & ~15ull, lo + share);
     for (unsigned long long off = lo; off < hi; off += 16384ull) {
       const unsigned n = (unsigned)min(16384ull, hi - off);
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.p.prefetch + off), "r"(n) : "memory");
+      asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;"
+                   ::"l"(a.p.prefetch + off), "r"(n), "l"(pf_policy) : "memory");
     }
   }
   if (threadIdx.x == 0) {
@@ -171,10 +183,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int k = (kb0 + it) * kBK;
       mbar_expect_tx(bar_full + 8u * it, kABytes + b_bytes);
       if (!B_MN) {
-        tma_load_4d(sb, &map_b, bar_full + 8u * it, k, tile_n * BN, cb2, cb3);
+        load_b(sb, bar_full + 8u * it, k, tile_n * BN, cb2, cb3);
       } else {
         for (int g = 0; g < BN / 32; ++g)
-          tma_load_4d(sb + (uint32_t)g * (kBK * 128), &map_b, bar_full + 8u * it, tile_n * BN + g * 32, k, cb2, cb3);
+          load_b(sb + (uint32_t)g * (kBK * 128), bar_full + 8u * it, tile_n * BN + g * 32, k, cb2, cb3);
       }
     }
   }
@@ -212,11 +224,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(bar_full + 8u * s, kABytes + b_bytes);
         tma_load_4d(sa, &map_a, bar_full + 8u * s, k, tile_m * kBM, ca2, ca3);
         if (!B_MN) {
-          tma_load_4d(sb, &map_b, bar_full + 8u * s, k, tile_n * BN, cb2, cb3);
+          load_b(sb, bar_full + 8u * s, k, tile_n * BN, cb2, cb3);
         } else {
           for (int g = 0; g < BN / 32; ++g)  // one 32-wide column group per box
-            tma_load_4d(sb + (uint32_t)g * (kBK * 128), &map_b, bar_full + 8u * s,
-                        tile_n * BN + g * 32, k, cb2, cb3);
+            load_b(sb + (uint32_t)g * (kBK * 128), bar_full + 8u * s, tile_n * BN + g * 32, k, cb2, cb3);
         }
         ++issued;
       }
