@@ -166,6 +166,18 @@ __device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   trace_stamp();
 }
+// For the stretch between launch_dependents and the wait: asks L2 for the first `bytes` (at
+// most `cap`) of a weight tensor, one 128-byte line per thread of the grid's first row of
+// blocks.  Weights are cold in a pass that streams more bytes than L2 holds; a prefetch moves
+// nothing into the SM, so it is safe whoever produces the bytes.
+__device__ __forceinline__ void l2_prefetch_span(const void *p, int64_t bytes, int64_t cap = 1 << 20) {
+  if (!p || blockIdx.y != 0 || blockIdx.z != 0) return;
+  if (bytes > cap) bytes = cap;
+  const char *c = static_cast<const char *>(p);
+  for (int64_t off = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 128; off < bytes;
+       off += (int64_t)gridDim.x * blockDim.x * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
+}
 __device__ __forceinline__ void pdl_prologue() {
   pdl_launch_dependents();
   pdl_wait();

@@ -15,6 +15,7 @@ struct ConvArgs {
   int64_t ph, pw, sh, sw, dh, dw;
   int64_t xs[4], ws[4], ys[4];  // element strides n/c/h/w, o/i/h/w, n/c/h/w
   int64_t bias_stride;
+  int64_t w_span, bias_span;  // bytes from the first to the last element of w / bias
   const float *x, *w, *bias;
   float *y;
   int act;
@@ -33,7 +34,10 @@ __device__ __forceinline__ float conv_act(int act, float v) {
 constexpr int CB = 64, CK = 16;
 
 __global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
-  pdl_prologue();
+  pdl_launch_dependents();
+  l2_prefetch_span(a.w, a.w_span);
+  l2_prefetch_span(a.bias, a.bias_span);
+  pdl_wait();
   __shared__ float As[CK][CB + 4];
   __shared__ float Bs[CK][CB + 4];
   const int64_t Mtot = a.N * a.OH * a.OW, Ktot = a.IC * a.KH * a.KW;
@@ -97,7 +101,10 @@ __global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
 }
 
 __global__ void conv_depthwise_kernel(ConvArgs a) {
-  pdl_prologue();
+  pdl_launch_dependents();
+  l2_prefetch_span(a.w, a.w_span);
+  l2_prefetch_span(a.bias, a.bias_span);
+  pdl_wait();
   const int64_t total = a.N * a.OC * a.OH * a.OW;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
        e += (int64_t)gridDim.x * blockDim.x) {
@@ -182,6 +189,12 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
                 "fml_conv: bias must hold one value per output channel");
     a.bias = (const float *)bias->data;
     for (int i = 0; i < bias->rank; ++i) if (bias->shape[i] != 1) a.bias_stride = bias->stride[i];
+  }
+  {
+    int64_t last = 0;
+    for (int i = 0; i < w->rank; ++i) last += (w->shape[i] - 1) * (w->stride[i] > 0 ? w->stride[i] : 0);
+    a.w_span = (last + 1) * (int64_t)sizeof(float);
+    a.bias_span = a.bias ? ((a.OC - 1) * (a.bias_stride > 0 ? a.bias_stride : 0) + 1) * (int64_t)sizeof(float) : 0;
   }
   a.act = p->act;
   const int64_t M = a.N * a.OH * a.OW;

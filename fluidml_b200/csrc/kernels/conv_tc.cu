@@ -119,6 +119,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   while (tmem_cols < a_col0 + a_cols * (uint32_t)NS) tmem_cols <<= 1;
 
   pdl_launch_dependents();
+  if (threadIdx.x == 32) {  // descriptors ready for the first loads after the dependency wait
+    tma_prefetch_map(&map_x);
+    tma_prefetch_map(&map_w);
+  }
+  // this tile's slice of the bias (a weight, cold when the epilogue asks for it) into L2; a
+  // prefetch moves nothing into the SM, so it is safe whoever produces the vector
+  if (warp == 2 && a.bias && a.bias_stride == 1)
+    for (int oc = oc0 + lane * 8; oc < min(oc0 + BN, a.OC); oc += 256)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a.bias + oc));
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar_bfull + 8u * s, 1);

@@ -38,7 +38,10 @@ struct SkinnyArgs {
 
 template <bool KMAJOR>
 __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
-  pdl_prologue();
+  pdl_launch_dependents();
+  // B is what this kernel streams; while the preceding kernel drains, start it towards L2
+  l2_prefetch_span(a.p.b, ((a.p.K - 1) * a.p.b_sk + (a.p.N - 1) * a.p.b_sn + 1) * (int64_t)sizeof(float), 4 << 20);
+  pdl_wait();
   __shared__ float a_sh[KMAJOR ? 1 : kMaxM * 128];
   __shared__ float red[kMaxM][kColsPerCta];
   __shared__ int last_flag;

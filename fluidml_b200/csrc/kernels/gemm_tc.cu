@@ -140,6 +140,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   while (tmem_cols < tmem_need) tmem_cols <<= 1;
 
   pdl_launch_dependents();  // the next kernel may start its own set-up while this one runs
+  if (threadIdx.x == 0) {  // the first A load comes right after the dependency wait: have its descriptor ready
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_b);
+  }
   if (a.p.prefetch_bytes && threadIdx.x == 64) {
     // Constant bytes a later launch will stream (the next weights): each CTA asks L2 to fetch
     // its share now, before this kernel even waits for its own inputs.  Fire and forget.

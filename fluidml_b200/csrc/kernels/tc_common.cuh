@@ -45,6 +45,10 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// Fetches a tensor map into the TMA unit's descriptor cache ahead of its first use.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // The same load with an L2 eviction policy (createpolicy): weights that are streamed once per
 // pass are marked evict-first so that they do not push the pass's small hot set (activations,
 // bias / scale vectors, kernel code) out of L2.
