@@ -310,3 +310,102 @@ def device_count() -> int:
     n = ctypes.c_int()
     check(lib().fml_device_count(ctypes.byref(n)))
     return n.value
+
+
+# ------------------------------------------------------------------ resident stage program
+RESIDENT_GEMM, RESIDENT_ATTENTION = 1, 2
+
+
+class ResidentStage(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("out_external", ctypes.c_int32), ("out", Tensor),
+                ("a", Tensor), ("w", Tensor), ("bias", Tensor), ("residual", Tensor),
+                ("act", ctypes.c_int32), ("act_param", ctypes.c_float * 3),
+                ("layernorm", ctypes.c_int32), ("ln_scale", Tensor), ("ln_bias", Tensor),
+                ("ln_eps", ctypes.c_float), ("tile_n", ctypes.c_int32), ("split_k", ctypes.c_int32),
+                ("q", Tensor), ("kt", Tensor), ("v", Tensor), ("mask", Tensor),
+                ("divisor", ctypes.c_float)]
+
+
+class ResidentInfo(ctypes.Structure):
+    _fields_ = [("ctas", ctypes.c_int32), ("stages", ctypes.c_int32), ("steps", ctypes.c_int32),
+                ("counters", ctypes.c_int32), ("ring_slots", ctypes.c_int32), ("slot_bytes", ctypes.c_int32),
+                ("packed_weight_bytes", ctypes.c_uint64), ("scratch_bytes", ctypes.c_uint64),
+                ("shared_memory_bytes", ctypes.c_uint64)]
+
+
+def _t(x) -> Tensor:
+    """DeviceTensor, ctypes Tensor or None -> Tensor (a null data pointer means "absent")."""
+    if x is None:
+        return Tensor()
+    return x if isinstance(x, Tensor) else x.c()
+
+
+def resident_gemm_stage(a, w, out, bias=None, residual=None, act=ACT_NONE, act_param=(1.4142135381698608, 1.0, 0.5),
+                        ln_scale=None, ln_bias=None, ln_eps=1e-5, out_external=False, tile_n=0,
+                        split_k=0) -> ResidentStage:
+    s = ResidentStage()
+    s.kind, s.out_external, s.out = RESIDENT_GEMM, int(out_external), _t(out)
+    s.a, s.w, s.bias, s.residual = _t(a), _t(w), _t(bias), _t(residual)
+    s.act = act
+    for i in range(3):
+        s.act_param[i] = act_param[i]
+    s.layernorm = int(ln_scale is not None)
+    s.ln_scale, s.ln_bias, s.ln_eps = _t(ln_scale), _t(ln_bias), ln_eps
+    s.tile_n, s.split_k = tile_n, split_k
+    s._keep = (a, w, out, bias, residual, ln_scale, ln_bias)  # the struct holds raw pointers only
+    return s
+
+
+def resident_attention_stage(q, kt, v, out, mask=None, divisor=1.0, out_external=False) -> ResidentStage:
+    s = ResidentStage()
+    s.kind, s.out_external, s.out = RESIDENT_ATTENTION, int(out_external), _t(out)
+    s.q, s.kt, s.v, s.mask, s.divisor = _t(q), _t(kt), _t(v), _t(mask), divisor
+    s._keep = (q, kt, v, out, mask)
+    return s
+
+
+def resident_plan(stages, ctas: int = 0) -> ResidentInfo:
+    """Plans and checks a program on the host; `ctas` > 0 needs no device."""
+    arr = (ResidentStage * len(stages))(*stages)
+    info = ResidentInfo()
+    check(lib().fml_resident_plan(arr, len(stages), int(ctas), ctypes.byref(info)))
+    return info
+
+
+class ResidentProgram:
+    """A created resident program (fml_resident_create); destroyed on garbage collection."""
+
+    def __init__(self, stages):
+        arr = (ResidentStage * len(stages))(*stages)
+        self._stages = list(stages)  # keeps the operands' device buffers alive as long as the program
+        self._h = ctypes.c_void_p()
+        check(lib().fml_resident_create(arr, len(stages), ctypes.byref(self._h)))
+
+    def launch(self, stream=None):
+        check(lib().fml_resident_launch(self._h, stream))
+
+    def info(self) -> ResidentInfo:
+        info = ResidentInfo()
+        check(lib().fml_resident_info_of(self._h, ctypes.byref(info)))
+        return info
+
+    def set_trace(self, on: bool):
+        check(lib().fml_resident_set_trace(self._h, int(on)))
+
+    def read_trace(self) -> np.ndarray:
+        """[cta][step][2] uint64 nanosecond stamps (start after the step's wait, end) of the last traced pass."""
+        info = self.info()
+        cap = info.ctas * 4096 * 2
+        buf = np.zeros(cap, np.uint64)
+        ctas, steps = ctypes.c_int32(), ctypes.c_int32()
+        check(lib().fml_resident_read_trace(self._h, buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(cap),
+                                            ctypes.byref(ctas), ctypes.byref(steps)))
+        return buf[:ctas.value * steps.value * 2].reshape(ctas.value, steps.value, 2)
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib().fml_resident_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass

@@ -200,13 +200,32 @@ private:
     json::Value plan_json = json::Value::Object();
     // Plan cache: layouts and GEMM tiles of an earlier Compile of the same bytes and options.
     PlanCacheEntry cached;
-    const std::string cache_path = dry_run ? std::string() : PlanCachePath();
-    const bool cache_hit = !cache_path.empty() && cached.Load(cache_path);
+    const std::string cache_path = PlanCachePath();  // a planning-only run reads the cache too, but never writes it
+    bool cache_hit = !cache_path.empty() && cached.Load(cache_path);
+    if (cache_hit) {
+      // A stale, hand-edited or corrupt file must not reach the stride computation: every layout
+      // it names has to be a permutation of 0..rank-1 of a tensor of this model.  Anything else
+      // makes the whole file a miss and the model is planned afresh.
+      for (const auto &r : sequence.regions) {
+        auto it = cached.layouts.find(r->name);
+        if (it == cached.layouts.end()) continue;
+        const size_t rank = r->meta.GetRank();
+        std::vector<bool> seen(rank, false);
+        bool ok = it->second.size() == rank;
+        for (size_t v : it->second) {
+          if (!ok) break;
+          if (v >= rank || seen[v]) ok = false;
+          else seen[v] = true;
+        }
+        if (!ok) { cache_hit = false; break; }
+      }
+      if (!cache_hit) cached = PlanCacheEntry();
+    }
     options_.gemm_tiles = std::make_shared<std::map<std::string, std::pair<int, int>>>();
     if (cache_hit) {
       for (const auto &r : sequence.regions) {
         auto it = cached.layouts.find(r->name);
-        if (it != cached.layouts.end() && it->second.size() == r->meta.GetRank()) r->layout = it->second;
+        if (it != cached.layouts.end()) r->layout = it->second;
       }
       *options_.gemm_tiles = cached.tiles;
       dp_json.Set("plan_cache", json::Value(cache_path));
@@ -259,6 +278,7 @@ private:
     stats_.Set("flow_nodes", json::Value((double)flow.nodes.size()));
     stats_.Set("aliased_nodes", json::Value((double)aliases.size()));
     stats_.Set("plan_cache", json::Value(std::string(cache_path.empty() ? "off" : cache_hit ? "hit" : "miss")));
+    stats_.Set("plan_cache_file", json::Value(cache_path));
     json::Value seq = json::Value::Array();
     for (const auto &n : sequence.nodes) {
       json::Value e = json::Value::Object();

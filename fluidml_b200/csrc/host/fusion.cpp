@@ -352,7 +352,15 @@ bool MergeSiblingGemms(flow::Flow &f) {
     if (n->inputs.size() != 1 || n->output->kind != flow::Region::kInner) return false;
     const RegionPtr &w = n->consts[0];
     if (w->meta.GetRank() != 2 || w->meta.GetType() != Type::kFloat32 || !utils::IsDefaultLayout(w->layout)) return false;
-    if (n->has_bias && (n->consts.size() < 2 || n->consts[1]->meta.GetRank() != 1)) return false;
+    // the merge copies K * N weights and N bias values per sibling: both constants must hold exactly that
+    const int64_t K = w->meta.GetShape()[0], N = w->meta.GetShape()[1];
+    if (!w->constant || w->constant->Bytes().size() != (size_t)K * (size_t)N * 4) return false;
+    if (n->has_bias) {
+      if (n->consts.size() < 2 || n->consts[1]->meta.GetRank() != 1 || n->consts[1]->meta.GetShape()[0] != N) return false;
+      if (n->consts[1]->meta.GetType() != Type::kFloat32 || !n->consts[1]->constant ||
+          n->consts[1]->constant->Bytes().size() != (size_t)N * 4)
+        return false;
+    }
     return true;
   };
   for (size_t i = 0; i < f.nodes.size(); ++i) {

@@ -338,6 +338,13 @@ extern "C" int fml_gemm_skinny_noalloc(const fml_tensor *a, const fml_tensor *b,
   {
     std::lock_guard<std::mutex> lock(g_static_mu);
     if (!g_static_scratch_addr[dev]) {
+      // The set-up below enqueues a memset and waits for it; inside a capture that would end up
+      // in the caller's graph and the wait would invalidate the capture.  Refuse instead.
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      FML_CUDA(cudaStreamIsCapturing(s, &cap));
+      FML_REQUIRE(cap == cudaStreamCaptureStatusNone, FML_CUDA_ERROR,
+                  "fml_gemm_skinny_noalloc: the first call on a device sets up the scratch array and must be made "
+                  "outside stream capture");
       void *addr = nullptr;
       FML_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
       FML_REQUIRE(addr != nullptr, FML_CUDA_ERROR, "fml_gemm_skinny_noalloc: no device address for the scratch array");

@@ -328,6 +328,88 @@ int fml_conv_uses_tensor_cores(const fml_tensor *x, const fml_tensor *w, const f
 int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t *kernel,
                const int64_t *strides, void *stream);
 
+/* ---------------------------------------------------------------- resident stage program
+ * The reference runs a whole model as ONE call into one compiled function
+ * (src/worker/runner.cpp:101-112 invokes the single func that GeneralBuilder assembled,
+ * src/worker/builder.cpp:400-491).  A resident program is the counterpart here for a chain of
+ * operators over one block of 128 activation rows (batch x sequence = 128): every stage of the
+ * chain runs inside ONE persistent kernel, one CTA per SM, so no kernel boundary separates
+ * dependent operators.  The weights of all stages are packed once, at creation, into one
+ * stream per CTA which a producer warp copies into a shared-memory ring without ever waiting
+ * for activations; stages synchronise through counters in global memory that consumers poll
+ * (bounded) just before they need a tile.
+ *
+ * Stage kinds
+ *   FML_RESIDENT_GEMM       out = [LayerNorm]( act(A W + bias) + residual ): MatMulKernel /
+ *                           GemmConstantBiasKernel (matmul.cpp:28-59, gemm.cpp:39-182) with the
+ *                           epilogue of fml_gemm, optionally followed by
+ *                           LayerNormalizationConstantScaleBiasKernel
+ *                           (layer_normalization.cpp:33-220) over the output row.  W is constant.
+ *                           3xTF32 on tcgen05, split-K partial sums added in split order.
+ *   FML_RESIDENT_ATTENTION  out = softmax(Q K^T / divisor + mask) V per head, as fml_attention.
+ * Tensors are described as the launcher of the separate kernels would describe them (device
+ * pointers, shapes, element strides).  An input that lies inside the output of an earlier stage
+ * is taken from that stage; such outputs are kept in a tiled order private to the program
+ * unless the stage sets `out_external`, which stores them with the strides given so that code
+ * outside the program can read them.  Inputs that no stage produces are read as described.
+ * fml_resident_create returns FML_UNSUPPORTED (and creates nothing) when a stage does not fit:
+ * the caller then launches the operators one by one.
+ */
+typedef enum fml_resident_kind { FML_RESIDENT_GEMM = 1, FML_RESIDENT_ATTENTION = 2 } fml_resident_kind;
+
+typedef struct fml_resident_stage {
+  int32_t kind;
+  int32_t out_external;   /* non-zero: `out` is also read outside the program               */
+  fml_tensor out;         /* GEMM [.., 128, N]; attention [.., H, 128, Dv]                   */
+  /* GEMM */
+  fml_tensor a;           /* [.., 128, K]                                                    */
+  fml_tensor w;           /* [K, N] constant, any strides                                    */
+  fml_tensor bias;        /* [N], data == NULL: none                                         */
+  fml_tensor residual;    /* [.., 128, N], data == NULL: none                                */
+  int32_t act;            /* fml_gemm_act: NONE, GELU_ERF, RELU, TANH, SIGMOID               */
+  float act_param[3];
+  int32_t layernorm;      /* non-zero: LayerNorm over N with ln_scale, ln_bias [N], ln_eps   */
+  fml_tensor ln_scale, ln_bias;
+  float ln_eps;
+  int32_t tile_n, split_k; /* 0 = let the library choose                                     */
+  /* attention */
+  fml_tensor q, kt, v;    /* [.., H, 128, D], [.., H, D, 128], [.., H, 128, Dv]              */
+  fml_tensor mask;        /* broadcasts to [.., H, 128, 128]; data == NULL: none             */
+  float divisor;
+} fml_resident_stage;
+
+typedef struct fml_resident fml_resident;
+
+typedef struct fml_resident_info {
+  int32_t ctas, stages, steps, counters;
+  int32_t ring_slots, slot_bytes;
+  uint64_t packed_weight_bytes, scratch_bytes, shared_memory_bytes;
+} fml_resident_info;
+
+/* Pure host computation: plans the program for `ctas` resident CTAs (0 = the SM count of the
+ * current device), checks that every read is ordered after the writes it needs and every
+ * overwrite after the reads of what it replaces, and reports the plan.  Needs no device when
+ * `ctas` is given. */
+int fml_resident_plan(const fml_resident_stage *stages, int32_t count, int32_t ctas,
+                      fml_resident_info *info);
+/* Plans, packs the weights (a device kernel on the default stream; synchronises) and allocates
+ * the program's scratch.  Not capturable. */
+int fml_resident_create(const fml_resident_stage *stages, int32_t count, fml_resident **out);
+/* One pass: clears the counters and launches the persistent kernel (cooperatively, so that all
+ * CTAs are co-resident).  Capturable.  A bounded wait that expires sets the device status word
+ * (fml_check_device) and ends the pass early on every CTA. */
+int fml_resident_launch(fml_resident *program, void *stream);
+int fml_resident_info_of(const fml_resident *program, fml_resident_info *info);
+int fml_resident_destroy(fml_resident *program);
+/* Timing aid: after a pass launched with `trace` != 0 ... (see fml_resident_trace). */
+/* Copies per-step time stamps of the last traced pass to `host` (u64 nanoseconds of the
+ * device's global timer: step start after its wait, step end), laid out
+ * [cta][step][2]; `capacity` counts u64 entries.  fml_resident_launch records them only after
+ * fml_resident_set_trace(program, 1), which selects a kernel variant that carries the stamps. */
+int fml_resident_set_trace(fml_resident *program, int32_t on);
+int fml_resident_read_trace(fml_resident *program, uint64_t *host, uint64_t capacity,
+                            int32_t *ctas, int32_t *max_steps);
+
 #ifdef __cplusplus
 }
 #endif
