@@ -328,7 +328,7 @@ class ResidentStage(ctypes.Structure):
 
 class ResidentInfo(ctypes.Structure):
     _fields_ = [("ctas", ctypes.c_int32), ("stages", ctypes.c_int32), ("steps", ctypes.c_int32),
-                ("counters", ctypes.c_int32), ("ring_slots", ctypes.c_int32), ("slot_bytes", ctypes.c_int32),
+                ("buffers", ctypes.c_int32), ("ring_slots", ctypes.c_int32), ("slot_bytes", ctypes.c_int32),
                 ("packed_weight_bytes", ctypes.c_uint64), ("scratch_bytes", ctypes.c_uint64),
                 ("shared_memory_bytes", ctypes.c_uint64)]
 
@@ -389,18 +389,21 @@ class ResidentProgram:
         check(lib().fml_resident_info_of(self._h, ctypes.byref(info)))
         return info
 
+    def reset(self, stream=None):
+        check(lib().fml_resident_reset(self._h, stream))
+
     def set_trace(self, on: bool):
         check(lib().fml_resident_set_trace(self._h, int(on)))
 
     def read_trace(self) -> np.ndarray:
-        """[cta][step][2] uint64 nanosecond stamps (start after the step's wait, end) of the last traced pass."""
+        """[cta][step][8] uint64 nanosecond stamps of the last traced pass (fml_resident_set_trace)."""
         info = self.info()
-        cap = info.ctas * 4096 * 2
+        cap = info.ctas * 2048 * 8
         buf = np.zeros(cap, np.uint64)
         ctas, steps = ctypes.c_int32(), ctypes.c_int32()
         check(lib().fml_resident_read_trace(self._h, buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(cap),
                                             ctypes.byref(ctas), ctypes.byref(steps)))
-        return buf[:ctas.value * steps.value * 2].reshape(ctas.value, steps.value, 2)
+        return buf[:ctas.value * steps.value * 8].reshape(ctas.value, steps.value, 8)
 
     def __del__(self):
         try:

@@ -8,15 +8,22 @@
 // tiles of a slab cross L2 twice), or given by the caller.  After its unit a CTA "finishes"
 // part of the stage: without LayerNorm the rows [s * 128 / S, (s + 1) * 128 / S) of its own
 // slab (it only needs the S partial tiles of that slab), with LayerNorm whole rows (it needs
-// every slab).  An attention stage is cut into (head, 16 query rows) steps.  Steps name the
-// counters they wait for and the counters they bump; a counter's target is always the number of
-// steps that bump it, so "counter reached" means "all of them are done".
+// every slab).  An attention stage is cut into (head, 16 query rows) steps.
 //
-// Checking.  The plan is executed symbolically with a vector clock per step (how many steps of
-// each CTA are known to be complete when it starts).  Every pair of accesses to overlapping
-// memory, at least one of them a write, must be ordered by those clocks in stage order; the
-// partial-tile buffers are shared between stages only as far as that holds.  A plan that fails
-// the check is not created.
+// Buffers.  Stage outputs and split-K partial tiles live in buffers the program owns; every
+// word in them carries the parity of the buffer's write generation (resident.cuh), which is all
+// the synchronisation there is.  A buffer is handed to a later stage once its last reader is a
+// given number of stages back; the plan is then checked and the distance doubled until it
+// passes.
+//
+// Checking.  The plan is executed symbolically: a step can run once every step that writes
+// words it reads (same buffer, same generation, overlapping region) has run; each step gets a
+// vector clock (how many steps of every CTA must be complete before it can start, by program
+// order and by those read-after-write edges alone).  The check demands that every read is
+// covered exactly by writes of its generation, that no two steps write the same word of one
+// generation, and that every step that overwrites a buffer region is ordered, by those clocks,
+// after every reader and writer of the region's previous generation.  A plan that fails is not
+// created.
 #include "resident_host.h"
 #include <algorithm>
 #include <cstdlib>
@@ -29,7 +36,7 @@ struct fml_resident {
   int ctas = 0;
   size_t smem_bytes = 0;
   void *scratch = nullptr, *packed = nullptr;
-  size_t counter_bytes = 0;
+  size_t tagged_offset = 0, tagged_bytes = 0;  // the tagged buffers inside scratch
   bool trace = false;
   size_t trace_entries = 0;
   fml_resident_info info{};
@@ -58,49 +65,9 @@ bool as_rows(const fml_tensor &t, Rows &r) {
   return r.ld >= r.cols;
 }
 
-struct OutInfo {
-  const char *base = nullptr;  // out.data: bytes [base, base + 128 * N * 4) when internal
-  int N = 0;
-  bool external = false;
-  size_t tiled_offset = 0;     // external: offset of the tiled shadow in scratch
-  bool needs_shadow = false;   // external and read by a later stage
-  int matrix = -1;             // access-tracking id of the tiled matrix
-  int matrix_rm = -1;          // ... of the row-major copy
-};
-
-struct Access {
-  int matrix;            // tracking id
-  int r0, r1, c0, c1;    // rows, quads (or columns / 4) touched
-  uintptr_t lo, hi;      // conservative byte range
-  bool write;
-  int cta, index;        // the step
-  int order;             // stage order key: earlier must happen-before later
-};
-
 struct PackDesc {
   unsigned long long dst;
   int n0, k0, tile_n, pad;
-};
-
-struct Plan {
-  int ctas = 0;
-  std::vector<std::vector<Step>> steps;           // per CTA (without the end marker)
-  std::vector<GemmStage> gemm;                    // pointers into scratch are OFFSETS until resolved
-  std::vector<AttnStage> attn;
-  std::vector<int> stage_to_gemm, stage_to_attn;  // stage index -> index in gemm / attn
-  std::vector<std::vector<PackDesc>> pack;        // per GEMM stage
-  std::vector<unsigned long long> weight_begin;   // per CTA
-  size_t packed_bytes = 0;
-  int counters = 0;
-  std::vector<uint32_t> counter_total;
-  std::vector<size_t> partial_offset;             // per partial slot
-  std::vector<size_t> partial_bytes;
-  std::vector<int> gemm_partial_slot;
-  size_t shadow_bytes = 0;
-  int slot_bytes = 0, nslots = 0, overlay_bytes = 0, max_steps = 0;
-  std::vector<OutInfo> outs;
-  std::vector<Access> accesses;
-  std::string error;
 };
 
 constexpr size_t kSmemMax = 227 * 1024;
@@ -165,29 +132,64 @@ bool env_tiles(int gemm_index, int &tn, int &s) {
   return true;
 }
 
+
+struct Buffer {
+  size_t bytes = 0, offset = 0;
+  int uses = 0;          // stages that write it in one pass
+  int free_after = -1;   // last stage that reads the current content
+};
+
+struct Access {
+  int buffer, gen;       // gen < 0: an input from outside the program (never written here)
+  int r0, r1, c0, c1;    // rows, quads
+  bool write;
+  int cta, index;        // the step
+};
+
+struct OutInfo {
+  const char *base = nullptr;  // out.data: bytes [base, base + 128 * N * 4) identify the tensor
+  int N = 0;
+  bool external = false;
+  int buffer = -1, gen = 0;    // tiled copy inside the program (absent for an external output nobody reads)
+};
+
+struct Plan {
+  int ctas = 0;
+  std::vector<std::vector<Step>> steps;           // per CTA (without the end marker)
+  std::vector<GemmStage> gemm;                    // buffer pointers are resolved at creation
+  std::vector<AttnStage> attn;
+  std::vector<int> stage_to_gemm, stage_to_attn;  // stage index -> index in gemm / attn
+  std::vector<std::vector<PackDesc>> pack;        // per GEMM stage
+  std::vector<unsigned long long> weight_begin;   // per CTA
+  size_t packed_bytes = 0;
+  std::vector<Buffer> buffers;
+  size_t buffer_bytes = 0;
+  int slot_bytes = 0, nslots = 0, overlay_bytes = 0, max_steps = 0;
+  std::vector<OutInfo> outs;
+  std::vector<Access> accesses;
+  std::string error;
+};
+
+struct Operand {  // a [128 x cols] input of a stage
+  bool tiled = false;
+  int producer = -1, col0 = 0;
+  const float *ptr = nullptr;  // row-major: element (0, 0)
+  int64_t ld = 0;
+};
+struct GemmOperands { Operand a, res; bool has_res = false; int part_buffer = -1, part_gen = 0; };
+struct AttnSources { int producer[3]; };
+
 struct Planner {
   const fml_resident_stage *stages;
   int count, ctas;
+  int lag;  // stages between a buffer's last reader and its next writer
   Plan plan;
-  // counters of each stage
-  struct StageCounters {
-    std::vector<int> unit_slab;  // per slab: units done (non-LN)
-    int unit_all = -1;           // all units done (LN)
-    std::vector<int> fin_slab;   // per slab: finish tiles done (non-LN)
-    int fin_all = -1;            // all finish steps done
-    int fin_all_total = 0;
-    std::vector<int> head;       // attention: per head
-    int head_all = -1, head_all_total = 0;
-    int tile_n = 0, S = 0, rowblocks = 0;
-    bool ln = false;
-  };
-  std::vector<StageCounters> sc;
-  int next_matrix = 0;
+  std::vector<GemmOperands> gemm_operands;
+  std::vector<AttnSources> attn_sources;
+  std::vector<int> last_reader;  // per stage: last stage that reads its output
 
   bool fail(const std::string &msg) { plan.error = msg; return false; }
-  int new_counter() { plan.counter_total.push_back(0); return plan.counters++; }
 
-  // operand lookup: which earlier stage's output contains this address
   int producer_of(const void *p, int before, int64_t *elem) const {
     const char *c = (const char *)p;
     for (int j = before - 1; j >= 0; --j) {
@@ -199,62 +201,53 @@ struct Planner {
     }
     return -1;
   }
-  // counters a reader of columns [c0, c1) of stage j's output has to wait for
-  void deps_for(int j, int c0, int c1, std::vector<std::pair<int, uint32_t>> &w, bool coarse = false) const {
-    const StageCounters &s = sc[j];
-    if (stages[j].kind == FML_RESIDENT_GEMM) {
-      if (!s.ln && !coarse) {
-        const int n0 = c0 / s.tile_n, n1 = (c1 - 1) / s.tile_n;
-        if (n1 - n0 + 1 <= 2) {
-          for (int n = n0; n <= n1; ++n) w.push_back({s.fin_slab[n], (uint32_t)s.S});
-          return;
+  // same lookup before plan.outs exists (first pass over the stages)
+  static bool out_extent(const fml_resident_stage &st, const char **base, int64_t *n) {
+    if (!st.out.data || st.out.rank < 2) return false;
+    *base = (const char *)st.out.data;
+    if (st.kind == FML_RESIDENT_GEMM) *n = st.out.shape[st.out.rank - 1];
+    else *n = st.out.stride[st.out.rank - 2];
+    return *n > 0;
+  }
+  void find_last_readers() {
+    last_reader.assign(count, -1);
+    for (int i = 0; i < count; ++i) {
+      const fml_resident_stage &st = stages[i];
+      const fml_tensor *ins[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+      if (st.kind == FML_RESIDENT_GEMM) { ins[0] = &st.a; ins[1] = &st.residual; }
+      else { ins[0] = &st.q; ins[1] = &st.kt; ins[2] = &st.v; }
+      for (const fml_tensor *t : ins) {
+        if (!t || !t->data) continue;
+        for (int j = i - 1; j >= 0; --j) {
+          const char *base; int64_t n;
+          if (!out_extent(stages[j], &base, &n)) continue;
+          const char *c = (const char *)t->data;
+          if (c >= base && c < base + (size_t)kRows * n * 4) { last_reader[j] = std::max(last_reader[j], i); break; }
         }
       }
-      w.push_back({s.fin_all, (uint32_t)s.fin_all_total});
-    } else {
-      const fml_resident_stage &st = stages[j];
-      const int dv = (int)st.v.shape[st.v.rank - 1];
-      const int hs = plan.attn[plan.stage_to_attn[j]].o_hs, oc = plan.attn[plan.stage_to_attn[j]].o_col;
-      // heads whose output columns [oc + h * hs, oc + h * hs + dv) meet [c0, c1)
-      std::vector<int> hit;
-      for (int h = 0; h < (int)s.head.size(); ++h)
-        if (oc + h * hs < c1 && oc + h * hs + dv > c0) hit.push_back(h);
-      if (hit.size() <= 2 && !coarse) for (int h : hit) w.push_back({s.head[h], (uint32_t)s.rowblocks});
-      else w.push_back({s.head_all, (uint32_t)s.head_all_total});
     }
   }
-  void set_waits(Step &st, std::vector<std::pair<int, uint32_t>> w) {
-    std::sort(w.begin(), w.end());
-    w.erase(std::unique(w.begin(), w.end()), w.end());
-    st.nwait = 0;
-    for (auto &p : w) {
-      if (st.nwait == kMaxWait) break;  // cannot happen: callers keep the lists short
-      st.wait_ctr[st.nwait] = p.first;
-      st.wait_target[st.nwait] = p.second;
-      ++st.nwait;
+  // a buffer of `bytes` for stage `stage`, whose content is last read by stage `free_after`
+  int take_buffer(size_t bytes, int stage, int free_after, int *gen) {
+    int best = -1;
+    for (size_t b = 0; b < plan.buffers.size(); ++b) {
+      Buffer &bf = plan.buffers[b];
+      if (bf.bytes == bytes && bf.free_after + lag <= stage) { best = (int)b; break; }
     }
+    if (best < 0) {
+      Buffer bf;
+      bf.bytes = bytes;
+      plan.buffers.push_back(bf);
+      best = (int)plan.buffers.size() - 1;
+    }
+    Buffer &bf = plan.buffers[best];
+    *gen = bf.uses++;
+    bf.free_after = free_after;
+    return best;
   }
-  void access(int matrix, int r0, int r1, int c0, int c1, uintptr_t lo, uintptr_t hi, bool write, int cta, int order) {
-    plan.accesses.push_back({matrix, r0, r1, c0, c1, lo, hi, write, cta, (int)plan.steps[cta].size(), order});
+  void access(int buffer, int gen, int r0, int r1, int c0, int c1, bool write, int cta) {
+    plan.accesses.push_back({buffer, gen, r0, r1, c0, c1, write, cta, (int)plan.steps[cta].size()});
   }
-  // a tiled matrix at `base`: byte range of quads [c0, c1)
-  void access_tiled(int matrix, const void *base, int r0, int r1, int c0, int c1, bool write, int cta, int order) {
-    const uintptr_t b = (uintptr_t)base;
-    access(matrix, r0, r1, c0, c1, b + (uintptr_t)c0 * kRows * 16, b + (uintptr_t)c1 * kRows * 16, write, cta, order);
-  }
-  void access_rm(int matrix, const void *base, int64_t ld, int r0, int r1, int c0, int c1, bool write, int cta, int order) {
-    const uintptr_t b = (uintptr_t)base;
-    access(matrix, r0, r1, c0, c1, b + (uintptr_t)r0 * ld * 4 + (uintptr_t)c0 * 16, b + (uintptr_t)(r1 - 1) * ld * 4 + (uintptr_t)c1 * 16, write, cta, order);
-  }
-
-  struct Operand {  // a [128 x cols] input
-    bool tiled = false;
-    int producer = -1, col0 = 0;
-    const float *ptr = nullptr;  // row-major: element (0, 0); tiled: resolved later from the producer
-    int64_t ld = 0;
-    int matrix = -1;
-  };
-  std::map<const void *, int> external_ids;  // row-major inputs nobody in the program writes
 
   bool operand(const fml_tensor &t, int i, int64_t cols, Operand &op, const char *what) {
     Rows r;
@@ -266,41 +259,40 @@ struct Planner {
       const OutInfo &o = plan.outs[j];
       if (r.ld != o.N || e >= o.N || (e & 3) || e + cols > o.N)
         return fail(std::string(what) + ": not a column range of the producing stage's rows");
-      op.tiled = true; op.producer = j; op.col0 = (int)e; op.matrix = o.matrix;
-      plan.outs[j].needs_shadow = plan.outs[j].external;
+      op.tiled = true; op.producer = j; op.col0 = (int)e;
       return true;
     }
     if (((uintptr_t)t.data & 15) || (r.ld & 3)) return fail(std::string(what) + ": external operand is not 16-byte aligned");
     op.tiled = false; op.ptr = (const float *)t.data; op.ld = r.ld;
-    auto it = external_ids.find(t.data);
-    if (it == external_ids.end()) it = external_ids.insert({t.data, next_matrix++}).first;
-    op.matrix = it->second;
     return true;
   }
+  static int tagsel(int gen, int uses) { return (gen & 1) | ((uses & 1) << 1); }
 
   bool run() {
+    plan = Plan();
+    gemm_operands.clear();
+    attn_sources.clear();
     plan.ctas = ctas;
     plan.steps.assign(ctas, {});
     plan.weight_begin.assign(ctas, 0);
     plan.stage_to_gemm.assign(count, -1);
     plan.stage_to_attn.assign(count, -1);
-    sc.assign(count, {});
     if (count < 1) return fail("no stages");
     if (ctas < 1) return fail("no CTAs");
-    std::vector<std::vector<uint32_t>> cta_bytes(ctas);  // chunk sizes per CTA in stream order
+    find_last_readers();
     std::vector<std::vector<std::pair<int, PackDesc>>> cta_chunks(ctas);
     int max_tile_n = 16;
     size_t attn_bytes = 0;
+    int max_finish_slots = 1;
 
     for (int i = 0; i < count; ++i) {
       const fml_resident_stage &st = stages[i];
       OutInfo o;
       o.external = st.out_external != 0;
       o.base = (const char *)st.out.data;
-      o.matrix = next_matrix++;
-      o.matrix_rm = o.external ? next_matrix++ : -1;
       if (!st.out.data || ((uintptr_t)st.out.data & 15)) return fail("stage output is null or not 16-byte aligned");
-      const int order_unit = 3 * i, order_fin = 3 * i + 1;
+      const bool read_inside = last_reader[i] >= 0;
+      if (!o.external && !read_inside) return fail("a stage output that nothing reads");
 
       if (st.kind == FML_RESIDENT_GEMM) {
         Rows ro;
@@ -308,17 +300,17 @@ struct Planner {
         const int N = (int)ro.cols;
         if (st.w.rank != 2 || st.w.dtype != FML_F32 || !st.w.data || st.w.shape[1] != N) return fail("GEMM weights must be a [K, N] fp32 matrix");
         const int K = (int)st.w.shape[0];
-        if (K < kBK || K % kBK || N % 16 || N > 4096 * 4) return fail("GEMM needs K a multiple of 32 and N a multiple of 16");
+        if (K < kBK || K % kBK || N % 16 || N > 4096) return fail("GEMM needs K a multiple of 32 and N a multiple of 16 up to 4096");
         if (!o.external && ro.ld != N) return fail("an internal GEMM output must be dense");
         if (o.external && (ro.ld & 3)) return fail("external GEMM output rows must be 16-byte multiples");
-        if (st.layernorm && N > 4096) return fail("LayerNorm rows longer than 4096");
         if (st.act < FML_ACT_NONE || st.act > FML_ACT_SIGMOID) return fail("unsupported activation");
         o.N = N;
+        if (read_inside) o.buffer = take_buffer((size_t)kRows * N * 4, i, last_reader[i], &o.gen);
         plan.outs.push_back(o);
-        Operand a, res;
-        if (!operand(st.a, i, K, a, "GEMM input")) return false;
-        const bool has_res = st.residual.data != nullptr;
-        if (has_res && !operand(st.residual, i, N, res, "GEMM residual")) return false;
+        GemmOperands ops;
+        if (!operand(st.a, i, K, ops.a, "GEMM input")) return false;
+        ops.has_res = st.residual.data != nullptr;
+        if (ops.has_res && !operand(st.residual, i, N, ops.res, "GEMM residual")) return false;
         if (st.bias.data && (st.bias.dtype != FML_F32 || st.bias.shape[st.bias.rank - 1] != N || st.bias.stride[st.bias.rank - 1] != 1 ||
                              ((uintptr_t)st.bias.data & 15)))
           return fail("GEMM bias must be a dense, aligned [N] vector");
@@ -338,100 +330,61 @@ struct Planner {
           fprintf(stderr, "resident: stage %d GEMM K=%d N=%d -> tile_n %d x %d splits (%d units, model %.2f us)\n", i, K, N,
                   tc.tile_n, tc.S, N / tc.tile_n * tc.S, stage_cost(K, N, tc.tile_n, tc.S, st.layernorm != 0));
         const int slabs = N / tc.tile_n, S = tc.S, nkb_total = K / kBK, NC = N / 4;
-
-        StageCounters &c = sc[i];
-        c.tile_n = tc.tile_n; c.S = S; c.ln = st.layernorm != 0;
-        if (c.ln) c.unit_all = new_counter();
-        else { c.unit_slab.resize(slabs); for (int &x : c.unit_slab) x = new_counter(); }
-        if (!c.ln) { c.fin_slab.resize(slabs); for (int &x : c.fin_slab) x = new_counter(); }
-        c.fin_all = new_counter();
+        const bool ln = st.layernorm != 0;
+        const bool res_tagged = ops.has_res && ops.res.tiled;
+        // fetch slots a finishing thread needs at once: LayerNorm keeps all its quads of a row
+        const int per = S + (res_tagged ? 1 : 0);
+        max_finish_slots = std::max(max_finish_slots, ln ? ((NC + kWorkers - 1) / kWorkers) * per : per);
+        if (ln && (NC + kWorkers - 1) / kWorkers > 4) return fail("LayerNorm rows longer than 4096");
+        ops.part_buffer = take_buffer((size_t)S * N * kRows * 4, i, i, &ops.part_gen);
 
         GemmStage g{};
         g.N = N; g.K = K; g.S = S; g.tile_n = tc.tile_n;
-        g.a_tiled = a.tiled; g.a_ld = a.ld;
-        g.a = a.tiled ? (const float *)(uintptr_t)a.col0 : a.ptr;  // tiled: resolved in resolve()
+        g.a_tiled = ops.a.tiled; g.a_ld = ops.a.ld; g.a = ops.a.ptr;
+        g.a_tag = ops.a.tiled ? 0 : -1;  // selectors are filled in once every buffer's use count is known
         g.bias = (const float *)st.bias.data;
-        g.res_tiled = has_res && res.tiled; g.res_ld = res.ld;
-        g.res = has_res ? (res.tiled ? (const float *)(uintptr_t)res.col0 : res.ptr) : nullptr;
+        g.res_tiled = res_tagged; g.res_ld = ops.res.ld; g.res = ops.has_res ? ops.res.ptr : nullptr;
+        g.res_tag = res_tagged ? 0 : -1;
         g.act = st.act; g.c0 = st.act_param[0]; g.c1 = st.act_param[1]; g.c2 = st.act_param[2];
-        g.ln = c.ln; g.gamma = (const float *)st.ln_scale.data; g.beta = (const float *)st.ln_bias.data; g.eps = st.ln_eps;
+        g.ln = ln; g.gamma = (const float *)st.ln_scale.data; g.beta = (const float *)st.ln_bias.data; g.eps = st.ln_eps;
         g.out_rm = o.external ? (float *)st.out.data : nullptr;
         g.out_ld = ro.ld;
         plan.gemm.push_back(g);
         plan.stage_to_gemm[i] = gi;
-        gemm_operands.push_back({a, res, has_res});
+        gemm_operands.push_back(ops);
         plan.pack.push_back({});
-        plan.gemm_partial_slot.push_back(-1);  // assigned by assign_partials()
 
-        // ---- units
-        const int partial_matrix = next_matrix++;
-        partial_matrix_of.push_back(partial_matrix);
+        // ---- units: read A columns [kb0 * 32, kb1 * 32), write their partial tile
         for (int n = 0; n < slabs; ++n)
           for (int s = 0; s < S; ++s) {
             const int cta = (n * S + s) % ctas;
             const int kb0 = (int)((long long)s * nkb_total / S), kb1 = (int)((long long)(s + 1) * nkb_total / S);
             Step u{};
             u.kind = kUnit; u.stage = gi; u.p0 = n; u.p1 = s; u.p2 = kb0; u.p3 = kb1 - kb0;
-            u.sig[0] = c.ln ? c.unit_all : c.unit_slab[n];
-            u.sig[1] = -1;
-            ++plan.counter_total[u.sig[0]];
-            std::vector<std::pair<int, uint32_t>> w;
-            if (a.tiled) deps_for(a.producer, a.col0 + kb0 * kBK, a.col0 + kb1 * kBK, w);
-            set_waits(u, w);
-            // reads A columns [kb0*32, kb1*32), writes its partial tile
-            if (a.tiled) access_tiled(a.matrix, tiled_base_key(a.producer), 0, kRows, (a.col0 + kb0 * kBK) / 4, (a.col0 + kb1 * kBK) / 4, false, cta, order_unit);
-            else access_rm(a.matrix, a.ptr, a.ld, 0, kRows, kb0 * 8, kb1 * 8, false, cta, order_unit);
-            pending_partial.push_back({(int)plan.accesses.size(), gi});
-            access(partial_matrix, 0, kRows, s * NC + n * tc.tile_n / 4, s * NC + (n + 1) * tc.tile_n / 4, 0, 0, true, cta, order_unit);
+            if (ops.a.tiled)
+              access(plan.outs[ops.a.producer].buffer, plan.outs[ops.a.producer].gen, 0, kRows, (ops.a.col0 + kb0 * kBK) / 4,
+                     (ops.a.col0 + kb1 * kBK) / 4, false, cta);
+            access(ops.part_buffer, ops.part_gen, 0, kRows, s * NC + n * tc.tile_n / 4, s * NC + (n + 1) * tc.tile_n / 4, true, cta);
             plan.steps[cta].push_back(u);
-            for (int kb = kb0; kb < kb1; ++kb) {
-              cta_chunks[cta].push_back({gi, PackDesc{0, n * tc.tile_n, kb * kBK, tc.tile_n, 0}});
-              cta_bytes[cta].push_back((uint32_t)tc.tile_n * 128u);
-            }
+            for (int kb = kb0; kb < kb1; ++kb) cta_chunks[cta].push_back({gi, PackDesc{0, n * tc.tile_n, kb * kBK, tc.tile_n, 0}});
           }
         // ---- finish steps
-        auto finish = [&](int cta, int r0, int r1, int q0, int q1, int n) {
+        auto finish = [&](int cta, int r0, int r1, int q0, int q1) {
           Step f{};
           f.kind = kFinish; f.stage = gi; f.p0 = r0; f.p1 = r1; f.p2 = q0; f.p3 = q1;
-          f.sig[0] = c.fin_all; f.sig[1] = c.ln ? -1 : c.fin_slab[n];
-          ++plan.counter_total[c.fin_all];
-          if (f.sig[1] >= 0) ++plan.counter_total[f.sig[1]];
-          std::vector<std::pair<int, uint32_t>> w;
-          if (c.ln) w.push_back({c.unit_all, (uint32_t)(slabs * S)});
-          else w.push_back({c.unit_slab[n], (uint32_t)S});
-          if (has_res && res.tiled) {
-            std::vector<std::pair<int, uint32_t>> wr;
-            deps_for(res.producer, res.col0 + q0 * 4, res.col0 + q1 * 4, wr);
-            for (auto &p : wr) w.push_back(p);
-          }
-          set_waits(f, w);
-          for (int s = 0; s < S; ++s) {
-            pending_partial.push_back({(int)plan.accesses.size(), gi});
-            access(partial_matrix, r0, r1, s * NC + q0, s * NC + q1, 0, 0, false, cta, order_fin);
-          }
-          if (has_res) {
-            if (res.tiled) access_tiled(res.matrix, tiled_base_key(res.producer), r0, r1, res.col0 / 4 + q0, res.col0 / 4 + q1, false, cta, order_fin);
-            else access_rm(res.matrix, res.ptr, res.ld, r0, r1, q0, q1, false, cta, order_fin);
-          }
-          pending_out.push_back({(int)plan.accesses.size(), i});
-          access(o.matrix, r0, r1, q0, q1, 0, 0, true, cta, order_fin);
-          if (o.external) access_rm(o.matrix_rm, st.out.data, ro.ld, r0, r1, q0, q1, true, cta, order_fin);
+          for (int s = 0; s < S; ++s) access(ops.part_buffer, ops.part_gen, r0, r1, s * NC + q0, s * NC + q1, false, cta);
+          if (res_tagged)
+            access(plan.outs[ops.res.producer].buffer, plan.outs[ops.res.producer].gen, r0, r1, ops.res.col0 / 4 + q0, ops.res.col0 / 4 + q1, false, cta);
+          if (o.buffer >= 0) access(o.buffer, o.gen, r0, r1, q0, q1, true, cta);
           plan.steps[cta].push_back(f);
         };
-        if (c.ln) {
+        if (ln) {
           const int owners = std::min(ctas, kRows);
-          for (int k = 0; k < owners; ++k) {
-            const int r0 = k * kRows / owners, r1 = (k + 1) * kRows / owners;
-            finish(k, r0, r1, 0, NC, -1);
-          }
-          c.fin_all_total = owners;
+          for (int k = 0; k < owners; ++k) finish(k, k * kRows / owners, (k + 1) * kRows / owners, 0, NC);
         } else {
           for (int n = 0; n < slabs; ++n)
-            for (int s = 0; s < S; ++s) {
-              const int r0 = s * kRows / S, r1 = (s + 1) * kRows / S;
-              finish((n * S + s) % ctas, r0, r1, n * tc.tile_n / 4, (n + 1) * tc.tile_n / 4, n);
-            }
-          c.fin_all_total = slabs * S;
+            for (int s = 0; s < S; ++s)
+              finish((n * S + s) % ctas, s * kRows / S, (s + 1) * kRows / S, n * tc.tile_n / 4, (n + 1) * tc.tile_n / 4);
         }
       } else if (st.kind == FML_RESIDENT_ATTENTION) {
         // q [.., H, 128, D], kt [.., H, D, 128], v [.., H, 128, Dv], out [.., H, 128, Dv]
@@ -453,13 +406,14 @@ struct Planner {
         if (o_ld < (int64_t)(H - 1) * o_hs + Dv || (o_hs & 3) || (o_ld & 3) || o_hs < Dv) return fail("attention output heads overlap or are misaligned");
         if (!o.external && o_ld != (int64_t)H * o_hs) return fail("an internal attention output must be dense");
         o.N = (int)o_ld;
+        if (read_inside) o.buffer = take_buffer((size_t)kRows * o.N * 4, i, last_reader[i], &o.gen);
         plan.outs.push_back(o);
         AttnStage A{};
         A.heads = H; A.D = D; A.Dv = Dv; A.Sk = Sk; A.divisor = st.divisor;
         A.o_col = 0; A.o_hs = (int)o_hs; A.out_ld = o_ld;
         A.out_rm = o.external ? (float *)out.data : nullptr;
         // q / k / v: column ranges of earlier stages' tiled outputs
-        struct Src { int producer, col0, hs, matrix; } src[3];
+        struct Src { int producer, col0, hs; } src[3];
         const fml_tensor *ts[3] = {&q, &kt, &v};
         for (int k = 0; k < 3; ++k) {
           const fml_tensor &t = *ts[k];
@@ -473,8 +427,7 @@ struct Planner {
           if (t.stride[col_dim] != 1 || t.stride[row_dim] != p.N || e >= p.N || (e & 3) || (hs & 3) || hs < 0 ||
               e + (int64_t)(H - 1) * hs + width > p.N)
             return fail("attention input is not a per-head column range of the producing stage's rows");
-          src[k] = {j, (int)e, (int)hs, p.matrix};
-          plan.outs[j].needs_shadow = plan.outs[j].external;
+          src[k] = {j, (int)e, (int)hs};
         }
         A.q_col = src[0].col0; A.q_hs = src[0].hs; A.k_col = src[1].col0; A.k_hs = src[1].hs; A.v_col = src[2].col0; A.v_hs = src[2].hs;
         if (st.mask.data) {
@@ -495,41 +448,21 @@ struct Planner {
         const int ai = (int)plan.attn.size();
         plan.attn.push_back(A);
         plan.stage_to_attn[i] = ai;
-        attn_sources.push_back({src[0].producer, src[1].producer, src[2].producer});
-        StageCounters &c = sc[i];
-        c.rowblocks = kRows / kAttnRows;
-        c.head.resize(H);
-        for (int &x : c.head) x = new_counter();
-        c.head_all = new_counter();
-        c.head_all_total = H * c.rowblocks;
+        attn_sources.push_back({{src[0].producer, src[1].producer, src[2].producer}});
+        const int rowblocks = kRows / kAttnRows;
         for (int h = 0; h < H; ++h)
-          for (int rb = 0; rb < c.rowblocks; ++rb) {
-            const int cta = (h * c.rowblocks + rb) % ctas;
+          for (int rb = 0; rb < rowblocks; ++rb) {
+            const int cta = (h * rowblocks + rb) % ctas;
             Step a{};
             a.kind = kAttention; a.stage = ai; a.p0 = h; a.p1 = rb * kAttnRows;
-            a.sig[0] = c.head[h]; a.sig[1] = c.head_all;
-            ++plan.counter_total[a.sig[0]];
-            ++plan.counter_total[a.sig[1]];
-            std::vector<std::pair<int, uint32_t>> w;
             const int widths[3] = {D, D, Dv};
-            for (int pass = 0; pass < 2; ++pass) {  // per-slab counters first, whole-stage counters if those are too many
-              w.clear();
-              for (int k = 0; k < 3; ++k)
-                deps_for(src[k].producer, src[k].col0 + h * src[k].hs, src[k].col0 + h * src[k].hs + widths[k], w, pass == 1);
-              std::sort(w.begin(), w.end());
-              w.erase(std::unique(w.begin(), w.end()), w.end());
-              if (w.size() <= (size_t)kMaxWait) break;
-            }
-            if (w.size() > (size_t)kMaxWait) return fail("attention step depends on too many counters");
-            set_waits(a, w);
             for (int k = 0; k < 3; ++k) {
               const int c0 = (src[k].col0 + h * src[k].hs) / 4, c1 = c0 + widths[k] / 4;
               const int r0 = k == 0 ? rb * kAttnRows : 0, r1 = k == 0 ? r0 + kAttnRows : kRows;
-              access_tiled(src[k].matrix, tiled_base_key(src[k].producer), r0, r1, c0, c1, false, cta, order_unit);
+              access(plan.outs[src[k].producer].buffer, plan.outs[src[k].producer].gen, r0, r1, c0, c1, false, cta);
             }
-            pending_out.push_back({(int)plan.accesses.size(), i});
-            access(o.matrix, rb * kAttnRows, (rb + 1) * kAttnRows, (int)(h * o_hs / 4), (int)((h * o_hs + Dv) / 4), 0, 0, true, cta, order_unit);
-            if (o.external) access_rm(o.matrix_rm, out.data, o_ld, rb * kAttnRows, (rb + 1) * kAttnRows, (int)(h * o_hs / 4), (int)((h * o_hs + Dv) / 4), true, cta, order_unit);
+            if (o.buffer >= 0)
+              access(o.buffer, o.gen, rb * kAttnRows, (rb + 1) * kAttnRows, (int)(h * o_hs / 4), (int)((h * o_hs + Dv) / 4), true, cta);
             plan.steps[cta].push_back(a);
           }
       } else {
@@ -537,9 +470,35 @@ struct Planner {
       }
     }
 
-    // ---- shared memory: ring slots sized for the widest tile, overlay for lo(B) / attention
+    // ---- tag selectors, now that every buffer's number of generations per pass is known
+    for (int i = 0; i < count; ++i) {
+      const OutInfo &o = plan.outs[i];
+      const int out_tag = o.buffer >= 0 ? tagsel(o.gen, plan.buffers[o.buffer].uses) : 0;
+      auto tag_of = [&](int producer) { const OutInfo &p = plan.outs[producer]; return tagsel(p.gen, plan.buffers[p.buffer].uses); };
+      if (plan.stage_to_gemm[i] >= 0) {
+        const int gi = plan.stage_to_gemm[i];
+        GemmStage &g = plan.gemm[gi];
+        const GemmOperands &ops = gemm_operands[gi];
+        if (ops.a.tiled) g.a_tag = tag_of(ops.a.producer);
+        if (ops.has_res && ops.res.tiled) g.res_tag = tag_of(ops.res.producer);
+        g.part_tag = tagsel(ops.part_gen, plan.buffers[ops.part_buffer].uses);
+        g.out_tag = out_tag;
+      } else {
+        const int ai = plan.stage_to_attn[i];
+        AttnStage &a = plan.attn[ai];
+        a.q_tag = tag_of(attn_sources[ai].producer[0]);
+        a.k_tag = tag_of(attn_sources[ai].producer[1]);
+        a.v_tag = tag_of(attn_sources[ai].producer[2]);
+        a.out_tag = out_tag;
+      }
+    }
+
+    // ---- shared memory: ring slots sized for the widest tile; the overlay holds the lo(B) slots
+    // and staged A rows of a unit, the fetch slots of a finish step, or the attention tiles
     plan.slot_bytes = max_tile_n * 128;
-    size_t overlay = std::max((size_t)kConvDepth * plan.slot_bytes, attn_bytes);
+    size_t overlay = (size_t)kConvDepth * plan.slot_bytes + (size_t)kAStages * kRows * kAPitch * 4;
+    overlay = std::max(overlay, attn_bytes);
+    overlay = std::max(overlay, (size_t)max_finish_slots * kWorkers * 16);
     overlay = (overlay + 1023) / 1024 * 1024;
     plan.overlay_bytes = (int)overlay;
     int nslots = 8;
@@ -560,133 +519,105 @@ struct Planner {
     }
     plan.packed_bytes = std::max<size_t>(off, 1024);
     for (int c = 0; c < ctas; ++c) plan.max_steps = std::max(plan.max_steps, (int)plan.steps[c].size());
-
-    // ---- tiled shadows of external outputs that later stages read
-    for (int i = 0; i < count; ++i)
-      if (plan.outs[i].external && plan.outs[i].needs_shadow) {
-        plan.outs[i].tiled_offset = plan.shadow_bytes;
-        plan.shadow_bytes += (size_t)kRows * plan.outs[i].N * 4;
-      }
-    return assign_partials();
+    size_t boff = 0;
+    for (Buffer &b : plan.buffers) { b.offset = boff; boff += (b.bytes + 1023) / 1024 * 1024; }
+    plan.buffer_bytes = std::max<size_t>(boff, 1024);
+    std::string why;
+    if (!check(why)) return fail("plan check failed: " + why);
+    return true;
   }
 
-  // bookkeeping for addresses that are only known once scratch is laid out
-  struct GemmOperands { Operand a, res; bool has_res; };
-  std::vector<GemmOperands> gemm_operands;
-  std::vector<std::vector<int>> attn_sources;
-  std::vector<int> partial_matrix_of;
-  std::vector<std::pair<int, int>> pending_partial;  // (access index, gemm index)
-  std::vector<std::pair<int, int>> pending_out;      // (access index, stage index)
-
-  // Address key of stage j's tiled output for the alias check: its own bytes when internal, a
-  // private range (never aliasing anything else) when it is a shadow in scratch.
-  const void *tiled_base_key(int j) const {
-    const OutInfo &o = plan.outs[j];
-    return o.external ? (const void *)((uintptr_t)1 << 60 | ((uintptr_t)j << 40)) : (const void *)o.base;
-  }
-
-  // Partial-tile buffers: stages share `period` buffers round robin; the smallest period whose
-  // plan passes the ordering check is taken.
-  bool assign_partials() {
-    const int ng = (int)plan.gemm.size();
-    std::vector<int> periods;
-    for (int x = 2; x < ng; x *= 2) periods.push_back(x);
-    periods.push_back(std::max(ng, 1));
-    for (int period : periods) {
-      plan.partial_bytes.assign(std::max(period, 1), 0);
-      for (int g = 0; g < ng; ++g) {
-        plan.gemm_partial_slot[g] = g % period;
-        plan.partial_bytes[g % period] = std::max(plan.partial_bytes[g % period], (size_t)plan.gemm[g].S * plan.gemm[g].N * kRows * 4);
-      }
-      // address keys for the check: partial slot p lives in its own private range
-      for (auto &pa : pending_partial) {
-        Access &a = plan.accesses[pa.first];
-        const uintptr_t base = ((uintptr_t)2 << 60) | ((uintptr_t)plan.gemm_partial_slot[pa.second] << 40);
-        a.lo = base + (uintptr_t)a.c0 * kRows * 16;
-        a.hi = base + (uintptr_t)a.c1 * kRows * 16;
-      }
-      for (auto &po : pending_out) {
-        Access &a = plan.accesses[po.first];
-        const uintptr_t base = (uintptr_t)tiled_base_key(po.second);
-        a.lo = base + (uintptr_t)a.c0 * kRows * 16;
-        a.hi = base + (uintptr_t)a.c1 * kRows * 16;
-      }
-      std::string why;
-      if (check(why)) return true;
-      if (ng == 0 || period >= ng) return fail("plan check failed: " + why);
-    }
-    return fail("plan check failed");
-  }
-
-  // Symbolic execution with vector clocks, then the pairwise ordering check.
+  // Symbolic execution over read-after-write edges with vector clocks, then the ordering checks.
   bool check(std::string &why) const {
     const int C = ctas;
-    std::vector<size_t> pc(C, 0);
-    std::vector<uint32_t> value(plan.counters, 0);
-    std::vector<std::vector<int>> closure(plan.counters, std::vector<int>(C, 0));  // clock implied by "counter complete"
+    // accesses of each (buffer, generation)
+    std::map<std::pair<int, int>, std::vector<const Access *>> by_gen;
+    std::vector<std::vector<std::vector<const Access *>>> of_step(C);
+    for (int c = 0; c < C; ++c) of_step[c].resize(plan.steps[c].size());
+    for (const Access &a : plan.accesses) {
+      by_gen[{a.buffer, a.gen}].push_back(&a);
+      of_step[a.cta][a.index].push_back(&a);
+    }
+    auto overlap = [](const Access &x, const Access &y) {
+      const long long r = std::min(x.r1, y.r1) - std::max(x.r0, y.r0), c = std::min(x.c1, y.c1) - std::max(x.c0, y.c0);
+      return r > 0 && c > 0 ? r * c : 0ll;
+    };
+    // coverage and write-write exclusion inside a generation
+    for (const auto &kv : by_gen) {
+      const auto &v = kv.second;
+      for (size_t i = 0; i < v.size(); ++i) {
+        if (v[i]->write) {
+          for (size_t j = i + 1; j < v.size(); ++j)
+            if (v[j]->write && overlap(*v[i], *v[j])) { why = "two steps write the same word of one generation"; return false; }
+        } else {
+          long long covered = 0;
+          for (const Access *w : v)
+            if (w->write) covered += overlap(*v[i], *w);
+          if (covered != (long long)(v[i]->r1 - v[i]->r0) * (v[i]->c1 - v[i]->c0)) { why = "a read that no write of its generation covers"; return false; }
+        }
+      }
+    }
+    // run: a step is ready when every write its reads overlap has run
+    std::vector<std::vector<char>> done(C);
     std::vector<std::vector<std::vector<int>>> clock(C);  // clock[cta][step] at step start
-    for (int c = 0; c < C; ++c) clock[c].resize(plan.steps[c].size());
-    std::vector<std::vector<int>> last(C, std::vector<int>(C, 0));  // running clock of each CTA
-    for (int c = 0; c < plan.counters; ++c)
-      if (plan.counter_total[c] == 0) { why = "a counter nobody bumps"; return false; }
-    bool progress = true;
-    size_t done = 0, total = 0;
+    for (int c = 0; c < C; ++c) { done[c].assign(plan.steps[c].size(), 0); clock[c].resize(plan.steps[c].size()); }
+    std::vector<size_t> pc(C, 0);
+    std::vector<std::vector<int>> last(C, std::vector<int>(C, 0));
+    size_t finished = 0, total = 0;
     for (int c = 0; c < C; ++c) total += plan.steps[c].size();
+    bool progress = true;
     while (progress) {
       progress = false;
       for (int c = 0; c < C; ++c) {
         while (pc[c] < plan.steps[c].size()) {
-          const Step &st = plan.steps[c][pc[c]];
+          const size_t k = pc[c];
           bool ready = true;
-          for (int w = 0; w < st.nwait; ++w) {
-            if (st.wait_target[w] != plan.counter_total[st.wait_ctr[w]]) { why = "a wait target differs from the counter's total"; return false; }
-            if (value[st.wait_ctr[w]] < st.wait_target[w]) ready = false;
+          std::vector<int> clk = last[c];
+          for (const Access *r : of_step[c][k]) {
+            if (r->write) continue;
+            for (const Access *w : by_gen.at({r->buffer, r->gen})) {
+              if (!w->write || !overlap(*r, *w)) continue;
+              if (w->cta == c && (size_t)w->index == k) continue;
+              if (!done[w->cta][w->index]) { ready = false; break; }
+              // everything known at the writer's start, plus the writer itself
+              const std::vector<int> &wc = clock[w->cta][w->index];
+              for (int x = 0; x < C; ++x) clk[x] = std::max(clk[x], wc[x]);
+              clk[w->cta] = std::max(clk[w->cta], w->index + 1);
+            }
+            if (!ready) break;
           }
           if (!ready) break;
-          std::vector<int> &k = last[c];
-          for (int w = 0; w < st.nwait; ++w)
-            for (int x = 0; x < C; ++x) k[x] = std::max(k[x], closure[st.wait_ctr[w]][x]);
-          clock[c][pc[c]] = k;
-          k[c] = (int)pc[c] + 1;  // at its end the step itself is complete
-          for (int sgi = 0; sgi < 2; ++sgi)
-            if (st.sig[sgi] >= 0) {
-              ++value[st.sig[sgi]];
-              for (int x = 0; x < C; ++x) closure[st.sig[sgi]][x] = std::max(closure[st.sig[sgi]][x], k[x]);
-            }
+          clock[c][k] = clk;
+          last[c] = clk;
+          last[c][c] = (int)k + 1;
+          done[c][k] = 1;
           ++pc[c];
-          ++done;
+          ++finished;
           progress = true;
         }
       }
     }
-    if (done != total) { why = "the step lists deadlock"; return false; }
-    // pairwise: group by matrix; different matrices only where byte ranges overlap
-    std::vector<const Access *> acc;
-    for (const Access &a : plan.accesses) acc.push_back(&a);
-    std::sort(acc.begin(), acc.end(), [](const Access *x, const Access *y) { return x->lo < y->lo; });
-    auto before = [&](const Access &x, const Access &y) {  // x's step complete when y's starts
+    if (finished != total) { why = "the step lists cannot all run (a step waits for data written after it)"; return false; }
+    // every overwrite is ordered after the readers and writers of the previous generation
+    auto before = [&](const Access &x, const Access &y) {  // x's step is complete when y's may start
       if (x.cta == y.cta) return x.index < y.index;
       return clock[y.cta][y.index][x.cta] > x.index;
     };
-    for (size_t i = 0; i < acc.size(); ++i) {
-      const Access &x = *acc[i];
-      for (size_t j = i + 1; j < acc.size() && acc[j]->lo < x.hi; ++j) {
-        const Access &y = *acc[j];
-        if (!x.write && !y.write) continue;
-        if (x.cta == y.cta && x.index == y.index) continue;
-        if (x.matrix == y.matrix) {
-          if (x.r1 <= y.r0 || y.r1 <= x.r0 || x.c1 <= y.c0 || y.c1 <= x.c0) continue;
-        }
-        const Access &first = (x.order < y.order || (x.order == y.order && !y.write)) ? x : y;
-        const Access &second = &first == &x ? y : x;
-        if (first.order == second.order && x.matrix == y.matrix && x.write && y.write) { why = "two steps of one stage write the same element"; return false; }
-        if (!before(first, second)) {
-          char buf[200];
-          snprintf(buf, sizeof(buf), "unordered accesses: cta %d step %d (%s, order %d) and cta %d step %d (%s, order %d), matrices %d / %d",
-                   first.cta, first.index, first.write ? "write" : "read", first.order, second.cta, second.index,
-                   second.write ? "write" : "read", second.order, first.matrix, second.matrix);
-          why = buf;
-          return false;
+    for (const auto &kv : by_gen) {
+      if (kv.first.second == 0) continue;
+      auto prev = by_gen.find({kv.first.first, kv.first.second - 1});
+      if (prev == by_gen.end()) continue;
+      for (const Access *w : kv.second) {
+        if (!w->write) continue;
+        for (const Access *p : prev->second) {
+          if (!overlap(*w, *p)) continue;
+          if (!before(*p, *w)) {
+            char buf[220];
+            snprintf(buf, sizeof(buf), "buffer %d reused too early: cta %d step %d writes generation %d while cta %d step %d may still %s generation %d",
+                     w->buffer, w->cta, w->index, w->gen, p->cta, p->index, p->write ? "write" : "read", p->gen);
+            why = buf;
+            return false;
+          }
         }
       }
     }
@@ -694,18 +625,28 @@ struct Planner {
   }
 };
 
+// Plans with the shortest buffer-reuse distance that passes the check.
+bool plan_program(const fml_resident_stage *stages, int count, int ctas, Planner &pl) {
+  std::string first_error;
+  for (int lag = 4; lag <= std::max(8, 2 * count); lag *= 2) {
+    pl = Planner{stages, count, ctas, lag};
+    if (pl.run()) return true;
+    if (pl.plan.error.find("reused too early") == std::string::npos) return false;  // nothing a longer distance would cure
+    if (first_error.empty()) first_error = pl.plan.error;
+  }
+  return false;
+}
+
 void fill_info(const Plan &p, fml_resident_info *info) {
   memset(info, 0, sizeof(*info));
   info->ctas = p.ctas;
   info->stages = (int)(p.gemm.size() + p.attn.size());
   for (const auto &s : p.steps) info->steps += (int)s.size();
-  info->counters = p.counters;
+  info->buffers = (int)p.buffers.size();
   info->ring_slots = p.nslots;
   info->slot_bytes = p.slot_bytes;
   info->packed_weight_bytes = p.packed_bytes;
-  size_t scratch = p.shadow_bytes;
-  for (size_t b : p.partial_bytes) scratch += b;
-  info->scratch_bytes = scratch;
+  info->scratch_bytes = p.buffer_bytes;
   info->shared_memory_bytes = kernel_smem_bytes(p.nslots, p.slot_bytes, p.overlay_bytes);
 }
 
@@ -726,6 +667,8 @@ __global__ void pack_weights_kernel(const float *w, long long sk, long long sn, 
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+
+
 }  // namespace
 }  // namespace res
 }  // namespace fml
@@ -741,8 +684,8 @@ extern "C" int fml_resident_plan(const fml_resident_stage *stages, int32_t count
     FML_CUDA(cudaGetDevice(&dev));
     FML_CUDA(cudaDeviceGetAttribute(&ctas, cudaDevAttrMultiProcessorCount, dev));
   }
-  Planner pl{stages, count, ctas};
-  FML_REQUIRE(pl.run(), FML_UNSUPPORTED, "fml_resident_plan: %s", pl.plan.error.c_str());
+  Planner pl{stages, count, ctas, 4};
+  FML_REQUIRE(plan_program(stages, count, ctas, pl), FML_UNSUPPORTED, "fml_resident_plan: %s", pl.plan.error.c_str());
   fill_info(pl.plan, info);
   return FML_OK;
 }
@@ -753,8 +696,8 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
   int dev = 0, ctas = 0;
   FML_CUDA(cudaGetDevice(&dev));
   FML_CUDA(cudaDeviceGetAttribute(&ctas, cudaDevAttrMultiProcessorCount, dev));
-  Planner pl{stages, count, ctas};
-  FML_REQUIRE(pl.run(), FML_UNSUPPORTED, "fml_resident_create: %s", pl.plan.error.c_str());
+  Planner pl{stages, count, ctas, 4};
+  FML_REQUIRE(plan_program(stages, count, ctas, pl), FML_UNSUPPORTED, "fml_resident_create: %s", pl.plan.error.c_str());
   Plan &p = pl.plan;
   int *status = device_status_word();
   FML_REQUIRE(status, FML_CUDA_ERROR, "fml_resident_create: no device status word");
@@ -769,12 +712,9 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
   const size_t o_gemm = take(std::max<size_t>(1, p.gemm.size()) * sizeof(GemmStage), 256);
   const size_t o_attn = take(std::max<size_t>(1, p.attn.size()) * sizeof(AttnStage), 256);
   const size_t o_wbegin = take((size_t)p.ctas * sizeof(unsigned long long), 256);
-  const size_t counter_bytes = align_up((size_t)(p.counters + 1) * 4, 256);  // + the abort word
-  const size_t o_counters = take(counter_bytes, 256);
-  std::vector<size_t> o_partial(p.partial_bytes.size());
-  for (size_t i = 0; i < p.partial_bytes.size(); ++i) o_partial[i] = take(p.partial_bytes[i], 1024);
-  const size_t o_shadow = take(p.shadow_bytes, 1024);
-  const size_t trace_entries = (size_t)p.ctas * p.max_steps * 2;
+  const size_t o_words = take(256, 256);  // [0] pass number, [32] abort word
+  const size_t o_buffers = take(p.buffer_bytes, 1024);
+  const size_t trace_entries = (size_t)p.ctas * p.max_steps * kTraceSlots;
   const size_t o_trace = take(trace_entries * 8, 256);
   size_t pack_descs = 0;
   for (const auto &v : p.pack) pack_descs = std::max(pack_descs, v.size());
@@ -795,28 +735,27 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
   auto fail_free = [&](int st) { cudaFree(r->scratch); cudaFree(r->packed); delete r; return st; };
 #define FML_TRY(call) do { cudaError_t e__ = (call); if (e__ != cudaSuccess) return fail_free(cuda_fail(e__, #call)); } while (0)
   FML_TRY(cudaMemset(r->scratch, 0, off));
+  FML_TRY(cudaMemset(base + o_buffers, 0x01, p.buffer_bytes));  // every word's generation bit starts at 1
   FML_TRY(cudaMemset(r->packed, 0, p.packed_bytes));
 
-  // ---- resolve addresses
-  auto tiled_ptr = [&](int stage) -> float * {
-    const OutInfo &o = p.outs[stage];
-    return o.external ? (o.needs_shadow ? (float *)(base + o_shadow + o.tiled_offset) : nullptr) : (float *)o.base;
-  };
+  // ---- resolve buffer addresses
+  auto buffer_ptr = [&](int b) -> float * { return (float *)(base + o_buffers + p.buffers[b].offset); };
+  auto tiled_ptr = [&](int stage) -> float * { return p.outs[stage].buffer >= 0 ? buffer_ptr(p.outs[stage].buffer) : nullptr; };
   for (int i = 0; i < count; ++i) {
     if (p.stage_to_gemm[i] >= 0) {
       const int gi = p.stage_to_gemm[i];
       GemmStage &g = p.gemm[gi];
-      const auto &ops = pl.gemm_operands[gi];
+      const GemmOperands &ops = pl.gemm_operands[gi];
       if (ops.a.tiled) g.a = tiled_ptr(ops.a.producer) + (size_t)(ops.a.col0 / 4) * kRows * 4;
       if (ops.has_res && ops.res.tiled) g.res = tiled_ptr(ops.res.producer) + (size_t)(ops.res.col0 / 4) * kRows * 4;
-      g.partial = (float *)(base + o_partial[p.gemm_partial_slot[gi]]);
+      g.partial = buffer_ptr(ops.part_buffer);
       g.out_tiled = tiled_ptr(i);
     } else {
       const int ai = p.stage_to_attn[i];
       AttnStage &a = p.attn[ai];
-      a.q = tiled_ptr(pl.attn_sources[ai][0]);
-      a.k = tiled_ptr(pl.attn_sources[ai][1]);
-      a.v = tiled_ptr(pl.attn_sources[ai][2]);
+      a.q = tiled_ptr(pl.attn_sources[ai].producer[0]);
+      a.k = tiled_ptr(pl.attn_sources[ai].producer[1]);
+      a.v = tiled_ptr(pl.attn_sources[ai].producer[2]);
       a.out_tiled = tiled_ptr(i);
     }
   }
@@ -849,7 +788,8 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
   }
 #undef FML_TRY
   r->ctas = p.ctas;
-  r->counter_bytes = counter_bytes;
+  r->tagged_offset = o_buffers;
+  r->tagged_bytes = p.buffer_bytes;
   r->trace_entries = trace_entries;
   r->smem_bytes = kernel_smem_bytes(p.nslots, p.slot_bytes, p.overlay_bytes);
   KernelArgs &a = r->args;
@@ -859,8 +799,8 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
   a.attn = (const AttnStage *)(base + o_attn);
   a.weights = (const uint8_t *)r->packed;
   a.weight_begin = (const unsigned long long *)(base + o_wbegin);
-  a.counters = (unsigned *)(base + o_counters);
-  a.abort_word = a.counters + p.counters;
+  a.epoch = (unsigned *)(base + o_words);
+  a.abort_word = a.epoch + 32;
   a.status = status;
   a.trace = (unsigned long long *)(base + o_trace);
   a.nslots = p.nslots; a.slot_bytes = p.slot_bytes; a.overlay_bytes = p.overlay_bytes; a.max_steps = p.max_steps;
@@ -872,9 +812,15 @@ extern "C" int fml_resident_create(const fml_resident_stage *stages, int32_t cou
 
 extern "C" int fml_resident_launch(fml_resident *r, void *stream) {
   FML_REQUIRE(r, FML_BAD_ARG, "fml_resident_launch: null program");
+  return launch_resident_kernel(r->args, r->ctas, r->smem_bytes, r->trace, as_stream(stream));
+}
+
+extern "C" int fml_resident_reset(fml_resident *r, void *stream) {
+  FML_REQUIRE(r, FML_BAD_ARG, "fml_resident_reset: null program");
   cudaStream_t s = as_stream(stream);
-  FML_CUDA(cudaMemsetAsync(r->args.counters, 0, r->counter_bytes, s));
-  return launch_resident_kernel(r->args, r->ctas, r->smem_bytes, r->trace, s);
+  FML_CUDA(cudaMemsetAsync((char *)r->scratch + r->tagged_offset, 0x01, r->tagged_bytes, s));
+  FML_CUDA(cudaMemsetAsync(r->args.epoch, 0, 256, s));  // pass number and abort word
+  return FML_OK;
 }
 
 extern "C" int fml_resident_info_of(const fml_resident *r, fml_resident_info *info) {

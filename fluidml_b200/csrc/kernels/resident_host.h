@@ -14,10 +14,10 @@ struct KernelArgs {
   const AttnStage *attn;
   const uint8_t *weights;                  // packed weight streams
   const unsigned long long *weight_begin;  // [ctas]: byte offset of each CTA's stream
-  unsigned *counters;
-  unsigned *abort_word;
+  unsigned *epoch;                         // pass number: selects the parity of every buffer generation
+  unsigned *abort_word;                    // set by whichever CTA gives up a wait first
   int *status;
-  unsigned long long *trace;               // traced variant only: [cta][max_steps][2]
+  unsigned long long *trace;               // traced variant only: [cta][max_steps][kTraceSlots]
   int32_t nslots, slot_bytes, overlay_bytes, max_steps;
 };
 

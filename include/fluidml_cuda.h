@@ -336,8 +336,10 @@ int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t
  * chain runs inside ONE persistent kernel, one CTA per SM, so no kernel boundary separates
  * dependent operators.  The weights of all stages are packed once, at creation, into one
  * stream per CTA which a producer warp copies into a shared-memory ring without ever waiting
- * for activations; stages synchronise through counters in global memory that consumers poll
- * (bounded) just before they need a tile.
+ * for activations.  Stages exchange data through buffers the program owns; every word stored
+ * there carries a one-bit generation tag in the least significant bit of its mantissa, so a
+ * consumer validates what it fetched instead of polling a flag, and a producer never fences
+ * (values inside the program are therefore truncated to 23 mantissa bits).
  *
  * Stage kinds
  *   FML_RESIDENT_GEMM       out = [LayerNorm]( act(A W + bias) + residual ): MatMulKernel /
@@ -348,10 +350,11 @@ int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, const int64_t
  *                           3xTF32 on tcgen05, split-K partial sums added in split order.
  *   FML_RESIDENT_ATTENTION  out = softmax(Q K^T / divisor + mask) V per head, as fml_attention.
  * Tensors are described as the launcher of the separate kernels would describe them (device
- * pointers, shapes, element strides).  An input that lies inside the output of an earlier stage
- * is taken from that stage; such outputs are kept in a tiled order private to the program
- * unless the stage sets `out_external`, which stores them with the strides given so that code
- * outside the program can read them.  Inputs that no stage produces are read as described.
+ * pointers, shapes, element strides).  An input that lies inside the `out` bytes of an earlier
+ * stage is taken from that stage; such outputs live in the program's own buffers and `out` is
+ * only their name, unless the stage sets `out_external`, which also stores them at `out` with the
+ * strides given so that code outside the program can read them.  Inputs that no stage produces
+ * are read as described and must be complete before the launch.
  * fml_resident_create returns FML_UNSUPPORTED (and creates nothing) when a stage does not fit:
  * the caller then launches the operators one by one.
  */
@@ -381,31 +384,35 @@ typedef struct fml_resident_stage {
 typedef struct fml_resident fml_resident;
 
 typedef struct fml_resident_info {
-  int32_t ctas, stages, steps, counters;
+  int32_t ctas, stages, steps, buffers;
   int32_t ring_slots, slot_bytes;
   uint64_t packed_weight_bytes, scratch_bytes, shared_memory_bytes;
 } fml_resident_info;
 
 /* Pure host computation: plans the program for `ctas` resident CTAs (0 = the SM count of the
- * current device), checks that every read is ordered after the writes it needs and every
- * overwrite after the reads of what it replaces, and reports the plan.  Needs no device when
- * `ctas` is given. */
+ * current device), checks that every read is covered by writes of its generation and that a
+ * buffer is only overwritten once the data dependences alone guarantee that all readers of its
+ * previous content are done, and reports the plan.  Needs no device when `ctas` is given. */
 int fml_resident_plan(const fml_resident_stage *stages, int32_t count, int32_t ctas,
                       fml_resident_info *info);
 /* Plans, packs the weights (a device kernel on the default stream; synchronises) and allocates
- * the program's scratch.  Not capturable. */
+ * the program's buffers.  Not capturable. */
 int fml_resident_create(const fml_resident_stage *stages, int32_t count, fml_resident **out);
-/* One pass: clears the counters and launches the persistent kernel (cooperatively, so that all
- * CTAs are co-resident).  Capturable.  A bounded wait that expires sets the device status word
- * (fml_check_device) and ends the pass early on every CTA. */
+/* One pass: launches the persistent kernel (cooperatively, so that all CTAs are co-resident) and
+ * a one-thread kernel that advances the pass number.  Capturable.  Passes of one program must
+ * not overlap.  A bounded wait that expires sets the device status word (fml_check_device) and
+ * ends the pass early on every CTA; call fml_resident_reset before the next pass then. */
 int fml_resident_launch(fml_resident *program, void *stream);
+/* Restores the initial state of the program's buffers and pass number (after a timeout). */
+int fml_resident_reset(fml_resident *program, void *stream);
 int fml_resident_info_of(const fml_resident *program, fml_resident_info *info);
 int fml_resident_destroy(fml_resident *program);
-/* Timing aid: after a pass launched with `trace` != 0 ... (see fml_resident_trace). */
-/* Copies per-step time stamps of the last traced pass to `host` (u64 nanoseconds of the
- * device's global timer: step start after its wait, step end), laid out
- * [cta][step][2]; `capacity` counts u64 entries.  fml_resident_launch records them only after
- * fml_resident_set_trace(program, 1), which selects a kernel variant that carries the stamps. */
+/* Timing aid.  After fml_resident_set_trace(program, 1), fml_resident_launch runs a kernel
+ * variant that records nanosecond stamps of the device's global timer per step: slot 0 start,
+ * 1 end; GEMM units also 2 = A rows fetched, 3 = last k block converted, 4 = accumulator
+ * complete; attention steps 2 = operands staged, 3 = scores, 4 = softmax done.
+ * fml_resident_read_trace copies them to `host` as [cta][step][8] u64 (`capacity` counts u64
+ * entries) and reports the two leading extents. */
 int fml_resident_set_trace(fml_resident *program, int32_t on);
 int fml_resident_read_trace(fml_resident *program, uint64_t *host, uint64_t capacity,
                             int32_t *ctas, int32_t *max_steps);
