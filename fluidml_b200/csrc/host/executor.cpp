@@ -118,6 +118,22 @@ public:
     return o.Dump();
   }
 
+  std::string TraceJson(const std::unordered_map<std::string, void *> &args, size_t passes) {
+    if (!runner_) throw Error("Trace called before Compile");
+    double pass_us = 0.0;
+    json::Value kernels = json::Value::Object();
+    for (const auto &kv : runner_->Trace(args, passes ? passes : 1, &pass_us)) {
+      json::Value e = json::Value::Object();
+      e.Set("us", json::Value(kv.second.us));
+      e.Set("launches", json::Value((double)kv.second.launches));
+      kernels.Set(kv.first, e);
+    }
+    json::Value o = json::Value::Object();
+    o.Set("pass_us", json::Value(pass_us));
+    o.Set("kernels", kernels);
+    return o.Dump();
+  }
+
 private:
   // One file per (model bytes, mode, options that shape the plan): text lines
   //   layout <tensor> <p0> <p1> ...      physical position of every logical dim
@@ -492,6 +508,17 @@ int fml_executor_profile(fml_executor *e, const char *const *names, void *const 
     std::unordered_map<std::string, void *> args;
     for (size_t i = 0; i < count; ++i) args[names[i]] = buffers[i];
     e->stats = static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->ProfileJson(args, passes);
+    *json_out = e->stats.c_str();
+  });
+}
+
+int fml_executor_trace(fml_executor *e, const char *const *names, void *const *buffers, size_t count,
+                       size_t passes, const char **json_out) {
+  if (!e || !e->impl || !json_out || (count && (!names || !buffers))) return 1;
+  return Guard(e, [&] {
+    std::unordered_map<std::string, void *> args;
+    for (size_t i = 0; i < count; ++i) args[names[i]] = buffers[i];
+    e->stats = static_cast<fluidml::worker::ExecutorImpl *>(e->impl.get())->TraceJson(args, passes);
     *json_out = e->stats.c_str();
   });
 }

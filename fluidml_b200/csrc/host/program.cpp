@@ -1,6 +1,7 @@
 #include "program.h"
 #include <algorithm>
 #include <cstdlib>
+#include <vector>
 
 namespace fluidml {
 namespace worker {
@@ -351,6 +352,62 @@ std::map<std::string, Runner::KernelTime> Runner::Profile(const std::unordered_m
     }
   }
   for (auto &e : events) fml_event_destroy(e);
+  return out;
+}
+
+std::map<std::string, Runner::KernelTime> Runner::Trace(const std::unordered_map<std::string, void *> &args,
+                                                        size_t passes, double *pass_us) {
+  Check(fml_set_device(options_.device), "selecting the device");
+  if (passes < 1) passes = 1;
+  for (const auto &b : program_->inputs)
+    Check(fml_memcpy_h2d(b.device, args.at(b.name), b.bytes, stream_), "copying an input");
+  const size_t n = program_->launches.size(), reps = passes + 2, cap = n * reps;
+  std::map<std::string, KernelTime> out;
+  if (n == 0) return out;
+  void *buf = nullptr, *cursor = nullptr;
+  Check(fml_malloc(&buf, cap * 8), "allocating the trace buffer");
+  Check(fml_malloc(&cursor, 4), "allocating the trace cursor");
+  Check(fml_memset(cursor, 0, 4, stream_), "clearing the trace cursor");
+  Check(fml_stream_sync(stream_), "clearing the trace cursor");
+  std::vector<unsigned long long> stamps(cap, 0);
+  unsigned stamped = 0;
+  int st = fml_set_kernel_trace(buf, cursor, (unsigned)cap);
+  if (st == FML_OK) {
+    for (size_t r = 0; r < reps && st == FML_OK; ++r) {
+      if (graph_exec_) st = fml_graph_launch(graph_exec_, stream_);
+      else for (const auto &l : program_->launches) { st = l.fn(stream_); if (st != FML_OK) break; }
+    }
+    if (st == FML_OK) st = fml_check_device(stream_);
+    fml_set_kernel_trace(nullptr, nullptr, 0);
+    if (st == FML_OK) st = fml_memcpy_d2h(stamps.data(), buf, cap * 8, stream_);
+    if (st == FML_OK) st = fml_memcpy_d2h(&stamped, cursor, 4, stream_);
+    if (st == FML_OK) st = fml_stream_sync(stream_);
+  }
+  fml_free(buf);
+  fml_free(cursor);
+  Check(st, "tracing the forward pass");
+  if (stamped != cap)
+    throw Error("the launch list does not stamp once per launch (" + std::to_string(stamped) + " stamps for " +
+                std::to_string(cap) + " launches): use Profile for this model");
+  // every launch stamps once: launch i of replay r is entry r * n + i
+  std::vector<double> period(n, 0.0);
+  std::vector<unsigned long long> v(passes);
+  for (size_t i = 0; i < n; ++i) {
+    for (size_t r = 0; r < passes; ++r) {
+      const size_t at = (r + 1) * n + i;
+      v[r] = stamps[at + 1] - stamps[at];
+    }
+    std::sort(v.begin(), v.end());
+    period[i] = (double)v[passes / 2] * 1e-3;
+  }
+  double total = 0.0;
+  for (size_t i = 0; i < n; ++i) {
+    KernelTime &k = out[program_->launches[i].kernel];
+    k.us += period[i];
+    k.launches += 1;
+    total += period[i];
+  }
+  if (pass_us) *pass_us = total;
   return out;
 }
 

@@ -92,6 +92,10 @@ public:
   // the key "(empty event pair)".
   struct KernelTime { double us = 0; size_t launches = 0; };
   std::map<std::string, KernelTime> Profile(const std::unordered_map<std::string, void *> &args, size_t passes);
+  // In-graph breakdown from kernel-start stamps: per kernel name the microseconds per pass from
+  // each of its launches' start to the next launch's start (median over `passes` inner replays
+  // of the captured graph) and its launches per pass; `pass_us` receives their sum.
+  std::map<std::string, KernelTime> Trace(const std::unordered_map<std::string, void *> &args, size_t passes, double *pass_us);
 
 private:
   void Replay();

@@ -113,7 +113,6 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
   cp_async_commit();
   cp_async_wait<1>();
   __syncthreads();
-  trace_stamp();
 
   // ---- scores: Ps[r][j] = q_r . k_j
   {
@@ -167,7 +166,6 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
   }
   cp_async_wait<0>();
   __syncthreads();
-  trace_stamp();
   // ---- softmax(s / divisor + mask) over each row; a row's 16 threads are half a warp
   {
     const int r = threadIdx.x >> 4, cg = threadIdx.x & 15;
@@ -197,7 +195,6 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
     for (int j = cg; j < Sk; j += 16) p[j] = live ? p[j] / sum : 0.0f;
   }
   __syncthreads();
-  trace_stamp();
   // ---- context: out[r][dv] = sum_j P[r][j] V[j][dv]
   {
     const int rg = lane >> 3, cgp = lane & 7;
@@ -249,7 +246,6 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
       }
     }
   }
-  trace_stamp();
 }
 
 // Keys and values that do not fit in shared memory at once (long sequences) stream through it in

@@ -135,11 +135,12 @@ __device__ __forceinline__ void offsets_of(const Iter<NOPS> &it, int64_t lin, in
 bool pdl_enabled();
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-#ifdef FML_KERNEL_TRACE
-// Debug builds only (-DFML_KERNEL_TRACE): the first thread of every kernel writes %globaltimer
-// when its dependency wait returns, so consecutive stamps give each kernel's period inside a
-// stream or graph (its run time plus the gap to the next start).  Each translation unit has
-// its own copy of the pointers; fml_debug_set_kernel_trace sets them all.
+// Kernel-start stamps, switched on at run time (fml_set_kernel_trace): when a trace buffer is set,
+// the first thread of every kernel of the library writes %globaltimer as its dependency wait
+// returns, so consecutive stamps give each kernel's period inside a stream or a replayed graph
+// (its run time plus the gap to the next start) without event pairs between the launches.  With
+// no buffer set the cost is one predicated load in one thread per kernel.  Each translation unit
+// has its own copy of the pointers; fml_set_kernel_trace sets them all.
 static __device__ unsigned long long *g_trace_buf;
 static __device__ unsigned *g_trace_cursor;
 static __device__ unsigned g_trace_cap;
@@ -159,9 +160,6 @@ __device__ __forceinline__ void trace_stamp() {
     if (i < g_trace_cap) g_trace_buf[i] = t;
   }
 }
-#else
-__device__ __forceinline__ void trace_stamp() {}
-#endif
 __device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   trace_stamp();

@@ -53,9 +53,13 @@ struct TcArgs {
   int tile_n, split_k, stages, b_mn_major, three_pass, a_tmem;
   int tiles_m, tiles_n, kb_total, kb_per_split;
   int *status;
-  unsigned long long *trace;  // optional: 16 stamps per CTA (fml_debug_set_gemm_trace)
+#ifdef FML_GEMM_PHASE_TRACE
+  unsigned long long *trace;  // 16 stamps per CTA (fml_debug_set_gemm_trace)
+#endif
 };
 
+#ifdef FML_GEMM_PHASE_TRACE
+// Debug builds only (-DFML_GEMM_PHASE_TRACE): per-CTA stamps of the kernel's phases.
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -66,6 +70,9 @@ __device__ __forceinline__ unsigned long long gtime() {
     if (a.trace)                                                                           \
       a.trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = ((slot) >= 8 ? (unsigned long long)clock64() : gtime()); \
   } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------- epilogue helpers
 // The activation is a template parameter of the kernel and bias / residual / scaling are
@@ -581,7 +588,9 @@ size_t smem_for(int tile_n, int stages, int three_pass, int a_tmem) {
   return data + (3 * stages + 1) * 8 + 16 + 1024;
 }
 
+#ifdef FML_GEMM_PHASE_TRACE
 unsigned long long *g_trace = nullptr;
+#endif
 
 }  // namespace
 
@@ -685,7 +694,9 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
   a.kb_total = (int)((p.K + kBK - 1) / kBK);
   a.kb_per_split = (a.kb_total + plan.split_k - 1) / plan.split_k;
   a.status = device_status_word();
+#ifdef FML_GEMM_PHASE_TRACE
   a.trace = g_trace;
+#endif
   FML_REQUIRE(a.status, FML_CUDA_ERROR, "fml_gemm: no device status word");
   CUtensorMap map_a, map_b;
   int st = make_map(&map_a, p.a, p.K, p.M, p.a_sm, p.nb0, p.a_b0, p.nb1, p.a_b1, kBK, kBM,
@@ -739,6 +750,7 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
 
 }  // namespace fml
 
+#ifdef FML_GEMM_PHASE_TRACE
 // Tracing hook: when set to a device buffer of 16 x (number of CTAs) u64, every tensor-core GEMM
 // launch stamps %globaltimer at: 0 CTA start, 1 set-up done, 2 first stage landed, 3 last MMA
 // issued, 4 accumulator ready, 5 epilogue done, 6 CTA end, 7 tile staged; 8 / 9 hold clock64()
@@ -746,3 +758,4 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
 extern "C" void fml_debug_set_gemm_trace(void *device_buffer) {
   fml::g_trace = static_cast<unsigned long long *>(device_buffer);
 }
+#endif

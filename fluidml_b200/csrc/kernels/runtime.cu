@@ -220,7 +220,6 @@ int fml_check_device(void *stream) {
 
 }  // extern "C"
 
-#ifdef FML_KERNEL_TRACE
 namespace fml {
 namespace {
 std::vector<cudaError_t (*)(unsigned long long *, unsigned *, unsigned)> &trace_setters() {
@@ -232,10 +231,9 @@ void register_trace_setter(cudaError_t (*setter)(unsigned long long *, unsigned 
   trace_setters().push_back(setter);
 }
 }  // namespace fml
-// Debug builds only: buf = device array of `cap` 64-bit stamps, cursor = device counter (zeroed
-// by the caller).  NULL buf switches the stamps off.
-extern "C" int fml_debug_set_kernel_trace(void *buf, void *cursor, unsigned cap) {
+// buf = device array of `cap` 64-bit stamps, cursor = device counter (zeroed by the caller).
+// NULL buf switches the stamps off.  Synchronises (the pointers are module variables).
+extern "C" int fml_set_kernel_trace(void *buf, void *cursor, unsigned cap) {
   for (auto f : fml::trace_setters()) FML_CUDA(f((unsigned long long *)buf, (unsigned *)cursor, cap));
   return FML_OK;
 }
-#endif

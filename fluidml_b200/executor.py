@@ -120,6 +120,17 @@ class Executor:
                                                ctypes.c_size_t(n), ctypes.c_size_t(passes), ctypes.byref(out)))
         return _json.loads(out.value.decode())
 
+    def trace(self, args: Dict[str, np.ndarray], passes: int = 5) -> dict:
+        """Per-kernel device time inside the replayed graph, from kernel-start stamps: the periods of a
+        pass add up to the pass ({"pass_us": .., "kernels": {name: {"us": per pass, "launches": n}}})."""
+        names = [k.encode() for k in args]
+        ptrs = [a.ctypes.data for a in args.values()]
+        n = len(names)
+        out = ctypes.c_char_p()
+        self._check(lib().fml_executor_trace(self._h, (ctypes.c_char_p * n)(*names), (ctypes.c_void_p * n)(*ptrs),
+                                             ctypes.c_size_t(n), ctypes.c_size_t(passes), ctypes.byref(out)))
+        return _json.loads(out.value.decode())
+
     def stats(self) -> dict:
         return _json.loads(lib().fml_executor_stats_json(self._h).decode())
 

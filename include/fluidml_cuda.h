@@ -89,6 +89,14 @@ int fml_graph_destroy(void *graph_exec);
  * settings) so that later calls can be stream-captured. */
 int fml_warmup(void);
 
+/* Timing aid.  With a trace buffer set, the first thread of every kernel of the library stores
+ * the device's global nanosecond timer as the kernel's dependency wait returns: `buf` is a device
+ * array of `cap` u64 entries, `cursor` a device u32 the caller zeroes (entry index of the next
+ * stamp).  Consecutive stamps give each kernel's period inside a stream or a replayed graph.
+ * buf == NULL switches the stamps off (the cost is then one predicated load per kernel).
+ * Synchronises the device. */
+int fml_set_kernel_trace(void *buf, void *cursor, unsigned cap);
+
 /* Reads and clears the device status word kernels write when a bounded wait expires or a
  * gather index is clamped.  Synchronises `stream`.  Returns FML_OK, FML_DEVICE_TIMEOUT or
  * FML_INDEX_OUT_OF_RANGE. */

@@ -52,6 +52,14 @@ int fml_executor_plan_buffer(fml_executor *e, const void *onnx_bytes, size_t siz
 int fml_executor_profile(fml_executor *e, const char *const *names, void *const *buffers,
                          size_t count, size_t passes, const char **json_out);
 
+/* The same breakdown without disturbing the pass: replays the captured graph `passes` + 2 times
+ * with the library's kernel-start stamps switched on (fml_set_kernel_trace) and attributes to
+ * every launch the time from its start to the next launch's start, median over the inner
+ * passes.  Returns {"pass_us": .., "kernels": {"<KernelName>": {"us": per pass, "launches": n}}}.
+ * The periods of a pass add up to the pass. */
+int fml_executor_trace(fml_executor *e, const char *const *names, void *const *buffers,
+                       size_t count, size_t passes, const char **json_out);
+
 /* JSON text owned by the handle, valid until the next call on it. */
 const char *fml_executor_stats_json(fml_executor *e);
 

@@ -515,6 +515,9 @@ int orc_conv(const orc_tensor *x, const orc_tensor *w, const orc_tensor *bias, o
   int64_t ysh = nd == 2 ? y->stride[2] : 0, ysw = y->stride[nd + 1];
   int64_t icg = IC / group, ocg = OC / group;
   const float *X = (const float *)x->data, *W = (const float *)w->data;
+  /* (image, output channel) pairs are independent: with orc_set_threads(n > 1) they are spread
+   * over n host threads; every output keeps its own summation order, so no bit changes. */
+#pragma omp parallel for collapse(2) schedule(static) num_threads(orc_threads) if (orc_threads > 1)
   for (int64_t n = 0; n < N; ++n)
     for (int64_t oc = 0; oc < OC; ++oc) {
       int64_t g = oc / ocg;

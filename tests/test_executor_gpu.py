@@ -1,8 +1,8 @@
 """End-to-end parity of the Executor (the drop-in boundary) against the CPU oracle.
 
-Final fp32 outputs must agree within max|gpu - ref| / max|ref| <= 1e-3, the tolerance the
-hot-path specification states; the indexing operators underneath are covered bit-exactly in
-test_kernels_gpu.py.
+Final fp32 outputs must agree within 1e-3 (the tolerance the hot-path specification states),
+both as max|gpu - ref| / max|ref| and element by element with an absolute floor (see relerr);
+the indexing operators underneath are covered bit-exactly in test_kernels_gpu.py.
 """
 import os
 
@@ -19,8 +19,15 @@ TOL = 1e-3
 
 
 def relerr(got, ref):
+    """The larger of two measures, both of which must stay within the tolerance:
+    the largest absolute error over the largest reference magnitude, and the largest
+    element-wise relative error |gpu - ref| / max(|ref|, floor) with floor = 5e-2 max|ref|
+    (an element-wise check that small-magnitude outputs cannot hide behind, while elements that
+    are numerically zero next to the tensor's scale are measured against the floor)."""
     ref = ref.astype(np.float64)
-    return float(np.abs(got.astype(np.float64) - ref).max() / max(1e-30, np.abs(ref).max()))
+    err = np.abs(got.astype(np.float64) - ref)
+    scale = max(1e-30, float(np.abs(ref).max()))
+    return float(max(err.max() / scale, (err / np.maximum(np.abs(ref), 5e-2 * scale)).max()))
 
 
 def run(model, inputs, factory, **options):
@@ -53,7 +60,8 @@ def test_bert_two_layers_all_modes(bert2, factory, fusion):
         assert st["flow_nodes"] < st["graph_nodes"]
 
 
-@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("3xtf32", 1e-4), ("tf32", 5e-3)])
+# single-pass TF32 is an option, not the default: it misses the 1e-3 bar (element-wise up to ~2e-2)
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("3xtf32", 1e-4), ("tf32", 4e-2)])
 def test_bert_gemm_precisions(bert2, precision, tol):
     m, x, ref = bert2
     outs, _ = run(m, x, Executor.make_dp_greedy, gemm_precision=precision)

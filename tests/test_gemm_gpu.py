@@ -199,3 +199,25 @@ def test_gemm_skinny_batched_and_tanh():
               cabi.gemm_params(act=cabi.ACT_TANH))
     cabi.check_device()
     assert relerr(out.numpy(), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("m,k,n,prec", [(128, 256, 192, cabi.GEMM_3XTF32), (128, 256, 192, cabi.GEMM_FP32),
+                                        (4, 300, 130, cabi.GEMM_FP32), (40, 96, 80, cabi.GEMM_FP32)])
+@pytest.mark.parametrize("bias_rank", [1, 2])
+def test_gemm_alpha_beta_with_bias_of_rank_one_and_two(m, k, n, prec, bias_rank):
+    """Gemm with alpha = 0.5, beta = 2 on the tcgen05, skinny and fp32-FMA paths against the
+    oracle's Gemm.  The library and the oracle compute the ONNX form alpha * (A B) + beta * C;
+    the reference's kernel swaps the two factors (gemm.cpp:166-181), which only agrees for
+    alpha = beta = 1, so this is the case where the two definitions part."""
+    alpha, beta = 0.5, 2.0
+    a, b = rnd(m, k), rnd(k, n)
+    bias = rnd(n) if bias_rank == 1 else rnd(m, n)
+    ref = orc.gemm(a, b, bias, np.empty((m, n), np.float32), alpha=alpha, beta=beta, acc64=True)
+    swapped = alpha * bias.astype(np.float64) + beta * ref_matmul(a, b).astype(np.float64)  # what the reference would give
+    assert relerr(swapped, ref) > 1e-2
+    da, db, out = DT.from_numpy(a), DT.from_numpy(b), DT((m, n), np.float32)
+    p = cabi.gemm_params(precision=prec, alpha=alpha, beta=beta)
+    assert cabi.gemm_uses_tensor_cores(da, db, out, p) == (prec == cabi.GEMM_3XTF32)
+    cabi.gemm(da, db, out, DT.from_numpy(bias), None, p)
+    cabi.check_device()
+    assert relerr(out.numpy(), ref) <= TOL[prec]
