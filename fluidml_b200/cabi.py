@@ -254,6 +254,15 @@ def gemm_plan(a, b, c, params) -> GemmPlanInfo:
     return info
 
 
+def gemm_autotune(a, b, c, params, bias=None, residual=None, stream=None) -> GemmParams:
+    """fml_gemm_autotune: times the candidate tiles on the device and returns the parameters with the
+    fastest tile_n / split_k filled in (C is overwritten with valid results)."""
+    tuned = GemmParams()
+    check(lib().fml_gemm_autotune(_ref(a), _ref(b), _ref(c), _ref(bias), _ref(residual), ctypes.byref(params),
+                                  stream, ctypes.byref(tuned)))
+    return tuned
+
+
 def gemm_uses_tensor_cores(a, b, c, params) -> bool:
     u = ctypes.c_int()
     check(lib().fml_gemm_uses_tensor_cores(_ref(a), _ref(b), _ref(c), ctypes.byref(params),

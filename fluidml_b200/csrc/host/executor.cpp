@@ -50,6 +50,7 @@ public:
     SetOption("autotune", EnvOr("FLUIDML_AUTOTUNE", "1"));
     SetOption("weight_prefetch", EnvOr("FLUIDML_WEIGHT_PREFETCH", "1"));
     SetOption("plan_cache", EnvOr("FLUIDML_PLAN_CACHE", ""));
+    SetOption("resident", EnvOr("FLUIDML_RESIDENT", "0"));
   }
 
   void SetOption(const std::string &key, const std::string &value) override {
@@ -60,6 +61,7 @@ public:
     else if (key == "autotune") options_.autotune = value != "0";
     else if (key == "weight_prefetch") options_.weight_prefetch = value != "0";
     else if (key == "plan_cache") options_.plan_cache = value;
+    else if (key == "resident") options_.resident = value != "0";
     else if (key == "alignment") {
       options_.alignment = (size_t)std::stoul(value);
       if (options_.alignment < 16 || (options_.alignment & (options_.alignment - 1)))
@@ -185,10 +187,10 @@ private:
   std::string PlanCachePath() const {
     if (options_.plan_cache.empty() || model_hash_ == 0) return std::string();
     char buf[160];
-    snprintf(buf, sizeof(buf), "/%016llx-%s-%s-p%d-f%d-c%d-a%d-t%d.plan", (unsigned long long)model_hash_,
+    snprintf(buf, sizeof(buf), "/%016llx-%s-%s-p%d-f%d-c%d-a%d-t%d-r%d.plan", (unsigned long long)model_hash_,
              layout_ == LayoutMode::kDP ? "dp" : "plain", plan_ == MemoryPlanKind::kGreedy ? "greedy" : "linear",
              options_.gemm_precision, options_.fusion ? 1 : 0, options_.dp_constant_cost ? 1 : 0, (int)options_.alignment,
-             options_.autotune ? 1 : 0);
+             options_.autotune ? 1 : 0, options_.resident ? 1 : 0);
     return options_.plan_cache + buf;
   }
 
@@ -313,6 +315,9 @@ private:
       stats_.Set("weight_bytes", json::Value((double)program->weight_bytes));
       stats_.Set("interface_bytes", json::Value((double)program->io_bytes));
       stats_.Set("launches", json::Value((double)program->launches.size()));
+      stats_.Set("resident_programs", json::Value((double)program->resident_programs.size()));
+      stats_.Set("resident_stages", json::Value((double)program->resident_stages));
+      stats_.Set("resident_bytes", json::Value((double)program->resident_scratch_bytes));
       json::Value iface = json::Value::Object();  // host buffer size of every argument of Invoke
       for (const auto &b : program->inputs) iface.Set(b.name, json::Value((double)b.bytes));
       for (const auto &b : program->outputs) iface.Set(b.name, json::Value((double)b.bytes));

@@ -408,6 +408,15 @@ public:
     const float d = divisor_;
     rec.Add(GetKernelName(), [=](void *s) { return fml_attention(&q, &kt, &v, hm ? &mask : nullptr, d, &output, s); });
   }
+  bool DescribeResident(const std::vector<fml_tensor> &in, const fml_tensor &output, fml_resident_stage *st) const override {
+    memset(st, 0, sizeof(*st));
+    st->kind = FML_RESIDENT_ATTENTION;
+    st->out = output;
+    st->q = in.at(0); st->kt = in.at(1); st->v = in.at(2);
+    if (has_mask_) st->mask = in.at(3);
+    st->divisor = divisor_;
+    return true;
+  }
 
 private:
   float divisor_;
@@ -429,6 +438,11 @@ public:
     const int axis = (int)axis_;
     const float eps = eps_;
     rec.Add(GetKernelName(), [=](void *s) { return fml_layernorm(&x, hr ? &r : nullptr, &g, &b, &output, axis, eps, s); });
+  }
+  bool DescribeLayerNorm(const fml_tensor &input, fml_tensor *scale, fml_tensor *bias, float *eps) const override {
+    if (residual_ || (axis_ != input.rank - 1 && axis_ != -1)) return false;
+    *scale = scale_; *bias = bias_; *eps = eps_;
+    return true;
   }
 
 private:
@@ -513,6 +527,24 @@ public:
     bias = c_.bias;
     if (c_.has_bias && c_.bias_is_input) bias = in.at(k++);
     if (c_.has_residual) res = in.at(k++);
+  }
+  bool DescribeResident(const std::vector<fml_tensor> &in, const fml_tensor &output, fml_resident_stage *st) const override {
+    const fml_gemm_params &p = c_.params;
+    if (!c_.has_const_b || c_.trans_a || c_.bias_is_input) return false;
+    if (p.alpha != 1.0f || (c_.has_bias && p.beta != 1.0f) || (p.divisor != 1.0f && p.divisor != 0.0f)) return false;
+    if (p.precision == FML_GEMM_FP32 || p.precision == FML_GEMM_TF32) return false;  // the resident GEMM is 3xTF32
+    if (p.act < FML_ACT_NONE || p.act > FML_ACT_SIGMOID) return false;
+    fml_tensor a, b, bias{}, res{};
+    Resolve(in, a, b, bias, res);
+    if (b.rank != 2 || (c_.has_bias && bias.rank != 1)) return false;
+    memset(st, 0, sizeof(*st));
+    st->kind = FML_RESIDENT_GEMM;
+    st->out = output; st->a = a; st->w = b;
+    if (c_.has_bias) st->bias = bias;
+    if (c_.has_residual) st->residual = res;
+    st->act = p.act;
+    for (int i = 0; i < 3; ++i) st->act_param[i] = p.act_param[i];
+    return true;
   }
   void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output,
               const Buffer &buf) const override {

@@ -72,6 +72,20 @@ public:
   // preset replaces the on-device tuning; TunedTiles reports what Launch ended up using.
   virtual void PresetTiles(int tile_n, int split_k) { (void)tile_n; (void)split_k; }
   virtual bool TunedTiles(int *tile_n, int *split_k) const { (void)tile_n; (void)split_k; return false; }
+  // Stage of a resident program (fml_resident_stage) that computes what this kernel's launch
+  // computes on these operands, if the kernel has such a form: a constant-weight GEMM with its
+  // epilogue, or the attention core.  `out_external` is left for the builder to decide.
+  virtual bool DescribeResident(const std::vector<fml_tensor> &inputs, const fml_tensor &output,
+                                fml_resident_stage *stage) const {
+    (void)inputs; (void)output; (void)stage;
+    return false;
+  }
+  // A LayerNorm over the last axis without a residual input can ride in the epilogue of the
+  // resident GEMM stage that produces its input.
+  virtual bool DescribeLayerNorm(const fml_tensor &input, fml_tensor *scale, fml_tensor *bias, float *eps) const {
+    (void)input; (void)scale; (void)bias; (void)eps;
+    return false;
+  }
 
 protected:
   Kernel() = default;

@@ -1,5 +1,7 @@
 #include "program.h"
 #include <algorithm>
+#include <unordered_set>
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 
@@ -113,6 +115,7 @@ std::vector<memory::Info> Lowering::Lifetimes(const flow::Sequence &sequence, co
 }
 
 Program::~Program() {
+  for (fml_resident *r : resident_programs) fml_resident_destroy(r);
   if (arena) fml_free(arena);
   if (weights) fml_free(weights);
   if (io) fml_free(io);
@@ -217,9 +220,117 @@ std::unique_ptr<Program> Builder::Run(const flow::Flow &flow, const flow::Sequen
       next_bytes = own_bytes;
     }
   }
-  for (const auto &kv : kernels) {
+  // ---- resident programs: maximal runs of nodes that have a resident stage form
+  std::vector<int> run_of(kernels.size(), -1);             // kernel index -> run index
+  std::vector<std::vector<fml_resident_stage>> run_stages;  // per run
+  std::vector<size_t> run_first;
+  if (options.resident) {
+    // regions read by nodes outside a run (through views as well) must be stored for them
+    auto consumers_outside = [&](const flow::Region *r, size_t lo, size_t hi) {
+      // kernels[lo..hi) is the run; any other node of the sequence reading r (or a view of it)?
+      std::unordered_set<const flow::Node *> inside;
+      for (size_t i = lo; i < hi; ++i) inside.insert(kernels[i].first.get());
+      if (r->kind != flow::Region::kInner) return true;
+      for (const auto &n : sequence.nodes) {
+        if (inside.count(n.get()) || aliases.count(n->output.get())) continue;
+        for (const auto &in : n->inputs)
+          if (Owner(aliases, in).get() == r) return true;
+      }
+      return false;
+    };
+    auto consumers_total = [&](const flow::Region *r) {
+      int count = 0;
+      for (const auto &n : sequence.nodes) {
+        if (aliases.count(n->output.get())) continue;
+        for (const auto &in : n->inputs)
+          if (Owner(aliases, in).get() == r) ++count;
+      }
+      return count;
+    };
+    auto inputs_of = [&](const flow::NodePtr &node) {
+      std::vector<fml_tensor> ins;
+      for (const auto &r : node->inputs) ins.push_back(tensor_of(r));
+      return ins;
+    };
+    size_t i = 0;
+    while (i < kernels.size()) {
+      std::vector<fml_resident_stage> stages;
+      std::vector<std::pair<size_t, size_t>> span;  // kernels covered by each stage: [first, last]
+      size_t j = i;
+      while (j < kernels.size()) {
+        fml_resident_stage st;
+        if (!kernels[j].second->DescribeResident(inputs_of(kernels[j].first), tensor_of(kernels[j].first->output), &st)) break;
+        size_t last = j;
+        if (st.kind == FML_RESIDENT_GEMM && j + 1 < kernels.size()) {
+          // a LayerNorm that is the only reader of this product rides in its epilogue
+          const flow::NodePtr &ln = kernels[j + 1].first;
+          fml_tensor scale, bias;
+          float eps = 0.0f;
+          if (!ln->inputs.empty() && ln->inputs[0].get() == kernels[j].first->output.get() &&
+              kernels[j].first->output->kind == flow::Region::kInner && consumers_total(kernels[j].first->output.get()) == 1 &&
+              kernels[j + 1].second->DescribeLayerNorm(tensor_of(ln->inputs[0]), &scale, &bias, &eps)) {
+            st.layernorm = 1; st.ln_scale = scale; st.ln_bias = bias; st.ln_eps = eps;
+            st.out = tensor_of(ln->output);
+            last = j + 1;
+          }
+        }
+        stages.push_back(st);
+        span.push_back({j, last});
+        j = last + 1;
+      }
+      if (getenv("FLUIDML_RESIDENT_VERBOSE") && !stages.empty())
+        fprintf(stderr, "resident: run of %zu stages starting at node '%s'\n", stages.size(), kernels[i].first->name.c_str());
+      // the longest prefix of the run the library accepts (a stage it cannot take, such as a
+      // product with fewer than 128 rows, ends the run there)
+      while (stages.size() >= 2) {
+        j = span.back().second + 1;
+        for (size_t s = 0; s < stages.size(); ++s) {
+          const flow::Region *out = kernels[span[s].second].first->output.get();
+          stages[s].out_external = consumers_outside(out, i, j) ? 1 : 0;
+        }
+        fml_resident_info info;
+        if (fml_resident_plan(stages.data(), (int32_t)stages.size(), 0, &info) == FML_OK) break;
+        if (getenv("FLUIDML_RESIDENT_VERBOSE"))
+          fprintf(stderr, "resident: %zu stages from node '%s' refused: %s\n", stages.size(), kernels[i].first->name.c_str(), fml_last_error());
+        stages.pop_back();
+        span.pop_back();
+      }
+      if (stages.size() >= 2) {
+        j = span.back().second + 1;
+        fml_resident *prog_r = nullptr;
+        const int st = fml_resident_create(stages.data(), (int32_t)stages.size(), &prog_r);
+        if (st == FML_OK) {
+          for (size_t k = i; k < j; ++k) run_of[k] = (int)run_stages.size();
+          run_stages.push_back(stages);
+          run_first.push_back(i);
+          prog->resident_programs.push_back(prog_r);
+          prog->resident_stages += stages.size();
+          fml_resident_info info;
+          if (fml_resident_info_of(prog_r, &info) == FML_OK) prog->resident_scratch_bytes += info.scratch_bytes + info.packed_weight_bytes;
+        } else if (st != FML_UNSUPPORTED) {
+          throw Error(std::string("creating a resident program: ") + fml_last_error());
+        } else if (getenv("FLUIDML_RESIDENT_VERBOSE")) {
+          fprintf(stderr, "resident: %zu stages from node '%s' stay separate launches: %s\n", stages.size(),
+                  kernels[i].first->name.c_str(), fml_last_error());
+        }
+        i = j;
+      } else {
+        i = std::max(j, i + 1);
+      }
+    }
+  }
+  for (size_t ki = 0; ki < kernels.size(); ++ki) {
+    const auto &kv = kernels[ki];
     const flow::NodePtr &node = kv.first;
     const std::unique_ptr<kernel::Kernel> &k = kv.second;
+    if (run_of[ki] >= 0) {
+      if (run_first[run_of[ki]] == ki) {
+        fml_resident *r = prog->resident_programs[run_of[ki]];
+        rec.SetNode(node->name);
+        rec.Add("ResidentProgramKernel", [r](void *s) { return fml_resident_launch(r, s); });
+      }
+      continue;
+    }
     std::vector<fml_tensor> ins;
     for (const auto &r : node->inputs) ins.push_back(tensor_of(r));
     const fml_tensor out = tensor_of(node->output);
@@ -311,7 +422,10 @@ size_t Runner::Run(const std::unordered_map<std::string, void *> &args, size_t e
     if (!out_host[i]) throw Error("output '" + program_->outputs[i].name + "' is a null pointer");
     Check(fml_memcpy_d2h(out_host[i], program_->outputs[i].device, program_->outputs[i].bytes, stream_), "copying an output");
   }
-  Check(fml_check_device(stream_), "forward pass");
+  const int status = fml_check_device(stream_);
+  if (status == FML_DEVICE_TIMEOUT)  // a resident program's buffers hold mixed generations after an abandoned pass
+    for (fml_resident *r : program_->resident_programs) fml_resident_reset(r, stream_);
+  Check(status, "forward pass");
   float ms = 0.0f;
   Check(fml_event_elapsed_ms(ev_start_, ev_stop_, &ms), "reading the timer");
   return (size_t)((double)ms * 1e6 / (double)epoch);

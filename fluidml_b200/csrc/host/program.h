@@ -29,6 +29,11 @@ struct Options {
   bool dp_constant_cost = false;
   bool autotune = true;  // tune GEMM tile / split-K choices on the device at Compile
   bool weight_prefetch = true;  // GEMMs ask L2 to fetch the next GEMM's weights while they run
+  // Runs of constant-weight GEMM (+ LayerNorm) and attention nodes over 128 rows become one
+  // resident program each (one persistent kernel, fml_resident_*) instead of one launch per
+  // node.  Off by default: on this part a dependent exchange through L2 inside one kernel costs
+  // about what a kernel boundary costs, and the separate kernels are the faster plan.
+  bool resident = false;
   // Directory of the plan cache (empty: none).  A compiled model leaves its DP layouts and the
   // tuned GEMM tiles there, keyed by a hash of the model bytes and the options that shape the
   // plan, so that compiling the same model again skips the layout search and the on-device tuning.
@@ -67,6 +72,8 @@ struct Program {
   size_t arena_bytes = 0, weight_bytes = 0, io_bytes = 0;
   size_t aliased_nodes = 0;
   std::map<std::string, int> kernel_histogram;
+  std::vector<fml_resident *> resident_programs;  // owned
+  size_t resident_stages = 0, resident_scratch_bytes = 0;
   ~Program();
   Program() = default;
   Program(const Program &) = delete;

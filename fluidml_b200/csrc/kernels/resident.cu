@@ -618,6 +618,7 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const KernelArgs 
   const int cta = blockIdx.x;
   const Step *steps = g.steps + g.step_begin[cta];
   const uint32_t epoch = ld_relaxed(g.epoch);
+  trace_stamp();  // kernel-start stamp for fml_set_kernel_trace (one per launch, as every kernel of the library)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nslots; ++s) {

@@ -103,6 +103,33 @@ def test_bert_base_full_size():
         assert np.array_equal(outs[k], outs3[k])
 
 
+def test_bert_base_as_one_resident_program():
+    """Option resident=1: the twelve encoder layers run as one persistent kernel (a resident stage
+    program) behind the same Executor calls.  Same tolerance, same bits on every pass, and the pass
+    is a handful of launches."""
+    m = models.build_bert()
+    x = models.bert_inputs()
+    ref = orc.run_model(m, x, acc64=True)
+    outs, ex = run(m, x, Executor.make_dp_greedy, resident=1)
+    for k in ref:
+        assert relerr(outs[k], ref[k]) <= TOL, k
+    st = ex.stats()
+    assert st["resident_programs"] == 1 and st["resident_stages"] == 60 and st["launches"] <= 14
+    assert st["kernels"].get("ResidentProgramKernel") == 1
+    for _ in range(3):
+        again = {o.name: np.zeros(o.shape, np.float32) for o in m.outputs}
+        ex.invoke({**x, **again})
+        for k in ref:
+            assert np.array_equal(outs[k], again[k])
+    ex5 = Executor.make_dp_greedy("bert", 5)
+    ex5.set_option("resident", 1)
+    ex5.compile(m.to_bytes())
+    outs5 = {o.name: np.zeros(o.shape, np.float32) for o in m.outputs}
+    ex5.invoke({**x, **outs5})
+    for k in ref:
+        assert np.array_equal(outs[k], outs5[k])
+
+
 def test_invoke_argument_errors(bert2):
     m, x, _ = bert2
     ex = Executor.make_plain_greedy("bert").compile(m.to_bytes())
