@@ -35,12 +35,28 @@ namespace evaluation {
 
 namespace {
 
-constexpr double kHbmBytesPerNs = 6500.0;      // ~6.5 TB/s measured copy bandwidth
-constexpr double kTf32FlopsPerNs = 800000.0;   // dense TF32 tensor throughput
-constexpr double kFp32FlopsPerNs = 30000.0;    // CUDA-core FMA kernel, achieved
-constexpr double kLaunchNs = 2000.0;           // cost of one more kernel in the graph
-constexpr double kStridedEfficiency = 0.125;   // 4 useful bytes per 32-byte sector
-constexpr double kTileEfficiency = 0.7;        // shared-memory tile transpose
+// Constants fitted to this library's kernels on a B200, each timed as a run of identical
+// launches inside one CUDA graph (the way they run in a compiled model):
+//   GEMM on tensor cores, 3xTF32: 128x768x768 8.1 us, 128x768x2304 11.0, 128x768x3072 11.3,
+//     128x3072x768 15.2, 1024x768x3072 28.6, 2048x1024x4096 98.9, 8192x4096x4096 1417;
+//   GEMM on CUDA cores (an operand layout the tensor-core kernel does not take):
+//     128x768x3072 84 us, 128x3072x768 278, 2048x1024x4096 596, 8192x4096x4096 10167;
+//   LayerNormalization over a contiguous axis: 128x768 2.8 us, 1024x768 3.5, 2048x1024 4.3;
+//     over a strided axis: 18, 41, 76;  attention 12 heads x 128 x 64: 10 us, 9.3 TFLOP/s at
+//     batch 32;  element-wise add of 8.4 M floats 16.5 us (6.1 TB/s), of 98 K floats 1.7 us.
+constexpr double kHbmBytesPerNs = 6500.0;        // copy-like kernels at full size
+constexpr double kTf32FlopsPerNs = 540000.0;     // TF32 passes of the tensor-core GEMM, large shapes
+constexpr double kFp32FlopsPerNs = 28000.0;      // CUDA-core FMA GEMM / convolution, large shapes
+constexpr double kLaunchNs = 2500.0;             // one more kernel in the graph
+constexpr double kGemmFixedNs = 5000.0;          // tensor-core GEMM: pipeline fill, split-K sum, epilogue
+constexpr double kGemmStreamBytesPerNs = 3000.0; // operand streaming of one GEMM launch
+constexpr double kFp32NsPerK = 90.0;             // CUDA-core GEMM: serial depth of the k loop
+constexpr double kAttentionFixedNs = 3000.0;     // staging K and V, softmax, exit
+constexpr double kAttentionFlopsPerNs = 9300.0;  // fp32 FMA attention, achieved
+constexpr double kStridedEfficiency = 0.125;     // 4 useful bytes per 32-byte sector
+constexpr double kStridedRowEfficiency = 0.035;  // row reductions walking a strided axis
+constexpr double kStridedRowNsPerElement = 20.0; // ... and their serial depth along the row
+constexpr double kTileEfficiency = 0.7;          // shared-memory tile transpose
 
 using Layout = std::vector<size_t>;
 
@@ -167,10 +183,31 @@ size_t CostModel::GetTimeCost(const flow::Node &n, const std::vector<Layout> &in
                     (const_b || ((b_sk == 1 && b_sn % 4 == 0) || (b_sn == 1 && b_sk % 4 == 0))) &&
                     M >= 32 && N >= 16 && K >= 16;
     const double passes = precision_ == FML_GEMM_TF32 ? 1.0 : 3.0;
-    const double compute = tc ? flops * passes / kTf32FlopsPerNs : flops / kFp32FlopsPerNs;
     const int64_t c_sm = os[ro - 2], c_sn = os[ro - 1];
     const double c_eff = (c_sn == 1 || c_sm == 1) ? 1.0 : kStridedEfficiency;
-    cost = kLaunchNs + std::max(compute, (bytes - obytes) / kHbmBytesPerNs + obytes / (kHbmBytesPerNs * c_eff));
+    if (M <= 32) {  // the skinny kernel: a weight-streaming matrix-vector product, any strides
+      cost = kLaunchNs + bytes / kGemmStreamBytesPerNs;
+    } else if (tc) {
+      const double stream = (bytes - obytes) / kGemmStreamBytesPerNs + obytes / (kGemmStreamBytesPerNs * c_eff);
+      cost = kLaunchNs + kGemmFixedNs + std::max(flops * passes / kTf32FlopsPerNs, stream);
+    } else {
+      const double stream = (bytes - obytes) / kHbmBytesPerNs + obytes / (kHbmBytesPerNs * c_eff);
+      cost = kLaunchNs + std::max({flops / kFp32FlopsPerNs, (double)K * kFp32NsPerK, stream});
+    }
+    break;
+  }
+  case Kind::FusedAttention: {
+    // Q [.., Sq, D], K^T [.., D, Sk], V [.., Sk, Dv].  The kernel takes any strides; it loads
+    // rows of Q, V and the output along their last axis and K^T along either of its last two,
+    // so those are the axes that must be contiguous for coalesced access.
+    const auto &kt = n.inputs[1]->meta.GetShape();
+    const double flops = 2.0 * (double)n.inputs[0]->meta.GetElementsNum() * (double)kt.back()   // scores
+                         + 2.0 * (double)o.meta.GetElementsNum() * (double)kt.back();            // context
+    const size_t r = o.meta.GetRank();
+    const bool dflt = os[r - 1] == 1 && is[0][r - 1] == 1 && is[2][r - 1] == 1 && (is[1][r - 1] == 1 || is[1][r - 2] == 1);
+    double bytes = obytes;
+    for (const auto &r : n.inputs) bytes += (double)r->meta.GetSize();
+    cost = kLaunchNs + kAttentionFixedNs + std::max(flops / kAttentionFlopsPerNs, bytes / kHbmBytesPerNs) * (dflt ? 1.0 : 8.0);
     break;
   }
   case Kind::Softmax: case Kind::FusedSoftmax: case Kind::LayerNormalizationConstantScaleBias:
@@ -179,7 +216,9 @@ size_t CostModel::GetTimeCost(const flow::Node &n, const std::vector<Layout> &in
     const bool contig = is[0][n.axis] == 1 && os[n.axis] == 1;
     double bytes = obytes + (double)n.inputs[0]->meta.GetSize();
     for (size_t i = 1; i < n.inputs.size(); ++i) bytes += (double)n.inputs[i]->meta.GetSize();
-    cost = kLaunchNs + bytes / (kHbmBytesPerNs * (contig ? 1.0 : kStridedEfficiency));
+    cost = contig ? kLaunchNs + bytes / kHbmBytesPerNs
+                  : kLaunchNs + std::max(bytes / (kHbmBytesPerNs * kStridedRowEfficiency),
+                                         (double)o.meta.GetShape()[n.axis] * kStridedRowNsPerElement);
     break;
   }
   case Kind::ConvWithPadding: case Kind::ConvWithoutPadding: case Kind::MaxPoolWithoutPadding:

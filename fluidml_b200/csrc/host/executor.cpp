@@ -16,6 +16,7 @@
 #include "planner.h"
 #include "program.h"
 #include <cstdlib>
+#include <set>
 #include <sstream>
 
 namespace fluidml {
@@ -380,7 +381,47 @@ private:
       *json << root.Dump();
     }
     if (program) runner_ = std::make_unique<Runner>(std::move(program), options_);
+    if (runner_ && options_.autotune && !options_.dp_constant_cost) ReportCostModel(sequence, aliases);
   }
+
+  // The reference's layout search runs on MEASURED kernel times (src/evaluation/eval.cpp:64-100,
+  // :261-302); this back end plans with a model.  After Compile the two are put side by side:
+  // per kernel class the modelled cost of its nodes under the chosen layouts and the time the
+  // same launches take inside the replayed graph (kernel-start stamps), so that a model that has
+  // drifted from the hardware shows in the stats ("cost_model").
+  void ReportCostModel(const flow::Sequence &sequence, const AliasMap &aliases) {
+    try {
+      double pass_us = 0.0;
+      const auto measured = runner_->Trace({}, 5, &pass_us);
+      evaluation::CostModel model(false, options_.gemm_precision);
+      std::unordered_map<std::string, const flow::Node *> by_name;
+      for (const auto &n : sequence.nodes)
+        if (!aliases.count(n->output.get())) by_name[n->name] = n.get();
+      std::map<std::string, double> modelled;
+      std::set<std::string> seen;
+      for (const auto &l : runner_->GetProgram().launches) {
+        if (!seen.insert(l.node).second) continue;  // a node with several launches is modelled once
+        auto it = by_name.find(l.node);
+        if (it == by_name.end()) continue;
+        std::vector<std::vector<size_t>> ins;
+        for (const auto &r : it->second->inputs) ins.push_back(r->layout);
+        modelled[l.kernel] += (double)model.GetTimeCost(*it->second, ins, it->second->output->layout) * 1e-3;
+      }
+      json::Value o = json::Value::Object();
+      for (const auto &kv : measured) {
+        json::Value e = json::Value::Object();
+        e.Set("measured_us", json::Value(kv.second.us));
+        e.Set("modelled_us", json::Value(modelled.count(kv.first) ? modelled[kv.first] : 0.0));
+        e.Set("launches", json::Value((double)kv.second.launches));
+        o.Set(kv.first, e);
+      }
+      stats_.Set("cost_model", o);
+      stats_.Set("cost_model_pass_us", json::Value(pass_us));
+    } catch (const std::exception &e) {
+      stats_.Set("cost_model", json::Value(std::string("not measured: ") + e.what()));
+    }
+  }
+
 
   std::string name_;
   size_t epoch_;

@@ -1,5 +1,6 @@
 // C entry points over the host helpers (layout/stride utilities, shape rules, memory plans).
 #include "base.h"
+#include "dp.h"
 #include "fluidml_executor.h"
 #include "memory.h"
 
@@ -49,6 +50,60 @@ int fml_host_memory_plan(int greedy, int n, const char *const *names, const size
   const memory::Index index = plan->Run(*infos);
   for (int i = 0; i < n; ++i) offset_out[i] = index.Get(names[i]);
   *maximum_out = index.GetMaximum();
+  return 0;
+}
+
+namespace {
+bool ReadLayout(const long long *layout, size_t rank, std::vector<size_t> *out) {
+  *out = utils::GenDefaultLayout(rank);
+  if (!layout) return true;
+  std::vector<bool> seen(rank, false);
+  for (size_t i = 0; i < rank; ++i) {
+    if (layout[i] < 0 || layout[i] >= (long long)rank || seen[(size_t)layout[i]]) return false;
+    seen[(size_t)layout[i]] = true;
+    (*out)[i] = (size_t)layout[i];
+  }
+  return true;
+}
+flow::RegionPtr MakeRegion(const char *name, flow::Region::Kind kind, std::vector<int64_t> shape) {
+  auto r = std::make_shared<flow::Region>();
+  r->kind = kind;
+  r->name = name;
+  r->meta = Meta(Type::kFloat32, std::move(shape));
+  r->layout = utils::GenDefaultLayout(r->meta.GetRank());
+  return r;
+}
+}  // namespace
+
+int fml_host_model_gemm_cost(long long m, long long k, long long n, const long long *a_layout,
+                             const long long *c_layout, int precision, double *ns) {
+  if (m <= 0 || k <= 0 || n <= 0 || !ns) return 1;
+  std::vector<size_t> la, lc;
+  if (!ReadLayout(a_layout, 2, &la) || !ReadLayout(c_layout, 2, &lc)) return 1;
+  flow::Node node;
+  node.kind = flow::Kind::MatMul;
+  node.name = "probe";
+  node.inputs = {MakeRegion("a", flow::Region::kInner, {m, k}), MakeRegion("b", flow::Region::kConstant, {k, n})};
+  node.output = MakeRegion("c", flow::Region::kInner, {m, n});
+  evaluation::CostModel model(false, precision);
+  *ns = (double)model.GetTimeCost(node, {la, node.inputs[1]->layout}, lc);
+  return 0;
+}
+
+int fml_host_model_layernorm_cost(long long rows, long long cols, const long long *in_layout,
+                                  const long long *out_layout, double *ns) {
+  if (rows <= 0 || cols <= 0 || !ns) return 1;
+  std::vector<size_t> li, lo;
+  if (!ReadLayout(in_layout, 2, &li) || !ReadLayout(out_layout, 2, &lo)) return 1;
+  flow::Node node;
+  node.kind = flow::Kind::LayerNormalizationConstantScaleBias;
+  node.name = "probe";
+  node.axis = 1;
+  node.inputs = {MakeRegion("x", flow::Region::kInner, {rows, cols})};
+  node.consts = {MakeRegion("scale", flow::Region::kConstant, {cols}), MakeRegion("bias", flow::Region::kConstant, {cols})};
+  node.output = MakeRegion("y", flow::Region::kInner, {rows, cols});
+  evaluation::CostModel model(false, 0);
+  *ns = (double)model.GetTimeCost(node, {li}, lo);
   return 0;
 }
 

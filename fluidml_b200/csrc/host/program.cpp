@@ -473,8 +473,9 @@ std::map<std::string, Runner::KernelTime> Runner::Trace(const std::unordered_map
                                                         size_t passes, double *pass_us) {
   Check(fml_set_device(options_.device), "selecting the device");
   if (passes < 1) passes = 1;
-  for (const auto &b : program_->inputs)
-    Check(fml_memcpy_h2d(b.device, args.at(b.name), b.bytes, stream_), "copying an input");
+  if (!args.empty())  // with no arguments the interface buffers are traced as they are
+    for (const auto &b : program_->inputs)
+      Check(fml_memcpy_h2d(b.device, args.at(b.name), b.bytes, stream_), "copying an input");
   const size_t n = program_->launches.size(), reps = passes + 2, cap = n * reps;
   std::map<std::string, KernelTime> out;
   if (n == 0) return out;

@@ -101,7 +101,8 @@ public:
   std::map<std::string, KernelTime> Profile(const std::unordered_map<std::string, void *> &args, size_t passes);
   // In-graph breakdown from kernel-start stamps: per kernel name the microseconds per pass from
   // each of its launches' start to the next launch's start (median over `passes` inner replays
-  // of the captured graph) and its launches per pass; `pass_us` receives their sum.
+  // of the captured graph) and its launches per pass; `pass_us` receives their sum.  With no
+  // arguments the pass runs on whatever the interface buffers hold (zeros after Compile).
   std::map<std::string, KernelTime> Trace(const std::unordered_map<std::string, void *> &args, size_t passes, double *pass_us);
 
 private:

@@ -143,6 +143,30 @@ class Executor:
             pass
 
 
+def _layout_arg(layout):
+    return None if layout is None else (ctypes.c_longlong * len(layout))(*layout)
+
+
+def model_gemm_cost_ns(m: int, k: int, n: int, a_layout=None, c_layout=None, precision: int = 0) -> float:
+    """What the layout search charges for a MatMul [m,k] x constant [k,n] (fml_host_model_gemm_cost)."""
+    ns = ctypes.c_double()
+    st = lib().fml_host_model_gemm_cost(ctypes.c_longlong(m), ctypes.c_longlong(k), ctypes.c_longlong(n),
+                                        _layout_arg(a_layout), _layout_arg(c_layout), int(precision), ctypes.byref(ns))
+    if st:
+        raise ValueError("fml_host_model_gemm_cost: bad arguments")
+    return ns.value
+
+
+def model_layernorm_cost_ns(rows: int, cols: int, in_layout=None, out_layout=None) -> float:
+    """What the layout search charges for a LayerNormalization over the last axis of [rows, cols]."""
+    ns = ctypes.c_double()
+    st = lib().fml_host_model_layernorm_cost(ctypes.c_longlong(rows), ctypes.c_longlong(cols),
+                                             _layout_arg(in_layout), _layout_arg(out_layout), ctypes.byref(ns))
+    if st:
+        raise ValueError("fml_host_model_layernorm_cost: bad arguments")
+    return ns.value
+
+
 _PINNED_OWNERS = []  # page-locked blocks live until the process exits
 
 

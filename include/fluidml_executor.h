@@ -78,6 +78,16 @@ int fml_host_memory_plan(int greedy, int n, const char *const *names, const size
                          const size_t *end, const size_t *size, size_t alignment, size_t *offset_out,
                          size_t *maximum_out);
 
+/* What the layout search charges, in nanoseconds, for one node (the model that stands where the
+ * reference measures: KernelEval::GetTimeCost, src/evaluation/eval.cpp:64-100, :261-302):
+ * a MatMul [m,k] x constant [k,n] with the given layouts of A and of the output (NULL = default
+ * layout), and a LayerNormalization over the last axis of [rows, cols].  `precision` is an
+ * fml_gemm_precision.  Tests rank these against measured kernel times. */
+int fml_host_model_gemm_cost(long long m, long long k, long long n, const long long *a_layout,
+                             const long long *c_layout, int precision, double *ns);
+int fml_host_model_layernorm_cost(long long rows, long long cols, const long long *in_layout,
+                                  const long long *out_layout, double *ns);
+
 #ifdef __cplusplus
 }
 #endif

@@ -334,3 +334,35 @@ def test_causal_where_becomes_an_additive_mask():
     assert "WhereConstantCondConstantScalarY" in unfused and "DivConstantRhs" in unfused
     assert "WhereConstantCondConstantScalarY" not in fused and "DivConstantRhs" not in fused
     assert ("FusedAttention" in fused) or ("FusedSoftmax" in fused)
+
+
+def test_plan_cache_file_that_names_a_non_permutation_is_a_miss(tmp_path):
+    """A plan-cache file is trusted only if every layout in it is a permutation of the dims of a
+    tensor of this model; a stale or damaged file is ignored as a whole and the model is planned
+    afresh instead of strides being computed from garbage."""
+    m = models.build_bert(layers=1, vocab=100)
+
+    def plan():
+        ex = Executor.make_dp_greedy("b")
+        ex.set_option("plan_cache", str(tmp_path))
+        return ex.plan(m.to_bytes())
+
+    fresh = plan()
+    assert fresh["plan_cache"] == "miss" and not os.path.exists(fresh["plan_cache_file"])  # planning never writes
+    path = fresh["plan_cache_file"]
+    inner = [n["output"] for n in fresh["sequence"] if n["kind"] == "Transpose"]
+    assert inner
+    # a well-formed file is taken: default layouts everywhere, so the transposes stop being views
+    with open(path, "w") as f:
+        f.write("".join(f"layout {name} 0 1 2 3\n" for name in inner) + "end\n")
+    hit = plan()
+    assert hit["plan_cache"] == "hit" and hit["aliased_nodes"] < fresh["aliased_nodes"]
+    for bad in ("0 0 1 2", "0 1 2 7", "0 1 2", "0 1 2 3 4"):  # repeated, out of range, short, long
+        with open(path, "w") as f:
+            f.write("".join(f"layout {name} 0 1 2 3\n" for name in inner[1:]) + f"layout {inner[0]} {bad}\nend\n")
+        again = plan()
+        assert again["plan_cache"] == "miss", bad
+        assert again["aliased_nodes"] == fresh["aliased_nodes"] and again["peak_arena_bytes"] == fresh["peak_arena_bytes"]
+    with open(path, "w") as f:  # a truncated file (no end marker) is a miss too
+        f.write(f"layout {inner[0]} 0 1 2 3\n")
+    assert plan()["plan_cache"] == "miss"
