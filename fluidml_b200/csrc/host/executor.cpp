@@ -125,15 +125,26 @@ public:
     if (!runner_) throw Error("Trace called before Compile");
     double pass_us = 0.0;
     json::Value kernels = json::Value::Object();
-    for (const auto &kv : runner_->Trace(args, passes ? passes : 1, &pass_us)) {
+    std::vector<double> per_launch;
+    for (const auto &kv : runner_->Trace(args, passes ? passes : 1, &pass_us, &per_launch)) {
       json::Value e = json::Value::Object();
       e.Set("us", json::Value(kv.second.us));
       e.Set("launches", json::Value((double)kv.second.launches));
       kernels.Set(kv.first, e);
     }
+    json::Value list = json::Value::Array();
+    const auto &launches = runner_->GetProgram().launches;
+    for (size_t i = 0; i < launches.size() && i < per_launch.size(); ++i) {
+      json::Value e = json::Value::Object();
+      e.Set("node", json::Value(launches[i].node));
+      e.Set("kernel", json::Value(launches[i].kernel));
+      e.Set("us", json::Value(per_launch[i]));
+      list.Push(e);
+    }
     json::Value o = json::Value::Object();
     o.Set("pass_us", json::Value(pass_us));
     o.Set("kernels", kernels);
+    o.Set("launch_list", list);
     return o.Dump();
   }
 

@@ -470,7 +470,8 @@ std::map<std::string, Runner::KernelTime> Runner::Profile(const std::unordered_m
 }
 
 std::map<std::string, Runner::KernelTime> Runner::Trace(const std::unordered_map<std::string, void *> &args,
-                                                        size_t passes, double *pass_us) {
+                                                        size_t passes, double *pass_us,
+                                                        std::vector<double> *per_launch_us) {
   Check(fml_set_device(options_.device), "selecting the device");
   if (passes < 1) passes = 1;
   if (!args.empty())  // with no arguments the interface buffers are traced as they are
@@ -523,6 +524,7 @@ std::map<std::string, Runner::KernelTime> Runner::Trace(const std::unordered_map
     total += period[i];
   }
   if (pass_us) *pass_us = total;
+  if (per_launch_us) *per_launch_us = period;
   return out;
 }
 

@@ -103,7 +103,9 @@ public:
   // each of its launches' start to the next launch's start (median over `passes` inner replays
   // of the captured graph) and its launches per pass; `pass_us` receives their sum.  With no
   // arguments the pass runs on whatever the interface buffers hold (zeros after Compile).
-  std::map<std::string, KernelTime> Trace(const std::unordered_map<std::string, void *> &args, size_t passes, double *pass_us);
+  // `per_launch_us`, when given, receives the period of every entry of the launch list in order.
+  std::map<std::string, KernelTime> Trace(const std::unordered_map<std::string, void *> &args, size_t passes, double *pass_us,
+                                          std::vector<double> *per_launch_us = nullptr);
 
 private:
   void Replay();

@@ -41,6 +41,20 @@ namespace {
 constexpr int kThreads = 320;  // producer warp, MMA warp, two sets of four converter / epilogue warps
 constexpr size_t kSmemBudget = 200 * 1024;
 
+#ifdef FML_CONV_PHASE_TRACE
+// Debug builds only (-DFML_CONV_PHASE_TRACE): per-CTA %globaltimer stamps of the kernel's phases.
+#define CTRACE(slot)                                                                            \
+  do {                                                                                          \
+    if (a.trace) {                                                                              \
+      unsigned long long t_;                                                                    \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
+      a.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = t_;                 \
+    }                                                                                           \
+  } while (0)
+#else
+#define CTRACE(slot) do { } while (0)
+#endif
+
 struct ConvTcArgs {
   int N, IC, OC, OH, OW, KH, KW, ph, pw;
   int TW, TH, PWD, PHT, xoff;  // tile geometry: patch PHT rows x PWD columns per channel
@@ -54,6 +68,9 @@ struct ConvTcArgs {
   int64_t bias_stride;
   int act;
   int *status;
+#ifdef FML_CONV_PHASE_TRACE
+  unsigned long long *trace;  // 8 stamps per CTA (fml_debug_set_conv_trace)
+#endif
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
@@ -72,16 +89,37 @@ __device__ __forceinline__ float conv_act(int act, float v) {
   switch (act) {
   case FML_ACT_RELU: return fmaxf(v, 0.0f);
   case FML_ACT_TANH: return tanhf(v);
-  case FML_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
-  case FML_ACT_SILU: return v * (1.0f / (1.0f + expf(-v)));
+  // exp2-based exponential and approximate reciprocal (about 2 ulp each): the exact forms are
+  // ~40 dependent instructions per element, which a TMEM-lane-per-thread epilogue with two warps
+  // per scheduler cannot hide (measured: 8.6 us of a 128x96 tile's epilogue against 1.x us)
+  case FML_ACT_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-v));
+  case FML_ACT_SILU: return __fdividef(v, 1.0f + __expf(-v));
   default: return v;
+  }
+}
+
+// One 32-column group of the epilogue for one activation.  The activation is a template
+// parameter and the dispatch sits outside the unrolled loop: with a switch inside it every one
+// of the 32 unrolled stores carried the code of all five activations, and fetching those
+// instructions (each CTA runs them once, cold) cost more than the stores themselves.
+template <int ACT>
+__device__ __forceinline__ void store_group(const float *v, const float *bias_s, float *yp, int64_t ys1, int oc_base,
+                                            int OC) {
+  float *p = yp + (int64_t)oc_base * ys1;
+  if (oc_base + 32 <= OC) {  // the usual case: no channel tail inside the group
+#pragma unroll
+    for (int i = 0; i < 32; ++i, p += ys1) *p = conv_act(ACT, v[i] + bias_s[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i, p += ys1)
+      if (oc_base + i < OC) *p = conv_act(ACT, v[i] + bias_s[i]);
   }
 }
 
 // ICB: input channels per k block (32, or 8 for the first layer's few channels).
 // MODE: 0 = box patch, 1 = flat rows, 2 = linear (whole planes), see the header.
 template <bool THREE_PASS, int ICB, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const ConvTcArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -104,6 +142,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t bar_accum = bar_rempty + 8u * RS;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * NS + 2 * RS + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *bias_s = reinterpret_cast<float *>(tmem_slot + 4);  // this tile's slice of the bias, [BN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int t = blockIdx.x;
@@ -119,6 +158,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   while (tmem_cols < a_col0 + a_cols * (uint32_t)NS) tmem_cols <<= 1;
 
   pdl_launch_dependents();
+  if (threadIdx.x == 0) CTRACE(0);
   if (threadIdx.x == 32) {  // descriptors ready for the first loads after the dependency wait
     tma_prefetch_map(&map_x);
     tma_prefetch_map(&map_w);
@@ -148,6 +188,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();
+  if (threadIdx.x == 0) CTRACE(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -233,10 +274,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     bool ok = true;
     int kb = 0;
     auto lo1 = [](uint32_t x) { return __float_as_uint(__uint_as_float(x) - __uint_as_float(x & 0xffffe000u)); };
+    // The bias slice goes to shared memory now.  Read from global memory inside the epilogue's
+    // store loop it would serialise that loop: the compiler must assume that a store to y may
+    // change the bias and orders every load behind the store before it (measured: 15 us of a
+    // 128-channel tile's epilogue, against about 1 us with the slice on chip).
+    {
+      const int i = threadIdx.x - 64;
+      if (i < BN) bias_s[i] = (a.bias && oc0 + i < a.OC) ? a.bias[(int64_t)(oc0 + i) * a.bias_stride] : 0.0f;
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight converter / epilogue warps
+    }
     for (int icb = 0; icb < a.n_icb && ok; ++icb) {
       const int rs = icb % RS;
       ok = mbar_wait(bar_rfull + 8u * rs, ((uint32_t)(icb / RS)) & 1u, abort_flag);
       if (!ok) break;
+      if (icb == 0 && threadIdx.x == 64) CTRACE(2);
       const uint32_t *rawp = reinterpret_cast<const uint32_t *>(raw_ptr + (size_t)rs * raw_pitch);
       for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
         if ((kb & 1) != set) continue;
@@ -299,6 +350,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       *abort_flag = 1;
     }
     tc_fence_after();
+    if (threadIdx.x == 64) CTRACE(3);
     // ---- epilogue: this thread's output position, all channels of the tile; for a fixed channel
     // the lanes of a warp write consecutive pixels of a row
     const int oh = oh0 + r, ow = ow0 + c;
@@ -313,26 +365,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         float v[32];
         tmem_ld32(lane_addr + (uint32_t)c0, v);
         if (inside) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int oc = oc0 + c0 + i;
-            if (oc < a.OC) {
-              float acc = v[i];
-              if (a.bias) acc += a.bias[(int64_t)oc * a.bias_stride];
-              yp[(int64_t)oc * a.ys[1]] = conv_act(a.act, acc);
-            }
+          switch (a.act) {
+          case FML_ACT_RELU: store_group<FML_ACT_RELU>(v, bias_s + c0, yp, a.ys[1], oc0 + c0, a.OC); break;
+          case FML_ACT_TANH: store_group<FML_ACT_TANH>(v, bias_s + c0, yp, a.ys[1], oc0 + c0, a.OC); break;
+          case FML_ACT_SIGMOID: store_group<FML_ACT_SIGMOID>(v, bias_s + c0, yp, a.ys[1], oc0 + c0, a.OC); break;
+          case FML_ACT_SILU: store_group<FML_ACT_SILU>(v, bias_s + c0, yp, a.ys[1], oc0 + c0, a.OC); break;
+          default: store_group<FML_ACT_NONE>(v, bias_s + c0, yp, a.ys[1], oc0 + c0, a.OC); break;
           }
         }
       }
     }
   }
+  if (threadIdx.x == 64) CTRACE(4);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+  if (threadIdx.x == 0) CTRACE(5);
 }
+
+#ifdef FML_CONV_PHASE_TRACE
+unsigned long long *g_conv_trace = nullptr;
+#endif
 
 int make_map_nd(CUtensorMap *map, const float *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
                 const cuuint32_t *box, CUtensorMapSwizzle swizzle) {
@@ -416,13 +472,17 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   // a patch feeds `taps` k blocks: with a single tap every k block waits for its own patch, so the
   // patch ring must be as deep as the operand ring to cover the load latency
   a.raw_stages = a.taps == 1 ? 6 : a.taps <= 4 ? 3 : 2;
+  // ... but never deeper than the work of one tile: a pointwise layer with few input channels is
+  // one or two k blocks per tile, and rings sized for long reductions would only keep a second
+  // CTA off the SM, whose loads and epilogue are what hides this one's latencies
+  a.raw_stages = std::max(1, std::min(a.raw_stages, a.n_icb));
   const size_t raw_pitch = ((size_t)a.raw_elems * icb * 4 + 127) / 128 * 128;
   const size_t stage = (size_t)icb * a.tile_n * 4 * (three ? 2 : 1);
   FML_REQUIRE(a.raw_stages * raw_pitch + 2 * stage <= kSmemBudget, FML_UNSUPPORTED, "fml_conv: patch does not fit in shared memory");
   int stages = (int)((kSmemBudget - a.raw_stages * raw_pitch) / stage);
   const int a_cols = (three ? 2 : 1) * icb;
   stages = std::min(stages, (512 - (a.tile_n + 31) / 32 * 32) / a_cols);
-  stages = std::max(2, std::min(stages, 8));
+  stages = std::max(2, std::min(std::min(stages, 8), a.n_icb * a.taps));
   a.stages = stages;
   a.tiles_w = (a.OW + a.TW - 1) / a.TW;
   a.tiles_h = (a.OH + a.TH - 1) / a.TH;
@@ -435,6 +495,9 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   }
   a.act = p->act;
   a.status = device_status_word();
+#ifdef FML_CONV_PHASE_TRACE
+  a.trace = g_conv_trace;
+#endif
   FML_REQUIRE(a.status, FML_CUDA_ERROR, "fml_conv: no device status word");
   const int64_t m_tiles = (int64_t)a.tiles_w * a.tiles_h * a.N;
   FML_REQUIRE(m_tiles <= 0x7fffffff && (a.OC + a.tile_n - 1) / a.tile_n <= 65535, FML_UNSUPPORTED, "fml_conv: grid too large");
@@ -462,7 +525,8 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
     int st = make_map_nd(&map_w, (const float *)w->data, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (st != FML_OK) return st;
   }
-  size_t smem = (size_t)stages * stage + a.raw_stages * raw_pitch + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 1024;
+  size_t smem = (size_t)stages * stage + a.raw_stages * raw_pitch + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 +
+                128 * 4 /* bias slice */ + 1024;
   {  // co-residency capped by TMEM columns, as in the GEMM
     unsigned need = (unsigned)((a.tile_n + 31) / 32 * 32 + a_cols * stages), cols = 32;
     while (cols < need) cols <<= 1;
@@ -491,3 +555,12 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
 }
 
 }  // namespace fml
+
+#ifdef FML_CONV_PHASE_TRACE
+// Tracing hook of debug builds: a device buffer of 8 x (number of CTAs) u64 receives, per CTA,
+// %globaltimer at 0 start, 1 dependency wait done, 2 first patch landed, 3 accumulator ready,
+// 4 epilogue done, 5 end.  NULL disables it.
+extern "C" void fml_debug_set_conv_trace(void *device_buffer) {
+  fml::g_conv_trace = static_cast<unsigned long long *>(device_buffer);
+}
+#endif

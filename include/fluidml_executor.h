@@ -55,8 +55,9 @@ int fml_executor_profile(fml_executor *e, const char *const *names, void *const 
 /* The same breakdown without disturbing the pass: replays the captured graph `passes` + 2 times
  * with the library's kernel-start stamps switched on (fml_set_kernel_trace) and attributes to
  * every launch the time from its start to the next launch's start, median over the inner
- * passes.  Returns {"pass_us": .., "kernels": {"<KernelName>": {"us": per pass, "launches": n}}}.
- * The periods of a pass add up to the pass. */
+ * passes.  Returns {"pass_us": .., "kernels": {"<KernelName>": {"us": per pass, "launches": n}},
+ * "launch_list": [{"node", "kernel", "us"} in launch order]}.  The periods of a pass add up to
+ * the pass. */
 int fml_executor_trace(fml_executor *e, const char *const *names, void *const *buffers,
                        size_t count, size_t passes, const char **json_out);
 

@@ -102,6 +102,9 @@ def main() -> None:
     c.add_argument("--k", type=int, default=3)
     c.add_argument("--precision", default="3xtf32", choices=["fp32", "3xtf32", "tf32"])
     c.add_argument("--reps", type=int, default=3)
+    c.add_argument("--act", default="relu", choices=["none", "relu", "silu"])
+    c.add_argument("--stride", type=int, default=1)
+    c.add_argument("--depthwise", action="store_true", help="group = channels (oc is ignored)")
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=1)
     a.add_argument("--heads", type=int, default=12)
@@ -175,15 +178,19 @@ def main() -> None:
     if args.op == "conv":
         prec = {"fp32": cabi.GEMM_FP32, "3xtf32": cabi.GEMM_3XTF32, "tf32": cabi.GEMM_TF32}[args.precision]
         pad = args.k // 2
+        act = {"none": cabi.ACT_NONE, "relu": cabi.ACT_RELU, "silu": cabi.ACT_SILU}[args.act]
+        oc, group, st = (args.ic, args.ic, args.stride) if args.depthwise else (args.oc, 1, args.stride)
+        ohw = (args.hw + 2 * pad - args.k) // st + 1
         x = DT.from_numpy(rng.standard_normal((args.batch, args.ic, args.hw, args.hw)).astype(np.float32))
-        w = DT.from_numpy((rng.standard_normal((args.oc, args.ic, args.k, args.k)) * 0.05).astype(np.float32),
-                          [3, 2, 0, 1])  # tap-major, output channel innermost: what the Builder bakes
-        b = DT.from_numpy(np.zeros(args.oc, np.float32))
-        y = DT((args.batch, args.oc, args.hw, args.hw), np.float32)
-        print("tensor cores:", cabi.conv_uses_tensor_cores(x, w, y, [pad, pad], prec))
-        us = _time(lambda: cabi.conv(x, w, b, y, [pad, pad], [1, 1], [1, 1], 1, act=cabi.ACT_RELU, precision=prec), args.reps)
-        flop = 2.0 * args.batch * args.oc * args.ic * args.k * args.k * args.hw * args.hw
-        nbytes = 4.0 * (args.batch * (args.ic + args.oc) * args.hw * args.hw + args.oc * args.ic * args.k * args.k)
+        wh = (rng.standard_normal((oc, args.ic // group, args.k, args.k)) * 0.05).astype(np.float32)
+        # group 1: tap-major, output channel innermost -- what the Builder bakes for the tensor-core path
+        w = DT.from_numpy(wh) if args.depthwise else DT.from_numpy(wh, [3, 2, 0, 1])
+        b = DT.from_numpy(np.zeros(oc, np.float32))
+        y = DT((args.batch, oc, ohw, ohw), np.float32)
+        print("tensor cores:", (not args.depthwise) and cabi.conv_uses_tensor_cores(x, w, y, [pad, pad], prec))
+        us = _time(lambda: cabi.conv(x, w, b, y, [pad, pad], [st, st], [1, 1], group, act=act, precision=prec), args.reps)
+        flop = 2.0 * args.batch * oc * (args.ic // group) * args.k * args.k * ohw * ohw
+        nbytes = 4.0 * (args.batch * (args.ic * args.hw * args.hw + oc * ohw * ohw) + wh.size)
         print(f"{us:.2f} us per launch, {flop / us / 1e6:.1f} TFLOP/s, {nbytes / us / 1e3:.1f} GB/s algorithmic")
     else:
         B, H, S, D = args.batch, args.heads, args.seq, args.dim

@@ -331,6 +331,41 @@ def test_conv(cfg):
     assert relerr(out.numpy(), ref) <= 1e-5
 
 
+@pytest.mark.parametrize("shape,k,stride,pad,act", [
+    ((2, 32, 112, 112), 3, 1, 1, 0),   # row-tiled plane, float4 stores
+    ((2, 24, 112, 112), 3, 2, 1, 5),   # stride 2, SiLU
+    ((3, 40, 56, 56), 5, 2, 2, 0),
+    ((2, 48, 28, 28), 5, 1, 2, 5),     # one whole plane per CTA
+    ((3, 37, 14, 14), 5, 1, 2, 0),     # planes batched four to a CTA, 14-wide rows (scalar stores), ragged plane count
+    ((5, 21, 7, 7), 3, 1, 1, 0),       # eighteen planes to a CTA, width 7
+    ((2, 19, 7, 7), 5, 1, 2, 5),
+    ((1, 8, 33, 45), 3, 2, 1, 0),      # odd sizes: ragged strips and row tiles
+    ((1, 6, 61, 130), 7, 1, 3, 0),     # 7x7 window
+    ((1, 5, 30, 30), 3, 1, 0, 0),      # no padding
+])
+def test_depthwise_conv_tiled(shape, k, stride, pad, act):
+    """The tiled depthwise kernel (every window / stride variant, every plane-batching mode) against
+    the oracle's convolution, bias and activation included."""
+    n, c, h, w_ = shape
+    x, w, b = rnd(*shape), rnd(c, 1, k, k) * 0.3, rnd(c)
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w_ + 2 * pad - k) // stride + 1
+    ref = orc.conv(x, w, b, np.empty((n, c, oh, ow), np.float32), (pad, pad), (stride, stride), (1, 1), c, acc64=True)
+    if act == cabi.ACT_SILU:
+        ref = ref / (1.0 + np.exp(-ref.astype(np.float64)))
+    out = DT((n, c, oh, ow), np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), out, (pad, pad), (stride, stride), (1, 1), c, act=act)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
+def test_depthwise_conv_1d_window_9():
+    """ConvBERT's span convolution: 1-D depthwise, window 9, rows of 128."""
+    x, w, b = rnd(8, 96, 128), rnd(96, 1, 9) * 0.3, rnd(96)
+    ref = orc.conv(x, w, b, np.empty((8, 96, 128), np.float32), (4,), (1,), (1,), 96, acc64=True)
+    out = DT((8, 96, 128), np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), out, (4,), (1,), (1,), 96)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
 @pytest.mark.parametrize("mode,shape,k,s", [(0, (1, 64, 32, 32), (2, 2), (2, 2)), (1, (2, 1280, 7, 7), (7, 7), (1, 1)),
                                             (0, (1, 3, 9, 11), (3, 2), (2, 3))])
 def test_pool(mode, shape, k, s):
