@@ -129,133 +129,279 @@ __global__ void conv_depthwise_kernel(ConvArgs a) {
   }
 }
 
-// Depthwise convolution, tiled (dilation 1, stride 1 or 2, compile-time window).  A depthwise
-// layer does KH*KW multiply-adds per element it moves, so it is bound by HBM, not by arithmetic,
-// and the kernel is built around the memory system: a CTA stages the input patch of its output
-// tile in shared memory with coalesced loads (rows and columns outside the image become the zero
-// padding there), every thread then produces a strip of four adjacent outputs from 16-byte
-// shared-memory loads with the window's weights in registers, and stores the strip as one float4
-// where the row length allows.  Each input element is read from global memory once per tile
-// (plus the halo rows between row tiles).  Planes too small to fill a CTA are batched: a CTA takes
-// PP whole planes of TH = OH rows, otherwise one plane and TH rows of it.
-struct DwArgs {
+// Direct convolution for a short reduction (IC * KH * KW <= 64: the strided first layer of an
+// image network, 3 x 3 x 3 = 27).  The implicit GEMM above spends its time on index arithmetic
+// when K is two k blocks long.  Here a thread owns one output pixel and OCB output channels:
+// the CTA's weights [K][OCB] and a table of the K taps' input offsets sit in shared memory, each
+// tap is one bounds-checked input load (lanes = consecutive pixels of a row) and OCB
+// multiply-adds against broadcast 16-byte weight loads, and for every channel a warp stores 32
+// consecutive pixels.  Any stride, dilation and padding.
+struct DirectArgs {
   ConvArgs c;
-  int TH, PP, SW;       // output rows per tile, planes per CTA, four-wide strips per output row
-  int PH, PWn, pitch;   // patch rows, patch columns that are loaded, shared-memory row pitch (floats)
-  int row_tiles;        // ceil(OH / TH)
-  int64_t planes;       // N * C
+  int K;
+  int64_t M;
 };
 
-template <int KH, int KW, int S>
+template <int OCB>
+__global__ void __launch_bounds__(128) conv_direct_small_kernel(const DirectArgs d) {
+  extern __shared__ __align__(16) float dc_smem[];
+  const ConvArgs &a = d.c;
+  float *w_s = dc_smem;                                   // [K][OCB]
+  float *b_s = dc_smem + d.K * OCB;                       // [OCB]: on chip, so that no global load sits between the stores
+  int *tab = reinterpret_cast<int *>(b_s + OCB);          // [K][3]: dy, dx, element offset
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int oc0 = (int)blockIdx.y * OCB;
+  const int taps = (int)(a.KH * a.KW), KW = (int)a.KW;
+  for (int i = tid; i < d.K * OCB; i += 128) {
+    const int k = i / OCB, o = i - k * OCB;
+    const int ic = k / taps, t = k - ic * taps, kh = t / KW, kw = t - kh * KW;
+    const int oc = oc0 + o;
+    w_s[i] = oc < (int)a.OC ? a.w[oc * a.ws[0] + ic * a.ws[1] + kh * a.ws[2] + kw * a.ws[3]] : 0.0f;
+  }
+  if (tid < OCB) b_s[tid] = (a.bias && oc0 + tid < (int)a.OC) ? a.bias[(oc0 + tid) * a.bias_stride] : 0.0f;
+  for (int k = tid; k < d.K; k += 128) {
+    const int ic = k / taps, t = k - ic * taps, kh = t / KW, kw = t - kh * KW;
+    tab[3 * k] = kh * (int)a.dh;
+    tab[3 * k + 1] = kw * (int)a.dw;
+    tab[3 * k + 2] = (int)(ic * a.xs[1] + kh * a.dh * a.xs[2] + kw * a.dw * a.xs[3]);
+  }
+  __syncthreads();
+  const int64_t m = (int64_t)blockIdx.x * 128 + tid;
+  if (m >= d.M) return;
+  const int OW = (int)a.OW, OH = (int)a.OH, IH = (int)a.IH, IW = (int)a.IW;
+  const int64_t row = m / OW;
+  const int ow = (int)(m - row * OW);
+  const int64_t n = row / OH;
+  const int oh = (int)(row - n * OH);
+  const int ih0 = oh * (int)a.sh - (int)a.ph, iw0 = ow * (int)a.sw - (int)a.pw;
+  const float *base = a.x + n * a.xs[0] + (int64_t)ih0 * a.xs[2] + (int64_t)iw0 * a.xs[3];
+  float acc[OCB];
+#pragma unroll
+  for (int o = 0; o < OCB; ++o) acc[o] = 0.0f;
+  for (int k = 0; k < d.K; ++k) {
+    const int ih = ih0 + tab[3 * k], iw = iw0 + tab[3 * k + 1];
+    const float v = ((unsigned)ih < (unsigned)IH && (unsigned)iw < (unsigned)IW) ? base[tab[3 * k + 2]] : 0.0f;
+    const float4 *wr = reinterpret_cast<const float4 *>(w_s + k * OCB);
+#pragma unroll
+    for (int q = 0; q < OCB / 4; ++q) {
+      const float4 w4 = wr[q];
+      acc[4 * q] = fmaf(v, w4.x, acc[4 * q]);
+      acc[4 * q + 1] = fmaf(v, w4.y, acc[4 * q + 1]);
+      acc[4 * q + 2] = fmaf(v, w4.z, acc[4 * q + 2]);
+      acc[4 * q + 3] = fmaf(v, w4.w, acc[4 * q + 3]);
+    }
+  }
+  float *yp = a.y + n * a.ys[0] + (int64_t)oc0 * a.ys[1] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3];
+  const int nb = min(OCB, (int)a.OC - oc0);
+  switch (a.act) {  // one dispatch per thread, outside the store loop
+#define FML_DC_STORE(ACT)                                                                   \
+  _Pragma("unroll") for (int o = 0; o < OCB; ++o)                                           \
+    if (o < nb) yp[o * a.ys[1]] = conv_act(ACT, acc[o] + b_s[o]);
+  case FML_ACT_RELU: FML_DC_STORE(FML_ACT_RELU) break;
+  case FML_ACT_TANH: FML_DC_STORE(FML_ACT_TANH) break;
+  case FML_ACT_SIGMOID: FML_DC_STORE(FML_ACT_SIGMOID) break;
+  case FML_ACT_SILU: FML_DC_STORE(FML_ACT_SILU) break;
+  default: FML_DC_STORE(FML_ACT_NONE) break;
+#undef FML_DC_STORE
+  }
+}
+
+// Depthwise convolution, tiled (dilation 1, stride 1 or 2, compile-time window).  A depthwise
+// layer does KH*KW multiply-adds per element it moves, so it is bound by HBM -- and, on the way
+// there, by the instructions issued per output, not by arithmetic.  The kernel is built around
+// both: a CTA stages the input patch of its output tile in shared memory with coalesced 16-byte
+// loads (rows and columns outside the image become the zero padding there); every thread then
+// produces a micro-tile of 4 x 4 outputs, reading each input row of the micro-tile once as
+// 16-byte shared-memory loads with the window's weights in registers (about 20 instructions per
+// output, against ~140 with one strip per thread), and stores rows as float4 where the row
+// length allows.  No index division sits inside a loop.  Planes too small to fill a CTA are
+// batched: a CTA takes PP whole planes, otherwise one plane and a band of its rows.
+struct DwArgs {
+  ConvArgs c;
+  int TR, PP, SW;       // thread rows (of 4 output rows) per tile, planes per CTA, strips per output row
+  int PH, PWn, pitch;   // patch rows, patch columns, shared-memory row pitch (floats)
+  int row_tiles;        // bands per plane
+  int vec;              // input rows can be fetched as aligned float4
+  int planes;           // N * C
+};
+
+template <int ACT>
+__device__ __forceinline__ void dw_store_row(float *yp, const float *v, float bias, bool vec, int valid, int64_t ys3) {
+  if (vec) {
+    *reinterpret_cast<float4 *>(yp) = make_float4(conv_act(ACT, v[0] + bias), conv_act(ACT, v[1] + bias),
+                                                  conv_act(ACT, v[2] + bias), conv_act(ACT, v[3] + bias));
+  } else {
+#pragma unroll
+    for (int o = 0; o < 4; ++o)
+      if (o < valid) yp[o * ys3] = conv_act(ACT, v[o] + bias);
+  }
+}
+
+// RT: output rows per thread (4; 1 for one-row images, i.e. 1-D convolutions)
+template <int KH, int KW, int S, int RT>
 __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs d) {
   extern __shared__ __align__(16) float dw_smem[];
   const ConvArgs &a = d.c;
-  float *patch = dw_smem;                                            // [PP][PH][pitch]
-  float *wts = dw_smem + (size_t)d.PP * d.PH * d.pitch;              // [PP][KH*KW + 1]: window, bias
+  float *patch = dw_smem;                          // [PP][PH][pitch]
+  float *wts = dw_smem + d.PP * d.PH * d.pitch;    // [PP][KH*KW + 1]: window, bias
   pdl_launch_dependents();
-  l2_prefetch_span(a.w, a.w_span);
-  l2_prefetch_span(a.bias, a.bias_span);
   pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t plane0 = (int64_t)(blockIdx.x / d.row_tiles) * d.PP;
-  const int oh0 = (int)(blockIdx.x % d.row_tiles) * d.TH;
+  const int tile = (int)blockIdx.x / d.row_tiles;
+  const int plane0 = tile * d.PP;
+  const int oh0 = ((int)blockIdx.x - tile * d.row_tiles) * d.TR * RT;
   const int ih0 = oh0 * S - (int)a.ph;
-  // ---- stage weights and bias of the CTA's planes
+  const int C = (int)a.OC, IH = (int)a.IH, IW = (int)a.IW, pw = (int)a.pw;
+  const int n0 = plane0 / C, c0 = plane0 - n0 * C;  // the only division by a tensor extent
+  // ---- weights and bias of the CTA's planes
   for (int i = tid; i < d.PP * (KH * KW + 1); i += 256) {
     const int pl = i / (KH * KW + 1), k = i - pl * (KH * KW + 1);
-    const int64_t plane = plane0 + pl;
     float v = 0.0f;
-    if (plane < d.planes) {
-      const int64_t ch = plane % a.OC;
+    if (plane0 + pl < d.planes) {
+      const int ch = (c0 + pl) % C;
       if (k < KH * KW) v = a.w[ch * a.ws[0] + (k / KW) * a.ws[2] + (k % KW) * a.ws[3]];
       else if (a.bias) v = a.bias[ch * a.bias_stride];
     }
     wts[i] = v;
   }
-  // ---- stage the patch: lanes run along a patch row (sub-warps share a warp when rows are short)
+  // ---- patch: a sub-warp per patch row, lanes along the row; (plane, row) advance by steps
   {
-    int p2 = 32;
-    while (p2 > 1 && (p2 >> 1) >= d.PWn) p2 >>= 1;  // smallest power of two >= PWn, at most 32
-    const int sub = lane / p2, pc0 = lane - sub * p2, rows_per_iter = 8 * (32 / p2);
+    const int units = d.vec ? IW >> 2 : d.PWn;     // float4 chunks of the image row, or patch columns
+    int p2 = 32, sh = 5;
+    while (p2 > 1 && (p2 >> 1) >= units) { p2 >>= 1; --sh; }
+    const int sub = lane >> sh, u0 = lane & (p2 - 1), step = 8 << (5 - sh);
     const int total_rows = d.PP * d.PH;
-    for (int row = warp * (32 / p2) + sub; row < total_rows; row += rows_per_iter) {
-      const int pl = row / d.PH, pr = row - pl * d.PH;
-      const int64_t plane = plane0 + pl;
+    int row = (warp << (5 - sh)) + sub;
+    int pl = row / d.PH, pr = row - pl * d.PH;     // once per thread
+    int n = n0, ch = c0 + pl;
+    while (ch >= C) { ch -= C; ++n; }
+    for (; row < total_rows; row += step) {
       const int ih = ih0 + pr;
-      const bool row_ok = plane < d.planes && ih >= 0 && ih < a.IH;
-      const float *src = a.x + (plane / a.IC) * a.xs[0] + (plane % a.IC) * a.xs[1] + (int64_t)ih * a.xs[2];
-      float *dst = patch + (size_t)row * d.pitch;
-      for (int pc = pc0; pc < d.PWn; pc += p2) {
-        const int iw = pc - (int)a.pw;
-        dst[pc] = (row_ok && iw >= 0 && iw < a.IW) ? src[(int64_t)iw * a.xs[3]] : 0.0f;
+      const bool row_ok = plane0 + pl < d.planes && ih >= 0 && ih < IH;
+      const float *src = a.x + n * a.xs[0] + ch * a.xs[1] + ih * a.xs[2];
+      float *dst = patch + row * d.pitch;
+      if (d.vec) {
+        if (row_ok) {
+          for (int u = u0; u < units; u += p2) {
+            const float4 t = *reinterpret_cast<const float4 *>(src + 4 * u);
+            float *q = dst + pw + 4 * u;
+            q[0] = t.x; q[1] = t.y; q[2] = t.z; q[3] = t.w;
+          }
+          for (int c = u0; c < pw; c += p2) dst[c] = 0.0f;
+          for (int c = pw + IW + u0; c < d.PWn; c += p2) dst[c] = 0.0f;
+        } else {
+          for (int c = u0; c < d.PWn; c += p2) dst[c] = 0.0f;
+        }
+      } else {
+        for (int c = u0; c < d.PWn; c += p2)
+          dst[c] = (row_ok && c >= pw && c - pw < IW) ? src[c - pw] : 0.0f;
       }
+      pr += step;
+      while (pr >= d.PH) { pr -= d.PH; ++pl; if (++ch == C) { ch = 0; ++n; } }
     }
   }
   __syncthreads();
-  // ---- compute: thread -> (plane, output row, strip of four outputs)
-  const int per_plane = d.TH * d.SW;
-  const int pl = tid / per_plane, rem = tid - pl * per_plane;
-  const int r = rem / d.SW, j = rem - r * d.SW;
-  const int64_t plane = plane0 + pl;
-  const int oh = oh0 + r, ow0 = j * 4;
-  if (pl >= d.PP || plane >= d.planes || oh >= a.OH) return;
-  constexpr int IN_W = 3 * S + KW;            // inputs a strip of four outputs reads per row
-  constexpr int IN_V = (IN_W + 3) / 4;        // ... as 16-byte loads
+  // ---- compute: thread -> (plane, thread row, strip): RT output rows x 4 output columns
+  const int per_plane = d.TR * d.SW;
+  const int pl = d.PP == 1 ? 0 : tid / per_plane, rem = tid - pl * per_plane;
+  const int tr = rem / d.SW, j = rem - tr * d.SW;
+  const int oh = oh0 + tr * RT, ow0 = j * 4;
+  if (pl >= d.PP || tr >= d.TR || plane0 + pl >= d.planes || oh >= (int)a.OH) return;
+  constexpr int IN_V = (3 * S + KW + 3) / 4;   // 16-byte loads per input row of the micro-tile
+  constexpr int ROWS = (RT - 1) * S + KH;      // input rows of the micro-tile
   float w[KH * KW];
   const float *wp = wts + pl * (KH * KW + 1);
 #pragma unroll
   for (int k = 0; k < KH * KW; ++k) w[k] = wp[k];
   const float bias = wp[KH * KW];
-  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // window first, bias last: the reference's order
-  const float *prow = patch + ((size_t)pl * d.PH + (size_t)r * S) * d.pitch + (size_t)ow0 * S;
+  float acc[RT][4];
 #pragma unroll
-  for (int kh = 0; kh < KH; ++kh) {
+  for (int i = 0; i < RT; ++i)
+#pragma unroll
+    for (int o = 0; o < 4; ++o) acc[i][o] = 0.0f;  // window first, bias last: the reference's order
+  const float *prow = patch + (pl * d.PH + tr * RT * S) * d.pitch + ow0 * S;
+#pragma unroll
+  for (int ir = 0; ir < ROWS; ++ir) {
     float in[IN_V * 4];
 #pragma unroll
     for (int v = 0; v < IN_V; ++v) {
-      const float4 t = *reinterpret_cast<const float4 *>(prow + (size_t)kh * d.pitch + v * 4);
+      const float4 t = *reinterpret_cast<const float4 *>(prow + ir * d.pitch + v * 4);
       in[4 * v] = t.x; in[4 * v + 1] = t.y; in[4 * v + 2] = t.z; in[4 * v + 3] = t.w;
     }
 #pragma unroll
-    for (int kw = 0; kw < KW; ++kw)
+    for (int rr = 0; rr < RT; ++rr) {
+      const int kh = ir - rr * S;  // compile-time after unrolling
+      if (kh >= 0 && kh < KH) {
 #pragma unroll
-      for (int o = 0; o < 4; ++o) acc[o] = fmaf(in[o * S + kw], w[kh * KW + kw], acc[o]);
+        for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+          for (int o = 0; o < 4; ++o) acc[rr][o] = fmaf(in[o * S + kw], w[kh * KW + kw], acc[rr][o]);
+      }
+    }
   }
-  float *yp = a.y + (plane / a.OC) * a.ys[0] + (plane % a.OC) * a.ys[1] + (int64_t)oh * a.ys[2] + (int64_t)ow0 * a.ys[3];
-  if (a.ys[3] == 1 && ow0 + 4 <= a.OW && ((reinterpret_cast<uintptr_t>(yp) & 15) == 0)) {
-    *reinterpret_cast<float4 *>(yp) = make_float4(conv_act(a.act, acc[0] + bias), conv_act(a.act, acc[1] + bias),
-                                                  conv_act(a.act, acc[2] + bias), conv_act(a.act, acc[3] + bias));
-  } else {
-#pragma unroll
-    for (int o = 0; o < 4; ++o)
-      if (ow0 + o < a.OW) yp[(int64_t)o * a.ys[3]] = conv_act(a.act, acc[o] + bias);
+  int n = n0, ch = c0 + pl;
+  while (ch >= C) { ch -= C; ++n; }
+  float *yp = a.y + n * a.ys[0] + ch * a.ys[1] + oh * a.ys[2] + ow0 * a.ys[3];
+  const int valid = (int)a.OW - ow0;
+  const bool vec = a.ys[3] == 1 && valid >= 4 && ((reinterpret_cast<uintptr_t>(yp) & 15) == 0) && (a.ys[2] & 3) == 0;
+  const int rows = min(RT, (int)a.OH - oh);
+  switch (a.act) {  // one dispatch per thread, outside the store loops
+#define FML_DW_ROWS(ACT)                                                                  \
+  _Pragma("unroll") for (int rr = 0; rr < RT; ++rr)                                          \
+    if (rr < rows) dw_store_row<ACT>(yp + rr * a.ys[2], acc[rr], bias, vec, valid, a.ys[3]);
+  case FML_ACT_RELU: FML_DW_ROWS(FML_ACT_RELU) break;
+  case FML_ACT_TANH: FML_DW_ROWS(FML_ACT_TANH) break;
+  case FML_ACT_SIGMOID: FML_DW_ROWS(FML_ACT_SIGMOID) break;
+  case FML_ACT_SILU: FML_DW_ROWS(FML_ACT_SILU) break;
+  default: FML_DW_ROWS(FML_ACT_NONE) break;
+#undef FML_DW_ROWS
   }
 }
 
 // Launches the tiled depthwise kernel when it has a variant for the window and stride; returns
 // false (nothing launched) otherwise.
-template <int KH, int KW, int S>
-static bool launch_depthwise_tiled(const ConvArgs &a, cudaStream_t s, int *status) {
+template <int KH, int KW, int S, int RT>
+static bool launch_depthwise_tiled(const ConvArgs &a, const void *x_base, cudaStream_t s, int *status) {
   DwArgs d;
   d.c = a;
   d.SW = (int)((a.OW + 3) / 4);
-  if (d.SW > 256) return false;
-  const int per_plane = (int)a.OH * d.SW;
-  if (per_plane <= 256) { d.TH = (int)a.OH; d.PP = 256 / per_plane; }
-  else { d.TH = 256 / d.SW; d.PP = 1; }
-  d.planes = a.N * a.OC;
-  if (d.PP > d.planes) d.PP = (int)d.planes;
-  d.PH = (d.TH - 1) * S + KH;
-  // columns a row of strips reads: the last strip starts at (SW - 1) * 4 * S and reads IN_V float4
+  const int RW = (int)((a.OH + RT - 1) / RT);  // thread rows per plane
+  if (d.SW > 256 || a.N * a.OC >= (1ll << 30) || a.IH * a.IW >= (1ll << 30)) return false;
   const int in_v = (3 * S + KW + 3) / 4;
-  d.PWn = (d.SW - 1) * 4 * S + in_v * 4;
+  d.PWn = (d.SW - 1) * 4 * S + in_v * 4;  // the last strip starts at (SW - 1) * 4 * S and reads in_v float4
+  if (d.PWn < (int)(a.pw + a.IW)) d.PWn = (int)(a.pw + a.IW + 3) / 4 * 4;  // the staged row always fits
   d.pitch = d.PWn + 4;  // rows 16 bytes apart modulo the bank cycle
-  d.row_tiles = (int)((a.OH + d.TH - 1) / d.TH);
-  const size_t smem = ((size_t)d.PP * d.PH * d.pitch + (size_t)d.PP * (KH * KW + 1)) * sizeof(float);
-  if (smem > 48 * 1024) return false;
-  const int64_t ctas = (d.planes + d.PP - 1) / d.PP * d.row_tiles;
+  const int per_plane = RW * d.SW;
+  d.row_tiles = 1;
+  if (per_plane <= 256) {
+    d.TR = RW; d.PP = 256 / per_plane;
+  } else {  // bands of equal height
+    const int tr_max = 256 / d.SW;
+    d.row_tiles = (RW + tr_max - 1) / tr_max;
+    d.TR = (RW + d.row_tiles - 1) / d.row_tiles;
+    d.PP = 1;
+  }
+  d.planes = (int)(a.N * a.OC);
+  if (d.PP > d.planes) d.PP = d.planes;
+  auto smem_of = [&]() {
+    d.PH = (d.TR * RT - 1) * S + KH;
+    return ((size_t)d.PP * d.PH * d.pitch + (size_t)d.PP * (KH * KW + 1)) * sizeof(float);
+  };
+  while (smem_of() > 48 * 1024) {  // fewer planes, then shorter bands
+    if (d.PP > 1) { d.PP = (d.PP + 1) / 2; continue; }
+    if (d.TR == 1) return false;
+    d.row_tiles += 1;
+    d.TR = (RW + d.row_tiles - 1) / d.row_tiles;
+  }
+  d.row_tiles = (RW + d.TR - 1) / d.TR;
+  const size_t smem = smem_of();
+  d.vec = (a.IW % 4 == 0) && (a.xs[2] % 4 == 0) && (a.xs[1] % 4 == 0) && (a.xs[0] % 4 == 0) &&
+          ((reinterpret_cast<uintptr_t>(x_base) & 15) == 0) ? 1 : 0;
+  const int64_t ctas = (int64_t)((d.planes + d.PP - 1) / d.PP) * d.row_tiles;
   if (ctas > 0x7fffffff) return false;
-  *status = launch_kernel(conv_depthwise_tiled_kernel<KH, KW, S>, dim3((unsigned)ctas), dim3(256), smem, s, d) == cudaSuccess
+  *status = launch_kernel(conv_depthwise_tiled_kernel<KH, KW, S, RT>, dim3((unsigned)ctas), dim3(256), smem, s, d) == cudaSuccess
                 ? FML_OK : FML_CUDA_ERROR;
   return true;
 }
@@ -350,7 +496,24 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     e.divisor = 1.0f; e.alpha = 1.0f; e.beta = 1.0f; e.act = a.act;
     e.c0 = 1.4142135381698608f; e.c1 = 1.0f; e.c2 = 0.5f;
     e.has_bias = a.bias != nullptr; e.has_res = 0;
-    return skinny_eligible(g) ? launch_gemm_skinny(g, e, s) : launch_gemm_simt(g, e, s);
+    if (skinny_eligible(g)) return launch_gemm_skinny(g, e, s);
+    // more images than the weight-streaming kernel takes: the general product, on tensor cores
+    // when the shapes and alignments allow
+    fml_tensor A, B, Cc, bias_t;
+    memset(&A, 0, sizeof(A)); memset(&B, 0, sizeof(B)); memset(&Cc, 0, sizeof(Cc)); memset(&bias_t, 0, sizeof(bias_t));
+    A.data = const_cast<float *>(g.a); A.dtype = FML_F32; A.rank = 2;
+    A.shape[0] = g.M; A.shape[1] = g.K; A.stride[0] = g.a_sm; A.stride[1] = g.a_sk;
+    B.data = const_cast<float *>(g.b); B.dtype = FML_F32; B.rank = 2;
+    B.shape[0] = g.K; B.shape[1] = g.N; B.stride[0] = g.b_sk; B.stride[1] = g.b_sn;
+    Cc.data = g.c; Cc.dtype = FML_F32; Cc.rank = 2;
+    Cc.shape[0] = g.M; Cc.shape[1] = g.N; Cc.stride[0] = g.c_sm; Cc.stride[1] = g.c_sn;
+    bias_t.data = const_cast<float *>(a.bias); bias_t.dtype = FML_F32; bias_t.rank = 1;
+    bias_t.shape[0] = g.N; bias_t.stride[0] = a.bias_stride;
+    fml_gemm_params gp;
+    fml_gemm_default_params(&gp);
+    gp.precision = p->precision;
+    gp.act = a.act;
+    return fml_gemm(&A, &B, &Cc, a.bias ? &bias_t : nullptr, nullptr, &gp, stream);
   }
   if (group == 1 && nd == 2 && conv_tc_eligible(x, w, y, p)) return launch_conv_tc(x, w, bias, y, p, s);
   if (group == 1 && a.KH == 1 && a.KW == 1 && a.ph == 0 && a.pw == 0 && a.sh == 1 && a.sw == 1 && a.ws[1] == 1 &&
@@ -378,6 +541,15 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     const int st = fml_gemm(&A, &B, &C, a.bias ? &bias_t : nullptr, nullptr, &gp, stream);
     if (st != FML_MISALIGNED) return st;  // a forced tensor-core precision on unaligned planes: CUDA cores below
   }
+  if (group == 1 && a.IC * a.KH * a.KW <= 64 && a.IC * a.IH * a.IW < (1ll << 31) / 4 && (a.OC + 31) / 32 <= 65535 &&
+      (M + 127) / 128 <= 0x7fffffff) {
+    DirectArgs d;
+    d.c = a; d.K = (int)(a.IC * a.KH * a.KW); d.M = M;
+    const dim3 grid((unsigned)((M + 127) / 128), (unsigned)((a.OC + 31) / 32));
+    const size_t smem = ((size_t)d.K * 32 + 32) * sizeof(float) + (size_t)d.K * 3 * sizeof(int);
+    FML_LAUNCH((conv_direct_small_kernel<32>), grid, 128, smem, s, d);
+    return FML_OK;
+  }
   if (group == 1) {
     FML_REQUIRE((M + CB - 1) / CB <= 65535 * 32768ll, FML_UNSUPPORTED, "fml_conv: too many output pixels");
     dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));
@@ -389,13 +561,13 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
       bool done = false;
       const int key = (int)(a.KH * 100 + a.KW * 10 + a.sh);
       switch (key) {
-      case 331: done = launch_depthwise_tiled<3, 3, 1>(a, s, &st); break;
-      case 332: done = launch_depthwise_tiled<3, 3, 2>(a, s, &st); break;
-      case 551: done = launch_depthwise_tiled<5, 5, 1>(a, s, &st); break;
-      case 552: done = launch_depthwise_tiled<5, 5, 2>(a, s, &st); break;
-      case 191: done = launch_depthwise_tiled<1, 9, 1>(a, s, &st); break;
-      case 131: done = launch_depthwise_tiled<1, 3, 1>(a, s, &st); break;
-      case 771: done = launch_depthwise_tiled<7, 7, 1>(a, s, &st); break;
+      case 331: done = launch_depthwise_tiled<3, 3, 1, 4>(a, a.x, s, &st); break;
+      case 332: done = launch_depthwise_tiled<3, 3, 2, 4>(a, a.x, s, &st); break;
+      case 551: done = launch_depthwise_tiled<5, 5, 1, 4>(a, a.x, s, &st); break;
+      case 552: done = launch_depthwise_tiled<5, 5, 2, 4>(a, a.x, s, &st); break;
+      case 191: done = launch_depthwise_tiled<1, 9, 1, 1>(a, a.x, s, &st); break;
+      case 131: done = launch_depthwise_tiled<1, 3, 1, 1>(a, a.x, s, &st); break;
+      case 771: done = launch_depthwise_tiled<7, 7, 1, 4>(a, a.x, s, &st); break;
       default: break;
       }
       if (done) {

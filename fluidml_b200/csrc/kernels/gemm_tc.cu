@@ -85,6 +85,7 @@ __device__ __forceinline__ float act_op(const GemmEpilogue &e, float v) {
   if (ACT == FML_ACT_RELU) return fmaxf(v, 0.0f);
   if (ACT == FML_ACT_TANH) return tanhf(v);
   if (ACT == FML_ACT_SIGMOID) return 1.0f / (1.0f + expf(-v));
+  if (ACT == FML_ACT_SILU) return v / (1.0f + expf(-v));
   return v;
 }
 
@@ -713,14 +714,15 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
 #define FML_TC_ROW(T, M, A)                                                               \
   gemm_tc_kernel<T, M, FML_ACT_NONE, A>, gemm_tc_kernel<T, M, FML_ACT_GELU_ERF, A>,       \
   gemm_tc_kernel<T, M, FML_ACT_RELU, A>, gemm_tc_kernel<T, M, FML_ACT_TANH, A>,           \
-  gemm_tc_kernel<T, M, FML_ACT_SIGMOID, A>
-  static const KernelFn kernels[30] = {FML_TC_ROW(false, false, false), FML_TC_ROW(false, true, false),
+  gemm_tc_kernel<T, M, FML_ACT_SIGMOID, A>, gemm_tc_kernel<T, M, FML_ACT_SILU, A>
+  static const KernelFn kernels[36] = {FML_TC_ROW(false, false, false), FML_TC_ROW(false, true, false),
                                        FML_TC_ROW(true, false, false),  FML_TC_ROW(true, true, false),
                                        FML_TC_ROW(true, false, true),   FML_TC_ROW(true, true, true)};
 #undef FML_TC_ROW
-  const int act = (e.act >= 0 && e.act <= FML_ACT_SIGMOID) ? e.act : 0;
+  FML_REQUIRE(e.act >= 0 && e.act <= FML_ACT_SILU, FML_BAD_ARG, "fml_gemm: unknown activation %d", e.act);
+  const int act = e.act;
   const int row = plan.a_tmem ? 4 + (plan.b_mn_major ? 1 : 0) : (plan.three_pass ? 2 : 0) + (plan.b_mn_major ? 1 : 0);
-  const KernelFn kernel = kernels[row * 5 + act];
+  const KernelFn kernel = kernels[row * 6 + act];
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));

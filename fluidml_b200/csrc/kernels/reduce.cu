@@ -256,6 +256,39 @@ __global__ void __launch_bounds__(256) reduce_mean_contig_kernel(ReduceArgs a, f
   }
 }
 
+// The same contiguous run, one WARP per output: for runs of a few thousand floats or fewer (the
+// squeeze-and-excite pools over 56 x 56 ... 7 x 7 planes) a CTA per output spends more on its
+// set-up and barrier than on the run.  Lanes take 16-byte pieces when the run is aligned and a
+// multiple of four long; the sum order is fixed (lane-strided, then the shuffle tree).
+__global__ void __launch_bounds__(256) reduce_mean_rows_kernel(ReduceArgs a, float *out, const float *in) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int64_t o = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (o >= a.keep.total) return;
+  int64_t off[2];
+  offsets_of(a.keep, o, off);
+  const float *src = in + off[1];
+  const int count = (int)a.count;
+  float s = 0.0f;
+  if ((count & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    const int n4 = count >> 2;
+    float t0 = 0.0f, t1 = 0.0f;  // two chains: the loads of consecutive pieces overlap
+    int i = lane;
+    for (; i + 32 < n4; i += 64) {
+      const float4 u = s4[i], v = s4[i + 32];
+      t0 += (u.x + u.y) + (u.z + u.w);
+      t1 += (v.x + v.y) + (v.z + v.w);
+    }
+    if (i < n4) { const float4 u = s4[i]; t0 += (u.x + u.y) + (u.z + u.w); }
+    s = t0 + t1;
+  } else {
+    for (int i = lane; i < count; i += 32) s += src[i];
+  }
+  s = warp_sum(s);
+  if (lane == 0) out[off[0]] = s / (float)a.count;
+}
+
 __global__ void cumsum_kernel(RowArgs a, int64_t *out, const int64_t *in) {
   pdl_prologue();
   const int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -434,6 +467,11 @@ extern "C" int fml_reduce_mean(const fml_tensor *in, const fml_tensor *out, cons
       if (a.rshape[d] != 1 && a.rstride[d] != expect) contig = false;
       expect *= a.rshape[d];
     }
+  }
+  if (contig && a.count < 8192 && a.keep.total * 32 < (1ll << 40)) {
+    FML_LAUNCH((reduce_mean_rows_kernel), (unsigned)((a.keep.total * 32 + 255) / 256), 256, 0, as_stream(stream), a,
+               (float *)out->data, (const float *)in->data);
+    return FML_OK;
   }
   if (contig && a.count >= 256 && a.keep.total <= 0x7fffffff) {
     FML_LAUNCH((reduce_mean_contig_kernel), (unsigned)a.keep.total, 256, 0, as_stream(stream), a, (float *)out->data,

@@ -231,7 +231,7 @@ typedef enum fml_gemm_act {
   FML_ACT_RELU = 2,
   FML_ACT_TANH = 3,
   FML_ACT_SIGMOID = 4,
-  FML_ACT_SILU = 5 /* x * sigmoid(x); fml_conv only */
+  FML_ACT_SILU = 5 /* x * sigmoid(x) */
 } fml_gemm_act;
 
 typedef enum fml_gemm_precision {

@@ -315,6 +315,10 @@ def test_reduce_mean_cumsum():
     dict(x=(1, 12, 20, 20), w=(12, 1, 5, 5), pads=(2, 2), strides=(2, 2), dil=(1, 1), group=12),
     dict(x=(2, 24, 64), w=(24, 1, 9), pads=(4,), strides=(1,), dil=(1,), group=24),
     dict(x=(1, 4, 12, 12), w=(6, 4, 3, 3), pads=(2, 2), strides=(1, 1), dil=(2, 2), group=1),
+    # short reductions (IC * KH * KW <= 64): the direct kernel, strided / dilated / 1-D / ragged channel block
+    dict(x=(2, 3, 33, 37), w=(32, 3, 3, 3), pads=(1, 1), strides=(2, 2), dil=(1, 1), group=1),
+    dict(x=(1, 2, 16, 16), w=(40, 2, 5, 5), pads=(2, 2), strides=(1, 1), dil=(1, 1), group=1),
+    dict(x=(2, 4, 50), w=(5, 4, 7), pads=(3,), strides=(3,), dil=(2,), group=1),
 ])
 def test_conv(cfg):
     x, w = rnd(*cfg["x"]), rnd(*cfg["w"]) * 0.2
