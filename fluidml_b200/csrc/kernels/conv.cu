@@ -406,6 +406,52 @@ static bool launch_depthwise_tiled(const ConvArgs &a, const void *x_base, cudaSt
   return true;
 }
 
+// Depthwise convolution over channel-innermost operands (x and y with channel stride 1: what a
+// [batch, length, channels] activation looks like through the transposed view a Conv node reads
+// it by).  Threads run along the channels, so every tap is one coalesced load and the weights of
+// a thread's channels stay in L1; V channels per thread (4 when the channel count and the
+// addresses allow 16-byte accesses).
+template <int V>
+__global__ void __launch_bounds__(256) conv_depthwise_cl_kernel(const ConvArgs a) {
+  pdl_prologue();
+  const unsigned CV = (unsigned)(a.OC / V), OW = (unsigned)a.OW, OH = (unsigned)a.OH;
+  const unsigned total = (unsigned)a.N * OH * OW * CV;
+  for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+    const unsigned pix = e / CV, c = (e - pix * CV) * V;
+    const unsigned row = pix / OW, ow = pix - row * OW;
+    const unsigned n = row / OH, oh = row - n * OH;
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+    const float *xn = a.x + n * a.xs[0] + c;
+    for (int kh = 0; kh < (int)a.KH; ++kh) {
+      const int ih = (int)oh * (int)a.sh - (int)a.ph + kh * (int)a.dh;
+      if (ih < 0 || ih >= (int)a.IH) continue;
+      for (int kw = 0; kw < (int)a.KW; ++kw) {
+        const int iw = (int)ow * (int)a.sw - (int)a.pw + kw * (int)a.dw;
+        if (iw < 0 || iw >= (int)a.IW) continue;
+        const float *xp = xn + ih * a.xs[2] + iw * a.xs[3];
+        const float *wp = a.w + c * a.ws[0] + kh * a.ws[2] + kw * a.ws[3];
+        float xv[V];
+        if (V == 4) {
+          const float4 t = *reinterpret_cast<const float4 *>(xp);
+          xv[0] = t.x; xv[1] = t.y; xv[2] = t.z; xv[3] = t.w;
+        } else {
+          xv[0] = xp[0];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(xv[v], __ldg(wp + v * a.ws[0]), acc[v]);
+      }
+    }
+    float r[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) r[v] = conv_act(a.act, acc[v] + (a.bias ? __ldg(a.bias + (c + v) * a.bias_stride) : 0.0f));
+    float *yp = a.y + n * a.ys[0] + oh * a.ys[2] + ow * a.ys[3] + c;
+    if (V == 4) *reinterpret_cast<float4 *>(yp) = make_float4(r[0], r[1], r[2], r[3]);
+    else yp[0] = r[0];
+  }
+}
+
 struct PoolArgs {
   int64_t N, C, OH, OW, KH, KW, sh, sw;
   int64_t xs[4], ys[4];
@@ -556,6 +602,18 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     FML_REQUIRE(grid.y <= 65535, FML_UNSUPPORTED, "fml_conv: too many output pixels for one launch");
     FML_LAUNCH((conv_igemm_kernel), grid, 256, 0, s, a);
   } else {
+    if (a.xs[1] == 1 && a.ys[1] == 1 && a.OC > 1 && M * a.OC < (1ll << 31)) {  // channel-innermost operands
+      bool narrow = true;  // 32-bit offsets
+      for (int i = 0; i < 4; ++i) narrow = narrow && a.xs[i] >= 0 && a.ys[i] >= 0;
+      narrow = narrow && a.N * a.xs[0] < (1ll << 31) && a.N * a.ys[0] < (1ll << 31);
+      if (narrow) {
+        const bool v4 = a.OC % 4 == 0 && aligned16(a.x) && aligned16(a.y) && a.xs[0] % 4 == 0 && a.xs[2] % 4 == 0 &&
+                        a.xs[3] % 4 == 0 && a.ys[0] % 4 == 0 && a.ys[2] % 4 == 0 && a.ys[3] % 4 == 0;
+        if (v4) FML_LAUNCH((conv_depthwise_cl_kernel<4>), grid_for(M * a.OC / 4, 256), 256, 0, s, a);
+        else FML_LAUNCH((conv_depthwise_cl_kernel<1>), grid_for(M * a.OC, 256), 256, 0, s, a);
+        return FML_OK;
+      }
+    }
     if (a.dh == 1 && a.dw == 1 && a.sh == a.sw && (a.sh == 1 || a.sh == 2) && a.xs[3] == 1) {
       int st = FML_OK;
       bool done = false;

@@ -449,32 +449,53 @@ extern "C" int fml_embedding(const fml_tensor *table, const fml_tensor *ids, con
   return FML_OK;
 }
 
+namespace fml {
+namespace {
+struct PadArgs {
+  int rank;
+  int64_t oshape[kMaxDims], ostride[kMaxDims], istride[kMaxDims], begin[kMaxDims], ishape[kMaxDims];
+  int64_t total;
+};
+// One pass over the output: an element inside the window of the input copies it, the rest is
+// zero.  (A fill followed by a copy of the interior would be two launches and write the interior
+// twice.)
+__global__ void pad_kernel(PadArgs a, float *out, const float *in) {
+  pdl_prologue();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < a.total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t lin = i, oo = 0, io = 0;
+    bool inside = true;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t q = lin / a.oshape[d], c = lin - q * a.oshape[d];
+      lin = q;
+      oo += c * a.ostride[d];
+      const int64_t ci = c - a.begin[d];
+      inside = inside && ci >= 0 && ci < a.ishape[d];
+      io += ci * a.istride[d];
+    }
+    out[oo] = inside ? in[io] : 0.0f;
+  }
+}
+}  // namespace
+}  // namespace fml
+
 extern "C" int fml_pad(const fml_tensor *in, const fml_tensor *out, const int64_t *pads_begin,
                        void *stream) {
   FML_REQUIRE(valid_tensor(in) && valid_tensor(out) && pads_begin, FML_BAD_ARG, "fml_pad: bad argument");
   FML_REQUIRE(in->rank == out->rank && in->dtype == out->dtype && in->dtype == FML_F32, FML_BAD_ARG,
               "fml_pad: rank/dtype mismatch (fp32 only)");
-  // zero the whole destination through a strided fill, then copy the interior
-  fml_tensor zero = *out;
-  static float *zero_word[64] = {nullptr};
-  int dev = 0;
-  FML_CUDA(cudaGetDevice(&dev));
-  if (!zero_word[dev]) {
-    FML_CUDA(cudaMalloc(&zero_word[dev], sizeof(float)));
-    FML_CUDA(cudaMemset(zero_word[dev], 0, sizeof(float)));
-  }
-  zero.data = zero_word[dev];
-  for (int i = 0; i < zero.rank; ++i) zero.stride[i] = 0;
-  int st = fml_copy_strided(&zero, out, stream);
-  if (st != FML_OK) return st;
-  fml_tensor interior = *out;
-  int64_t off = 0;
+  fml::PadArgs a;
+  a.rank = out->rank;
+  a.total = 1;
   for (int i = 0; i < out->rank; ++i) {
     FML_REQUIRE(pads_begin[i] >= 0 && pads_begin[i] + in->shape[i] <= out->shape[i], FML_BAD_ARG,
                 "fml_pad: pads do not fit the output");
-    off += pads_begin[i] * out->stride[i];
-    interior.shape[i] = in->shape[i];
+    a.oshape[i] = out->shape[i]; a.ostride[i] = out->stride[i];
+    a.ishape[i] = in->shape[i]; a.istride[i] = in->stride[i];
+    a.begin[i] = pads_begin[i];
+    a.total *= out->shape[i];
   }
-  interior.data = (float *)out->data + off;
-  return fml_copy_strided(in, &interior, stream);
+  if (a.total == 0) return FML_OK;
+  FML_LAUNCH((fml::pad_kernel), fml::grid_for(a.total, 256), 256, 0, fml::as_stream(stream), a, (float *)out->data,
+             (const float *)in->data);
+  return FML_OK;
 }

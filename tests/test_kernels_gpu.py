@@ -370,6 +370,26 @@ def test_depthwise_conv_1d_window_9():
     assert relerr(out.numpy(), ref) <= 1e-5
 
 
+@pytest.mark.parametrize("shape,k,stride,pad,act", [((8, 96, 128), 9, 1, 4, 0), ((2, 37, 50), 3, 2, 1, 5),
+                                                    ((2, 16, 9, 11), 3, 1, 1, 0)])
+def test_depthwise_conv_channel_innermost(shape, k, stride, pad, act):
+    """Depthwise convolution whose operands are transposed views of channel-last buffers (how ConvBERT's
+    span convolution reads a [batch, length, channels] activation)."""
+    nd = len(shape) - 2
+    c = shape[1]
+    x, w, b = rnd(*shape), rnd(c, 1, *([k] * nd)) * 0.3, rnd(c)
+    osp = [(d + 2 * pad - k) // stride + 1 for d in shape[2:]]
+    oshape = (shape[0], c, *osp)
+    ref = orc.conv(x, w, b, np.empty(oshape, np.float32), (pad,) * nd, (stride,) * nd, (1,) * nd, c, acc64=True)
+    if act == cabi.ACT_SILU:
+        ref = ref / (1.0 + np.exp(-ref.astype(np.float64)))
+    cl = [0, nd + 1] + list(range(1, nd + 1))  # channel dim physically innermost
+    xd, out = DT.from_numpy(x, cl), DT(oshape, np.float32, cl)
+    assert xd.strides[1] == 1 and out.strides[1] == 1
+    cabi.conv(xd, DT.from_numpy(w), DT.from_numpy(b), out, (pad,) * nd, (stride,) * nd, (1,) * nd, c, act=act)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
 @pytest.mark.parametrize("mode,shape,k,s", [(0, (1, 64, 32, 32), (2, 2), (2, 2)), (1, (2, 1280, 7, 7), (7, 7), (1, 1)),
                                             (0, (1, 3, 9, 11), (3, 2), (2, 3))])
 def test_pool(mode, shape, k, s):
