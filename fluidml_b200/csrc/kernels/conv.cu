@@ -452,6 +452,35 @@ __global__ void __launch_bounds__(256) conv_depthwise_cl_kernel(const ConvArgs a
   }
 }
 
+// 1-D depthwise convolution, unit stride, reading a channel-innermost input ([batch, length,
+// channels] through a transposed view) and writing a length-innermost output: a 32-channel x
+// 32-position tile goes through shared memory, loaded with lanes along the channels and consumed
+// with lanes along the positions, so both sides are coalesced (pitch 33: conflict-free).
+constexpr int kDwT = 32, kDwSpanMax = 64;
+__global__ void __launch_bounds__(256) conv_depthwise_1d_transposing_kernel(const ConvArgs a) {
+  __shared__ float tile[kDwT + kDwSpanMax][kDwT + 1];
+  pdl_prologue();
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int ow0 = (int)blockIdx.x * kDwT, c0 = (int)blockIdx.y * kDwT, n = (int)blockIdx.z;
+  const int span = ((int)a.KW - 1) * (int)a.dw + 1, rows = kDwT + span - 1;
+  const int C = (int)a.OC, IW = (int)a.IW, OW = (int)a.OW;
+  for (int r = ty; r < rows; r += 8) {
+    const int iw = ow0 - (int)a.pw + r, c = c0 + tx;
+    tile[r][tx] = (iw >= 0 && iw < IW && c < C) ? a.x[n * a.xs[0] + iw * a.xs[3] + c] : 0.0f;
+  }
+  __syncthreads();
+  const int ow = ow0 + tx;
+  for (int cc = ty; cc < kDwT; cc += 8) {
+    const int c = c0 + cc;
+    if (c >= C) break;
+    float acc = 0.0f;
+    const float *wp = a.w + c * a.ws[0];
+    for (int k = 0; k < (int)a.KW; ++k) acc = fmaf(tile[tx + k * (int)a.dw][cc], __ldg(wp + k * a.ws[3]), acc);
+    if (a.bias) acc += __ldg(a.bias + c * a.bias_stride);
+    if (ow < OW) a.y[n * a.ys[0] + c * a.ys[1] + ow * a.ys[3]] = conv_act(a.act, acc);
+  }
+}
+
 struct PoolArgs {
   int64_t N, C, OH, OW, KH, KW, sh, sw;
   int64_t xs[4], ys[4];
@@ -476,6 +505,30 @@ __global__ void pool2d_kernel(PoolArgs a) {
       }
     if (a.mode) r = r / (float)(a.KH * a.KW);
     a.y[n * a.ys[0] + c * a.ys[1] + oh * a.ys[2] + ow * a.ys[3]] = r;
+  }
+}
+
+// 2 x 2 / stride 2 pooling over dense NCHW planes whose rows are a multiple of 4 long (every
+// pooling layer of VGG-16): a thread reads 16 bytes from each of the two input rows and writes two
+// outputs; 32-bit index arithmetic with two divisions per thread.
+__global__ void __launch_bounds__(256) pool2x2_kernel(const float *__restrict__ x, float *__restrict__ y, unsigned planes,
+                                                     unsigned OH, unsigned OW2, unsigned IW, unsigned in_plane, int mode) {
+  pdl_prologue();
+  const unsigned total = planes * OH * OW2;
+  for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+    const unsigned row = e / OW2, j = e - row * OW2;
+    const unsigned plane = row / OH, oh = row - plane * OH;
+    const float *src = x + (size_t)plane * in_plane + (size_t)(2 * oh) * IW + 4 * j;
+    const float4 r0 = *reinterpret_cast<const float4 *>(src), r1 = *reinterpret_cast<const float4 *>(src + IW);
+    float2 o;
+    if (mode) {
+      o.x = (((r0.x + r0.y) + r1.x) + r1.y) / 4.0f;  // the window's elements in row-major order
+      o.y = (((r0.z + r0.w) + r1.z) + r1.w) / 4.0f;
+    } else {
+      o.x = fmaxf(fmaxf(r0.x, r0.y), fmaxf(r1.x, r1.y));
+      o.y = fmaxf(fmaxf(r0.z, r0.w), fmaxf(r1.z, r1.w));
+    }
+    *reinterpret_cast<float2 *>(y + (size_t)row * (2 * OW2) + 2 * j) = o;
   }
 }
 
@@ -614,6 +667,12 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
         return FML_OK;
       }
     }
+    if (a.IH == 1 && a.OH == 1 && a.KH == 1 && a.sw == 1 && a.xs[1] == 1 && a.ys[3] == 1 && a.OC > 1 &&
+        (a.KW - 1) * a.dw + 1 <= kDwSpanMax && a.N <= 65535 && (a.OC + kDwT - 1) / kDwT <= 65535) {
+      const dim3 grid((unsigned)((a.OW + kDwT - 1) / kDwT), (unsigned)((a.OC + kDwT - 1) / kDwT), (unsigned)a.N);
+      FML_LAUNCH((conv_depthwise_1d_transposing_kernel), grid, 256, 0, s, a);
+      return FML_OK;
+    }
     if (a.dh == 1 && a.dw == 1 && a.sh == a.sw && (a.sh == 1 || a.sh == 2) && a.xs[3] == 1) {
       int st = FML_OK;
       bool done = false;
@@ -665,6 +724,20 @@ extern "C" int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, co
   a.x = (const float *)x->data; a.y = (float *)y->data; a.mode = mode;
   const int64_t total = a.N * a.C * a.OH * a.OW;
   if (total == 0) return FML_OK;
+  {
+    const int64_t IH = x->shape[2], IW = x->shape[3];
+    const bool dense_in = x->stride[3] == 1 && x->stride[2] == IW && x->stride[1] == IH * IW && x->stride[0] == a.C * IH * IW;
+    const bool dense_out = y->stride[3] == 1 && y->stride[2] == a.OW && y->stride[1] == a.OH * a.OW &&
+                           y->stride[0] == a.C * a.OH * a.OW;
+    if (a.KH == 2 && a.KW == 2 && a.sh == 2 && a.sw == 2 && dense_in && dense_out && IW % 4 == 0 && 2 * a.OW == IW &&
+        (IH * IW) % 4 == 0 && aligned16(x->data) && (reinterpret_cast<uintptr_t>(y->data) & 7) == 0 &&
+        total < (1ll << 31) && a.N * a.C * IH * IW < (1ll << 40)) {
+      FML_LAUNCH((pool2x2_kernel), grid_for(total / 2, 256), 256, 0, as_stream(stream), (const float *)x->data,
+                 (float *)y->data, (unsigned)(a.N * a.C), (unsigned)a.OH, (unsigned)(a.OW / 2), (unsigned)IW,
+                 (unsigned)(IH * IW), mode);
+      return FML_OK;
+    }
+  }
   FML_LAUNCH((pool2d_kernel), grid_for(total, 256), 256, 0, as_stream(stream), a);
   FML_CUDA(cudaGetLastError());
   return FML_OK;

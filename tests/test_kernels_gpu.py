@@ -390,8 +390,23 @@ def test_depthwise_conv_channel_innermost(shape, k, stride, pad, act):
     assert relerr(out.numpy(), ref) <= 1e-5
 
 
+@pytest.mark.parametrize("shape,k,pad,dil", [((8, 96, 128), 9, 4, 1), ((3, 45, 70), 5, 4, 2), ((1, 7, 33), 3, 0, 1)])
+def test_depthwise_conv_1d_channel_innermost_input_only(shape, k, pad, dil):
+    """The mixed case: the input is a transposed view of a channel-last buffer, the output is in the
+    default layout (the tile goes through shared memory)."""
+    c = shape[1]
+    x, w, b = rnd(*shape), rnd(c, 1, k) * 0.3, rnd(c)
+    ol = shape[2] + 2 * pad - dil * (k - 1)
+    ref = orc.conv(x, w, b, np.empty((shape[0], c, ol), np.float32), (pad,), (1,), (dil,), c, acc64=True)
+    xd, out = DT.from_numpy(x, [0, 2, 1]), DT((shape[0], c, ol), np.float32)
+    assert xd.strides[1] == 1 and out.strides[2] == 1
+    cabi.conv(xd, DT.from_numpy(w), DT.from_numpy(b), out, (pad,), (1,), (dil,), c)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
 @pytest.mark.parametrize("mode,shape,k,s", [(0, (1, 64, 32, 32), (2, 2), (2, 2)), (1, (2, 1280, 7, 7), (7, 7), (1, 1)),
-                                            (0, (1, 3, 9, 11), (3, 2), (2, 3))])
+                                            (0, (1, 3, 9, 11), (3, 2), (2, 3)), (1, (2, 8, 16, 20), (2, 2), (2, 2)),
+                                            (0, (3, 5, 6, 8), (2, 2), (2, 2))])
 def test_pool(mode, shape, k, s):
     x = rnd(*shape)
     oshape = (shape[0], shape[1], (shape[2] - k[0]) // s[0] + 1, (shape[3] - k[1]) // s[1] + 1)
