@@ -209,6 +209,12 @@ def attention(q, kt, v, mask, divisor, out, stream=None):
     check(lib().fml_attention(_ref(q), _ref(kt), _ref(v), _ref(mask), ctypes.c_float(divisor), _ref(out), stream))
 
 
+def attention_uses_tensor_cores(q, kt, v) -> bool:
+    uses = ctypes.c_int()
+    check(lib().fml_attention_uses_tensor_cores(_ref(q), _ref(kt), _ref(v), ctypes.byref(uses)))
+    return bool(uses.value)
+
+
 def attention_supported(s_q, s_k, d, d_v) -> bool:
     f = lib().fml_attention_supported
     f.argtypes = [ctypes.c_int64] * 4

@@ -303,11 +303,12 @@ bool FuseAttention(Rewriter &rw, const NodePtr &qk) {
   for (size_t i = 0; i + 2 < rank; ++i)
     if (qs[i] != ks[i] || qs[i] != vs[i]) return false;  // no batch broadcasting between the operands
   if (!fml_attention_supported(qs[rank - 2], ks[rank - 1], qs[rank - 1], vs[rank - 1])) return false;
-  // The fused kernel computes in fp32 FMA (about 10 TFLOP/s): it wins while the three launches it
-  // replaces are latency-bound; large score matrices are faster as tensor-core products.
+  // The CUDA-core fused kernel computes in fp32 FMA (about 10 TFLOP/s): it wins while the three
+  // launches it replaces are latency-bound; larger blocks are fused only when the tensor-core
+  // attention kernel takes their head sizes (otherwise the score products are faster as GEMMs).
   double flops = 4.0 * (double)qs[rank - 2] * (double)ks[rank - 1] * (double)qs[rank - 1];
   for (size_t i = 0; i + 2 < rank; ++i) flops *= (double)qs[i];
-  if (flops > 256e6) return false;
+  if (flops > 256e6 && !fml_attention_on_tensor_cores(qs[rank - 2], ks[rank - 1], qs[rank - 1], vs[rank - 1])) return false;
   qk->kind = Kind::FusedAttention;
   qk->inputs = {q, kt, v};
   qk->divisor = sm->kind == Kind::FusedSoftmax ? sm->divisor : 1.0f;

@@ -479,6 +479,22 @@ bool as4(const fml_tensor *t, int64_t shape[4], int64_t stride[4]) {
 
 using namespace fml;
 
+namespace fml {  // attention_tc.cu
+bool attention_tc_shape_ok(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v);
+bool attention_tc_eligible(int64_t nb1, int64_t nb0, int64_t Sq, int64_t Sk, int64_t D, int64_t Dv, const int64_t *q_s,
+                           const int64_t *k_s, const int64_t *v_s, const void *q, const void *k, const void *v);
+int launch_attention_tc(int64_t nb1, int64_t nb0, int64_t Sq, int64_t Sk, int64_t D, int64_t Dv, const float *q,
+                        const int64_t *q_s, const float *k, const int64_t *k_s, const float *v, const int64_t *v_s,
+                        const float *mask, const int64_t *m_s, float divisor, float *out, const int64_t *o_s,
+                        cudaStream_t s);
+}  // namespace fml
+
+// 1 when the tensor-core kernel (attention_tc.cu) takes blocks of these head sizes: such blocks are
+// worth fusing whatever their size, the CUDA-core kernel only while the block is small.
+extern "C" int fml_attention_on_tensor_cores(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v) {
+  return attention_tc_shape_ok(s_q, s_k, d, d_v) ? 1 : 0;
+}
+
 extern "C" int fml_attention_supported(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v) {
   // any number of keys: those that do not fit in shared memory at once stream through it
   return s_q >= 1 && s_k >= 1 && d >= 4 && d_v >= 4 && d <= 128 && d_v <= 128 && (d & 3) == 0 && (d_v & 3) == 0 &&
@@ -520,6 +536,9 @@ extern "C" int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fm
   a.mask = mask ? (const float *)mask->data : nullptr;
   a.out = (float *)out->data;
   a.divisor = divisor;
+  if (attention_tc_eligible(a.nb1, a.nb0, a.Sq, a.Sk, a.D, a.Dv, a.q_s, a.k_s, a.v_s, a.q, a.k, a.v))
+    return launch_attention_tc(a.nb1, a.nb0, a.Sq, a.Sk, a.D, a.Dv, a.q, a.q_s, a.k, a.k_s, a.v, a.v_s, a.mask, a.m_s,
+                               divisor, a.out, a.o_s, as_stream(stream));
   const bool whole = attn_smem_bytes(a.Sk, a.D, a.Dv) <= attn_flash_smem_bytes(a.D, a.Dv) ||
                      attn_flash_smem_bytes(a.D, a.Dv) > kSmemLimit;  // K and V of a head fit at once
   const size_t smem = whole ? attn_smem_bytes(a.Sk, a.D, a.Dv) : attn_flash_smem_bytes(a.D, a.Dv);
@@ -534,5 +553,17 @@ extern "C" int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fm
   const dim3 grid((unsigned)((a.Sq + kRows - 1) / kRows), (unsigned)(a.nb0 * a.nb1));
   if (whole) FML_LAUNCH((attention_kernel), grid, kThreads, smem, as_stream(stream), a);
   else FML_LAUNCH((attention_flash_kernel), grid, kThreads, smem, as_stream(stream), a);
+  return FML_OK;
+}
+
+// Whether fml_attention would run these operands on the tensor cores (tests and planners).
+extern "C" int fml_attention_uses_tensor_cores(const fml_tensor *q, const fml_tensor *kt, const fml_tensor *v, int *uses) {
+  FML_REQUIRE(q && kt && v && uses, FML_BAD_ARG, "fml_attention_uses_tensor_cores: null argument");
+  AttnArgs a;
+  int64_t qs[4], ks[4], vs[4];
+  *uses = 0;
+  if (q->dtype != FML_F32 || kt->dtype != FML_F32 || v->dtype != FML_F32) return FML_OK;
+  if (!as4(q, qs, a.q_s) || !as4(kt, ks, a.k_s) || !as4(v, vs, a.v_s)) return FML_OK;
+  *uses = attention_tc_eligible(qs[0], qs[1], qs[2], ks[3], qs[3], vs[3], a.q_s, a.k_s, a.v_s, q->data, kt->data, v->data) ? 1 : 0;
   return FML_OK;
 }

@@ -198,6 +198,12 @@ int fml_softmax(const fml_tensor *in, const fml_tensor *mask, float divisor,
  * tells whether a shape is taken (head sizes multiples of 4 up to 128); fml_attention returns
  * FML_UNSUPPORTED otherwise. */
 int fml_attention_supported(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v);
+/* 1 when blocks of these head sizes run on the tensor cores (tcgen05, scores in tensor memory,
+ * 3xTF32) once they are large enough (about 200 Mflop) and their operands are 16-byte aligned
+ * views with unit innermost stride; smaller or unaligned blocks take the CUDA-core kernel. */
+int fml_attention_on_tensor_cores(int64_t s_q, int64_t s_k, int64_t d, int64_t d_v);
+/* The same question for concrete operands (shapes, strides, alignment, size). */
+int fml_attention_uses_tensor_cores(const fml_tensor *q, const fml_tensor *kt, const fml_tensor *v, int *uses);
 int fml_attention(const fml_tensor *q, const fml_tensor *kt, const fml_tensor *v,
                   const fml_tensor *mask, float divisor, const fml_tensor *out, void *stream);
 

@@ -103,3 +103,57 @@ def test_attention_causal_mask(s):
     cabi.attention(DT.from_numpy(q), DT.from_numpy(kt), DT.from_numpy(v), DT.from_numpy(mask), 8.0, out)
     cabi.check_device()
     assert relerr(out.numpy(), oracle_attention(q, kt, v, mask, 8.0)) <= TOL
+
+
+# ------------------------------------------------------------------ tensor-core kernel
+def _as_kt(k):
+    """K [.., S_k, D] on the device, handed over as the K^T view [.., D, S_k] (D stride 1)."""
+    t = DT.from_numpy(k)
+    shape = (*k.shape[:-2], k.shape[-1], k.shape[-2])
+    strides = list(t.strides)
+    strides[-1], strides[-2] = strides[-2], strides[-1]
+    return t.view(shape, strides, 0)
+
+
+@pytest.mark.parametrize("cfg", [  # batch, heads, S_q, S_k, D, D_v, mask kind
+    (2, 4, 512, 512, 64, 64, "causal"), (1, 8, 300, 333, 64, 64, "key"), (4, 8, 256, 384, 32, 64, None),
+    (3, 16, 128, 640, 64, 32, "key"), (1, 16, 1024, 130, 64, 64, "causal"),
+])
+def test_attention_on_tensor_cores(cfg):
+    """The tcgen05 kernel (3xTF32, scores in tensor memory, streaming softmax over blocks of 128
+    keys) against the oracle's unfused chain: ragged sizes, key and causal masks, both head sizes."""
+    B, H, sq, sk, d, dv, kind = cfg
+    q, k, v = rnd(B, H, sq, d), rnd(B, H, sk, d), rnd(B, H, sk, dv)
+    mask = None
+    if kind == "key":
+        mask = np.where(RNG.random((B, 1, 1, sk)) < 0.2, -10000.0, 0.0).astype(np.float32)
+    elif kind == "causal":  # what the folded Where leaves: 0 where allowed, the lowest float elsewhere
+        mask = np.where(np.tril(np.ones((sq, sk), np.bool_), k=sk - sq), 0.0, np.finfo(np.float32).min)
+        mask = mask.astype(np.float32).reshape(1, 1, sq, sk)
+    qd, ktd, vd = DT.from_numpy(q), _as_kt(k), DT.from_numpy(v)
+    assert cabi.attention_uses_tensor_cores(qd, ktd, vd)
+    out = DT((B, H, sq, dv), np.float32)
+    cabi.attention(qd, ktd, vd, DT.from_numpy(mask) if mask is not None else None, float(np.sqrt(d)), out)
+    cabi.check_device()
+    ref = oracle_attention(q, np.ascontiguousarray(np.swapaxes(k, -1, -2)), v, mask, np.sqrt(d))
+    assert relerr(out.numpy(), ref) <= TOL
+
+
+def test_attention_on_tensor_cores_from_merged_projection_views():
+    """Batch 8 of BERT-base: Q, K^T, V as views of the merged [B*S, 3H] projection, context written
+    head-interleaved into [B*S, H] -- the call the executor makes."""
+    B, S, H, nh, hd = 8, 128, 768, 12, 64
+    qkv = rnd(B * S, 3 * H)
+    src = DT.from_numpy(qkv)
+    q = src.view((B, nh, S, hd), [S * 3 * H, hd, 3 * H, 1], 0)
+    k_t = src.view((B, nh, hd, S), [S * 3 * H, hd, 1, 3 * H], H)
+    v = src.view((B, nh, S, hd), [S * 3 * H, hd, 3 * H, 1], 2 * H)
+    assert cabi.attention_uses_tensor_cores(q, k_t, v)
+    mask = np.where(RNG.random((B, 1, 1, S)) < 0.1, -10000.0, 0.0).astype(np.float32)
+    ctx = DT((B * S, H), np.float32)
+    cabi.attention(q, k_t, v, DT.from_numpy(mask), 8.0, ctx.view((B, nh, S, hd), [S * H, hd, H, 1], 0))
+    cabi.check_device()
+    x = qkv.reshape(B, S, 3, nh, hd)
+    qn, kn, vn = (np.ascontiguousarray(x[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))
+    ref = oracle_attention(qn, np.ascontiguousarray(kn.transpose(0, 1, 3, 2)), vn, mask, 8.0)
+    assert relerr(ctx.numpy(), ref.transpose(0, 2, 1, 3).reshape(B * S, H)) <= TOL
