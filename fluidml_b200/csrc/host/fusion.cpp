@@ -1,4 +1,5 @@
 #include "fusion.h"
+#include <cstdlib>
 #include "fluidml_cuda.h"
 #include <algorithm>
 #include <unordered_map>
@@ -308,7 +309,15 @@ bool FuseAttention(Rewriter &rw, const NodePtr &qk) {
   // attention kernel takes their head sizes (otherwise the score products are faster as GEMMs).
   double flops = 4.0 * (double)qs[rank - 2] * (double)ks[rank - 1] * (double)qs[rank - 1];
   for (size_t i = 0; i + 2 < rank; ++i) flops *= (double)qs[i];
-  if (flops > 256e6 && !fml_attention_on_tensor_cores(qs[rank - 2], ks[rank - 1], qs[rank - 1], vs[rank - 1])) return false;
+  {
+    // FLUIDML_ATTENTION_FUSION_MFLOP moves the limit (for measurements); blocks the tensor-core
+    // kernel takes are fused up to `tc_limit`: beyond a few key blocks its serial phases lose to
+    // the two batched tensor-core GEMMs around a softmax.
+    static const double limit = [] { const char *e = getenv("FLUIDML_ATTENTION_FUSION_MFLOP"); return e ? atof(e) * 1e6 : 256e6; }();
+    static const double tc_limit = [] { const char *e = getenv("FLUIDML_ATTENTION_TC_FUSION_MFLOP"); return e ? atof(e) * 1e6 : 256e6; }();
+    const bool tc = fml_attention_on_tensor_cores(qs[rank - 2], ks[rank - 1], qs[rank - 1], vs[rank - 1]) != 0;
+    if (flops > (tc ? std::max(limit, tc_limit) : limit)) return false;
+  }
   qk->kind = Kind::FusedAttention;
   qk->inputs = {q, kt, v};
   qk->divisor = sm->kind == Kind::FusedSoftmax ? sm->divisor : 1.0f;

@@ -64,6 +64,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                  bar_p = bar_q + 32, bar_o = bar_q + 40;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // a 128-row x 32-key piece of a mask that differs between query rows (pitch 33: the piece is
+  // written with lanes along the keys and read with lanes along the rows)
+  float *mask_s = reinterpret_cast<float *>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = (int)blockIdx.x * kBM;
@@ -198,6 +201,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int u = 0; u < 4; ++u) if (i + 128 * u < n) dst[i + 128 * u] = lo4(x[u]);
       }
     };
+    // The workers meet at named barriers below, so they must agree on whether to go on: a wait's
+    // outcome is reduced over the 128 of them before anyone acts on it.
+    auto all_ok = [](bool mine) -> bool {
+      uint32_t r;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 q, %1, 0;\n\t"
+          "bar.red.and.pred p, 2, 128, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(r) : "r"((uint32_t)mine) : "memory");
+      return r != 0;
+    };
     float o_acc[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) o_acc[i] = 0.0f;
@@ -207,11 +222,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int it = 0; it < nkb && ok; ++it) {
       const uint32_t ph = (uint32_t)it & 1u;
       if (it == 0) {
-        ok = mbar_wait(bar_q, 0u, abort_flag);
+        ok = all_ok(mbar_wait(bar_q, 0u, abort_flag));
         if (!ok) break;
         split_tile(q_hi, q_lo, q_bytes);
       }
-      ok = mbar_wait(bar_kv, ph, abort_flag);
+      ok = all_ok(mbar_wait(bar_kv, ph, abort_flag));
       if (!ok) break;
       split_tile(k_hi, k_lo, k_bytes);
       split_tile(v_hi, v_lo, v_bytes);
@@ -220,25 +235,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv);
 
-      ok = mbar_wait(bar_s, ph, abort_flag);
+      ok = all_ok(mbar_wait(bar_s, ph, abort_flag));
       if (!ok) break;
       tc_fence_after();
       const int key0 = it * kKeys;
-      // pass 1: the block's row maximum
+      // pass 1: scaled and masked scores back into tensor memory, and the block's row maximum.
+      // A mask that is the same for every query row is read directly (all lanes, one address); one
+      // that differs between rows goes through shared memory in pieces of 32 keys, loaded with
+      // lanes along the keys: read per thread along its own row it would touch 32 cache lines per
+      // load instruction.
+      const bool per_row_mask = mrow && a.m_s[2] != 0;
       float bmax = kNegBig;
       for (int c = 0; c < 4; ++c) {
+        if (per_row_mask) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous piece has been consumed
+          const float *mb = a.mask + (int64_t)b * a.m_s[0] + (int64_t)h * a.m_s[1];
+          const int key = key0 + c * 32 + lane;
+          for (int r = qw; r < kBM; r += 4) {
+            const int qq = min(q0 + r, a.Sq - 1);
+            mask_s[r * 33 + lane] = key < a.Sk ? __ldg(mb + (int64_t)qq * a.m_s[2] + (int64_t)key * m_sk) : 0.0f;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         float v[32];
         tmem_ld32(lane_addr + kColS + (uint32_t)c * 32u, v);
+        uint32_t sv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int key = key0 + c * 32 + i;
+          float s = kNegBig;
           if (key < a.Sk) {
-            float s = v[i] * a.inv_divisor;
-            if (mrow) s += __ldg(mrow + (int64_t)key * m_sk);
-            bmax = fmaxf(bmax, fmaxf(s, kNegBig));
+            s = v[i] * a.inv_divisor;
+            if (per_row_mask) s += mask_s[row * 33 + i];
+            else if (mrow) s += __ldg(mrow + (int64_t)key * m_sk);
+            s = fmaxf(s, kNegBig);
+            bmax = fmaxf(bmax, s);
           }
+          sv[i] = __float_as_uint(s);
         }
+        tmem_st32(lane_addr + kColS + (uint32_t)c * 32u, sv);
       }
+      tmem_wait_st();
       const float m_new = fmaxf(m_run, bmax);
       const float alpha = exp2f((m_run - m_new) * log2e);
       // pass 2: P = exp(s - m), split into hi / lo, into tensor memory; row sum
@@ -250,12 +287,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int key = key0 + c * 32 + i;
-          float p = 0.0f;
-          if (key < a.Sk) {
-            float s = v[i] * a.inv_divisor;
-            if (mrow) s += __ldg(mrow + (int64_t)key * m_sk);
-            p = exp2f((fmaxf(s, kNegBig) - m_new) * log2e);
-          }
+          const float p = key < a.Sk ? exp2f((v[i] - m_new) * log2e) : 0.0f;
           bsum += p;
           const uint32_t u = __float_as_uint(p), uh = u & 0xffffe000u;
           hi[i] = uh;
@@ -269,7 +301,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
 
-      ok = mbar_wait(bar_o, ph, abort_flag);
+      ok = all_ok(mbar_wait(bar_o, ph, abort_flag));
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -350,8 +382,10 @@ bool attention_tc_eligible(int64_t nb1, int64_t nb0, int64_t Sq, int64_t Sk, int
     return false;
   if (nb0 * nb1 > 65535 || nb0 * nb1 < 1) return false;
   if (mode == 1) return true;
-  // below ~200 Mflop the CUDA-core kernel's many small CTAs finish sooner than a few large tiles
-  return 4.0 * (double)nb0 * (double)nb1 * (double)Sq * (double)Sk * (double)D >= 200e6;
+  // below ~200 Mflop, or with fewer tiles than two thirds of the SMs, the CUDA-core kernel's many
+  // small CTAs finish sooner than a few large tiles (8 x 6 heads x 128 rows: 25 us against 30)
+  return 4.0 * (double)nb0 * (double)nb1 * (double)Sq * (double)Sk * (double)D >= 200e6 &&
+         nb0 * nb1 * ((Sq + kBM - 1) / kBM) >= 96;
 }
 
 int launch_attention_tc(int64_t nb1, int64_t nb0, int64_t Sq, int64_t Sk, int64_t D, int64_t Dv, const float *q,
@@ -372,7 +406,7 @@ int launch_attention_tc(int64_t nb1, int64_t nb0, int64_t Sq, int64_t Sk, int64_
   if (st != FML_OK) return st;
   st = make_map4(&mv, v, Dv, Sk, v_s[2], nb0, v_s[1], nb1, v_s[0], 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (st != FML_OK) return st;
-  const size_t smem = (size_t)(D / 32) * 16384 * 4 + (size_t)(Dv / 32) * 4096 * 4 * 2 + 6 * 8 + 16 + 1024;
+  const size_t smem = (size_t)(D / 32) * 16384 * 4 + (size_t)(Dv / 32) * 4096 * 4 * 2 + 6 * 8 + 16 + 128 * 33 * 4 + 1024;
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
