@@ -194,12 +194,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
-      int kb = 0;
+      int kb = 0, raw_issued = 0, b_issued = 0;
       for (int icb = 0; icb < a.n_icb && ok; ++icb) {
         const int rs = icb % RS;
         ok = mbar_wait(bar_rempty + 8u * rs, (((uint32_t)(icb / RS)) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         mbar_expect_tx(bar_rfull + 8u * rs, raw_bytes);
+        ++raw_issued;
         // x = ow0 - pw - xoff is a multiple of 4 by construction; rows / columns / channels outside
         // the image are filled with zeros: the padding, and the channel tail of the last block
         if (MODE == 0)
@@ -221,11 +222,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           mbar_expect_tx(bar_bfull + 8u * s, b_bytes);
           for (int g = 0; g < BN / 32; ++g)
             tma_load_3d(sb + (uint32_t)g * (ICB * 128), &map_w, bar_bfull + 8u * s, oc0 + g * 32, icb * ICB, tap);
+          ++b_issued;
         }
       }
       if (!ok) {
         atomicOr(a.status, kStatusTimeout);
         *abort_flag = 1;
+        // bounded drain: no copy may still be on its way into this CTA's shared memory when it exits
+        volatile int never = 0;
+        for (int it = max(0, raw_issued - RS); it < raw_issued; ++it)
+          mbar_wait(bar_rfull + 8u * (it % RS), ((uint32_t)(it / RS)) & 1u, &never);
+        for (int it = max(0, b_issued - NS); it < b_issued; ++it)
+          mbar_wait(bar_bfull + 8u * (it % NS), ((uint32_t)(it / NS)) & 1u, &never);
       }
     }
   } else if (warp == 1) {

@@ -60,6 +60,12 @@ int fml_device_count(int *count) {
   return FML_OK;
 }
 
+int fml_mem_info(size_t *free_bytes, size_t *total_bytes) {
+  FML_REQUIRE(free_bytes && total_bytes, FML_BAD_ARG, "fml_mem_info: null argument");
+  FML_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+  return FML_OK;
+}
+
 int fml_set_device(int device) {
   FML_CUDA(cudaSetDevice(device));
   return FML_OK;

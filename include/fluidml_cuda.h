@@ -61,6 +61,7 @@ typedef struct fml_tensor {
 const char *fml_last_error(void);
 int fml_device_count(int *count);
 int fml_set_device(int device);
+int fml_mem_info(size_t *free_bytes, size_t *total_bytes); /* cudaMemGetInfo of the current device */
 int fml_malloc(void **ptr, size_t bytes);
 int fml_free(void *ptr);
 int fml_memset(void *ptr, int value, size_t bytes, void *stream);

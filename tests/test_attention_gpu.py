@@ -116,9 +116,9 @@ def _as_kt(k):
 
 
 @pytest.mark.parametrize("cfg", [  # batch, heads, S_q, S_k, D, D_v, mask kind
-    (2, 4, 512, 512, 64, 64, "causal"), (1, 8, 300, 333, 64, 64, "key"), (4, 8, 256, 384, 32, 64, None),
-    (3, 16, 128, 640, 64, 32, "key"), (1, 16, 1024, 130, 64, 64, "causal"),
-])
+    (4, 8, 512, 512, 64, 64, "causal"), (4, 8, 300, 333, 64, 64, "key"), (6, 8, 256, 384, 32, 64, None),
+    (6, 16, 128, 640, 64, 32, "key"), (1, 16, 1024, 130, 64, 64, "causal"),
+])  # each at least 96 tiles of 128 query rows and 200 Mflop: what fml_attention sends to this kernel
 def test_attention_on_tensor_cores(cfg):
     """The tcgen05 kernel (3xTF32, scores in tensor memory, streaming softmax over blocks of 128
     keys) against the oracle's unfused chain: ragged sizes, key and causal masks, both head sizes."""

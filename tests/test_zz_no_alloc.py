@@ -48,3 +48,24 @@ def test_noalloc_refuses_what_does_not_fit():
         cabi.gemm_skinny_noalloc(DT.from_numpy(a), DT.from_numpy(b), DT((32, 9000), np.float32))
     assert e.value.status == 6 and "scratch" in str(e.value)
     cabi.check_device()
+
+
+def test_noalloc_leaves_free_device_memory_unchanged():
+    """The property in the name: after the per-device set-up has happened, a call changes the
+    device's free memory by nothing (cudaMemGetInfo before and after, operands allocated first)."""
+    import ctypes
+    a, b, bias = _operands(4, 2048, 520, 11)
+    da, db, dbias, out = DT.from_numpy(a), DT.from_numpy(b), DT.from_numpy(bias), DT((4, 520), np.float32)
+    cabi.gemm_skinny_noalloc(da, db, out, dbias)  # set-up, if this is the first call of the process
+    cabi.sync()
+
+    def free_bytes():
+        f, t = ctypes.c_size_t(), ctypes.c_size_t()
+        cabi.check(cabi.lib().fml_mem_info(ctypes.byref(f), ctypes.byref(t)))
+        return f.value
+
+    before = free_bytes()
+    for _ in range(3):
+        cabi.gemm_skinny_noalloc(da, db, out, dbias)
+    cabi.sync()
+    assert free_bytes() == before
