@@ -34,6 +34,7 @@
 #include "gemm_common.cuh"
 #include "tc_common.cuh"
 #include <algorithm>
+#include <cstdlib>
 
 namespace fml {
 namespace {
@@ -61,6 +62,7 @@ struct ConvTcArgs {
   int flat, IW, plane, raw_elems;  // flat: 1 = the patch is a run of whole image rows, 2 = whole planes
   const float *x;                  // input base (linear mode copies without a tensor map)
   int n_icb, taps, tile_n, stages, raw_stages;
+  int split_k, icb_per_split;  // the channel blocks are split over blockIdx.z = the CTAs of a cluster (1, 1, split_k)
   int tiles_w, tiles_h;
   int64_t ys[4];
   float *y;
@@ -133,7 +135,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t b_base = smem_u32(smem);
   uint8_t *raw_ptr = smem + (size_t)NS * stage_bytes;
   const uint32_t raw_base = smem_u32(raw_ptr);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ptr + (size_t)RS * raw_pitch);
+  // split-K stages each CTA's partial tile over the (by then idle) rings: [128][BN + 4] floats
+  const int pitch = BN + 4;
+  const size_t ring_bytes = (size_t)NS * stage_bytes + (size_t)RS * raw_pitch;
+  const size_t staging_bytes = a.split_k > 1 ? (((size_t)kBM * pitch * 4 + 127) & ~(size_t)127) : 0;
+  float *staging = reinterpret_cast<float *>(smem);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (ring_bytes > staging_bytes ? ring_bytes : staging_bytes));
   const uint32_t bar_bfull = smem_u32(bars);
   const uint32_t bar_ready = bar_bfull + 8u * NS;
   const uint32_t bar_empty = bar_ready + 8u * NS;
@@ -151,7 +158,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int n = t;
   const int oc0 = blockIdx.y * BN;
   const int oh0 = th * a.TH, ow0 = tw * a.TW;
-  const int total_kb = a.n_icb * a.taps;
+  // split-K: this CTA reduces the channel blocks [icb_lo, icb_hi); ring positions count from icb_lo
+  const int S = a.split_k, split = (int)blockIdx.z;
+  const int icb_lo = min(a.n_icb, split * a.icb_per_split), icb_hi = min(a.n_icb, icb_lo + a.icb_per_split);
+  const int total_kb = (icb_hi - icb_lo) * a.taps;
   const uint32_t a_col0 = ((uint32_t)BN + 31u) & ~31u;
   const uint32_t a_cols = THREE_PASS ? 2u * ICB : (uint32_t)ICB;  // per stage: hi [, lo]
   uint32_t tmem_cols = 32;
@@ -195,9 +205,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (lane == 0) {
       bool ok = true;
       int kb = 0, raw_issued = 0, b_issued = 0;
-      for (int icb = 0; icb < a.n_icb && ok; ++icb) {
-        const int rs = icb % RS;
-        ok = mbar_wait(bar_rempty + 8u * rs, (((uint32_t)(icb / RS)) & 1u) ^ 1u, abort_flag);
+      for (int icb = icb_lo; icb < icb_hi && ok; ++icb) {
+        const int li = icb - icb_lo, rs = li % RS;
+        ok = mbar_wait(bar_rempty + 8u * rs, (((uint32_t)(li / RS)) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         mbar_expect_tx(bar_rfull + 8u * rs, raw_bytes);
         ++raw_issued;
@@ -291,11 +301,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (i < BN) bias_s[i] = (a.bias && oc0 + i < a.OC) ? a.bias[(int64_t)(oc0 + i) * a.bias_stride] : 0.0f;
       asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight converter / epilogue warps
     }
-    for (int icb = 0; icb < a.n_icb && ok; ++icb) {
-      const int rs = icb % RS;
-      ok = mbar_wait(bar_rfull + 8u * rs, ((uint32_t)(icb / RS)) & 1u, abort_flag);
+    for (int icb = icb_lo; icb < icb_hi && ok; ++icb) {
+      const int li = icb - icb_lo, rs = li % RS;
+      ok = mbar_wait(bar_rfull + 8u * rs, ((uint32_t)(li / RS)) & 1u, abort_flag);
       if (!ok) break;
-      if (icb == 0 && threadIdx.x == 64) CTRACE(2);
+      if (li == 0 && threadIdx.x == 64) CTRACE(2);
       const uint32_t *rawp = reinterpret_cast<const uint32_t *>(raw_ptr + (size_t)rs * raw_pitch);
       for (int tap = 0; tap < a.taps && ok; ++tap, ++kb) {
         if ((kb & 1) != set) continue;
@@ -365,10 +375,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const bool inside = oh < a.OH && ow < a.OW;  // lanes outside the image still take part in the
                                                  // warp-wide TMEM loads
     float *yp = a.y + (int64_t)n * a.ys[0] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3];
-    if (ok) {
-      // the two sets share the tile's columns: set 0 the first half of the 32-column groups
-      const int groups = BN / 32, half = (groups + 1) / 2;
-      const int c_lo = set == 0 ? 0 : half * 32, c_hi = set == 0 ? half * 32 : BN;
+    // the two sets share the tile's columns: set 0 the first half of the 32-column groups
+    const int groups = BN / 32, half = (groups + 1) / 2;
+    const int c_lo = set == 0 ? 0 : half * 32, c_hi = set == 0 ? half * 32 : BN;
+    if (S > 1) {
+      // split-K: the partial tile goes to shared memory (zeros when this CTA had no channel block
+      // or gave up); the cluster sums it below
+      float *dst = staging + (size_t)m * pitch;
+      for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        float v[32];
+        if (ok && total_kb > 0) {
+          tmem_ld32(lane_addr + (uint32_t)c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4 *>(dst + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      }
+    } else if (ok) {
       for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
         float v[32];
         tmem_ld32(lane_addr + (uint32_t)c0, v);
@@ -383,6 +408,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     }
+  }
+  if (S > 1) {
+    // ---- split-K reduction through distributed shared memory: rank r owns pixels
+    // [r * 128 / S, (r + 1) * 128 / S) of the tile, sums them over the ranks in rank order (the
+    // result does not depend on timing), adds the bias, applies the activation and stores
+    __syncthreads();
+    cluster_sync_all();  // every rank's partial tile is in its shared memory
+    if (warp >= 2) {
+      const int rows_per = kBM / S, r0 = split * rows_per;  // S is a power of two
+      const int t = threadIdx.x - 64;
+      const uint32_t staging_addr = smem_u32(staging);
+      for (int idx = t; idx < rows_per * BN; idx += 256) {
+        const int pm = r0 + (idx & (rows_per - 1)), ocl = idx / rows_per;  // lanes along the pixels
+        const int pr = pm / a.TW, pc = pm - pr * a.TW;
+        const int oh = oh0 + pr, ow = ow0 + pc, oc = oc0 + ocl;
+        if (oh >= a.OH || ow >= a.OW || oc >= a.OC) continue;
+        const uint32_t off = staging_addr + (uint32_t)(pm * pitch + ocl) * 4u;
+        float acc = 0.0f;
+        for (int rank = 0; rank < S; ++rank) acc += ld_cluster_f32(cluster_smem_addr(off, (uint32_t)rank));
+        a.y[(int64_t)n * a.ys[0] + (int64_t)oc * a.ys[1] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3]] =
+            conv_act(a.act, acc + bias_s[ocl]);
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its tile
   }
   if (threadIdx.x == 64) CTRACE(4);
   tc_fence_before();
@@ -494,6 +543,20 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   a.stages = stages;
   a.tiles_w = (a.OW + a.TW - 1) / a.TW;
   a.tiles_h = (a.OH + a.TH - 1) / a.TH;
+  {
+    // Split-K over the channel blocks when the tiles alone leave most of the machine idle (small
+    // maps at small batch: 512 -> 512 on 14 x 14, one image, is 8 tiles of 144 k blocks each):
+    // the largest power of two <= 8 that keeps the grid within the SM count and gives every rank
+    // at least one channel block.  FLUIDML_CONV_SPLIT_K forces a value (0 = never).
+    static const int forced = [] { const char *e = getenv("FLUIDML_CONV_SPLIT_K"); return e ? atoi(e) : -1; }();
+    const int64_t tiles = (int64_t)a.tiles_w * a.tiles_h * a.N * ((a.OC + a.tile_n - 1) / a.tile_n);
+    int sk = 1;
+    while (sk < 8 && tiles * (sk * 2) <= 148 && a.n_icb >= sk * 2 && a.n_icb * a.taps >= sk * 2 * 4) sk *= 2;
+    if (forced == 0) sk = 1;
+    else if (forced > 0) { sk = 1; while (sk < 8 && sk * 2 <= forced && a.n_icb >= sk * 2) sk *= 2; }
+    a.split_k = sk;
+    a.icb_per_split = (a.n_icb + sk - 1) / sk;
+  }
   for (int i = 0; i < 4; ++i) a.ys[i] = y->stride[i];
   a.y = (float *)y->data;
   a.bias = nullptr; a.bias_stride = 0;
@@ -533,8 +596,9 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
     int st = make_map_nd(&map_w, (const float *)w->data, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (st != FML_OK) return st;
   }
-  size_t smem = (size_t)stages * stage + a.raw_stages * raw_pitch + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 +
-                128 * 4 /* bias slice */ + 1024;
+  const size_t ring = (size_t)stages * stage + a.raw_stages * raw_pitch;
+  const size_t staging = a.split_k > 1 ? (((size_t)kBM * (a.tile_n + 4) * 4 + 127) & ~(size_t)127) : 0;
+  size_t smem = std::max(ring, staging) + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 128 * 4 /* bias slice */ + 1024;
   {  // co-residency capped by TMEM columns, as in the GEMM
     unsigned need = (unsigned)((a.tile_n + 31) / 32 * 32 + a_cols * stages), cols = 32;
     while (cols < need) cols <<= 1;
@@ -557,8 +621,22 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
     for (KernelFn k : kernels) FML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[dev & 63] = true;
   }
-  const dim3 grid((unsigned)m_tiles, (unsigned)((a.OC + a.tile_n - 1) / a.tile_n));
-  FML_CUDA(launch_kernel(kernel, grid, dim3(kThreads), smem, s, map_x, map_w, a));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)m_tiles, (unsigned)((a.OC + a.tile_n - 1) / a.tile_n), (unsigned)a.split_k);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;  // the split-K ranks of a tile share a cluster
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)a.split_k;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  FML_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_x, map_w, a));
   return FML_OK;
 }
 

@@ -319,6 +319,9 @@ def test_reduce_mean_cumsum():
     dict(x=(2, 3, 33, 37), w=(32, 3, 3, 3), pads=(1, 1), strides=(2, 2), dil=(1, 1), group=1),
     dict(x=(1, 2, 16, 16), w=(40, 2, 5, 5), pads=(2, 2), strides=(1, 1), dil=(1, 1), group=1),
     dict(x=(2, 4, 50), w=(5, 4, 7), pads=(3,), strides=(3,), dil=(2,), group=1),
+    # pointwise over a small map, one or two images: the weight-streaming product with 33-64 rows
+    dict(x=(1, 96, 7, 7), w=(40, 96, 1, 1), pads=(0, 0), strides=(1, 1), dil=(1, 1), group=1),
+    dict(x=(2, 640, 8, 8), w=(24, 640, 1, 1), pads=(0, 0), strides=(1, 1), dil=(1, 1), group=1),
 ])
 def test_conv(cfg):
     x, w = rnd(*cfg["x"]), rnd(*cfg["w"]) * 0.2
@@ -387,6 +390,18 @@ def test_depthwise_conv_channel_innermost(shape, k, stride, pad, act):
     xd, out = DT.from_numpy(x, cl), DT(oshape, np.float32, cl)
     assert xd.strides[1] == 1 and out.strides[1] == 1
     cabi.conv(xd, DT.from_numpy(w), DT.from_numpy(b), out, (pad,) * nd, (stride,) * nd, (1,) * nd, c, act=act)
+    assert relerr(out.numpy(), ref) <= 1e-5
+
+
+def test_pointwise_conv_on_a_small_map_with_baked_weight_layout():
+    """1152 -> 192 on a 7 x 7 map, one image, weights stored tap-major with the output channel
+    innermost (what the Builder bakes), SiLU: the N-major path of the wide weight-streaming kernel."""
+    x, w, b = rnd(1, 1152, 7, 7), rnd(192, 1152, 1, 1) * 0.05, rnd(192)
+    ref = orc.conv(x, w, b, np.empty((1, 192, 7, 7), np.float32), (0, 0), (1, 1), (1, 1), 1, acc64=True)
+    ref = ref / (1.0 + np.exp(-ref.astype(np.float64)))
+    out = DT((1, 192, 7, 7), np.float32)
+    cabi.conv(DT.from_numpy(x), DT.from_numpy(w, [3, 2, 0, 1]), DT.from_numpy(b), out, (0, 0), (1, 1), (1, 1), 1,
+              act=cabi.ACT_SILU)
     assert relerr(out.numpy(), ref) <= 1e-5
 
 
