@@ -58,7 +58,66 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
     // warp w owns columns n0 + w, n0 + w + 8, ... ; lanes stride over k in float4 steps
     const bool vec = a.p.a_sk == 1 && (a.p.a_sm & 3) == 0 && (a.p.b_sn & 3) == 0 && (k0 & 3) == 0 &&
                      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0;
-    for (int c = warp; c < kColsPerCta; c += kThreads / 32) {
+    // At most four rows (batch-1 classifier heads, the pooler): the warp takes its four columns
+    // at once, so that eight weight loads are in flight per lane, the row chunks are loaded once
+    // for all four columns, and the shuffle reductions are amortised.  Same per-lane summation
+    // order as the general loop below.
+    const bool few_rows = vec && M <= 4 && n0 + kColsPerCta <= a.p.N;
+    if (few_rows) {
+      const int64_t kv = k0 + ((k1 - k0) & ~(int64_t)3);
+      float acc4[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int m = 0; m < 4; ++m) acc4[j][m] = 0.0f;
+      const float *b0p = B + (n0 + warp * 4) * a.p.b_sn;
+      auto dot4 = [](float4 x, float4 y, float t) { return fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, t)))); };
+      int64_t k = k0 + lane * 4;
+      for (; k + 128 < kv; k += 256) {
+        float4 bw[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          bw[j][0] = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k));
+          bw[j][1] = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k + 128));
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+          if (m < M) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(A + m * a.p.a_sm + k);
+            const float4 a1 = *reinterpret_cast<const float4 *>(A + m * a.p.a_sm + k + 128);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc4[j][m] = dot4(a1, bw[j][1], dot4(a0, bw[j][0], acc4[j][m]));
+          }
+      }
+      for (; k < kv; k += 128) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 bv = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k));
+#pragma unroll
+          for (int m = 0; m < 4; ++m)
+            if (m < M) acc4[j][m] = dot4(*reinterpret_cast<const float4 *>(A + m * a.p.a_sm + k), bv, acc4[j][m]);
+        }
+      }
+      for (int64_t kt = kv + lane; kt < k1; kt += 32)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float bv = b0p[j * a.p.b_sn + kt];
+#pragma unroll
+          for (int m = 0; m < 4; ++m)
+            if (m < M) acc4[j][m] = fmaf(A[m * a.p.a_sm + kt], bv, acc4[j][m]);
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+          if (m < M) {
+            float v = acc4[j][m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red[m][warp * 4 + j] = v;
+          }
+    }
+    for (int c = few_rows ? kColsPerCta : warp; c < kColsPerCta; c += kThreads / 32) {
       const int64_t n = n0 + c;
       float acc[kMaxM];
 #pragma unroll
