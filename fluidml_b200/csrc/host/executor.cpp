@@ -276,6 +276,10 @@ private:
       if (n->group != 1 || n->consts.empty() || n->consts[0]->meta.GetRank() != 4) continue;
       const auto unit = [](const std::vector<int64_t> &v) { return std::all_of(v.begin(), v.end(), [](int64_t x) { return x == 1; }); };
       if (!unit(n->strides) || !unit(n->dilations)) continue;
+      // a convolution over a single pixel (squeeze-and-excite) is a weight-streaming product:
+      // [OC][IC] as stored is its K-major right-hand side, read with 16-byte loads along k
+      const auto &xs = n->inputs[0]->meta.GetShape();
+      if (xs.size() == 4 && xs[2] * xs[3] == 1) continue;
       n->consts[0]->layout = {3, 2, 0, 1};
     }
 

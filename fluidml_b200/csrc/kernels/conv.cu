@@ -266,9 +266,34 @@ __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs 
     }
     wts[i] = v;
   }
-  // ---- patch: a sub-warp per patch row, lanes along the row; (plane, row) advance by steps
-  {
-    const int units = d.vec ? IW >> 2 : d.PWn;     // float4 chunks of the image row, or patch columns
+  // ---- patch.  Rows that cannot be fetched as aligned float4 (14- and 7-wide planes): a flat
+  // walk over the patch, four independent elements per thread and step, loads before stores, so
+  // that a CTA's few dozen loads per thread overlap instead of queueing behind each other's latency.
+  if (!d.vec) {
+    const int per_plane_elems = d.PH * d.PWn, total = d.PP * per_plane_elems;
+    for (int base = tid; base < total; base += 1024) {
+      float v[4];
+      int at[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = base + 256 * u;
+        v[u] = 0.0f;
+        at[u] = -1;
+        if (e < total) {
+          const int pl = e / per_plane_elems, rem = e - pl * per_plane_elems;
+          const int pr = rem / d.PWn, pc = rem - pr * d.PWn;
+          const int ih = ih0 + pr, iw = pc - pw, lin = c0 + pl, nn = n0 + lin / C, ch = lin - (lin / C) * C;
+          at[u] = (pl * d.PH + pr) * d.pitch + pc;
+          if (plane0 + pl < d.planes && ih >= 0 && ih < IH && iw >= 0 && iw < IW)
+            v[u] = a.x[nn * a.xs[0] + ch * a.xs[1] + ih * a.xs[2] + iw];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (at[u] >= 0) patch[at[u]] = v[u];
+    }
+  } else {
+    const int units = IW >> 2;                     // float4 chunks of the image row
     int p2 = 32, sh = 5;
     while (p2 > 1 && (p2 >> 1) >= units) { p2 >>= 1; --sh; }
     const int sub = lane >> sh, u0 = lane & (p2 - 1), step = 8 << (5 - sh);
@@ -282,7 +307,7 @@ __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs 
       const bool row_ok = plane0 + pl < d.planes && ih >= 0 && ih < IH;
       const float *src = a.x + n * a.xs[0] + ch * a.xs[1] + ih * a.xs[2];
       float *dst = patch + row * d.pitch;
-      if (d.vec) {
+      {
         if (row_ok) {
           for (int u = u0; u < units; u += p2) {
             const float4 t = *reinterpret_cast<const float4 *>(src + 4 * u);
@@ -294,9 +319,6 @@ __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs 
         } else {
           for (int c = u0; c < d.PWn; c += p2) dst[c] = 0.0f;
         }
-      } else {
-        for (int c = u0; c < d.PWn; c += p2)
-          dst[c] = (row_ok && c >= pw && c - pw < IW) ? src[c - pw] : 0.0f;
       }
       pr += step;
       while (pr >= d.PH) { pr -= d.PH; ++pl; if (++ch == C) { ch = 0; ++n; } }

@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
     // at once, so that eight weight loads are in flight per lane, the row chunks are loaded once
     // for all four columns, and the shuffle reductions are amortised.  Same per-lane summation
     // order as the general loop below.
-    const bool few_rows = vec && M <= 4 && n0 + kColsPerCta <= a.p.N;
+    const bool few_rows = vec && M <= 4;
     if (few_rows) {
       const int64_t kv = k0 + ((k1 - k0) & ~(int64_t)3);
       float acc4[4][4];
@@ -70,15 +70,18 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int m = 0; m < 4; ++m) acc4[j][m] = 0.0f;
-      const float *b0p = B + (n0 + warp * 4) * a.p.b_sn;
+      // columns past the edge of a ragged tile read the last column again (their sums are dropped below)
+      const float *bcol[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bcol[j] = B + min(n0 + warp * 4 + j, a.p.N - 1) * a.p.b_sn;
       auto dot4 = [](float4 x, float4 y, float t) { return fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, t)))); };
       int64_t k = k0 + lane * 4;
       for (; k + 128 < kv; k += 256) {
         float4 bw[4][2];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          bw[j][0] = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k));
-          bw[j][1] = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k + 128));
+          bw[j][0] = __ldcs(reinterpret_cast<const float4 *>(bcol[j] + k));
+          bw[j][1] = __ldcs(reinterpret_cast<const float4 *>(bcol[j] + k + 128));
         }
 #pragma unroll
         for (int m = 0; m < 4; ++m)
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
       for (; k < kv; k += 128) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float4 bv = __ldcs(reinterpret_cast<const float4 *>(b0p + j * a.p.b_sn + k));
+          const float4 bv = __ldcs(reinterpret_cast<const float4 *>(bcol[j] + k));
 #pragma unroll
           for (int m = 0; m < 4; ++m)
             if (m < M) acc4[j][m] = dot4(*reinterpret_cast<const float4 *>(A + m * a.p.a_sm + k), bv, acc4[j][m]);
@@ -101,7 +104,7 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
       for (int64_t kt = kv + lane; kt < k1; kt += 32)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float bv = b0p[j * a.p.b_sn + kt];
+          const float bv = bcol[j][kt];
 #pragma unroll
           for (int m = 0; m < 4; ++m)
             if (m < M) acc4[j][m] = fmaf(A[m * a.p.a_sm + kt], bv, acc4[j][m]);
@@ -262,7 +265,9 @@ SkinnyPlan plan_skinny(const GemmProblem &p) {
   const int64_t tiles = (int64_t)pl.tiles_n * p.nb0 * p.nb1;
   // enough CTAs for ~8 per SM, each split at least 256 k values long
   int64_t s = (148 * 8 + tiles - 1) / tiles;
-  s = std::min<int64_t>(s, std::max<int64_t>(1, p.K / 256));
+  // (with at most four rows the kernel is a chain of load latencies, not arithmetic: slices of
+  // 128 k values already pay there; more rows keep slices of at least 256)
+  s = std::min<int64_t>(s, std::max<int64_t>(1, p.K / (p.M <= 4 ? 128 : 256)));
   s = std::max<int64_t>(1, std::min<int64_t>(s, 64));
   int64_t per = (p.K + s - 1) / s;
   per = (per + 127) / 128 * 128;  // keeps every slice start 16-byte aligned and chunked
