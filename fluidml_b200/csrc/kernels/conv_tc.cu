@@ -49,7 +49,7 @@ constexpr size_t kSmemBudget = 200 * 1024;
     if (a.trace) {                                                                              \
       unsigned long long t_;                                                                    \
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
-      a.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = t_;                 \
+      a.trace[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = t_;                 \
     }                                                                                           \
   } while (0)
 #else
@@ -71,7 +71,7 @@ struct ConvTcArgs {
   int act;
   int *status;
 #ifdef FML_CONV_PHASE_TRACE
-  unsigned long long *trace;  // 8 stamps per CTA (fml_debug_set_conv_trace)
+  unsigned long long *trace;  // 16 stamps per CTA (fml_debug_set_conv_trace)
 #endif
 };
 
@@ -257,6 +257,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int s = kb % NS;
         ok = mbar_wait(bar_ready + 8u * s, ((uint32_t)(kb / NS)) & 1u, abort_flag);
         if (!ok) break;
+        if (kb == 0) CTRACE(6);
         tc_fence_after();
         const uint32_t soff = ((uint32_t)s * stage_bytes) >> 4;
 #pragma unroll
@@ -335,6 +336,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         ok = mbar_wait(bar_bfull + 8u * s, phs, abort_flag);
         if (!ok) break;
+        if (kb == 0 && threadIdx.x == 64) CTRACE(7);
         if (THREE_PASS) {
           uint4 *hi_b = reinterpret_cast<uint4 *>(smem + (size_t)s * stage_bytes);
           uint4 *lo_b = reinterpret_cast<uint4 *>(smem + (size_t)s * stage_bytes + b_bytes);
@@ -414,23 +416,61 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // [r * 128 / S, (r + 1) * 128 / S) of the tile, sums them over the ranks in rank order (the
     // result does not depend on timing), adds the bias, applies the activation and stores
     __syncthreads();
+    if (threadIdx.x == 64) CTRACE(8);
     cluster_sync_all();  // every rank's partial tile is in its shared memory
+    if (threadIdx.x == 64) CTRACE(9);
     if (warp >= 2) {
       const int rows_per = kBM / S, r0 = split * rows_per;  // S is a power of two
       const int t = threadIdx.x - 64;
-      const uint32_t staging_addr = smem_u32(staging);
-      for (int idx = t; idx < rows_per * BN; idx += 256) {
-        const int pm = r0 + (idx & (rows_per - 1)), ocl = idx / rows_per;  // lanes along the pixels
-        const int pr = pm / a.TW, pc = pm - pr * a.TW;
-        const int oh = oh0 + pr, ow = ow0 + pc, oc = oc0 + ocl;
-        if (oh >= a.OH || ow >= a.OW || oc >= a.OC) continue;
-        const uint32_t off = staging_addr + (uint32_t)(pm * pitch + ocl) * 4u;
-        float acc = 0.0f;
-        for (int rank = 0; rank < S; ++rank) acc += ld_cluster_f32(cluster_smem_addr(off, (uint32_t)rank));
-        a.y[(int64_t)n * a.ys[0] + (int64_t)oc * a.ys[1] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3]] =
-            conv_act(a.act, acc + bias_s[ocl]);
+      // the ranks' staging tiles in this CTA's view of the cluster's shared memory (one mapa each)
+      uint32_t rank_base[8];
+#pragma unroll
+      for (int rank = 0; rank < 8; ++rank) rank_base[rank] = rank < S ? cluster_smem_addr(smem_u32(staging), (uint32_t)rank) : 0u;
+      // Lanes run along the channels: a warp reads 512 contiguous bytes of one pixel's row from each
+      // rank (16-byte loads; scalar loads along the pixels moved 6.5 GB/s per SM through the
+      // cluster network, a quarter of what 16-byte ones do), two quads per thread in flight.  The
+      // stores that follow are strided by the channel plane; the tile is small.
+      const int quads = BN >> 2;
+      for (int base = t; base < rows_per * quads; base += 512) {
+        float4 part[2][8];
+        int pmv[2], oq[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int idx = base + 256 * u;
+          pmv[u] = -1;
+          if (idx < rows_per * quads) {
+            pmv[u] = r0 + idx / quads;
+            oq[u] = (idx % quads) * 4;
+            const uint32_t off = (uint32_t)(pmv[u] * pitch + oq[u]) * 4u;
+#pragma unroll
+            for (int rank = 0; rank < 8; ++rank)
+              if (rank < S)
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(part[u][rank].x), "=f"(part[u][rank].y), "=f"(part[u][rank].z), "=f"(part[u][rank].w)
+                             : "r"(rank_base[rank] + off) : "memory");
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (pmv[u] < 0) continue;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int rank = 0; rank < 8; ++rank)
+            if (rank < S) { acc.x += part[u][rank].x; acc.y += part[u][rank].y; acc.z += part[u][rank].z; acc.w += part[u][rank].w; }
+          const int pr = pmv[u] / a.TW, pc = pmv[u] - pr * a.TW;
+          const int oh = oh0 + pr, ow = ow0 + pc;
+          if (oh >= a.OH || ow >= a.OW) continue;
+          float *yp = a.y + (int64_t)n * a.ys[0] + (int64_t)oh * a.ys[2] + (int64_t)ow * a.ys[3];
+          const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int ocl = oq[u] + i;
+            if (oc0 + ocl < a.OC) yp[(int64_t)(oc0 + ocl) * a.ys[1]] = conv_act(a.act, v[i] + bias_s[ocl]);
+          }
+        }
       }
     }
+    if (threadIdx.x == 64) CTRACE(10);
     cluster_sync_all();  // nobody leaves while a peer may still read its tile
   }
   if (threadIdx.x == 64) CTRACE(4);
@@ -643,9 +683,11 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
 }  // namespace fml
 
 #ifdef FML_CONV_PHASE_TRACE
-// Tracing hook of debug builds: a device buffer of 8 x (number of CTAs) u64 receives, per CTA,
+// Tracing hook of debug builds: a device buffer of 16 x (number of CTAs) u64 receives, per CTA,
 // %globaltimer at 0 start, 1 dependency wait done, 2 first patch landed, 3 accumulator ready,
-// 4 epilogue done, 5 end.  NULL disables it.
+// 4 epilogue done, 5 end, 6 first k block ready for the MMAs, 7 first weight tile landed; with
+// split-K 8 partial tile staged, 9 cluster barrier passed, 10 this rank's rows reduced and stored.
+// NULL disables it.
 extern "C" void fml_debug_set_conv_trace(void *device_buffer) {
   fml::g_conv_trace = static_cast<unsigned long long *>(device_buffer);
 }
