@@ -84,29 +84,50 @@ __global__ void ew_f32_vec4(Iter<3> it, int op, float *out, const float *a, cons
   const I inner4 = (I)(it.shape[it.rank - 1] >> 2);
   const I total4 = (I)(it.total >> 2);
   const bool a_vec = it.stride[1][it.rank - 1] == 1, b_vec = b && it.stride[2][it.rank - 1] == 1;
-  for (I i = (I)blockIdx.x * (I)blockDim.x + (I)threadIdx.x; i < total4; i += (I)gridDim.x * (I)blockDim.x) {
-    I row = it.rank > 1 ? i / inner4 : 0;
-    const I c4 = i - row * inner4;
-    I off[3] = {c4 * 4, a_vec ? c4 * 4 : 0, b_vec ? c4 * 4 : 0};
-    for (int d = it.rank - 2; d >= 0; --d) {
-      I c = row;
-      if (d > 0) { const I q = row / (I)it.shape[d]; c = row - q * (I)it.shape[d]; row = q; }
-      off[0] += c * (I)it.stride[0][d];
-      off[1] += c * (I)it.stride[1][d];
-      off[2] += c * (I)it.stride[2][d];
+  const I stride = (I)gridDim.x * (I)blockDim.x;
+  // two float4 per thread and step, both loaded before either is used: with one in flight per
+  // thread the broadcast forms (a division and a scalar load beside the 16-byte one) ran at a
+  // third of the copy bandwidth
+  for (I i0 = (I)blockIdx.x * (I)blockDim.x + (I)threadIdx.x; i0 < total4; i0 += 2 * stride) {
+    float4 av[2], bv[2];
+    I oo[2];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const I i = i0 + (I)u * stride;
+      live[u] = i < total4;
+      bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      av[u] = bv[u];
+      oo[u] = 0;
+      if (!live[u]) continue;
+      I row = it.rank > 1 ? i / inner4 : 0;
+      const I c4 = i - row * inner4;
+      I off[3] = {c4 * 4, a_vec ? c4 * 4 : 0, b_vec ? c4 * 4 : 0};
+      for (int d = it.rank - 2; d >= 0; --d) {
+        I c = row;
+        if (d > 0) { const I q = row / (I)it.shape[d]; c = row - q * (I)it.shape[d]; row = q; }
+        off[0] += c * (I)it.stride[0][d];
+        off[1] += c * (I)it.stride[1][d];
+        off[2] += c * (I)it.stride[2][d];
+      }
+      oo[u] = off[0];
+      if (a_vec) av[u] = *reinterpret_cast<const float4 *>(a + off[1]);
+      else { float s = a[off[1]]; av[u] = make_float4(s, s, s, s); }
+      if (b) {
+        if (b_vec) bv[u] = *reinterpret_cast<const float4 *>(b + off[2]);
+        else { float s = b[off[2]]; bv[u] = make_float4(s, s, s, s); }
+      }
     }
-    float4 av, bv = make_float4(0.f, 0.f, 0.f, 0.f), r;
-    if (a_vec) av = *reinterpret_cast<const float4 *>(a + off[1]);
-    else { float s = a[off[1]]; av = make_float4(s, s, s, s); }
-    if (b) {
-      if (b_vec) bv = *reinterpret_cast<const float4 *>(b + off[2]);
-      else { float s = b[off[2]]; bv = make_float4(s, s, s, s); }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (!live[u]) continue;
+      float4 r;
+      r.x = ew_apply(op, av[u].x, bv[u].x, p0, p1);
+      r.y = ew_apply(op, av[u].y, bv[u].y, p0, p1);
+      r.z = ew_apply(op, av[u].z, bv[u].z, p0, p1);
+      r.w = ew_apply(op, av[u].w, bv[u].w, p0, p1);
+      *reinterpret_cast<float4 *>(out + oo[u]) = r;
     }
-    r.x = ew_apply(op, av.x, bv.x, p0, p1);
-    r.y = ew_apply(op, av.y, bv.y, p0, p1);
-    r.z = ew_apply(op, av.z, bv.z, p0, p1);
-    r.w = ew_apply(op, av.w, bv.w, p0, p1);
-    *reinterpret_cast<float4 *>(out + off[0]) = r;
   }
 }
 
@@ -264,9 +285,11 @@ bool vec4_ok(const Iter<3> &it, const void *out, const void *a, const void *b) {
   if (!aligned16(out) || !aligned16(a) || (b && !aligned16(b))) return false;
   if (it.stride[1][l] != 1 && it.stride[1][l] != 0) return false;
   if (b && it.stride[2][l] != 1 && it.stride[2][l] != 0) return false;
+  // outer strides must keep 16-byte alignment only for operands that are read 16 bytes at a time; an
+  // operand broadcast along the innermost dim (a per-row scale) is read as one scalar per float4
   for (int d = 0; d < l; ++d)
     for (int o = 0; o < 3; ++o)
-      if (it.stride[o][d] % 4 != 0) return false;
+      if (it.stride[o][l] != 0 && it.stride[o][d] % 4 != 0) return false;
   return true;
 }
 

@@ -34,6 +34,9 @@ BIN_CASES = [
     ((3, 5, 7), (5, 1)),                # ragged broadcast, odd sizes
     ((2, 1, 3), (1, 4, 3)),             # both sides broadcast
     ((0, 4), (4,)),                     # empty
+    ((6, 10, 8, 12), (6, 10, 1, 1)),    # per-plane scale (squeeze-and-excite gate): 16-byte path, scalar rhs
+    ((5, 7, 3, 64), (5, 7, 3, 1)),      # per-row scale with odd outer extents
+    ((6, 10, 1, 1), (6, 10, 8, 12)),    # the same with the operands swapped
 ]
 
 
