@@ -13,7 +13,7 @@
 //   * the weights of ALL stages are packed at creation into one stream per CTA, already in the
 //     shared-memory image the tensor core reads (K-major rows of 128 bytes, 128-byte swizzle).
 //     Warp 0 copies that stream into a ring of shared-memory slots with plain bulk copies
-//     (cp.async.bulk, no tensor map, no multicast) and never waits for activations: weights
+//     (plain cp.async.bulk into this CTA only, no tensor map) and never waits for activations: weights
 //     arrive while the CTA is still waiting for, or reducing, the previous stage;
 //   * steps are ordered by the data itself: every word a step stores in the program's buffers
 //     carries its buffer generation's parity (resident.cuh), a consumer fetches what it needs
