@@ -172,6 +172,10 @@ def elementwise(op, a, b, out, p0=0.0, p1=0.0, stream=None):
                                 ctypes.c_double(p1), stream))
 
 
+def mul_add(a, b, c, out, stream=None):
+    check(lib().fml_mul_add(_ref(a), _ref(b), _ref(c), _ref(out), stream))
+
+
 def bias_gelu(x, bias, out, c0, c1, c2, stream=None):
     check(lib().fml_bias_gelu(_ref(x), _ref(bias), _ref(out), ctypes.c_float(c0),
                               ctypes.c_float(c1), ctypes.c_float(c2), stream))

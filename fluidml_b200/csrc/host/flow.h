@@ -52,6 +52,7 @@ enum class Kind {
   FusedLayerNorm,  // LayerNorm(x + residual)
   Silu,            // x * sigmoid(x)
   FusedAttention,  // softmax(Q K^T / divisor + mask) V; inputs: Q, K^T, V, [mask]
+  FusedMulAdd,     // a * b + c, broadcast; inputs: a, b, c
 };
 const char *KindName(Kind k);
 

@@ -340,6 +340,23 @@ bool FuseSilu(Rewriter &rw, const NodePtr &sg) {
   return true;
 }
 
+// ---- Mul -> Add: one pass over the data instead of two (the span convolution of ConvBERT is a
+// chain of nine such pairs, rotary embeddings two).  Same two roundings as the separate kernels.
+bool FuseMulAdd(Rewriter &rw, const NodePtr &mul) {
+  if (mul->kind != Kind::MulCommon || mul->inputs.size() != 2) return false;
+  NodePtr add = rw.SoleOfKind(mul->output, Kind::AddCommon);
+  if (!add || add->inputs.size() != 2 || add->inputs[0] == add->inputs[1]) return false;
+  const RegionPtr other = Other(add, mul->output);
+  for (const RegionPtr &r : {mul->inputs[0], mul->inputs[1], other, add->output})
+    if (r->meta.GetType() != Type::kFloat32) return false;
+  // the addend must not depend on this product (it cannot: the product has one consumer)
+  mul->kind = Kind::FusedMulAdd;
+  mul->inputs = {mul->inputs[0], mul->inputs[1], other};
+  mul->output = add->output;
+  rw.Kill(add);
+  return true;
+}
+
 // ---- Conv -> SiLU: the activation rides in the convolution's epilogue
 bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
   if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
@@ -462,7 +479,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseMulAdd};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

@@ -222,6 +222,16 @@ private:
   float y_scalar_;
 };
 
+// MulCommon -> AddCommon in one launch (mul.cpp + add.cpp of the reference run as two loop nests)
+class FusedMulAddKernel : public Kernel {
+public:
+  std::string GetKernelName() const override { return "FusedMulAddKernel"; }
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output, const Buffer &) const override {
+    const fml_tensor a = in.at(0), b = in.at(1), c = in.at(2);
+    rec.Add(GetKernelName(), [=](void *s) { return fml_mul_add(&a, &b, &c, &output, s); });
+  }
+};
+
 // ------------------------------------------------------------------ data movement
 // reshape.cpp:18-64, unsqueeze.cpp:20-63, squeeze.cpp:17-54, flatten.cpp:15-63
 class ReshapeLikeKernel : public SingleInputWithoutBufferKernel {
@@ -640,6 +650,7 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
   case Kind::Cast: return std::make_unique<CastKernel>();
   case Kind::Sigmoid: return std::make_unique<SigmoidKernel>();
   case Kind::Silu: return std::make_unique<SiluKernel>();
+  case Kind::FusedMulAdd: return std::make_unique<FusedMulAddKernel>();
   case Kind::AddCommon: return std::make_unique<AddCommonKernel>();
   case Kind::MulCommon: return std::make_unique<MulCommonKernel>();
   case Kind::DivCommon: return std::make_unique<DivCommonKernel>();
@@ -759,7 +770,7 @@ const char *KindName(Kind k) {
       "Not", "Pad", "Pow", "ReduceMean", "Relu", "Reshape", "Slice", "Softmax", "Sqrt", "Squeeze", "SubConstantLhs",
       "SubCommon", "Tanh", "Transpose", "Unsqueeze", "UnsqueezeSubLhsScalarMulRhsScalar",
       "WhereConstantCondConstantScalarY", "WhereConstantCondConstantTensorY", "Sigmoid", "Identity", "FusedGemm",
-      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention"};
+      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd"};
   return names[(int)k];
 }
 }  // namespace flow

@@ -276,6 +276,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         umma_commit(bar_empty + 8u * s);
       }
+      CTRACE(11);
       if (ok) umma_commit(bar_accum);
       else {
         atomicOr(a.status, kStatusTimeout);
@@ -360,10 +361,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ready + 8u * s);
+        if (kb == 0 && threadIdx.x == 64) CTRACE(12);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_rempty + 8u * rs);  // the patch may be overwritten
     }
+    if (threadIdx.x == 64) CTRACE(13);
     if (ok) ok = mbar_wait(bar_accum, 0u, abort_flag);
     if (!ok) {
       atomicOr(a.status, kStatusTimeout);
@@ -686,7 +689,8 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
 // Tracing hook of debug builds: a device buffer of 16 x (number of CTAs) u64 receives, per CTA,
 // %globaltimer at 0 start, 1 dependency wait done, 2 first patch landed, 3 accumulator ready,
 // 4 epilogue done, 5 end, 6 first k block ready for the MMAs, 7 first weight tile landed; with
-// split-K 8 partial tile staged, 9 cluster barrier passed, 10 this rank's rows reduced and stored.
+// split-K 8 partial tile staged, 9 cluster barrier passed, 10 this rank's rows reduced and stored;
+// 11 last MMA issued, 12 first k block converted, 13 converter loop left.
 // NULL disables it.
 extern "C" void fml_debug_set_conv_trace(void *device_buffer) {
   fml::g_conv_trace = static_cast<unsigned long long *>(device_buffer);

@@ -279,6 +279,43 @@ int make_iter(Iter<N> &it, const fml_tensor *out, const fml_tensor *const *ins, 
   return FML_OK;
 }
 
+// out = a * b + c, all broadcast to out: the multiply and the add as two IEEE operations (no
+// fused multiply-add: the result is what MulCommon followed by AddCommon gives, bit for bit).
+__global__ void mul_add_vec4(Iter<4> it, float *out, const float *a, const float *b, const float *c) {
+  pdl_prologue();
+  const uint32_t inner4 = (uint32_t)(it.shape[it.rank - 1] >> 2), total4 = (uint32_t)(it.total >> 2);
+  const int l = it.rank - 1;
+  const bool av = it.stride[1][l] == 1, bv = it.stride[2][l] == 1, cv = it.stride[3][l] == 1;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += gridDim.x * blockDim.x) {
+    uint32_t row = it.rank > 1 ? i / inner4 : 0;
+    const uint32_t c4 = i - row * inner4;
+    uint32_t off[4] = {c4 * 4, av ? c4 * 4 : 0, bv ? c4 * 4 : 0, cv ? c4 * 4 : 0};
+    for (int d = it.rank - 2; d >= 0; --d) {
+      uint32_t cc = row;
+      if (d > 0) { const uint32_t q = row / (uint32_t)it.shape[d]; cc = row - q * (uint32_t)it.shape[d]; row = q; }
+#pragma unroll
+      for (int o = 0; o < 4; ++o) off[o] += cc * (uint32_t)it.stride[o][d];
+    }
+    auto load = [](const float *p, uint32_t o, bool vec) {
+      if (vec) return *reinterpret_cast<const float4 *>(p + o);
+      const float t = p[o];
+      return make_float4(t, t, t, t);
+    };
+    const float4 x = load(a, off[1], av), y = load(b, off[2], bv), z = load(c, off[3], cv);
+    *reinterpret_cast<float4 *>(out + off[0]) =
+        make_float4(__fadd_rn(__fmul_rn(x.x, y.x), z.x), __fadd_rn(__fmul_rn(x.y, y.y), z.y),
+                    __fadd_rn(__fmul_rn(x.z, y.z), z.z), __fadd_rn(__fmul_rn(x.w, y.w), z.w));
+  }
+}
+__global__ void mul_add_generic(Iter<4> it, float *out, const float *a, const float *b, const float *c) {
+  pdl_prologue();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[4];
+    offsets_of(it, i, off);
+    out[off[0]] = __fadd_rn(__fmul_rn(a[off[1]], b[off[2]]), c[off[3]]);
+  }
+}
+
 bool vec4_ok(const Iter<3> &it, const void *out, const void *a, const void *b) {
   int l = it.rank - 1;
   if (it.shape[l] % 4 != 0 || it.stride[0][l] != 1) return false;
@@ -448,6 +485,41 @@ extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_
   FML_LAUNCH((where_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
       y ? (const float *)y->data : nullptr, y_scalar);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_mul_add(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c, const fml_tensor *out,
+                           void *stream) {
+  FML_REQUIRE(a && b && c && out, FML_BAD_ARG, "fml_mul_add: null tensor");
+  FML_REQUIRE(a->dtype == FML_F32 && b->dtype == FML_F32 && c->dtype == FML_F32 && out->dtype == FML_F32, FML_UNSUPPORTED,
+              "fml_mul_add: fp32 only");
+  Iter<4> it;
+  const fml_tensor *ins[3] = {a, b, c};
+  int st = make_iter(it, out, ins, "fml_mul_add");
+  if (st != FML_OK) return st;
+  if (it.total == 0) return FML_OK;
+  const int l = it.rank - 1;
+  bool ok = (it.shape[l] & 3) == 0 && it.stride[0][l] == 1 && aligned16(out->data) && aligned16(a->data) &&
+            aligned16(b->data) && aligned16(c->data) && it.total < (1ll << 30);
+  for (int o = 1; o < 4 && ok; ++o) {
+    ok = it.stride[o][l] == 1 || it.stride[o][l] == 0;
+    int64_t last = 0;
+    for (int d = 0; d < it.rank && ok; ++d) {
+      if (it.stride[o][d] < 0) ok = false;
+      last += (it.shape[d] - 1) * it.stride[o][d];
+      if (d < l && it.stride[o][l] != 0 && it.stride[o][d] % 4 != 0) ok = false;  // 16-byte rows for vector operands
+    }
+    ok = ok && last < (1ll << 31) - 8;
+  }
+  for (int d = 0; d < l && ok; ++d) ok = it.stride[0][d] % 4 == 0 && it.stride[0][d] >= 0;
+  if (ok) {
+    FML_LAUNCH((mul_add_vec4), grid_for(it.total / 4, 256), 256, 0, as_stream(stream), it, (float *)out->data,
+               (const float *)a->data, (const float *)b->data, (const float *)c->data);
+  } else {
+    FML_LAUNCH((mul_add_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), it, (float *)out->data,
+               (const float *)a->data, (const float *)b->data, (const float *)c->data);
+  }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }

@@ -146,6 +146,11 @@ int fml_elementwise(int op, const fml_tensor *a, const fml_tensor *b, const fml_
 int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor *out,
                   float c0, float c1, float c2, void *stream);
 
+/* MulCommonKernel followed by AddCommonKernel (mul.cpp, add.cpp) in one pass: out = a * b + c, all
+ * broadcast to out; two roundings, as the two kernels give (no fused multiply-add). */
+int fml_mul_add(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c, const fml_tensor *out,
+                void *stream);
+
 /* WhereConstantCond{ConstantScalarY,ConstantTensorY}Kernel (where.cpp:30-80, :90-150):
  * out = cond ? x : y, all broadcast to out.  y == NULL takes the scalar y_scalar. */
 int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_tensor *y, float y_scalar,

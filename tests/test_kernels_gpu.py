@@ -52,6 +52,26 @@ def test_binary_broadcast(op, name, sa, sb):
     assert np.array_equal(out.numpy(), ref)  # one IEEE operation per element: bit-exact
 
 
+@pytest.mark.parametrize("sa,sb,sc", [
+    ((8, 128, 6, 64), (8, 128, 6, 1), (8, 128, 6, 64)),   # ConvBERT's span convolution step: per-row weight
+    ((4, 16, 512, 32), (1, 1, 512, 32), (4, 16, 512, 32)),  # rotary embedding: table broadcast over batch and heads
+    ((3, 5, 7), (5, 1), (7,)),                             # ragged: the element-wise path
+    ((2, 6, 8), (2, 6, 8), (1,)),                          # scalar addend
+    ((0, 4), (4,), (4,)),
+])
+def test_mul_add_is_mul_then_add(sa, sb, sc):
+    """fml_mul_add rounds twice, like MulCommon followed by AddCommon: bit-exact against the oracle's
+    two kernels."""
+    a, b, c = rnd(*sa), rnd(*sb), rnd(*sc)
+    sp = np.broadcast_shapes(sa, sb)
+    so = np.broadcast_shapes(sp, sc)
+    prod = orc.binary("Mul", a, b, np.empty(sp, np.float32))
+    ref = orc.binary("Add", prod, c, np.empty(so, np.float32))
+    out = DT(so, np.float32)
+    cabi.mul_add(DT.from_numpy(a), DT.from_numpy(b), DT.from_numpy(c), out)
+    assert np.array_equal(out.numpy(), ref)
+
+
 @pytest.mark.parametrize("layouts", [((0, 1, 2), (2, 0, 1), (1, 2, 0)), ((2, 1, 0), (0, 1, 2), (0, 2, 1))])
 def test_binary_any_layout(layouts):
     la, lb, lo = layouts
