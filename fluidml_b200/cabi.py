@@ -189,6 +189,10 @@ def copy_strided(src, out, stream=None):
     check(lib().fml_copy_strided(_ref(src), _ref(out), stream))
 
 
+def concat2(lhs, rhs, out, axis, stream=None):
+    check(lib().fml_concat2(_ref(lhs), _ref(rhs), _ref(out), int(axis), stream))
+
+
 def reshape_copy(src, out, stream=None):
     check(lib().fml_reshape_copy(_ref(src), _ref(out), stream))
 

@@ -300,12 +300,8 @@ public:
   std::string GetKernelName() const override { return "Concat2Kernel"; }
   void Run(LaunchRecorder &rec, const fml_tensor &lhs, const fml_tensor &rhs,
            const fml_tensor &output) const override {
-    fml_tensor o0 = output, o1 = output;
-    o0.shape[axis_] = lhs.shape[axis_];
-    o1.shape[axis_] = rhs.shape[axis_];
-    o1.data = Offset(output, lhs.shape[axis_] * output.stride[axis_]);
-    rec.Add(GetKernelName(), [=](void *s) { return fml_copy_strided(&lhs, &o0, s); });
-    rec.Add(GetKernelName(), [=](void *s) { return fml_copy_strided(&rhs, &o1, s); });
+    const int axis = (int)axis_;
+    rec.Add(GetKernelName(), [=](void *s) { return fml_concat2(&lhs, &rhs, &output, axis, s); });
   }
 
 private:

@@ -499,3 +499,92 @@ extern "C" int fml_pad(const fml_tensor *in, const fml_tensor *out, const int64_
              (const float *)in->data);
   return FML_OK;
 }
+
+namespace fml {
+namespace {
+struct ConcatArgs {
+  int rank, axis;
+  uint32_t shape[kMaxDims];            // output shape, the innermost extent in units of V elements
+  int64_t ostride[kMaxDims], astride[kMaxDims], bstride[kMaxDims];
+  uint32_t split;                      // extent of the first operand along `axis` (in units of V if axis is innermost)
+  uint32_t total;                      // output elements / V
+};
+// Both halves of a two-operand Concat in one launch: an output element (or group of V along a
+// contiguous innermost dim) reads the first operand below the split and the second above it.
+template <typename T, int V>
+__global__ void concat2_kernel(const ConcatArgs a, T *out, const T *lhs, const T *rhs) {
+  pdl_prologue();
+  struct alignas(sizeof(T) * V) Vec { T v[V]; };
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += gridDim.x * blockDim.x) {
+    uint32_t lin = i;
+    int64_t oo = 0, ao = 0, bo = 0;
+    bool first = true;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      uint32_t c = lin;
+      if (d > 0) { const uint32_t q = lin / a.shape[d]; c = lin - q * a.shape[d]; lin = q; }
+      const int64_t unit = d == a.rank - 1 ? V : 1;
+      oo += (int64_t)c * unit * a.ostride[d];
+      if (d == a.axis) {
+        first = c < a.split;
+        ao += (int64_t)c * unit * a.astride[d];
+        bo += (int64_t)(c - a.split) * unit * a.bstride[d];
+      } else {
+        ao += (int64_t)c * unit * a.astride[d];
+        bo += (int64_t)c * unit * a.bstride[d];
+      }
+    }
+    *reinterpret_cast<Vec *>(out + oo) = *reinterpret_cast<const Vec *>(first ? lhs + ao : rhs + bo);
+  }
+}
+}  // namespace
+}  // namespace fml
+
+extern "C" int fml_concat2(const fml_tensor *lhs, const fml_tensor *rhs, const fml_tensor *out, int axis, void *stream) {
+  FML_REQUIRE(valid_tensor(lhs) && valid_tensor(rhs) && valid_tensor(out), FML_BAD_ARG, "fml_concat2: bad argument");
+  FML_REQUIRE(lhs->rank == out->rank && rhs->rank == out->rank && lhs->dtype == out->dtype && rhs->dtype == out->dtype,
+              FML_BAD_ARG, "fml_concat2: rank / dtype mismatch");
+  FML_REQUIRE(axis >= 0 && axis < out->rank, FML_BAD_ARG, "fml_concat2: axis %d out of range", axis);
+  int64_t total = 1;
+  for (int i = 0; i < out->rank; ++i) {
+    const int64_t want = i == axis ? lhs->shape[i] + rhs->shape[i] : lhs->shape[i];
+    FML_REQUIRE(out->shape[i] == want && (i == axis || rhs->shape[i] == lhs->shape[i]), FML_BAD_ARG,
+                "fml_concat2: shapes do not concatenate along axis %d", axis);
+    total *= out->shape[i];
+  }
+  if (total == 0) return FML_OK;
+  const size_t es = dtype_size(out->dtype);
+  if (total >= (1ll << 31) || (es != 4 && es != 8 && es != 1)) {  // beyond 32-bit indexing: the two strided copies
+    fml_tensor o0 = *out, o1 = *out;
+    o0.shape[axis] = lhs->shape[axis];
+    o1.shape[axis] = rhs->shape[axis];
+    o1.data = (char *)out->data + lhs->shape[axis] * out->stride[axis] * (int64_t)es;
+    int st = fml_copy_strided(lhs, &o0, stream);
+    return st != FML_OK ? st : fml_copy_strided(rhs, &o1, stream);
+  }
+  fml::ConcatArgs a;
+  a.rank = out->rank; a.axis = axis;
+  const int l = out->rank - 1;
+  // 16-byte groups along a contiguous innermost dim when every piece keeps the alignment
+  int V = es == 4 ? 4 : 1;
+  if (V == 4) {
+    bool ok = out->stride[l] == 1 && lhs->stride[l] == 1 && rhs->stride[l] == 1 && out->shape[l] % 4 == 0 &&
+              fml::aligned16(out->data) && fml::aligned16(lhs->data) && fml::aligned16(rhs->data) &&
+              (axis != l || (lhs->shape[l] % 4 == 0 && rhs->shape[l] % 4 == 0));
+    for (int d = 0; d < l && ok; ++d)
+      ok = out->stride[d] % 4 == 0 && lhs->stride[d] % 4 == 0 && rhs->stride[d] % 4 == 0;
+    if (!ok) V = 1;
+  }
+  for (int d = 0; d < out->rank; ++d) {
+    a.shape[d] = (uint32_t)(d == l ? out->shape[d] / V : out->shape[d]);
+    a.ostride[d] = out->stride[d]; a.astride[d] = lhs->stride[d]; a.bstride[d] = rhs->stride[d];
+  }
+  a.split = (uint32_t)(axis == l ? lhs->shape[axis] / V : lhs->shape[axis]);
+  a.total = (uint32_t)(total / V);
+  cudaStream_t s = fml::as_stream(stream);
+  const int grid = fml::grid_for(a.total, 256);
+  if (V == 4) FML_LAUNCH((fml::concat2_kernel<uint32_t, 4>), grid, 256, 0, s, a, (uint32_t *)out->data, (const uint32_t *)lhs->data, (const uint32_t *)rhs->data);
+  else if (es == 4) FML_LAUNCH((fml::concat2_kernel<uint32_t, 1>), grid, 256, 0, s, a, (uint32_t *)out->data, (const uint32_t *)lhs->data, (const uint32_t *)rhs->data);
+  else if (es == 8) FML_LAUNCH((fml::concat2_kernel<uint64_t, 1>), grid, 256, 0, s, a, (uint64_t *)out->data, (const uint64_t *)lhs->data, (const uint64_t *)rhs->data);
+  else FML_LAUNCH((fml::concat2_kernel<uint8_t, 1>), grid, 256, 0, s, a, (uint8_t *)out->data, (const uint8_t *)lhs->data, (const uint8_t *)rhs->data);
+  return FML_OK;
+}

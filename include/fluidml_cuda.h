@@ -163,6 +163,8 @@ int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_tensor *y, 
  * offset views of the output) and the interior of Pad (pad.cpp:15-51) through it.
  * Bit-exact for every dtype. */
 int fml_copy_strided(const fml_tensor *in, const fml_tensor *out, void *stream);
+/* Concat2Kernel (concat.cpp): out = lhs followed by rhs along `axis`, both halves in one launch. */
+int fml_concat2(const fml_tensor *lhs, const fml_tensor *rhs, const fml_tensor *out, int axis, void *stream);
 
 /* ReshapeKernel / UnsqueezeKernel / SqueezeKernel / FlattenKernel (reshape.cpp:18-64,
  * unsqueeze.cpp:20-63, squeeze.cpp:17-54, flatten.cpp:15-63): the e-th element in logical

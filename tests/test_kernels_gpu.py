@@ -72,6 +72,27 @@ def test_mul_add_is_mul_then_add(sa, sb, sc):
     assert np.array_equal(out.numpy(), ref)
 
 
+@pytest.mark.parametrize("sa,sb,axis,dtype", [
+    ((4, 16, 64, 16), (4, 16, 64, 16), 3, np.float32),   # rotary halves: 16-byte groups, split inside the innermost dim
+    ((2, 8, 12, 32), (2, 4, 12, 32), 1, np.float32),     # 16-byte groups, split along an outer dim
+    ((2, 3, 5), (2, 4, 5), 1, np.float32),               # ragged rows: element path
+    ((3, 7), (3, 2), 1, np.float32),
+    ((2, 5), (3, 5), 0, np.int64),
+    ((0, 4), (2, 4), 0, np.float32),
+])
+def test_concat2_in_one_launch(sa, sb, axis, dtype):
+    a = (RNG.standard_normal(sa) * 100).astype(dtype)
+    b = (RNG.standard_normal(sb) * 100).astype(dtype)
+    ref = np.concatenate([a, b], axis=axis)
+    out = DT(ref.shape, dtype)
+    cabi.concat2(DT.from_numpy(a), DT.from_numpy(b), out, axis)
+    assert np.array_equal(out.numpy(), ref)
+    if len(sa) == 3:  # operands and output in permuted layouts
+        out = DT(ref.shape, dtype, [1, 2, 0])
+        cabi.concat2(DT.from_numpy(a, [2, 0, 1]), DT.from_numpy(b, [0, 2, 1]), out, axis)
+        assert np.array_equal(out.numpy(), ref)
+
+
 @pytest.mark.parametrize("layouts", [((0, 1, 2), (2, 0, 1), (1, 2, 0)), ((2, 1, 0), (0, 1, 2), (0, 2, 1))])
 def test_binary_any_layout(layouts):
     la, lb, lo = layouts
