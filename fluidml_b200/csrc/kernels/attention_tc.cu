@@ -98,7 +98,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !g_drop_loads) {  // (the wait test switches the loads off)
       bool ok = true;
       mbar_expect_tx(bar_q, q_bytes);
       for (int d = 0; d < dblk; ++d) tma_load_4d(smem_u32(q_hi) + (uint32_t)d * 16384u, &map_q, bar_q, d * 32, q0, h * a.q_h, b * a.q_b);

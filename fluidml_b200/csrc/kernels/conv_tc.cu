@@ -202,7 +202,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !g_drop_loads) {  // (the wait test switches the loads off)
       bool ok = true;
       int kb = 0, raw_issued = 0, b_issued = 0;
       for (int icb = icb_lo; icb < icb_hi && ok; ++icb) {

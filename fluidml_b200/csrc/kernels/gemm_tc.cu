@@ -187,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // with a constant B the producer fills the B half of the first stages right away, so that
   // HBM latency overlaps the tail of that kernel; the A halves follow after the wait.
   int pre_b = 0;
-  if (a.p.b_constant && warp == 0 && lane == 0) {
+  if (a.p.b_constant && warp == 0 && lane == 0 && !g_drop_loads) {
     const int cb2 = a.p.b_b0 ? z0 : 0, cb3 = a.p.b_b1 ? z1 : 0;
     pre_b = min(a.stages, nkb);
     for (int it = 0; it < pre_b; ++it) {
@@ -216,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !g_drop_loads) {  // (the wait test switches the loads off: every wait below then runs out)
       const int ca2 = a.p.a_b0 ? z0 : 0, ca3 = a.p.a_b1 ? z1 : 0;
       const int cb2 = a.p.b_b0 ? z0 : 0, cb3 = a.p.b_b1 ? z1 : 0;
       int issued = 0;

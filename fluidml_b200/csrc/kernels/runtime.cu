@@ -236,7 +236,23 @@ std::vector<cudaError_t (*)(unsigned long long *, unsigned *, unsigned)> &trace_
 void register_trace_setter(cudaError_t (*setter)(unsigned long long *, unsigned *, unsigned)) {
   trace_setters().push_back(setter);
 }
+namespace {
+std::vector<cudaError_t (*)(uint32_t, int)> &wait_test_setters() {
+  static std::vector<cudaError_t (*)(uint32_t, int)> v;
+  return v;
+}
+}  // namespace
+void register_wait_test_setter(cudaError_t (*setter)(uint32_t, int)) { wait_test_setters().push_back(setter); }
 }  // namespace fml
+// Test hook: iteration limit of every bounded mbarrier wait of the tensor-core kernels (0 restores
+// the default) and whether their producers skip their loads.  With (small limit, 1) a launch's
+// waits all run out: the kernel sets the status bit fml_check_device reports as
+// FML_DEVICE_TIMEOUT and returns; the context stays usable.  Synchronises the device.
+extern "C" int fml_debug_wait_test(unsigned limit, int drop_loads) {
+  FML_CUDA(cudaDeviceSynchronize());
+  for (auto f : fml::wait_test_setters()) FML_CUDA(f(limit ? limit : (1u << 22), drop_loads));
+  return FML_OK;
+}
 // buf = device array of `cap` 64-bit stamps, cursor = device counter (zeroed by the caller).
 // NULL buf switches the stamps off.  Synchronises (the pointers are module variables).
 extern "C" int fml_set_kernel_trace(void *buf, void *cursor, unsigned cap) {

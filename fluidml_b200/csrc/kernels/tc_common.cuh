@@ -9,6 +9,19 @@ namespace fml {
 
 constexpr int kBM = 128;
 constexpr uint32_t kSpinLimit = 1u << 22;
+// Test hook for the bounded waits (fml_debug_wait_test): a shorter iteration limit, and a switch
+// that makes the producers of the tensor-core kernels issue no loads, so that every wait of a
+// launch runs out, the kernel reports kStatusTimeout and returns -- nothing faults, nothing hangs,
+// no copy is in flight.  Each translation unit has its own copy; the setter sets them all.
+static __device__ uint32_t g_wait_limit = kSpinLimit;
+static __device__ int g_drop_loads = 0;
+void register_wait_test_setter(cudaError_t (*setter)(uint32_t, int));
+static cudaError_t set_wait_test_this_unit(uint32_t limit, int drop) {
+  cudaError_t e = cudaMemcpyToSymbol(g_wait_limit, &limit, sizeof(limit));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_drop_loads, &drop, sizeof(drop));
+  return e;
+}
+static struct WaitTestRegistrar { WaitTestRegistrar() { register_wait_test_setter(&set_wait_test_this_unit); } } g_wait_test_registrar;
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -26,7 +39,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 // Bounded wait: false when the limit ran out or another role raised `abort`.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  const uint32_t limit = g_wait_limit;
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -102,6 +102,11 @@ int fml_set_kernel_trace(void *buf, void *cursor, unsigned cap);
  * gather index is clamped.  Synchronises `stream`.  Returns FML_OK, FML_DEVICE_TIMEOUT or
  * FML_INDEX_OUT_OF_RANGE. */
 int fml_check_device(void *stream);
+/* Test hook for the failure path: sets the iteration limit of every bounded wait in the
+ * tensor-core kernels (0 = default) and, with drop_loads != 0, makes their producers issue no
+ * loads, so that a launch's waits run out, the kernel reports the timeout through the status
+ * word and returns.  Nothing faults or hangs.  Restore with (0, 0). */
+int fml_debug_wait_test(unsigned limit, int drop_loads);
 
 /* ---------------------------------------------------------------- elementwise
  * Binary ops broadcast numpy-style (right-aligned; size-1 dims pinned to index 0), as
