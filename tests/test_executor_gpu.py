@@ -60,6 +60,20 @@ def test_bert_two_layers_all_modes(bert2, factory, fusion):
         assert st["flow_nodes"] < st["graph_nodes"]
 
 
+def test_fused_mul_add_chain_equals_the_unfused_plan_bit_for_bit():
+    """FusedMulAdd rounds twice like the Mul and Add kernels it replaces: both plans agree exactly."""
+    from test_host_cpu import _mul_add_chain
+    m = _mul_add_chain()
+    rng = np.random.Generator(np.random.PCG64(5))
+    x = {vi.name: rng.standard_normal(vi.shape).astype(np.float32) for vi in m.inputs}
+    a, _ = run(m, x, Executor.make_dp_greedy, fusion=0)
+    b, ex = run(m, x, Executor.make_dp_greedy, fusion=1)
+    assert np.array_equal(a["y"], b["y"])
+    ref = orc.run_model(m, x)["y"]
+    assert np.array_equal(b["y"], ref)
+    assert ex.stats()["launches"] == 7  # two fused pairs, two plain products, the Relu, two Adds
+
+
 # single-pass TF32 is an option, not the default: it misses the 1e-3 bar (element-wise up to ~2e-2)
 @pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("3xtf32", 1e-4), ("tf32", 4e-2)])
 def test_bert_gemm_precisions(bert2, precision, tol):

@@ -214,6 +214,28 @@ def test_fusion_passes_on_bert(bert_bytes):
         assert gone not in fused, gone
 
 
+def _mul_add_chain():
+    """y = ((x0*w0 + x1*w1) + x2*w2 + x3*w3) + relu(x3*w3): the last product has two consumers."""
+    g = models.GraphBuilder("chain")
+    xs = [g.input(f"x{i}", FLOAT, (2, 8, 6, 16)) for i in range(4)]
+    ws = [g.input(f"w{i}", FLOAT, (2, 8, 6, 1)) for i in range(4)]
+    acc = g.add(g.mul(xs[0], ws[0]), g.mul(xs[1], ws[1]))
+    acc = g.add(acc, g.mul(xs[2], ws[2]))
+    shared = g.mul(xs[3], ws[3])
+    acc = g.add(acc, shared)
+    g.add(acc, g.relu(shared), out="y")
+    g.output("y")
+    return g.finish()
+
+
+def test_mul_add_pairs_are_fused_when_the_product_has_one_consumer():
+    m = _mul_add_chain()
+    unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
+    assert unfused.count("MulCommon") == 4 and unfused.count("AddCommon") == 4
+    # one product of the first Add and x2*w2 ride in their Adds; x3*w3 also feeds the Relu and stays a Mul
+    assert fused.count("FusedMulAdd") == 2 and fused.count("MulCommon") == 2 and fused.count("AddCommon") == 2
+
+
 @pytest.mark.parametrize("factory", [Executor.make_plain_linear, Executor.make_plain_greedy, Executor.make_dp_greedy])
 def test_plan_is_consistent(bert_bytes, factory):
     with tempfile.TemporaryDirectory() as d:
