@@ -225,7 +225,13 @@ struct DwArgs {
   int row_tiles;        // bands per plane
   int vec;              // input rows can be fetched as aligned float4
   int planes;           // N * C
+  // ceil(2^32 / d) for d = PH * PWn, PWn and C: exact quotients by one multiply for dividends
+  // below 2^16 (the flat staging walk divides every element index three times; with hardware
+  // division the reciprocal unit was the busiest pipe of the kernel)
+  uint32_t m_plane, m_pwn, m_c;
 };
+
+__device__ __forceinline__ uint32_t div_magic(uint32_t n, uint32_t d, uint32_t magic) { return d == 1 ? n : __umulhi(n, magic); }
 
 template <int ACT>
 __device__ __forceinline__ void dw_store_row(float *yp, const float *v, float bias, bool vec, int valid, int64_t ys3) {
@@ -271,6 +277,7 @@ __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs 
   // that a CTA's few dozen loads per thread overlap instead of queueing behind each other's latency.
   if (!d.vec) {
     const int per_plane_elems = d.PH * d.PWn, total = d.PP * per_plane_elems;
+    const int xs0 = (int)a.xs[0], xs1 = (int)a.xs[1], xs2 = (int)a.xs[2];  // the launcher checked that offsets fit 31 bits
     for (int base = tid; base < total; base += 1024) {
       float v[4];
       int at[4];
@@ -280,12 +287,13 @@ __global__ void __launch_bounds__(256) conv_depthwise_tiled_kernel(const DwArgs 
         v[u] = 0.0f;
         at[u] = -1;
         if (e < total) {
-          const int pl = e / per_plane_elems, rem = e - pl * per_plane_elems;
-          const int pr = rem / d.PWn, pc = rem - pr * d.PWn;
-          const int ih = ih0 + pr, iw = pc - pw, lin = c0 + pl, nn = n0 + lin / C, ch = lin - (lin / C) * C;
+          const int pl = (int)div_magic((uint32_t)e, (uint32_t)per_plane_elems, d.m_plane), rem = e - pl * per_plane_elems;
+          const int pr = (int)div_magic((uint32_t)rem, (uint32_t)d.PWn, d.m_pwn), pc = rem - pr * d.PWn;
+          const int lin = c0 + pl, dn = (int)div_magic((uint32_t)lin, (uint32_t)C, d.m_c);
+          const int ih = ih0 + pr, iw = pc - pw, nn = n0 + dn, ch = lin - dn * C;
           at[u] = (pl * d.PH + pr) * d.pitch + pc;
           if (plane0 + pl < d.planes && ih >= 0 && ih < IH && iw >= 0 && iw < IW)
-            v[u] = a.x[nn * a.xs[0] + ch * a.xs[1] + ih * a.xs[2] + iw];
+            v[u] = a.x[nn * xs0 + ch * xs1 + ih * xs2 + iw];
         }
       }
 #pragma unroll
@@ -419,6 +427,10 @@ static bool launch_depthwise_tiled(const ConvArgs &a, const void *x_base, cudaSt
   }
   d.row_tiles = (RW + d.TR - 1) / d.TR;
   const size_t smem = smem_of();
+  auto magic = [](int64_t dv) { return (uint32_t)((0x100000000ull + (uint64_t)dv - 1) / (uint64_t)dv); };
+  d.m_plane = magic((int64_t)d.PH * d.PWn); d.m_pwn = magic(d.PWn); d.m_c = magic(a.OC);
+  if ((int64_t)d.PP * d.PH * d.PWn >= 65536 || a.OC + d.PP >= 65536) return false;  // the magic division's range
+  if (a.N * a.xs[0] >= (1ll << 31) || a.xs[0] < 0 || a.xs[1] < 0 || a.xs[2] < 0) return false;  // 31-bit input offsets
   d.vec = (a.IW % 4 == 0) && (a.xs[2] % 4 == 0) && (a.xs[1] % 4 == 0) && (a.xs[0] % 4 == 0) &&
           ((reinterpret_cast<uintptr_t>(x_base) & 15) == 0) ? 1 : 0;
   const int64_t ctas = (int64_t)((d.planes + d.PP - 1) / d.PP) * d.row_tiles;
