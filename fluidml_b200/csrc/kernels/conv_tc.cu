@@ -583,6 +583,19 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   const int a_cols = (three ? 2 : 1) * icb;
   stages = std::min(stages, (512 - (a.tile_n + 31) / 32 * 32) / a_cols);
   stages = std::max(2, std::min(std::min(stages, 8), a.n_icb * a.taps));
+  {
+    // A layer whose tiles are more than one wave of SMs runs two CTAs per SM with short rings
+    // rather than one with deep ones: the second CTA's loads, conversions and epilogue fill the
+    // gaps of the first (192 pointwise tiles of 7 x 7 maps took two rounds of 148 at one CTA per
+    // SM: 128 -> 79 us; VGG's 64 -> 64 layer at 224 x 224, batch 32: 86 -> 141 TFLOP/s; 128 -> 128
+    // at 112 x 112: 160 -> 203).  FLUIDML_CONV_RING=deep keeps the deep rings.
+    static const bool deep = [] { const char *e = getenv("FLUIDML_CONV_RING"); return e && e[0] == 'd'; }();
+    const int64_t ctas = (int64_t)((a.OW + a.TW - 1) / a.TW) * ((a.OH + a.TH - 1) / a.TH) * a.N * ((a.OC + a.tile_n - 1) / a.tile_n);
+    if (!deep && ctas > 148 && a.tile_n <= 128) {
+      stages = std::min(stages, 2);
+      a.raw_stages = a.taps == 1 ? std::min(a.raw_stages, 3) : 1;
+    }
+  }
   a.stages = stages;
   a.tiles_w = (a.OW + a.TW - 1) / a.TW;
   a.tiles_h = (a.OH + a.TH - 1) / a.TH;
