@@ -48,6 +48,9 @@ int *device_status_word() {
 
 }  // namespace fml
 
+// Takes the device status word: *out = old value, word = 0.  `out` is pinned host memory.
+static __global__ void status_take_kernel(int *word, int *out) { *out = atomicExch(word, 0); }
+
 using namespace fml;
 
 extern "C" {
@@ -204,15 +207,16 @@ int fml_warmup(void) {
 int fml_check_device(void *stream) {
   int *w = device_status_word();
   FML_REQUIRE(w, FML_CUDA_ERROR, "fml_check_device: no status word");
-  // The status word rides the stream into a pinned host word, so that one synchronisation serves
-  // both the caller's work and the check (a blocking copy after the synchronise costs a second
-  // round trip on every Invoke).  One pinned word per calling thread.
+  // One launch on the caller's stream takes the word (atomic exchange with 0, so a bit another
+  // stream's kernel sets at the same moment is either taken now or left for the next check, never
+  // lost) and writes it to a pinned host word; one synchronisation then serves both the caller's
+  // work and the check.  One pinned word per calling thread.
   static thread_local int *pinned = nullptr;
   if (!pinned) FML_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&pinned), sizeof(int), cudaHostAllocDefault));
-  FML_CUDA(cudaMemcpyAsync(pinned, w, sizeof(int), cudaMemcpyDeviceToHost, as_stream(stream)));
+  status_take_kernel<<<1, 1, 0, as_stream(stream)>>>(w, pinned);
+  FML_CUDA(cudaGetLastError());
   FML_CUDA(cudaStreamSynchronize(as_stream(stream)));
   const int v = *pinned;
-  if (v) FML_CUDA(cudaMemset(w, 0, sizeof(int)));
   if (v & kStatusTimeout) {
     set_error("a bounded device-side wait expired");
     return FML_DEVICE_TIMEOUT;
