@@ -176,6 +176,12 @@ def mul_add(a, b, c, out, stream=None):
     check(lib().fml_mul_add(_ref(a), _ref(b), _ref(c), _ref(out), stream))
 
 
+def squeeze_excite_gate(x, w1, b1, w2, b2, act1, act2, gate, stream=None):
+    """ReduceMean over H, W -> 1x1 conv (+act1) -> 1x1 conv (+act2) in one launch; b1 / b2 may be None."""
+    check(lib().fml_squeeze_excite_gate(_ref(x), _ref(w1), _ref(b1), _ref(w2), _ref(b2), int(act1), int(act2),
+                                        _ref(gate), stream))
+
+
 def bias_gelu(x, bias, out, c0, c1, c2, stream=None):
     check(lib().fml_bias_gelu(_ref(x), _ref(bias), _ref(out), ctypes.c_float(c0),
                               ctypes.c_float(c1), ctypes.c_float(c2), stream))

@@ -235,6 +235,12 @@ size_t CostModel::GetTimeCost(const flow::Node &n, const std::vector<Layout> &in
     cost = kLaunchNs + std::max(flops / kFp32FlopsPerNs, bytes / kHbmBytesPerNs) * (dflt ? 1.0 : 8.0);
     break;
   }
+  case Kind::SqueezeExciteGate: {
+    // one pass over x (planes read along their rows), a few kilobytes of weights, two cluster phases
+    const bool dflt = IsRowMajor(n.inputs[0]->meta.GetShape(), is[0]);
+    cost = kLaunchNs + 2000.0 + (double)n.inputs[0]->meta.GetSize() / kHbmBytesPerNs * (dflt ? 1.0 : 8.0);
+    break;
+  }
   default: {  // elementwise, gathers, where, slice, concat, pad, reduce-mean
     cost = kLaunchNs + write_cost;
     for (size_t i = 0; i < n.inputs.size(); ++i) cost += read_cost(*n.inputs[i], is[i]);

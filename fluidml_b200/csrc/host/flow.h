@@ -53,6 +53,7 @@ enum class Kind {
   Silu,            // x * sigmoid(x)
   FusedAttention,  // softmax(Q K^T / divisor + mask) V; inputs: Q, K^T, V, [mask]
   FusedMulAdd,     // a * b + c, broadcast; inputs: a, b, c
+  SqueezeExciteGate,  // act2(W2 act1(W1 mean_hw(x) + b1) + b2); consts: W1, [b1], W2, [b2]; has_bias / has_bias2 = b1 / b2 present; act, act2
 };
 const char *KindName(Kind k);
 
@@ -78,6 +79,8 @@ struct Node {
   // fused GEMM epilogue
   float divisor = 1.0f;
   int act = 0;
+  int act2 = 0;            // SqueezeExciteGate: activation of the second layer
+  bool has_bias2 = false;  // SqueezeExciteGate: the second layer has a bias
   float act_param[3] = {1.4142135381698608f, 1.0f, 0.5f};
   bool has_bias = false, has_residual = false, has_mask = false;
   bool b_is_const = false;  // FusedGemm: B is a captured constant (consts[0]) rather than inputs[1]

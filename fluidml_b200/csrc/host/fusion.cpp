@@ -357,6 +357,51 @@ bool FuseMulAdd(Rewriter &rw, const NodePtr &mul) {
   return true;
 }
 
+// ---- ReduceMean over H, W -> 1 x 1 Conv (+act) -> 1 x 1 Conv (+act): the gate of a squeeze-and-
+// excite block.  Three launches that move a few kilobytes each become one (FLUIDML_FUSE_SE=0
+// keeps them apart, for comparisons).
+bool FuseSqueezeExcite(Rewriter &rw, const NodePtr &rm) {
+  static const bool enabled = [] { const char *e = getenv("FLUIDML_FUSE_SE"); return !(e && e[0] == '0'); }();
+  if (!enabled || rm->kind != Kind::ReduceMean) return false;
+  const RegionPtr &x = rm->inputs[0];
+  if (x->meta.GetRank() != 4 || x->meta.GetType() != Type::kFloat32) return false;
+  std::vector<int64_t> axes = rm->axes;
+  std::sort(axes.begin(), axes.end());
+  if (axes != std::vector<int64_t>{2, 3}) return false;
+  auto gate_conv = [](const NodePtr &cv, int64_t in_channels) {
+    if (!cv || cv->group != 1 || cv->consts.empty() || cv->inputs.size() != 1) return false;
+    const auto &ws = cv->consts[0]->meta.GetShape();
+    if (ws.size() != 4 || ws[1] != in_channels || ws[2] != 1 || ws[3] != 1) return false;
+    if (cv->consts[0]->meta.GetType() != Type::kFloat32 || !utils::IsDefaultLayout(cv->consts[0]->layout)) return false;
+    if (cv->has_bias && (cv->consts.size() < 2 || cv->consts[1]->meta.GetElementsNum() != ws[0])) return false;
+    for (int64_t s : cv->strides) if (s != 1) return false;
+    for (int64_t d : cv->dilations) if (d != 1) return false;
+    return cv->act == FML_ACT_NONE || cv->act == FML_ACT_RELU || cv->act == FML_ACT_TANH || cv->act == FML_ACT_SIGMOID ||
+           cv->act == FML_ACT_SILU;
+  };
+  const int64_t C = x->meta.GetShape()[1];
+  NodePtr c1 = rw.SoleOfKind(rm->output, Kind::ConvWithoutPadding);
+  if (!gate_conv(c1, C)) return false;
+  const int64_t Cr = c1->consts[0]->meta.GetShape()[0];
+  NodePtr c2 = rw.SoleOfKind(c1->output, Kind::ConvWithoutPadding);
+  if (!gate_conv(c2, Cr) || c2->consts[0]->meta.GetShape()[0] != C) return false;
+  if (C > 4096 || Cr > 512 || x->meta.GetShape()[0] > 65535) return false;  // limits of fml_squeeze_excite_gate
+  rm->kind = Kind::SqueezeExciteGate;
+  rm->consts.clear();
+  rm->consts.push_back(c1->consts[0]);
+  if (c1->has_bias) rm->consts.push_back(c1->consts[1]);
+  rm->consts.push_back(c2->consts[0]);
+  if (c2->has_bias) rm->consts.push_back(c2->consts[1]);
+  rm->has_bias = c1->has_bias;
+  rm->has_bias2 = c2->has_bias;
+  rm->act = c1->act;
+  rm->act2 = c2->act;
+  rm->output = c2->output;
+  rw.Kill(c1);
+  rw.Kill(c2);
+  return true;
+}
+
 // ---- Conv -> SiLU: the activation rides in the convolution's epilogue
 bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
   if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
@@ -479,7 +524,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseMulAdd};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseMulAdd};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

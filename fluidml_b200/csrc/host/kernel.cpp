@@ -232,6 +232,28 @@ public:
   }
 };
 
+// ReduceMean over H, W -> 1 x 1 Conv -> 1 x 1 Conv (the gate of a squeeze-and-excite block) in one
+// launch (reduce_mean.cpp + conv.cpp twice in the reference)
+class SqueezeExciteGateKernel : public SingleInputWithoutBufferKernel {
+public:
+  SqueezeExciteGateKernel(fml_tensor w1, bool has_b1, fml_tensor b1, fml_tensor w2, bool has_b2, fml_tensor b2, int act1, int act2)
+      : w1_(w1), b1_(b1), w2_(w2), b2_(b2), has_b1_(has_b1), has_b2_(has_b2), act1_(act1), act2_(act2) {}
+  std::string GetKernelName() const override { return "SqueezeExciteGateKernel"; }
+  void Run(LaunchRecorder &rec, const fml_tensor &input, const fml_tensor &output) const override {
+    const fml_tensor w1 = w1_, b1 = b1_, w2 = w2_, b2 = b2_;
+    const bool hb1 = has_b1_, hb2 = has_b2_;
+    const int a1 = act1_, a2 = act2_;
+    rec.Add(GetKernelName(), [=](void *s) {
+      return fml_squeeze_excite_gate(&input, &w1, hb1 ? &b1 : nullptr, &w2, hb2 ? &b2 : nullptr, a1, a2, &output, s);
+    });
+  }
+
+private:
+  fml_tensor w1_, b1_, w2_, b2_;
+  bool has_b1_, has_b2_;
+  int act1_, act2_;
+};
+
 // ------------------------------------------------------------------ data movement
 // reshape.cpp:18-64, unsqueeze.cpp:20-63, squeeze.cpp:17-54, flatten.cpp:15-63
 class ReshapeLikeKernel : public SingleInputWithoutBufferKernel {
@@ -647,6 +669,14 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
   case Kind::Sigmoid: return std::make_unique<SigmoidKernel>();
   case Kind::Silu: return std::make_unique<SiluKernel>();
   case Kind::FusedMulAdd: return std::make_unique<FusedMulAddKernel>();
+  case Kind::SqueezeExciteGate: {
+    size_t k = 0;
+    const fml_tensor w1 = C(k++);
+    const fml_tensor b1 = n.has_bias ? C(k++) : fml_tensor{};
+    const fml_tensor w2 = C(k++);
+    const fml_tensor b2 = n.has_bias2 ? C(k++) : fml_tensor{};
+    return std::make_unique<SqueezeExciteGateKernel>(w1, n.has_bias, b1, w2, n.has_bias2, b2, n.act, n.act2);
+  }
   case Kind::AddCommon: return std::make_unique<AddCommonKernel>();
   case Kind::MulCommon: return std::make_unique<MulCommonKernel>();
   case Kind::DivCommon: return std::make_unique<DivCommonKernel>();
@@ -766,7 +796,7 @@ const char *KindName(Kind k) {
       "Not", "Pad", "Pow", "ReduceMean", "Relu", "Reshape", "Slice", "Softmax", "Sqrt", "Squeeze", "SubConstantLhs",
       "SubCommon", "Tanh", "Transpose", "Unsqueeze", "UnsqueezeSubLhsScalarMulRhsScalar",
       "WhereConstantCondConstantScalarY", "WhereConstantCondConstantTensorY", "Sigmoid", "Identity", "FusedGemm",
-      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd"};
+      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd", "SqueezeExciteGate"};
   return names[(int)k];
 }
 }  // namespace flow

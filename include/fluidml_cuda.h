@@ -156,6 +156,17 @@ int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor 
 int fml_mul_add(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c, const fml_tensor *out,
                 void *stream);
 
+/* The gate of a squeeze-and-excite block: ReduceMeanKernel over the two spatial axes
+ * (reduce_mean.cpp:16-98) followed by two 1 x 1 ConvWithoutPaddingKernel launches over the single
+ * remaining pixel (conv.cpp:27-280), in one launch:
+ *   gate[n, c, 0, 0] = act2(b2[c] + sum_j w2[c, j] * act1(b1[j] + sum_k w1[j, k] * mean(x[n, k, :, :])))
+ * x [N, C, H, W] (any strides; dense planes are the fast case), w1 [Cr, C(, 1, 1)], w2 [C, Cr(, 1, 1)],
+ * b1 / b2 may be NULL, act1 / act2 from fml_activation (none, relu, tanh, sigmoid, silu).  At most
+ * 4096 channels and 512 hidden units (FML_UNSUPPORTED beyond). */
+int fml_squeeze_excite_gate(const fml_tensor *x, const fml_tensor *w1, const fml_tensor *b1,
+                            const fml_tensor *w2, const fml_tensor *b2, int act1, int act2,
+                            const fml_tensor *gate, void *stream);
+
 /* WhereConstantCond{ConstantScalarY,ConstantTensorY}Kernel (where.cpp:30-80, :90-150):
  * out = cond ? x : y, all broadcast to out.  y == NULL takes the scalar y_scalar. */
 int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_tensor *y, float y_scalar,

@@ -226,6 +226,11 @@ def test_efficientnet_b0_and_full_size_vgg():
         outs, ex = run(e, xe, factory)
         assert relerr(outs["logits"], ref["logits"]) <= TOL
         assert "SiluKernel" not in ex.stats()["kernels"]  # every SiLU rides in a convolution epilogue
+        # each block's ReduceMean -> Conv -> Conv gate is one launch
+        assert ex.stats()["kernels"].get("SqueezeExciteGateKernel") == 16 and "ReduceMeanKernel" not in ex.stats()["kernels"]
+    # the same model with every fusion off (separate ReduceMean and gate convolutions) agrees too
+    outs, ex = run(e, xe, Executor.make_dp_greedy, fusion=0)
+    assert relerr(outs["logits"], ref["logits"]) <= TOL and ex.stats()["kernels"].get("ReduceMeanKernel") == 16
     # full-size EfficientNet-B0 (224 x 224: every map size from 112 down to 7 and 1) against the
     # oracle, again with weights wide enough for the logits to carry signal
     full = models.build_efficientnet_b0(std=0.16)

@@ -72,6 +72,60 @@ def test_mul_add_is_mul_then_add(sa, sb, sc):
     assert np.array_equal(out.numpy(), ref)
 
 
+def _oracle_act(v, act):
+    v = v.astype(np.float32)
+    if act == 2:
+        return np.maximum(v, np.float32(0))
+    if act == 4:
+        return orc.unary("Sigmoid", v, np.empty_like(v))
+    if act == 5:
+        return orc.binary("Mul", v, orc.unary("Sigmoid", v, np.empty_like(v)), np.empty_like(v))
+    return v
+
+
+@pytest.mark.parametrize("n,c,h,w,cr,act1,act2,bias,layout", [
+    (1, 32, 112, 112, 8, 5, 4, True, None),      # EfficientNet's first block: large planes, CTA per plane
+    (1, 144, 56, 56, 6, 5, 4, True, None),
+    (2, 240, 28, 28, 10, 5, 4, True, None),      # warp per plane
+    (1, 1152, 7, 7, 48, 5, 4, True, None),       # last stage: odd plane size
+    (3, 20, 5, 3, 7, 2, 0, False, None),         # ragged everything, relu / none, no biases
+    (2, 5, 4, 4, 3, 0, 4, True, None),           # fewer channels than a full cluster
+    (2, 24, 6, 10, 4, 5, 4, True, (0, 2, 3, 1)), # channel-innermost x: strided planes
+    (0, 8, 4, 4, 2, 5, 4, True, None),           # empty batch
+])
+def test_squeeze_excite_gate_matches_the_three_kernels(n, c, h, w, cr, act1, act2, bias, layout):
+    """fml_squeeze_excite_gate against the oracle's ReduceMean -> Conv -> Conv (activations applied
+    with the oracle's own kernels).  fp32 sums in another order: 2e-6 of the largest gate value
+    plus 1e-6 absolute."""
+    x = rnd(n, c, h, w)
+    w1, w2 = rnd(cr, c, 1, 1) * np.float32(0.3), rnd(c, cr, 1, 1) * np.float32(0.5)
+    b1 = rnd(cr) if bias else None
+    b2 = rnd(c) if bias else None
+    gate = DT((n, c, 1, 1), np.float32)
+    cabi.squeeze_excite_gate(DT.from_numpy(x, layout), DT.from_numpy(w1), DT.from_numpy(b1) if bias else None,
+                             DT.from_numpy(w2), DT.from_numpy(b2) if bias else None, act1, act2, gate)
+    got = gate.numpy()
+    if n == 0:
+        assert got.shape == (0, c, 1, 1)
+        return
+    mean = orc.reduce_mean(x, np.empty((n, c, 1, 1), np.float32), (2, 3))
+    hid = orc.conv(mean, w1, b1, np.empty((n, cr, 1, 1), np.float32), [0, 0, 0, 0], [1, 1], [1, 1])
+    hid = _oracle_act(hid, act1)
+    ref = orc.conv(hid, w2, b2, np.empty((n, c, 1, 1), np.float32), [0, 0, 0, 0], [1, 1], [1, 1])
+    ref = _oracle_act(ref, act2)
+    tol = 2e-6 * float(np.abs(ref).max()) + 1e-6
+    assert float(np.abs(got - ref).max()) <= tol
+
+
+def test_squeeze_excite_gate_rejects_what_it_cannot_take():
+    x = DT.from_numpy(rnd(1, 8, 4, 4))
+    gate = DT((1, 8, 1, 1), np.float32)
+    with pytest.raises(cabi.FmlError):   # hidden width of w2 does not match w1
+        cabi.squeeze_excite_gate(x, DT.from_numpy(rnd(2, 8, 1, 1)), None, DT.from_numpy(rnd(8, 3, 1, 1)), None, 5, 4, gate)
+    with pytest.raises(cabi.FmlError):   # exact GELU is not one of the gate activations
+        cabi.squeeze_excite_gate(x, DT.from_numpy(rnd(2, 8, 1, 1)), None, DT.from_numpy(rnd(8, 2, 1, 1)), None, 1, 4, gate)
+
+
 @pytest.mark.parametrize("sa,sb,axis,dtype", [
     ((4, 16, 64, 16), (4, 16, 64, 16), 3, np.float32),   # rotary halves: 16-byte groups, split inside the innermost dim
     ((2, 8, 12, 32), (2, 4, 12, 32), 1, np.float32),     # 16-byte groups, split along an outer dim
