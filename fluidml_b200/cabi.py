@@ -313,6 +313,18 @@ def conv(x, w, bias, y, pads_begin, strides, dilations, group=1, act=ACT_NONE, s
     check(lib().fml_conv(_ref(x), _ref(w), _ref(bias), _ref(y), ctypes.byref(p), stream))
 
 
+def conv_scaled(x, x_scale, w, bias, y, pads_begin, strides, dilations, act=ACT_NONE, stream=None, precision=None):
+    """y = conv(x * x_scale, w) + bias with x_scale broadcastable to [N, IC, 1, 1] (group 1)."""
+    p = ConvParams()
+    nd = len(pads_begin)
+    for i in range(2):
+        p.pads_begin[i] = pads_begin[i] if i < nd else 0
+        p.strides[i] = strides[i] if i < nd else 1
+        p.dilations[i] = dilations[i] if i < nd else 1
+    p.group, p.act, p.precision = 1, act, GEMM_AUTO if precision is None else precision
+    check(lib().fml_conv_scaled(_ref(x), _ref(x_scale), _ref(w), _ref(bias), _ref(y), ctypes.byref(p), stream))
+
+
 def conv_uses_tensor_cores(x, w, y, pads_begin, precision=None) -> bool:
     p = ConvParams()
     for i in range(2):

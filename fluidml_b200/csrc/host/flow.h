@@ -81,6 +81,7 @@ struct Node {
   int act = 0;
   int act2 = 0;            // SqueezeExciteGate: activation of the second layer
   bool has_bias2 = false;  // SqueezeExciteGate: the second layer has a bias
+  bool has_in_scale = false;  // Conv: inputs[1] scales x per (image, channel) (a Mul folded into the convolution)
   float act_param[3] = {1.4142135381698608f, 1.0f, 0.5f};
   bool has_bias = false, has_residual = false, has_mask = false;
   bool b_is_const = false;  // FusedGemm: B is a captured constant (consts[0]) rather than inputs[1]

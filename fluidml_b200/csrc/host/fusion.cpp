@@ -402,6 +402,32 @@ bool FuseSqueezeExcite(Rewriter &rw, const NodePtr &rm) {
   return true;
 }
 
+// ---- Mul(x [N, C, H, W], gate [N, C, 1, 1]) -> group-1 Conv: the gate multiplies x while the
+// convolution gathers its operand (same fp32 rounding of the product), so the gated tensor -- the
+// widest of a squeeze-and-excite block -- is neither written nor read back.
+bool FuseGateIntoConv(Rewriter &rw, const NodePtr &mul) {
+  if (mul->kind != Kind::MulCommon || mul->inputs.size() != 2) return false;
+  NodePtr cv = rw.Sole(mul->output);
+  if (!cv || (cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding)) return false;
+  if (cv->group != 1 || cv->has_in_scale || cv->inputs.size() != 1 || cv->inputs[0] != mul->output) return false;
+  const auto &os = mul->output->meta.GetShape();
+  if (os.size() != 4 || mul->output->meta.GetType() != Type::kFloat32 || os[1] > 4096) return false;
+  auto is_gate = [&](const RegionPtr &r) {
+    const auto &gs = r->meta.GetShape();
+    return r->meta.GetType() == Type::kFloat32 && gs.size() == 4 && (gs[0] == os[0] || gs[0] == 1) &&
+           (gs[1] == os[1] || gs[1] == 1) && gs[2] == 1 && gs[3] == 1;
+  };
+  RegionPtr x, gate;
+  if (mul->inputs[0]->meta.GetShape() == os && is_gate(mul->inputs[1])) { x = mul->inputs[0]; gate = mul->inputs[1]; }
+  else if (mul->inputs[1]->meta.GetShape() == os && is_gate(mul->inputs[0])) { x = mul->inputs[1]; gate = mul->inputs[0]; }
+  else return false;
+  if (os[2] * os[3] == 1) return false;  // a gate times a gate: nothing to save
+  cv->inputs = {x, gate};
+  cv->has_in_scale = true;
+  rw.Kill(mul);
+  return true;
+}
+
 // ---- Conv -> SiLU: the activation rides in the convolution's epilogue
 bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
   if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
@@ -524,7 +550,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseMulAdd};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseGateIntoConv, FuseMulAdd};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

@@ -620,6 +620,27 @@ private:
   fml_conv_params p_;
 };
 
+// mul.cpp + conv.cpp: the per-channel gate multiplies x inside the convolution's operand gather
+class ScaledConvKernel : public DoubleInputsWithoutBufferKernel {
+public:
+  ScaledConvKernel(const char *name, fml_tensor w, bool has_bias, fml_tensor bias, fml_conv_params p)
+      : name_(name), w_(w), has_bias_(has_bias), bias_(bias), p_(p) {}
+  std::string GetKernelName() const override { return name_; }
+  void Run(LaunchRecorder &rec, const fml_tensor &x, const fml_tensor &scale, const fml_tensor &output) const override {
+    const fml_tensor w = w_, b = bias_;
+    const bool hb = has_bias_;
+    const fml_conv_params p = p_;
+    rec.Add(name_, [=](void *s) { return fml_conv_scaled(&x, &scale, &w, hb ? &b : nullptr, &output, &p, s); });
+  }
+
+private:
+  const char *name_;
+  fml_tensor w_;
+  bool has_bias_;
+  fml_tensor bias_;
+  fml_conv_params p_;
+};
+
 // maxpool.cpp:17-82, averagepool.cpp:19-87
 class PoolKernel : public SingleInputWithoutBufferKernel {
 public:
@@ -772,8 +793,9 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
     p.group = n.group;
     p.act = n.act;
     p.precision = options.gemm_precision;
-    return std::make_unique<ConvKernel>(n.kind == Kind::ConvWithPadding ? "ConvWithPaddingKernel" : "ConvWithoutPaddingKernel",
-                                        C(0), n.has_bias, n.has_bias ? C(1) : fml_tensor{}, p);
+    const char *name = n.kind == Kind::ConvWithPadding ? "ConvWithPaddingKernel" : "ConvWithoutPaddingKernel";
+    if (n.has_in_scale) return std::make_unique<ScaledConvKernel>(name, C(0), n.has_bias, n.has_bias ? C(1) : fml_tensor{}, p);
+    return std::make_unique<ConvKernel>(name, C(0), n.has_bias, n.has_bias ? C(1) : fml_tensor{}, p);
   }
   case Kind::MaxPoolWithoutPadding:
     return std::make_unique<PoolKernel>("MaxPoolWithoutPaddingKernel", 0, n.kernel_shape, n.strides);

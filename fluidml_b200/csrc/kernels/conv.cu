@@ -19,6 +19,10 @@ struct ConvArgs {
   const float *x, *w, *bias;
   float *y;
   int act;
+  // optional per-(image, input channel) scale of x, applied (one fp32 rounding, as a separate
+  // Mul kernel would) while the operand is gathered
+  const float *scale;
+  int64_t scale_sn, scale_sc;
 };
 
 __device__ __forceinline__ float conv_act(int act, float v) {
@@ -59,8 +63,10 @@ __global__ void __launch_bounds__(256) conv_igemm_kernel(ConvArgs a) {
           const int64_t ow = gm % a.OW, oh = (gm / a.OW) % a.OH, n = gm / (a.OW * a.OH);
           const int64_t kw = gk % a.KW, kh = (gk / a.KW) % a.KH, ic = gk / (a.KW * a.KH);
           const int64_t ih = oh * a.sh - a.ph + kh * a.dh, iw = ow * a.sw - a.pw + kw * a.dw;
-          if (ih >= 0 && ih < a.IH && iw >= 0 && iw < a.IW)
+          if (ih >= 0 && ih < a.IH && iw >= 0 && iw < a.IW) {
             v = a.x[n * a.xs[0] + ic * a.xs[1] + ih * a.xs[2] + iw * a.xs[3]];
+            if (a.scale) v = __fmul_rn(v, a.scale[n * a.scale_sn + ic * a.scale_sc]);
+          }
         }
         As[kk][mm] = v;
       }
@@ -571,8 +577,9 @@ __global__ void __launch_bounds__(256) pool2x2_kernel(const float *__restrict__ 
 
 using namespace fml;
 
-extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
-                        const fml_tensor *y, const fml_conv_params *p, void *stream) {
+// x_scale: nullptr, or a tensor broadcastable to [N, IC, 1, 1] that multiplies x (fml_conv_scaled)
+static int conv_impl(const fml_tensor *x, const fml_tensor *x_scale, const fml_tensor *w, const fml_tensor *bias,
+                     const fml_tensor *y, const fml_conv_params *p, void *stream) {
   FML_REQUIRE(valid_tensor(x) && valid_tensor(w) && valid_tensor(y) && p, FML_BAD_ARG, "fml_conv: bad argument");
   FML_REQUIRE(x->dtype == FML_F32 && w->dtype == FML_F32 && y->dtype == FML_F32, FML_UNSUPPORTED, "fml_conv: fp32 only");
   FML_REQUIRE((x->rank == 3 || x->rank == 4) && w->rank == x->rank && y->rank == x->rank, FML_BAD_ARG,
@@ -610,9 +617,33 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
     a.bias_span = a.bias ? ((a.OC - 1) * (a.bias_stride > 0 ? a.bias_stride : 0) + 1) * (int64_t)sizeof(float) : 0;
   }
   a.act = p->act;
+  a.scale = nullptr; a.scale_sn = a.scale_sc = 0;
+  if (x_scale) {
+    FML_REQUIRE(valid_tensor(x_scale) && x_scale->dtype == FML_F32 && x_scale->rank == x->rank, FML_BAD_ARG,
+                "fml_conv_scaled: the scale must be an fp32 tensor of x's rank");
+    FML_REQUIRE(group == 1, FML_UNSUPPORTED, "fml_conv_scaled: group must be 1");
+    for (int i = 0; i < x_scale->rank; ++i) {
+      const int64_t want = i < 2 ? x->shape[i] : 1;
+      FML_REQUIRE(x_scale->shape[i] == want || (i < 2 && x_scale->shape[i] == 1), FML_BAD_ARG,
+                  "fml_conv_scaled: the scale must broadcast to [N, IC, 1, 1]");
+    }
+    a.scale = (const float *)x_scale->data;
+    a.scale_sn = x_scale->shape[0] == 1 ? 0 : x_scale->stride[0];
+    a.scale_sc = x_scale->shape[1] == 1 ? 0 : x_scale->stride[1];
+  }
   const int64_t M = a.N * a.OH * a.OW;
   if (M == 0 || a.OC == 0) return FML_OK;
   cudaStream_t s = as_stream(stream);
+  if (a.scale) {
+    // the tensor-core kernel applies the scale while it splits the operand; every other case
+    // takes the general implicit GEMM (the specialised CUDA-core paths below read x unscaled)
+    if (nd == 2 && a.IC <= 4096 && conv_tc_eligible(x, w, y, p))
+      return launch_conv_tc(x, w, bias, y, p, s, a.scale, a.scale_sn, a.scale_sc);
+    FML_REQUIRE((M + CB - 1) / CB <= 65535, FML_UNSUPPORTED, "fml_conv_scaled: too many output pixels for one launch");
+    dim3 grid((unsigned)((a.OC + CB - 1) / CB), (unsigned)((M + CB - 1) / CB));
+    FML_LAUNCH((conv_igemm_kernel), grid, 256, 0, s, a);
+    return FML_OK;
+  }
   if (group == 1 && a.IH == 1 && a.IW == 1 && a.OH == 1 && a.OW == 1 && a.ph < a.KH && a.pw < a.KW) {
     // One pixel in, one pixel out (the squeeze-and-excite convolutions): only the tap under the
     // pixel contributes, and the convolution is the product [N, IC] x [IC, OC] -- rows = images,
@@ -730,6 +761,17 @@ extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tens
   }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
+}
+
+extern "C" int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
+                        const fml_tensor *y, const fml_conv_params *p, void *stream) {
+  return conv_impl(x, nullptr, w, bias, y, p, stream);
+}
+
+extern "C" int fml_conv_scaled(const fml_tensor *x, const fml_tensor *x_scale, const fml_tensor *w,
+                               const fml_tensor *bias, const fml_tensor *y, const fml_conv_params *p, void *stream) {
+  FML_REQUIRE(x_scale, FML_BAD_ARG, "fml_conv_scaled: no scale");
+  return conv_impl(x, x_scale, w, bias, y, p, stream);
 }
 
 extern "C" int fml_conv_uses_tensor_cores(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y,

@@ -70,6 +70,10 @@ struct ConvTcArgs {
   int64_t bias_stride;
   int act;
   int *status;
+  // optional scale of x per (image, input channel): the product is rounded to fp32 (as a separate
+  // Mul kernel would) before the operand is split
+  const float *scale;
+  int64_t scale_sn, scale_sc;
 #ifdef FML_CONV_PHASE_TRACE
   unsigned long long *trace;  // 16 stamps per CTA (fml_debug_set_conv_trace)
 #endif
@@ -150,6 +154,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * NS + 2 * RS + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   float *bias_s = reinterpret_cast<float *>(tmem_slot + 4);  // this tile's slice of the bias, [BN]
+  float *scale_s = bias_s + 128;                             // this image's input scale, [n_icb * ICB] (when a.scale)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int t = blockIdx.x;
@@ -301,6 +306,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     {
       const int i = threadIdx.x - 64;
       if (i < BN) bias_s[i] = (a.bias && oc0 + i < a.OC) ? a.bias[(int64_t)(oc0 + i) * a.bias_stride] : 0.0f;
+      if (a.scale)
+        for (int k = i; k < a.n_icb * ICB; k += 256)
+          scale_s[k] = k < a.IC ? a.scale[(int64_t)n * a.scale_sn + (int64_t)k * a.scale_sc] : 0.0f;
       asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight converter / epilogue warps
     }
     for (int icb = icb_lo; icb < icb_hi && ok; ++icb) {
@@ -321,11 +329,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // flat mode has no zero columns left and right of the image rows: mask them here
         const bool col_ok = MODE == 0 || (MODE == 1 ? ((unsigned)(c + kw - a.pw) < (unsigned)a.IW) : m < a.plane);
         uint32_t hi[ICB], lo[ICB];
+        if (a.scale) {
+          const float *sc = scale_s + icb * ICB;
 #pragma unroll
-        for (int ic = 0; ic < ICB; ++ic) {
-          const uint32_t x = (MODE == 0 || col_ok) ? src[ic * plane] : 0u;
-          hi[ic] = x & 0xffffe000u;
-          if (THREE_PASS) lo[ic] = lo1(x);
+          for (int ic = 0; ic < ICB; ++ic) {
+            const uint32_t raw = (MODE == 0 || col_ok) ? src[ic * plane] : 0u;
+            const uint32_t x = __float_as_uint(__fmul_rn(__uint_as_float(raw), sc[ic]));
+            hi[ic] = x & 0xffffe000u;
+            if (THREE_PASS) lo[ic] = lo1(x);
+          }
+        } else {
+#pragma unroll
+          for (int ic = 0; ic < ICB; ++ic) {
+            const uint32_t x = (MODE == 0 || col_ok) ? src[ic * plane] : 0u;
+            hi[ic] = x & 0xffffe000u;
+            if (THREE_PASS) lo[ic] = lo1(x);
+          }
         }
         const uint32_t t_hi = lane_addr + a_col0 + (uint32_t)s * a_cols;
         if (ICB == 32) {
@@ -530,8 +549,9 @@ bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor
 }
 
 int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,
-                   const fml_conv_params *p, cudaStream_t s) {
+                   const fml_conv_params *p, cudaStream_t s, const float *x_scale, int64_t x_scale_sn, int64_t x_scale_sc) {
   ConvTcArgs a;
+  a.scale = x_scale; a.scale_sn = x_scale_sn; a.scale_sc = x_scale_sc;
   a.N = (int)x->shape[0]; a.IC = (int)x->shape[1]; a.OC = (int)w->shape[0];
   const int IH = (int)x->shape[2], IW = (int)x->shape[3];
   a.OH = (int)y->shape[2]; a.OW = (int)y->shape[3];
@@ -654,7 +674,8 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   }
   const size_t ring = (size_t)stages * stage + a.raw_stages * raw_pitch;
   const size_t staging = a.split_k > 1 ? (((size_t)kBM * (a.tile_n + 4) * 4 + 127) & ~(size_t)127) : 0;
-  size_t smem = std::max(ring, staging) + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 128 * 4 /* bias slice */ + 1024;
+  size_t smem = std::max(ring, staging) + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 128 * 4 /* bias slice */ +
+                (a.scale ? (size_t)a.n_icb * icb * 4 : 0) /* input scale */ + 1024;
   {  // co-residency capped by TMEM columns, as in the GEMM
     unsigned need = (unsigned)((a.tile_n + 31) / 32 * 32 + a_cols * stages), cols = 32;
     while (cols < need) cols <<= 1;

@@ -76,6 +76,7 @@ int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &pl
 // tcgen05 implicit-GEMM convolution (conv_tc.cu)
 bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y, const fml_conv_params *p);
 int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,
-                   const fml_conv_params *p, cudaStream_t s);
+                   const fml_conv_params *p, cudaStream_t s, const float *x_scale = nullptr, int64_t x_scale_sn = 0,
+                   int64_t x_scale_sc = 0);
 
 }  // namespace fml

@@ -354,6 +354,14 @@ typedef struct fml_conv_params {
 int fml_conv(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias,
              const fml_tensor *y, const fml_conv_params *p, void *stream);
 
+/* MulCommonKernel (mul.cpp) followed by a group-1 convolution (conv.cpp:27-280) without the
+ * product ever reaching memory: y = conv(x * x_scale, w) + bias, x_scale broadcastable to
+ * [N, IC, 1, 1] (the gate of a squeeze-and-excite block).  The product is rounded to fp32 before
+ * it enters the convolution, as the separate kernel's output would be.  Same paths as fml_conv:
+ * the tensor-core kernel when it is eligible, else the general implicit GEMM. */
+int fml_conv_scaled(const fml_tensor *x, const fml_tensor *x_scale, const fml_tensor *w,
+                    const fml_tensor *bias, const fml_tensor *y, const fml_conv_params *p, void *stream);
+
 /* Reports which path fml_conv takes: 1 = the tcgen05 implicit GEMM (2-D, group 1, unit stride
  * and dilation, dense NCHW input whose row length is a multiple of 4, weights stored
  * [KH][KW][IC][OC] -- the OIHW tensor with layout permutation (3, 2, 0, 1) -- with OC a

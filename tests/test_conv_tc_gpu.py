@@ -65,6 +65,37 @@ def test_conv_tensor_cores(xs, ws, pads, prec):
     assert relerr(out.numpy(), ref) <= (5e-5 if prec == cabi.GEMM_3XTF32 else 2e-3)
 
 
+@pytest.mark.parametrize("xs,ws,pads,gate_shape", [
+    ((2, 96, 16, 16), (32, 96, 1, 1), (0, 0), (2, 96, 1, 1)),      # box patches
+    ((3, 1152, 7, 7), (192, 1152, 1, 1), (0, 0), (3, 1152, 1, 1)), # whole planes, split over the channel blocks
+    ((2, 480, 14, 14), (112, 480, 1, 1), (0, 0), (2, 480, 1, 1)),  # flat rows
+    ((1, 40, 17, 12), (48, 40, 3, 3), (1, 1), (1, 40, 1, 1)),      # channel tail (40 = 32 + 8), 3 x 3 with padding
+    ((2, 64, 28, 28), (128, 64, 3, 3), (1, 1), (1, 64, 1, 1)),     # one gate for every image
+])
+@pytest.mark.parametrize("packed", [True, False])
+def test_conv_with_scaled_input_equals_mul_then_conv(xs, ws, pads, gate_shape, packed):
+    """fml_conv_scaled rounds x * gate to fp32 before the convolution, like MulCommon followed by
+    Conv: the same kernel fed the pre-multiplied tensor gives the same bits (tensor-core path with
+    packed weights, general implicit GEMM with OIHW weights); and the oracle's Mul -> Conv (fp64
+    accumulation) is matched within the 3xTF32 tolerance."""
+    x, w, b, gate = rnd(*xs), rnd(*ws) * 0.1, rnd(ws[0]), rnd(*gate_shape)
+    oh, ow = xs[2] + 2 * pads[0] - ws[2] + 1, xs[3] + 2 * pads[1] - ws[3] + 1
+    oshape = (xs[0], ws[0], oh, ow)
+    prod = orc.binary("Mul", x, gate, np.empty(xs, np.float32))
+    ref = orc.conv(prod, w, b, np.empty(oshape, np.float32), list(pads), [1, 1], [1, 1], 1, acc64=True)
+    dw = DT.from_numpy(w, PACKED if packed else None)
+    fused, plain = DT(oshape, np.float32), DT(oshape, np.float32)
+    cabi.conv_scaled(DT.from_numpy(x), DT.from_numpy(gate), dw, DT.from_numpy(b), fused, list(pads), [1, 1], [1, 1],
+                     act=cabi.ACT_SILU)
+    cabi.check_device()
+    if packed:
+        cabi.conv(DT.from_numpy(prod), dw, DT.from_numpy(b), plain, list(pads), [1, 1], [1, 1], 1, act=cabi.ACT_SILU)
+        assert np.array_equal(fused.numpy(), plain.numpy())
+    pre = ref.astype(np.float64)
+    ref_act = pre / (1.0 + np.exp(-pre))
+    assert relerr(fused.numpy(), ref_act) <= 5e-5
+
+
 def test_conv_paths_agree_and_repeat():
     """Same operands through the tensor-core path (packed weights) and the CUDA-core path (OIHW
     weights): equal within the 3xTF32 tolerance; the tensor-core result is bit-stable."""

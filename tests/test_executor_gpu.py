@@ -228,6 +228,7 @@ def test_efficientnet_b0_and_full_size_vgg():
         assert "SiluKernel" not in ex.stats()["kernels"]  # every SiLU rides in a convolution epilogue
         # each block's ReduceMean -> Conv -> Conv gate is one launch
         assert ex.stats()["kernels"].get("SqueezeExciteGateKernel") == 16 and "ReduceMeanKernel" not in ex.stats()["kernels"]
+        assert "MulCommonKernel" not in ex.stats()["kernels"]  # ... and the gate is applied inside the projection convolution
     # the same model with every fusion off (separate ReduceMean and gate convolutions) agrees too
     outs, ex = run(e, xe, Executor.make_dp_greedy, fusion=0)
     assert relerr(outs["logits"], ref["logits"]) <= TOL and ex.stats()["kernels"].get("ReduceMeanKernel") == 16

@@ -237,15 +237,17 @@ def test_mul_add_pairs_are_fused_when_the_product_has_one_consumer():
 
 
 def test_squeeze_excite_gates_become_one_node_each():
-    """ReduceMean over H, W -> 1x1 Conv -> 1x1 Conv collapses into SqueezeExciteGate; the Mul that
-    applies the gate stays.  A ReduceMean over other axes, or one whose result is read twice, is
-    left alone."""
+    """ReduceMean over H, W -> 1x1 Conv -> 1x1 Conv collapses into SqueezeExciteGate, and the Mul
+    that applies the gate is folded into the convolution reading its result.  A ReduceMean whose
+    result is read twice is left alone."""
     m = models.build_efficientnet_b0(image=64, width=0.5, classes=10)
     unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
     assert unfused.count("ReduceMean") == 16
     assert fused.count("SqueezeExciteGate") == 16 and fused.count("ReduceMean") == 0
     convs = lambda ks: ks.count("ConvWithoutPadding") + ks.count("ConvWithPadding")
     assert convs(unfused) - convs(fused) == 32
+    # the Mul that applies each gate rides in the projection convolution that follows it
+    assert unfused.count("MulCommon") - fused.count("MulCommon") >= 16 and fused.count("MulCommon") == 0
     g = models.GraphBuilder("not_a_gate")
     x = g.input("x", FLOAT, (2, 8, 6, 6))
     w1 = g.const("w1", np.ones((4, 8, 1, 1), np.float32)); w2 = g.const("w2", np.ones((8, 4, 1, 1), np.float32))
