@@ -738,6 +738,10 @@ static int conv_impl(const fml_tensor *x, const fml_tensor *x_scale, const fml_t
       FML_LAUNCH((conv_depthwise_1d_transposing_kernel), grid, 256, 0, s, a);
       return FML_OK;
     }
+    if (nd == 2) {
+      int st = FML_OK;
+      if (launch_depthwise_tma(x, w, bias, y, p, s, &st)) return st;
+    }
     if (a.dh == 1 && a.dw == 1 && a.sh == a.sw && (a.sh == 1 || a.sh == 2) && a.xs[3] == 1) {
       int st = FML_OK;
       bool done = false;

@@ -523,6 +523,11 @@ int make_map_nd(CUtensorMap *map, const float *base, int rank, const cuuint64_t 
 
 }  // namespace
 
+int make_f32_tensor_map(CUtensorMap *map, const float *base, int rank, const cuuint64_t *dims,
+                        const cuuint64_t *strides_bytes, const cuuint32_t *box) {
+  return make_map_nd(map, base, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 // Whether the tensor-core path takes this convolution (see the header of this file).
 bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y, const fml_conv_params *p) {
   if (x->rank != 4 || p->precision == FML_GEMM_FP32) return false;

@@ -73,6 +73,10 @@ struct TcPlan {
 bool plan_gemm_tc(const GemmProblem &p, const fml_gemm_params &gp, TcPlan &plan);
 int launch_gemm_tc(const GemmProblem &p, const GemmEpilogue &e, const TcPlan &plan, cudaStream_t s);
 
+// pipelined depthwise convolution over dense NCHW planes (conv_depthwise_tma.cu); false = not taken
+bool launch_depthwise_tma(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,
+                          const fml_conv_params *p, cudaStream_t s, int *status);
+
 // tcgen05 implicit-GEMM convolution (conv_tc.cu)
 bool conv_tc_eligible(const fml_tensor *x, const fml_tensor *w, const fml_tensor *y, const fml_conv_params *p);
 int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,

@@ -23,6 +23,11 @@ static cudaError_t set_wait_test_this_unit(uint32_t limit, int drop) {
 }
 static struct WaitTestRegistrar { WaitTestRegistrar() { register_wait_test_setter(&set_wait_test_this_unit); } } g_wait_test_registrar;
 
+// Tiled fp32 tensor map without swizzle, zero fill outside the tensor (conv_tc.cu); `rank` dims,
+// `rank - 1` byte strides, innermost first.
+int make_f32_tensor_map(CUtensorMap *map, const float *base, int rank, const cuuint64_t *dims,
+                        const cuuint64_t *strides_bytes, const cuuint32_t *box);
+
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

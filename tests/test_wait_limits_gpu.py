@@ -69,3 +69,15 @@ def test_attention_waits_run_out_and_the_context_survives():
     ref = np.einsum("bhqk,bhkd->bhqd", p / p.sum(-1, keepdims=True), v.astype(np.float64))
     expect_timeout_then_recover(lambda: cabi.attention(dq, kt, dv, None, 8.0, out),
                                 lambda: np.testing.assert_allclose(out.numpy(), ref, atol=2e-5 * np.abs(ref).max()))
+
+
+def test_depthwise_waits_run_out_and_the_context_survives():
+    """The pipelined depthwise kernel (one tensor-map copy per tile, two buffers): with the copies
+    dropped both buffers' waits run out, every CTA leaves through the uniform verdict, and the next
+    launch is correct."""
+    x, w, b = rnd(2, 24, 28, 28), rnd(24, 1, 3, 3), rnd(24)
+    dx, dw, db, dy = DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), DT((2, 24, 28, 28), np.float32)
+    from oracle import oracle as orc
+    ref = orc.conv(x, w, b, np.empty((2, 24, 28, 28), np.float32), (1, 1, 1, 1), (1, 1), (1, 1), 24)
+    expect_timeout_then_recover(lambda: cabi.conv(dx, dw, db, dy, (1, 1), (1, 1), (1, 1), 24),
+                                lambda: np.testing.assert_allclose(dy.numpy(), ref, atol=1e-5 * np.abs(ref).max()))
