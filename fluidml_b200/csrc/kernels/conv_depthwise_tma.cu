@@ -194,6 +194,280 @@ __global__ void __launch_bounds__(kDwThreads) conv_depthwise_tma_kernel(const __
   }
 }
 
+// ---- narrow planes (rows that are not a multiple of four floats, or shorter than 16: the 14 x 14
+// and 7 x 7 stages of an image network).  A tensor map cannot describe such rows (their pitch is
+// not a multiple of 16 bytes), but a run of whole planes is one contiguous block: the persistent
+// CTA fetches PP planes per tile with one bulk copy (cp.async.bulk) into a ring of two raw
+// buffers, repacks them into a zero-padded patch (shared memory to shared memory), and computes
+// 4 x 4 micro-tiles from the patch as above; the copy of tile i + 1 runs under all of that.
+struct DwFlatArgs {
+  int C, IH, IW, OH, OW, ph, pw;
+  int TR, PP, SW;            // thread rows per plane, planes per tile, strips per output row
+  int PH, PWn, pitch;        // patch rows, patch columns, patch row pitch (floats)
+  int planes, items;
+  int dense_y;               // y is dense NCHW on a 16-byte base: a tile's results are one contiguous block
+  uint32_t m_plane, m_pwn;   // ceil(2^32 / d) for d = PH * PWn and PWn (dividends below 2^16)
+  const float *x;
+  const float *w;
+  int64_t ws0, ws2, ws3;
+  const float *bias;
+  int64_t bias_stride;
+  float *y;
+  int64_t ys[4];
+  int act;
+  int *status;
+};
+
+__device__ __forceinline__ void dwt_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+template <int KH, int KW, int S>
+__global__ void __launch_bounds__(kDwThreads) conv_depthwise_planes_kernel(const DwFlatArgs d) {
+  constexpr int RT = 4;
+  constexpr int IN_V = (3 * S + KW + 3) / 4;
+  constexpr int ROWS = (RT - 1) * S + KH;
+  extern __shared__ __align__(128) uint8_t dwt_smem[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int abort_flag;
+  const int HW = d.IH * d.IW;
+  const uint32_t raw_pitch = ((uint32_t)(d.PP * HW) * 4u + 127u) & ~127u;
+  uint8_t *smem = dwt_smem + ((128u - (smem_u32(dwt_smem) & 127u)) & 127u);
+  float *patch = reinterpret_cast<float *>(smem + 2 * (size_t)raw_pitch);  // [PP][PH][pitch]
+  // results of a tile, dense [PP][OH * OW]: with y dense they leave as ONE bulk copy (rows of 7 or
+  // 14 floats stored by the threads themselves are 4-byte writes scattered over partial sectors)
+  const int OHW = d.OH * d.OW;
+  float *out_s = patch + (((size_t)d.PP * d.PH * d.pitch + 31) & ~(size_t)31);
+  const int tid = threadIdx.x;
+
+  pdl_launch_dependents();
+  if (tid == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[1]), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+
+  const int per_plane = d.TR * d.SW;
+  const int pl = tid / per_plane, rem = tid - pl * per_plane;
+  const int tr = rem / d.SW, j = rem - tr * d.SW;
+  const bool worker = pl < d.PP;
+  const int drop = g_drop_loads;
+  const int per_plane_elems = d.PH * d.PWn, patch_elems = d.PP * per_plane_elems;
+
+  auto issue = [&](int item, int stage) {  // thread 0 only: the planes [item * PP, ...) of the tensor
+    const int count = min(d.PP, d.planes - item * d.PP);
+    const uint32_t bytes = (uint32_t)(count * HW) * 4u;
+    const uint32_t bar = smem_u32(&bars[stage]);
+    mbar_expect_tx(bar, bytes);
+    if (!drop) dwt_bulk_load(smem_u32(smem) + (uint32_t)stage * raw_pitch, d.x + (size_t)item * d.PP * HW, bytes, bar);
+  };
+
+  int issued = 0, consumed = 0;
+  const int first = (int)blockIdx.x, stride = (int)gridDim.x;
+  if (tid == 0 && first < d.items) { issue(first, 0); issued = 1; }
+  bool ok = true;
+  for (int item = first, k = 0; item < d.items; item += stride, ++k) {
+    const int stage = k & 1;
+    if (tid == 0 && item + stride < d.items) { issue(item + stride, stage ^ 1); ++issued; }  // released after the repack of tile k - 1
+    const int plane = item * d.PP + pl;
+    const int oh = tr * RT, ow0 = j * 4;
+    const bool active = worker && plane < d.planes && oh < d.OH;
+    float w[KH * KW], bias = 0.0f;
+    int ch = 0, n = 0;
+    if (active) {  // the window and the bias of this thread's plane travel while the planes do
+      n = plane / d.C;
+      ch = plane - n * d.C;
+#pragma unroll
+      for (int q = 0; q < KH * KW; ++q) w[q] = __ldg(d.w + ch * d.ws0 + (q / KW) * d.ws2 + (q % KW) * d.ws3);
+      if (d.bias) bias = __ldg(d.bias + ch * d.bias_stride);
+    }
+    ok = __syncthreads_and(mbar_wait(smem_u32(&bars[stage]), ((uint32_t)(k >> 1)) & 1u, &abort_flag) ? 1 : 0) != 0;
+    if (!ok) break;
+    if (tid == 0) consumed = k + 1;
+    // ---- repack: raw planes -> zero-padded patch (the previous tile's readers left it at the
+    // barrier that ended their iteration)
+    {
+      const float *raw = reinterpret_cast<const float *>(smem + (size_t)stage * raw_pitch);
+      for (int base = tid; base < patch_elems; base += 4 * kDwThreads) {
+        float v[4];
+        int at[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = base + kDwThreads * u;
+          v[u] = 0.0f;
+          at[u] = -1;
+          if (e < patch_elems) {
+            const int p = (int)__umulhi((uint32_t)e, d.m_plane), r2 = e - p * per_plane_elems;
+            const int pr = (int)__umulhi((uint32_t)r2, d.m_pwn), pc = r2 - pr * d.PWn;
+            const int ih = pr - d.ph, iw = pc - d.pw;
+            at[u] = (p * d.PH + pr) * d.pitch + pc;
+            if ((unsigned)ih < (unsigned)d.IH && (unsigned)iw < (unsigned)d.IW) v[u] = raw[p * HW + ih * d.IW + iw];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (at[u] >= 0) patch[at[u]] = v[u];
+      }
+    }
+    // the previous tile's results have left shared memory before this tile's are written
+    if (d.dense_y && tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncthreads();
+    if (active) {
+      float acc[RT][4];
+#pragma unroll
+      for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int o = 0; o < 4; ++o) acc[i][o] = 0.0f;  // window first, bias last: the reference's order
+      const float *prow = patch + ((size_t)pl * d.PH + (size_t)tr * RT * S) * d.pitch + ow0 * S;
+#pragma unroll
+      for (int ir = 0; ir < ROWS; ++ir) {
+        float in[IN_V * 4];
+#pragma unroll
+        for (int v = 0; v < IN_V; ++v) {
+          const float4 t = *reinterpret_cast<const float4 *>(prow + ir * d.pitch + v * 4);
+          in[4 * v] = t.x; in[4 * v + 1] = t.y; in[4 * v + 2] = t.z; in[4 * v + 3] = t.w;
+        }
+#pragma unroll
+        for (int rr = 0; rr < RT; ++rr) {
+          const int kh = ir - rr * S;  // compile-time after unrolling
+          if (kh >= 0 && kh < KH) {
+#pragma unroll
+            for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+              for (int o = 0; o < 4; ++o) acc[rr][o] = fmaf(in[o * S + kw], w[kh * KW + kw], acc[rr][o]);
+          }
+        }
+      }
+      const int valid = d.OW - ow0;
+      const int rows = min(RT, d.OH - oh);
+      if (d.dense_y) {
+        float *op = out_s + (size_t)pl * OHW + oh * d.OW + ow0;
+        switch (d.act) {  // one dispatch per thread, outside the store loops
+#define FML_DWT_SROWS(ACT)                                                                \
+  _Pragma("unroll") for (int rr = 0; rr < RT; ++rr)                                          \
+    if (rr < rows) dwt_store_row<ACT>(op + rr * d.OW, acc[rr], bias, false, valid, 1);
+        case FML_ACT_RELU: FML_DWT_SROWS(FML_ACT_RELU) break;
+        case FML_ACT_TANH: FML_DWT_SROWS(FML_ACT_TANH) break;
+        case FML_ACT_SIGMOID: FML_DWT_SROWS(FML_ACT_SIGMOID) break;
+        case FML_ACT_SILU: FML_DWT_SROWS(FML_ACT_SILU) break;
+        default: FML_DWT_SROWS(FML_ACT_NONE) break;
+#undef FML_DWT_SROWS
+        }
+      } else {
+        float *yp = d.y + n * d.ys[0] + ch * d.ys[1] + oh * d.ys[2] + ow0 * d.ys[3];
+        const bool vec = d.ys[3] == 1 && valid >= 4 && ((reinterpret_cast<uintptr_t>(yp) & 15) == 0) && (d.ys[2] & 3) == 0;
+        switch (d.act) {
+#define FML_DWT_ROWS(ACT)                                                                 \
+  _Pragma("unroll") for (int rr = 0; rr < RT; ++rr)                                          \
+    if (rr < rows) dwt_store_row<ACT>(yp + rr * d.ys[2], acc[rr], bias, vec, valid, d.ys[3]);
+        case FML_ACT_RELU: FML_DWT_ROWS(FML_ACT_RELU) break;
+        case FML_ACT_TANH: FML_DWT_ROWS(FML_ACT_TANH) break;
+        case FML_ACT_SIGMOID: FML_DWT_ROWS(FML_ACT_SIGMOID) break;
+        case FML_ACT_SILU: FML_DWT_ROWS(FML_ACT_SILU) break;
+        default: FML_DWT_ROWS(FML_ACT_NONE) break;
+#undef FML_DWT_ROWS
+        }
+      }
+    }
+    __syncthreads();  // the patch may be rebuilt; the tile's results are complete
+    if (d.dense_y && tid == 0) {
+      const int count = min(d.PP, d.planes - item * d.PP);
+      fence_async_smem();  // the threads' writes, before the copy engine reads them
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                   ::"l"(d.y + (size_t)item * d.PP * OHW), "r"(smem_u32(out_s)), "r"((uint32_t)(count * OHW) * 4u) : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  if (d.dense_y && tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before the CTA leaves
+  if (!ok && tid == 0) {
+    atomicOr(d.status, kStatusTimeout);
+    abort_flag = 1;
+    volatile int never = 0;
+    if (!drop)
+      for (int k = consumed; k < issued; ++k) mbar_wait(smem_u32(&bars[k & 1]), ((uint32_t)(k >> 1)) & 1u, &never);
+  }
+}
+
+template <int KH, int KW, int S>
+int launch_planes_variant(const DwFlatArgs &d, size_t smem, int ctas, cudaStream_t s) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  FML_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    FML_CUDA(cudaFuncSetAttribute(conv_depthwise_planes_kernel<KH, KW, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set[dev & 63] = true;
+  }
+  FML_LAUNCH((conv_depthwise_planes_kernel<KH, KW, S>), dim3((unsigned)ctas), dim3(kDwThreads), smem, s, d);
+  return FML_OK;
+}
+
+// The narrow-plane variant: dense NCHW x on a 16-byte base, planes of at most 1024 elements that
+// fit one CTA's threads, a plane count that is a multiple of 4 (so that every copy is a multiple
+// of 16 bytes).
+bool launch_depthwise_planes(const fml_tensor *x, const fml_tensor *w, const fml_tensor *bias, const fml_tensor *y,
+                             const fml_conv_params *p, cudaStream_t s, int *status) {
+  const int64_t N = x->shape[0], C = x->shape[1], IH = x->shape[2], IW = x->shape[3];
+  const int64_t OH = y->shape[2], OW = y->shape[3], KH = w->shape[2], KW = w->shape[3];
+  const int64_t S = p->strides[0], HW = IH * IW;
+  if (HW > 1024 || ((N * C) & 3) || N * C >= (1ll << 30)) return false;
+  if (p->pads_begin[0] < 0 || p->pads_begin[0] > 8 || p->pads_begin[1] < 0 || p->pads_begin[1] > 8) return false;
+  constexpr int RT = 4;
+  DwFlatArgs d;
+  memset(&d, 0, sizeof(d));
+  d.C = (int)C; d.IH = (int)IH; d.IW = (int)IW; d.OH = (int)OH; d.OW = (int)OW;
+  d.ph = (int)p->pads_begin[0]; d.pw = (int)p->pads_begin[1];
+  d.SW = (int)((OW + 3) / 4);
+  d.TR = (int)((OH + RT - 1) / RT);
+  const int per_plane = d.TR * d.SW;
+  if (per_plane > kDwThreads / 4) return false;  // at least four planes per tile
+  const int in_v = (3 * (int)S + (int)KW + 3) / 4;
+  d.PWn = (d.SW - 1) * 4 * (int)S + in_v * 4;
+  d.pitch = d.PWn + 4;  // rows 16 bytes apart modulo the bank cycle
+  d.PH = (d.TR * RT - 1) * (int)S + (int)KH;
+  d.planes = (int)(N * C);
+  d.PP = std::min(kDwThreads / per_plane / 4 * 4, d.planes);
+  static const int bulk_store_env = [] { const char *e = getenv("FLUIDML_DEPTHWISE_BULK_STORE"); return e ? atoi(e) : -1; }();
+  // (measured: the block store pays at stride 1, +10-20 %; at stride 2 the extra buffer costs more than it saves)
+  d.dense_y = (bulk_store_env == 1 || (bulk_store_env < 0 && S == 1)) && aligned16(y->data) && y->stride[3] == 1 && y->stride[2] == OW && y->stride[1] == OH * OW &&
+                      (N == 1 || y->stride[0] == C * OH * OW) ? 1 : 0;
+  auto smem_of = [&]() {
+    const size_t raw = ((size_t)d.PP * HW * 4 + 127) / 128 * 128;
+    const size_t patch = ((size_t)d.PP * d.PH * d.pitch + 31) / 32 * 32 * 4;
+    return 2 * raw + patch + (d.dense_y ? (size_t)d.PP * OH * OW * 4 : 0) + 128;
+  };
+  while (d.PP > 4 && smem_of() > 56 * 1024) d.PP -= 4;
+  if (smem_of() > 100 * 1024 || (int64_t)d.PP * d.PH * d.PWn >= 65536) return false;
+  d.items = (d.planes + d.PP - 1) / d.PP;
+  auto magic = [](int64_t dv) { return (uint32_t)((0x100000000ull + (uint64_t)dv - 1) / (uint64_t)dv); };
+  d.m_plane = magic((int64_t)d.PH * d.PWn); d.m_pwn = magic(d.PWn);
+  d.x = (const float *)x->data;
+  d.w = (const float *)w->data; d.ws0 = w->stride[0]; d.ws2 = w->stride[2]; d.ws3 = w->stride[3];
+  if (bias) {
+    d.bias = (const float *)bias->data;
+    for (int i = 0; i < bias->rank; ++i) if (bias->shape[i] != 1) d.bias_stride = bias->stride[i];
+  }
+  d.y = (float *)y->data;
+  for (int i = 0; i < 4; ++i) d.ys[i] = y->stride[i];
+  d.act = p->act;
+  d.status = device_status_word();
+  if (!d.status) return false;
+  const size_t smem = smem_of();
+  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(200 * 1024) / (smem + 1024)));
+  const int ctas = (int)std::min<int64_t>(d.items, (int64_t)148 * per_sm);
+  const int key = (int)(KH * 10 + S);
+  switch (key) {
+  case 31: *status = launch_planes_variant<3, 3, 1>(d, smem, ctas, s); break;
+  case 32: *status = launch_planes_variant<3, 3, 2>(d, smem, ctas, s); break;
+  case 51: *status = launch_planes_variant<5, 5, 1>(d, smem, ctas, s); break;
+  default: *status = launch_planes_variant<5, 5, 2>(d, smem, ctas, s); break;
+  }
+  return true;
+}
+
 using DwKernelFn = void (*)(const CUtensorMap, const DwTmaArgs);
 
 template <int KH, int KW, int S>
@@ -223,12 +497,13 @@ bool launch_depthwise_tma(const fml_tensor *x, const fml_tensor *w, const fml_te
   const int64_t S = p->strides[0];
   if (p->strides[1] != S || (S != 1 && S != 2) || p->dilations[0] != 1 || p->dilations[1] != 1) return false;
   if (!((KH == 3 && KW == 3) || (KH == 5 && KW == 5))) return false;
-  if (p->pads_begin[1] != (KW - 1) / 2 || p->pads_begin[0] < 0 || p->pads_begin[0] > 8) return false;
-  if ((IW & 3) || IW < 16 || !aligned16(x->data) || x->stride[3] != 1 || x->stride[2] != IW || x->stride[1] != IH * IW ||
+  if (!aligned16(x->data) || x->stride[3] != 1 || x->stride[2] != IW || x->stride[1] != IH * IW ||
       (N > 1 && x->stride[0] != C * IH * IW))
     return false;
   if (N * C >= (1ll << 30) || IH >= (1 << 20) || y->stride[3] != 1) return false;
   for (int i = 0; i < 4; ++i) if (y->stride[i] < 0) return false;
+  if ((IW & 3) || IW < 16) return launch_depthwise_planes(x, w, bias, y, p, s, status);
+  if (p->pads_begin[1] != (KW - 1) / 2 || p->pads_begin[0] < 0 || p->pads_begin[0] > 8) return false;
   constexpr int RT = 4;
   DwTmaArgs d;
   memset(&d, 0, sizeof(d));

@@ -447,6 +447,14 @@ def test_conv(cfg):
     ((1, 8, 33, 45), 3, 2, 1, 0),      # odd sizes: ragged strips and row tiles
     ((1, 6, 61, 130), 7, 1, 3, 0),     # 7x7 window
     ((1, 5, 30, 30), 3, 1, 0, 0),      # no padding
+    # the pipelined kernels: several tiles per persistent CTA (both buffers reused, parities wrap)
+    ((16, 144, 56, 56), 3, 1, 1, 5),   # tensor-map copies, one plane per tile
+    ((8, 40, 112, 112), 3, 2, 1, 5),   # ... two bands per plane, stride 2
+    ((64, 48, 28, 28), 5, 1, 2, 0),    # ... five planes per tile, the last tile ragged
+    ((64, 672, 14, 14), 5, 1, 2, 5),   # bulk copies of whole planes, sixteen per tile
+    ((2, 50, 14, 14), 5, 2, 2, 0),     # ... stride 2, a ragged last tile
+    ((4, 33, 7, 7), 3, 1, 1, 0),       # ... width 7
+    ((64, 1152, 7, 7), 5, 1, 2, 5),
 ])
 def test_depthwise_conv_tiled(shape, k, stride, pad, act):
     """The tiled depthwise kernel (every window / stride variant, every plane-batching mode) against
