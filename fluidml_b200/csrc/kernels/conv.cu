@@ -804,6 +804,13 @@ extern "C" int fml_pool2d(const fml_tensor *x, const fml_tensor *y, int mode, co
   a.x = (const float *)x->data; a.y = (float *)y->data; a.mode = mode;
   const int64_t total = a.N * a.C * a.OH * a.OW;
   if (total == 0) return FML_OK;
+  if (mode == 1 && a.OH == 1 && a.OW == 1 && a.KH == x->shape[2] && a.KW == x->shape[3]) {
+    // global average pooling is the mean over the two spatial axes: one warp per plane with
+    // coalesced loads (the window kernel below gives a thread a whole plane, 196 bytes from its
+    // neighbour's)
+    const int32_t spatial[4] = {0, 0, 1, 1};
+    return fml_reduce_mean(x, y, spatial, stream);
+  }
   {
     const int64_t IH = x->shape[2], IW = x->shape[3];
     const bool dense_in = x->stride[3] == 1 && x->stride[2] == IW && x->stride[1] == IH * IW && x->stride[0] == a.C * IH * IW;

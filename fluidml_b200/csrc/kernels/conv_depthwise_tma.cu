@@ -23,6 +23,18 @@ constexpr int kDwThreads = 256;
 constexpr int kDwMaxStages = 4;
 constexpr size_t kDwStageBytes = 36 * 1024;  // measured best cap for a patch buffer (18 / 26 / 36 / 52 / 100 KB tried)
 
+// A persistent grid is as large as the device can hold at once (registers count as much as shared
+// memory: the occupancy calculator knows both) and no larger than the tile list.
+template <typename Kernel>
+int persistent_ctas(Kernel kernel, size_t smem, int items, int *ctas) {
+  int per_sm = 0, sms = 0, dev = 0;
+  FML_CUDA(cudaGetDevice(&dev));
+  FML_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  FML_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kDwThreads, smem));
+  *ctas = std::max(1, std::min(items, std::max(1, per_sm) * std::max(1, sms)));
+  return FML_OK;
+}
+
 struct DwTmaArgs {
   int C, OH, OW, ph;
   int TR, PP, SW;          // thread rows (of 4 output rows) per tile, planes per tile, strips per output row
@@ -393,7 +405,7 @@ __global__ void __launch_bounds__(kDwThreads) conv_depthwise_planes_kernel(const
 }
 
 template <int KH, int KW, int S>
-int launch_planes_variant(const DwFlatArgs &d, size_t smem, int ctas, cudaStream_t s) {
+int launch_planes_variant(const DwFlatArgs &d, size_t smem, cudaStream_t s) {
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
@@ -401,6 +413,9 @@ int launch_planes_variant(const DwFlatArgs &d, size_t smem, int ctas, cudaStream
     FML_CUDA(cudaFuncSetAttribute(conv_depthwise_planes_kernel<KH, KW, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set[dev & 63] = true;
   }
+  int ctas = 1;
+  const int st = persistent_ctas(conv_depthwise_planes_kernel<KH, KW, S>, smem, d.items, &ctas);
+  if (st != FML_OK) return st;
   FML_LAUNCH((conv_depthwise_planes_kernel<KH, KW, S>), dim3((unsigned)ctas), dim3(kDwThreads), smem, s, d);
   return FML_OK;
 }
@@ -456,14 +471,12 @@ bool launch_depthwise_planes(const fml_tensor *x, const fml_tensor *w, const fml
   d.status = device_status_word();
   if (!d.status) return false;
   const size_t smem = smem_of();
-  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(200 * 1024) / (smem + 1024)));
-  const int ctas = (int)std::min<int64_t>(d.items, (int64_t)148 * per_sm);
   const int key = (int)(KH * 10 + S);
   switch (key) {
-  case 31: *status = launch_planes_variant<3, 3, 1>(d, smem, ctas, s); break;
-  case 32: *status = launch_planes_variant<3, 3, 2>(d, smem, ctas, s); break;
-  case 51: *status = launch_planes_variant<5, 5, 1>(d, smem, ctas, s); break;
-  default: *status = launch_planes_variant<5, 5, 2>(d, smem, ctas, s); break;
+  case 31: *status = launch_planes_variant<3, 3, 1>(d, smem, s); break;
+  case 32: *status = launch_planes_variant<3, 3, 2>(d, smem, s); break;
+  case 51: *status = launch_planes_variant<5, 5, 1>(d, smem, s); break;
+  default: *status = launch_planes_variant<5, 5, 2>(d, smem, s); break;
   }
   return true;
 }
@@ -471,7 +484,7 @@ bool launch_depthwise_planes(const fml_tensor *x, const fml_tensor *w, const fml
 using DwKernelFn = void (*)(const CUtensorMap, const DwTmaArgs);
 
 template <int KH, int KW, int S>
-int launch_variant(const CUtensorMap &map, const DwTmaArgs &d, size_t smem, int ctas, cudaStream_t s) {
+int launch_variant(const CUtensorMap &map, const DwTmaArgs &d, size_t smem, cudaStream_t s) {
   static bool attr_set[64] = {false};
   int dev = 0;
   FML_CUDA(cudaGetDevice(&dev));
@@ -479,6 +492,9 @@ int launch_variant(const CUtensorMap &map, const DwTmaArgs &d, size_t smem, int 
     FML_CUDA(cudaFuncSetAttribute(conv_depthwise_tma_kernel<KH, KW, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set[dev & 63] = true;
   }
+  int ctas = 1;
+  const int st = persistent_ctas(conv_depthwise_tma_kernel<KH, KW, S>, smem, d.items, &ctas);
+  if (st != FML_OK) return st;
   FML_LAUNCH((conv_depthwise_tma_kernel<KH, KW, S>), dim3((unsigned)ctas), dim3(kDwThreads), smem, s, map, d);
   return FML_OK;
 }
@@ -563,14 +579,12 @@ bool launch_depthwise_tma(const fml_tensor *x, const fml_tensor *w, const fml_te
   static const int stages_env = [] { const char *e = getenv("FLUIDML_DEPTHWISE_STAGES"); return e ? atoi(e) : 0; }();
   d.stages = stages_env >= 2 && stages_env <= kDwMaxStages ? stages_env : 2;  // measured: more resident CTAs beat deeper rings
   const size_t smem = d.stages * ((stage + 127) / 128 * 128) + 128;
-  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(200 * 1024) / (smem + 1024)));
-  const int ctas = (int)std::min<int64_t>(items, (int64_t)148 * per_sm);
   const int key = (int)(KH * 10 + S);
   switch (key) {
-  case 31: *status = launch_variant<3, 3, 1>(map, d, smem, ctas, s); break;
-  case 32: *status = launch_variant<3, 3, 2>(map, d, smem, ctas, s); break;
-  case 51: *status = launch_variant<5, 5, 1>(map, d, smem, ctas, s); break;
-  default: *status = launch_variant<5, 5, 2>(map, d, smem, ctas, s); break;
+  case 31: *status = launch_variant<3, 3, 1>(map, d, smem, s); break;
+  case 32: *status = launch_variant<3, 3, 2>(map, d, smem, s); break;
+  case 51: *status = launch_variant<5, 5, 1>(map, d, smem, s); break;
+  default: *status = launch_variant<5, 5, 2>(map, d, smem, s); break;
   }
   return true;
 }
