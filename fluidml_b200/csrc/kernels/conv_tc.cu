@@ -154,7 +154,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * NS + 2 * RS + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   float *bias_s = reinterpret_cast<float *>(tmem_slot + 4);  // this tile's slice of the bias, [BN]
-  float *scale_s = bias_s + 128;                             // this image's input scale, [n_icb * ICB] (when a.scale)
+  float *scale_s = bias_s + 256;                             // this image's input scale, [n_icb * ICB] (when a.scale)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int t = blockIdx.x;
@@ -594,6 +594,26 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   const bool three = p->precision != FML_GEMM_TF32;
   a.tile_n = a.OC >= 128 ? 128 : (a.OC + 31) / 32 * 32;
   if (a.tile_n > 128) a.tile_n = 128;
+  {
+    // A tile of ONE k block is paid per tile, not per column: set-up, the first patch, the operand
+    // split and the 12 MMAs cost the same for 16 columns as for 128 (a 144-channel layer cut
+    // 128 + 16 ran two CTAs per pixel tile, each with the full fixed cost).  When such a layer has
+    // more pixel tiles than SMs it takes the widest tile (a multiple of 32, at most 256) that
+    // minimises tiles x (fixed cost + columns), the fixed cost counted as 128 columns; with one
+    // operand stage two CTAs still share an SM up to 192 columns.  Measured on EfficientNet-B0:
+    // batch 64 2.54 -> 2.47 ms; at batch 1, and for layers of two to eight k blocks, wide tiles
+    // lose (FLUIDML_CONV_WIDE_TILES=1 takes those too, =0 none).
+    static const int wide = [] { const char *e = getenv("FLUIDML_CONV_WIDE_TILES"); return e ? atoi(e) : 2; }();
+    const int64_t px_tiles = (int64_t)((a.OW + a.TW - 1) / a.TW) * ((a.OH + a.TH - 1) / a.TH) * a.N;
+    if (wide && a.OC > 128 && a.n_icb * a.taps <= (wide == 2 ? 1 : 8) && (wide == 1 || px_tiles > 148)) {
+      int best = 128, best_cost = ((a.OC + 127) / 128) * (128 + 128);
+      for (int tn = 160; tn <= 256; tn += 32) {
+        const int cost = ((a.OC + tn - 1) / tn) * (128 + tn);
+        if (cost < best_cost) { best = tn; best_cost = cost; }
+      }
+      a.tile_n = best;
+    }
+  }
   // a patch feeds `taps` k blocks: with a single tap every k block waits for its own patch, so the
   // patch ring must be as deep as the operand ring to cover the load latency
   a.raw_stages = a.taps == 1 ? 6 : a.taps <= 4 ? 3 : 2;
@@ -603,11 +623,13 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   a.raw_stages = std::max(1, std::min(a.raw_stages, a.n_icb));
   const size_t raw_pitch = ((size_t)a.raw_elems * icb * 4 + 127) / 128 * 128;
   const size_t stage = (size_t)icb * a.tile_n * 4 * (three ? 2 : 1);
-  FML_REQUIRE(a.raw_stages * raw_pitch + 2 * stage <= kSmemBudget, FML_UNSUPPORTED, "fml_conv: patch does not fit in shared memory");
+  const int min_stages = a.n_icb * a.taps == 1 ? 1 : 2;  // a tile of one k block needs one operand stage
+  while (a.raw_stages > 1 && a.raw_stages * raw_pitch + min_stages * stage > kSmemBudget) --a.raw_stages;  // wide tiles: shorter patch ring
+  FML_REQUIRE(a.raw_stages * raw_pitch + min_stages * stage <= kSmemBudget, FML_UNSUPPORTED, "fml_conv: patch does not fit in shared memory");
   int stages = (int)((kSmemBudget - a.raw_stages * raw_pitch) / stage);
   const int a_cols = (three ? 2 : 1) * icb;
   stages = std::min(stages, (512 - (a.tile_n + 31) / 32 * 32) / a_cols);
-  stages = std::max(2, std::min(std::min(stages, 8), a.n_icb * a.taps));
+  stages = std::max(min_stages, std::min(std::min(stages, 8), a.n_icb * a.taps));
   {
     // A layer whose tiles are more than one wave of SMs runs two CTAs per SM with short rings
     // rather than one with deep ones: the second CTA's loads, conversions and epilogue fill the
@@ -679,7 +701,7 @@ int launch_conv_tc(const fml_tensor *x, const fml_tensor *w, const fml_tensor *b
   }
   const size_t ring = (size_t)stages * stage + a.raw_stages * raw_pitch;
   const size_t staging = a.split_k > 1 ? (((size_t)kBM * (a.tile_n + 4) * 4 + 127) & ~(size_t)127) : 0;
-  size_t smem = std::max(ring, staging) + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 128 * 4 /* bias slice */ +
+  size_t smem = std::max(ring, staging) + (3 * stages + 2 * a.raw_stages + 1) * 8 + 16 + 256 * 4 /* bias slice */ +
                 (a.scale ? (size_t)a.n_icb * icb * 4 : 0) /* input scale */ + 1024;
   {  // co-residency capped by TMEM columns, as in the GEMM
     unsigned need = (unsigned)((a.tile_n + 31) / 32 * 32 + a_cols * stages), cols = 32;

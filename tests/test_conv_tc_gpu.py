@@ -44,6 +44,9 @@ CASES = [  # (x shape, w shape, pads) -- VGG blocks, ragged tiles, 1x1, 5x5, few
     # 1x1 kernels over 7 x 7 planes: whole planes fetched with a plain bulk copy
     ((1, 64, 7, 7), (96, 64, 1, 1), (0, 0)),
     ((3, 1152, 7, 7), (192, 1152, 1, 1), (0, 0)),
+    # one k block per tile and more pixel tiles than SMs: output tiles wider than 128 channels
+    ((6, 24, 56, 56), (144, 24, 1, 1), (0, 0)),    # 160-wide tile, one operand stage, two CTAs per SM
+    ((20, 32, 28, 28), (240, 32, 1, 1), (0, 0)),   # 256-wide tile
 ]
 
 
