@@ -182,6 +182,15 @@ def squeeze_excite_gate(x, w1, b1, w2, b2, act1, act2, gate, stream=None):
                                         _ref(gate), stream))
 
 
+def sum_of_products(a_list, b_list, out, stream=None):
+    """out = a0*b0 + a1*b1 + ... in the rounding order of the Mul / Add chain (up to 12 pairs)."""
+    n = len(a_list)
+    assert n == len(b_list)
+    arr_a = (ctypes.POINTER(Tensor) * n)(*[ctypes.pointer(t.c()) for t in a_list])
+    arr_b = (ctypes.POINTER(Tensor) * n)(*[ctypes.pointer(t.c()) for t in b_list])
+    check(lib().fml_sum_of_products(n, arr_a, arr_b, _ref(out), stream))
+
+
 def bias_gelu(x, bias, out, c0, c1, c2, stream=None):
     check(lib().fml_bias_gelu(_ref(x), _ref(bias), _ref(out), ctypes.c_float(c0),
                               ctypes.c_float(c1), ctypes.c_float(c2), stream))

@@ -428,6 +428,41 @@ bool FuseGateIntoConv(Rewriter &rw, const NodePtr &mul) {
   return true;
 }
 
+// ---- MulCommon -> FusedMulAdd -> FusedMulAdd ...: a sum of products (ConvBERT's span convolution
+// adds nine windows times nine softmax columns) becomes one pass.  Matched at the last node of the
+// chain and walked back to the plain product it starts from; every intermediate sum must have the
+// next link as its only reader.  Same rounding order as the chain.
+bool FuseMulAddChain(Rewriter &rw, const NodePtr &last) {
+  if (last->kind != Kind::FusedMulAdd || last->inputs.size() != 3) return false;
+  {  // `last` must end the chain: its result is not the addend of another link
+    NodePtr next = rw.Sole(last->output);
+    if (next && next->kind == Kind::FusedMulAdd && next->inputs.size() == 3 && next->inputs[2] == last->output) return false;
+  }
+  std::vector<NodePtr> links = {last};  // from the end backwards
+  NodePtr head;                         // the MulCommon the chain starts from
+  for (;;) {
+    const RegionPtr &addend = links.back()->inputs[2];
+    auto it = rw.producer.find(addend.get());
+    if (it == rw.producer.end() || rw.Sole(addend) != links.back()) return false;
+    const NodePtr &prod = it->second;
+    if (prod->kind == Kind::FusedMulAdd && prod->inputs.size() == 3) { links.push_back(prod); continue; }
+    if (prod->kind == Kind::MulCommon && prod->inputs.size() == 2) { head = prod; break; }
+    return false;
+  }
+  const size_t pairs = links.size() + 1;
+  if (pairs < 3 || pairs > 12) return false;  // fml_sum_of_products takes up to 12
+  std::vector<RegionPtr> ops = {head->inputs[0], head->inputs[1]};
+  for (size_t i = links.size(); i-- > 0;) { ops.push_back(links[i]->inputs[0]); ops.push_back(links[i]->inputs[1]); }
+  for (const RegionPtr &r : ops)
+    if (r->meta.GetType() != Type::kFloat32) return false;
+  if (last->output->meta.GetType() != Type::kFloat32) return false;
+  last->kind = Kind::FusedMulAddChain;
+  last->inputs = ops;
+  rw.Kill(head);
+  for (size_t i = 1; i < links.size(); ++i) rw.Kill(links[i]);
+  return true;
+}
+
 // ---- Conv -> SiLU: the activation rides in the convolution's epilogue
 bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
   if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
@@ -550,7 +585,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseGateIntoConv, FuseMulAdd};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseGateIntoConv, FuseMulAdd, FuseMulAddChain};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

@@ -232,6 +232,21 @@ public:
   }
 };
 
+// A chain MulCommon -> FusedMulAdd -> FusedMulAdd ... that sums products, in one launch
+class FusedMulAddChainKernel : public Kernel {
+public:
+  std::string GetKernelName() const override { return "FusedMulAddChainKernel"; }
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output, const Buffer &) const override {
+    const std::vector<fml_tensor> ops = in;  // a0, b0, a1, b1, ...
+    rec.Add(GetKernelName(), [=](void *s) {
+      const int n = (int)(ops.size() / 2);
+      std::vector<const fml_tensor *> a(n), b(n);
+      for (int i = 0; i < n; ++i) { a[i] = &ops[2 * i]; b[i] = &ops[2 * i + 1]; }
+      return fml_sum_of_products(n, a.data(), b.data(), &output, s);
+    });
+  }
+};
+
 // ReduceMean over H, W -> 1 x 1 Conv -> 1 x 1 Conv (the gate of a squeeze-and-excite block) in one
 // launch (reduce_mean.cpp + conv.cpp twice in the reference)
 class SqueezeExciteGateKernel : public SingleInputWithoutBufferKernel {
@@ -690,6 +705,7 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
   case Kind::Sigmoid: return std::make_unique<SigmoidKernel>();
   case Kind::Silu: return std::make_unique<SiluKernel>();
   case Kind::FusedMulAdd: return std::make_unique<FusedMulAddKernel>();
+  case Kind::FusedMulAddChain: return std::make_unique<FusedMulAddChainKernel>();
   case Kind::SqueezeExciteGate: {
     size_t k = 0;
     const fml_tensor w1 = C(k++);
@@ -818,7 +834,7 @@ const char *KindName(Kind k) {
       "Not", "Pad", "Pow", "ReduceMean", "Relu", "Reshape", "Slice", "Softmax", "Sqrt", "Squeeze", "SubConstantLhs",
       "SubCommon", "Tanh", "Transpose", "Unsqueeze", "UnsqueezeSubLhsScalarMulRhsScalar",
       "WhereConstantCondConstantScalarY", "WhereConstantCondConstantTensorY", "Sigmoid", "Identity", "FusedGemm",
-      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd", "SqueezeExciteGate"};
+      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd", "FusedMulAddChain", "SqueezeExciteGate"};
   return names[(int)k];
 }
 }  // namespace flow

@@ -316,6 +316,66 @@ __global__ void mul_add_generic(Iter<4> it, float *out, const float *a, const fl
   }
 }
 
+// out = a0*b0 + a1*b1 + ... + a(n-1)*b(n-1), all broadcast to out, evaluated as the chain of
+// MulCommon / AddCommon kernels it replaces: acc = rn(a0*b0); acc = rn(rn(ai*bi) + acc) for
+// i = 1 .. n-1 (every product and every sum rounded to fp32, no fused multiply-add), so the result
+// is theirs bit for bit.  One pass: every operand read once, nothing written in between.
+constexpr int kMaxPairs = 12;
+struct PairPtrs { const float *a[kMaxPairs], *b[kMaxPairs]; };
+
+__global__ void sum_products_vec4(Iter<2 * kMaxPairs + 1> it, float *out, PairPtrs ptr, int n) {
+  pdl_prologue();
+  constexpr int NO = 2 * kMaxPairs + 1;
+  const uint32_t inner4 = (uint32_t)(it.shape[it.rank - 1] >> 2), total4 = (uint32_t)(it.total >> 2);
+  const int l = it.rank - 1;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += gridDim.x * blockDim.x) {
+    uint32_t row = it.rank > 1 ? i / inner4 : 0;
+    const uint32_t c4 = i - row * inner4;
+    uint32_t off[NO];
+#pragma unroll
+    for (int o = 0; o < NO; ++o) off[o] = it.stride[o][l] == 1 ? c4 * 4 : 0;
+    for (int d = it.rank - 2; d >= 0; --d) {
+      uint32_t cc = row;
+      if (d > 0) { const uint32_t q = row / (uint32_t)it.shape[d]; cc = row - q * (uint32_t)it.shape[d]; row = q; }
+#pragma unroll
+      for (int o = 0; o < NO; ++o)
+        if (o <= 2 * n) off[o] += cc * (uint32_t)it.stride[o][d];
+    }
+    auto load = [](const float *p, uint32_t o, bool vec) {
+      if (vec) return *reinterpret_cast<const float4 *>(p + o);
+      const float t = p[o];
+      return make_float4(t, t, t, t);
+    };
+    float4 x[kMaxPairs], y[kMaxPairs];
+#pragma unroll
+    for (int p = 0; p < kMaxPairs; ++p)
+      if (p < n) {
+        x[p] = load(ptr.a[p], off[1 + 2 * p], it.stride[1 + 2 * p][l] == 1);
+        y[p] = load(ptr.b[p], off[2 + 2 * p], it.stride[2 + 2 * p][l] == 1);
+      }
+    float4 acc = make_float4(__fmul_rn(x[0].x, y[0].x), __fmul_rn(x[0].y, y[0].y), __fmul_rn(x[0].z, y[0].z), __fmul_rn(x[0].w, y[0].w));
+#pragma unroll
+    for (int p = 1; p < kMaxPairs; ++p)
+      if (p < n) {
+        acc.x = __fadd_rn(__fmul_rn(x[p].x, y[p].x), acc.x);
+        acc.y = __fadd_rn(__fmul_rn(x[p].y, y[p].y), acc.y);
+        acc.z = __fadd_rn(__fmul_rn(x[p].z, y[p].z), acc.z);
+        acc.w = __fadd_rn(__fmul_rn(x[p].w, y[p].w), acc.w);
+      }
+    *reinterpret_cast<float4 *>(out + off[0]) = acc;
+  }
+}
+__global__ void sum_products_generic(Iter<2 * kMaxPairs + 1> it, float *out, PairPtrs ptr, int n) {
+  pdl_prologue();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < it.total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[2 * kMaxPairs + 1];
+    offsets_of(it, i, off);
+    float acc = __fmul_rn(ptr.a[0][off[1]], ptr.b[0][off[2]]);
+    for (int p = 1; p < n; ++p) acc = __fadd_rn(__fmul_rn(ptr.a[p][off[1 + 2 * p]], ptr.b[p][off[2 + 2 * p]]), acc);
+    out[off[0]] = acc;
+  }
+}
+
 bool vec4_ok(const Iter<3> &it, const void *out, const void *a, const void *b) {
   int l = it.rank - 1;
   if (it.shape[l] % 4 != 0 || it.stride[0][l] != 1) return false;
@@ -485,6 +545,51 @@ extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_
   FML_LAUNCH((where_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
       y ? (const float *)y->data : nullptr, y_scalar);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_sum_of_products(int n, const fml_tensor *const *a, const fml_tensor *const *b, const fml_tensor *out,
+                                   void *stream) {
+  FML_REQUIRE(a && b && out && n >= 1 && n <= kMaxPairs, FML_BAD_ARG, "fml_sum_of_products: 1 to %d pairs", kMaxPairs);
+  FML_REQUIRE(out->dtype == FML_F32, FML_UNSUPPORTED, "fml_sum_of_products: fp32 only");
+  constexpr int NO = 2 * kMaxPairs + 1;
+  Iter<NO> it;
+  const fml_tensor *ins[NO - 1];
+  PairPtrs ptr;
+  for (int p = 0; p < kMaxPairs; ++p) {
+    ins[2 * p] = p < n ? a[p] : nullptr;
+    ins[2 * p + 1] = p < n ? b[p] : nullptr;
+    if (p < n) {
+      FML_REQUIRE(a[p] && b[p] && a[p]->dtype == FML_F32 && b[p]->dtype == FML_F32, FML_BAD_ARG,
+                  "fml_sum_of_products: pair %d must be two fp32 tensors", p);
+      ptr.a[p] = (const float *)a[p]->data;
+      ptr.b[p] = (const float *)b[p]->data;
+    } else {
+      ptr.a[p] = ptr.b[p] = nullptr;
+    }
+  }
+  int st = make_iter(it, out, ins, "fml_sum_of_products");
+  if (st != FML_OK) return st;
+  if (it.total == 0) return FML_OK;
+  const int l = it.rank - 1;
+  bool ok = (it.shape[l] & 3) == 0 && it.stride[0][l] == 1 && aligned16(out->data) && it.total < (1ll << 30);
+  for (int o = 1; o <= 2 * n && ok; ++o) {
+    ok = (it.stride[o][l] == 1 || it.stride[o][l] == 0) && aligned16(o & 1 ? ptr.a[(o - 1) / 2] : ptr.b[(o - 2) / 2]);
+    int64_t last = 0;
+    for (int d = 0; d < it.rank && ok; ++d) {
+      if (it.stride[o][d] < 0) ok = false;
+      last += (it.shape[d] - 1) * it.stride[o][d];
+      if (d < l && it.stride[o][l] != 0 && it.stride[o][d] % 4 != 0) ok = false;  // 16-byte rows for vector operands
+    }
+    ok = ok && last < (1ll << 31) - 8;
+  }
+  for (int d = 0; d < l && ok; ++d) ok = it.stride[0][d] % 4 == 0 && it.stride[0][d] >= 0;
+  if (ok) {
+    FML_LAUNCH((sum_products_vec4), grid_for(it.total / 4, 256), 256, 0, as_stream(stream), it, (float *)out->data, ptr, n);
+  } else {
+    FML_LAUNCH((sum_products_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), it, (float *)out->data, ptr, n);
+  }
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }

@@ -156,6 +156,14 @@ int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor 
 int fml_mul_add(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c, const fml_tensor *out,
                 void *stream);
 
+/* A chain of MulCommonKernel / AddCommonKernel launches (mul.cpp, add.cpp) that sums n products
+ * (ConvBERT's span convolution: nine sliding windows times nine softmax columns) in one pass:
+ *   acc = a[0] * b[0];  acc = a[i] * b[i] + acc  for i = 1 .. n-1,
+ * every product and every sum rounded to fp32 as the separate kernels round them, all operands
+ * broadcast to out.  1 <= n <= 12. */
+int fml_sum_of_products(int n, const fml_tensor *const *a, const fml_tensor *const *b, const fml_tensor *out,
+                        void *stream);
+
 /* The gate of a squeeze-and-excite block: ReduceMeanKernel over the two spatial axes
  * (reduce_mean.cpp:16-98) followed by two 1 x 1 ConvWithoutPaddingKernel launches over the single
  * remaining pixel (conv.cpp:27-280), in one launch:

@@ -120,6 +120,7 @@ def main() -> None:
     g.add_argument("--precision", default="3xtf32", choices=["fp32", "3xtf32", "tf32"])
     g.add_argument("--tile-n", type=int, default=0)
     g.add_argument("--split-k", type=int, default=0)
+    g.add_argument("--b-kmajor", action="store_true", help="B stored [n, k] (a Gemm with transB = 1: a classifier's weights)")
     r = sub.add_parser("resident")
     r.add_argument("--layers", type=int, default=2)
     r.add_argument("--reps", type=int, default=20)
@@ -136,7 +137,13 @@ def main() -> None:
         prec = {"fp32": cabi.GEMM_FP32, "3xtf32": cabi.GEMM_3XTF32, "tf32": cabi.GEMM_TF32}[args.precision]
         lead = (args.batch,) if args.batch > 1 else ()
         a = DT.from_numpy(rng.standard_normal((*lead, args.m, args.k)).astype(np.float32))
-        b = DT.from_numpy(rng.standard_normal((*lead, args.k, args.n)).astype(np.float32))
+        if args.b_kmajor:
+            bt = DT.from_numpy(rng.standard_normal((*lead, args.n, args.k)).astype(np.float32))
+            st = list(bt.strides)
+            st[-1], st[-2] = st[-2], st[-1]
+            b = bt.view((*lead, args.k, args.n), st, 0)
+        else:
+            b = DT.from_numpy(rng.standard_normal((*lead, args.k, args.n)).astype(np.float32))
         c = DT((*lead, args.m, args.n), np.float32)
         p = cabi.gemm_params(precision=prec, tile_n=args.tile_n, split_k=args.split_k)
         info = cabi.gemm_plan(a, b, c, p)

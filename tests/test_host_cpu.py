@@ -232,8 +232,17 @@ def test_mul_add_pairs_are_fused_when_the_product_has_one_consumer():
     m = _mul_add_chain()
     unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
     assert unfused.count("MulCommon") == 4 and unfused.count("AddCommon") == 4
-    # one product of the first Add and x2*w2 ride in their Adds; x3*w3 also feeds the Relu and stays a Mul
-    assert fused.count("FusedMulAdd") == 2 and fused.count("MulCommon") == 2 and fused.count("AddCommon") == 2
+    # one product of the first Add and x2*w2 ride in their Adds; x3*w3 also feeds the Relu and stays a Mul;
+    # the plain product x1*w1 and the two links after it are then one sum of three products
+    assert fused.count("FusedMulAddChain") == 1 and fused.count("FusedMulAdd") == 0
+    assert fused.count("MulCommon") == 1 and fused.count("AddCommon") == 2
+
+
+def test_convbert_span_convolution_is_one_sum_of_products():
+    m = models.build_convbert(layers=2, hidden=256, heads=8, ffn=512, vocab=400, batch=3, seq=48)
+    unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
+    assert unfused.count("MulCommon") >= 2 * 10 and unfused.count("AddCommon") >= 2 * 8
+    assert fused.count("FusedMulAddChain") == 2 and fused.count("FusedMulAdd") == 0
 
 
 def test_squeeze_excite_gates_become_one_node_each():

@@ -126,6 +126,39 @@ def test_squeeze_excite_gate_rejects_what_it_cannot_take():
         cabi.squeeze_excite_gate(x, DT.from_numpy(rnd(2, 8, 1, 1)), None, DT.from_numpy(rnd(8, 2, 1, 1)), None, 1, 4, gate)
 
 
+@pytest.mark.parametrize("shape,bshape,n,windows", [
+    ((8, 128, 6, 64), (8, 128, 6, 1), 9, True),    # ConvBERT's span convolution: sliding windows of one padded tensor x softmax columns
+    ((2, 5, 7, 3), (2, 5, 7, 3), 3, False),       # odd sizes: element path
+    ((4, 32, 16), (1, 32, 1), 12, False),          # the maximum number of pairs, broadcast along two dims
+    ((3, 40), (3, 40), 1, False),                  # a single product
+])
+def test_sum_of_products_equals_the_mul_add_chain(shape, bshape, n, windows):
+    """fml_sum_of_products rounds every product and every partial sum like the chain MulCommon ->
+    (MulCommon, AddCommon) x (n - 1) it replaces: bit-exact against the oracle's kernels run in
+    that order, also when the operands are overlapping strided views of one buffer."""
+    if windows:  # a_i = padded[:, i : i + L] (views), b_i = columns of one [..., n] tensor (views)
+        B, L, H, D = shape
+        padded = rnd(B, L + n - 1, H, D)
+        taps = rnd(B, L, H, n)
+        dp, dt = DT.from_numpy(padded), DT.from_numpy(taps)
+        a_h = [padded[:, i:i + L] for i in range(n)]
+        b_h = [taps[..., i:i + 1] for i in range(n)]
+        a_d = [dp.view(shape, dp.strides, i * dp.strides[1]) for i in range(n)]
+        b_d = [dt.view(bshape, dt.strides, i) for i in range(n)]
+    else:
+        a_h = [rnd(*shape) for _ in range(n)]
+        b_h = [rnd(*bshape) for _ in range(n)]
+        a_d = [DT.from_numpy(t) for t in a_h]
+        b_d = [DT.from_numpy(t) for t in b_h]
+    acc = orc.binary("Mul", np.ascontiguousarray(a_h[0]), np.ascontiguousarray(b_h[0]), np.empty(shape, np.float32))
+    for i in range(1, n):
+        prod = orc.binary("Mul", np.ascontiguousarray(a_h[i]), np.ascontiguousarray(b_h[i]), np.empty(shape, np.float32))
+        acc = orc.binary("Add", prod, acc, np.empty(shape, np.float32))
+    out = DT(shape, np.float32)
+    cabi.sum_of_products(a_d, b_d, out)
+    assert np.array_equal(out.numpy(), acc)
+
+
 @pytest.mark.parametrize("sa,sb,axis,dtype", [
     ((4, 16, 64, 16), (4, 16, 64, 16), 3, np.float32),   # rotary halves: 16-byte groups, split inside the innermost dim
     ((2, 8, 12, 32), (2, 4, 12, 32), 1, np.float32),     # 16-byte groups, split along an outer dim
