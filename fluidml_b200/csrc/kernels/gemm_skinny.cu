@@ -36,8 +36,12 @@ struct SkinnyArgs {
   float *partials;     // [batch * tiles_n][splits][M][kColsPerCta]
 };
 
-template <bool KMAJOR>
-__global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
+// FEW: the instantiation for at most four rows over 16-byte-aligned K-major operands (classifier
+// heads and poolers at batch 1 to 4).  It holds only that path's registers (the general path's 32
+// accumulators per lane made the shared kernel 176 registers = one CTA per SM = 12 % occupancy, and
+// a 411 MB weight matrix streamed at 48 % of DRAM's cycles), so three CTAs share an SM.
+template <bool KMAJOR, bool FEW>
+__global__ void __launch_bounds__(kThreads, FEW ? 3 : 1) gemm_skinny_kernel(SkinnyArgs a) {
   pdl_launch_dependents();
   // B is what this kernel streams; while the preceding kernel drains, start it towards L2
   l2_prefetch_span(a.p.b, ((a.p.K - 1) * a.p.b_sk + (a.p.N - 1) * a.p.b_sn + 1) * (int64_t)sizeof(float), 4 << 20);
@@ -62,8 +66,7 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
     // at once, so that eight weight loads are in flight per lane, the row chunks are loaded once
     // for all four columns, and the shuffle reductions are amortised.  Same per-lane summation
     // order as the general loop below.
-    const bool few_rows = vec && M <= 4;
-    if (few_rows) {
+    if (FEW) {  // the launcher checks `vec && M <= 4` before it picks this instantiation
       const int64_t kv = k0 + ((k1 - k0) & ~(int64_t)3);
       float acc4[4][4];
 #pragma unroll
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(kThreads) gemm_skinny_kernel(SkinnyArgs a) {
             if (lane == 0) red[m][warp * 4 + j] = v;
           }
     }
-    for (int c = few_rows ? kColsPerCta : warp; c < kColsPerCta; c += kThreads / 32) {
+    for (int c = FEW ? kColsPerCta : warp; c < kColsPerCta; c += kThreads / 32) {
       const int64_t n = n0 + c;
       float acc[kMaxM];
 #pragma unroll
@@ -289,8 +292,15 @@ int launch_skinny(const GemmProblem &p, const GemmEpilogue &e, const SkinnyPlan 
   a.counters = reinterpret_cast<unsigned *>(scratch);
   a.partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + pl.counter_bytes);
   const dim3 grid((unsigned)pl.tiles_n, (unsigned)pl.splits, (unsigned)(p.nb0 * p.nb1));
-  if (p.b_sk == 1 && p.b_sn != 1) FML_LAUNCH((gemm_skinny_kernel<true>), grid, kThreads, 0, s, a);
-  else FML_LAUNCH((gemm_skinny_kernel<false>), grid, kThreads, 0, s, a);
+  if (p.b_sk == 1 && p.b_sn != 1) {
+    // (k slices start at multiples of 128, so every slice keeps the 16-byte alignment of its row)
+    const bool few = p.M <= 4 && p.a_sk == 1 && (p.a_sm & 3) == 0 && (p.b_sn & 3) == 0 && aligned16(p.a) && aligned16(p.b) &&
+                     (p.a_b0 & 3) == 0 && (p.a_b1 & 3) == 0 && (p.b_b0 & 3) == 0 && (p.b_b1 & 3) == 0;
+    if (few) FML_LAUNCH((gemm_skinny_kernel<true, true>), grid, kThreads, 0, s, a);
+    else FML_LAUNCH((gemm_skinny_kernel<true, false>), grid, kThreads, 0, s, a);
+  } else {
+    FML_LAUNCH((gemm_skinny_kernel<false, false>), grid, kThreads, 0, s, a);
+  }
   return FML_OK;
 }
 
