@@ -191,6 +191,11 @@ def sum_of_products(a_list, b_list, out, stream=None):
     check(lib().fml_sum_of_products(n, arr_a, arr_b, _ref(out), stream))
 
 
+def rotary(x, cosv, sinv, rot, out, stream=None):
+    """Rotary position embedding over the first `rot` features (halves convention)."""
+    check(lib().fml_rotary(_ref(x), _ref(cosv), _ref(sinv), ctypes.c_int64(int(rot)), _ref(out), stream))
+
+
 def bias_gelu(x, bias, out, c0, c1, c2, stream=None):
     check(lib().fml_bias_gelu(_ref(x), _ref(bias), _ref(out), ctypes.c_float(c0),
                               ctypes.c_float(c1), ctypes.c_float(c2), stream))

@@ -54,6 +54,7 @@ enum class Kind {
   FusedAttention,  // softmax(Q K^T / divisor + mask) V; inputs: Q, K^T, V, [mask]
   FusedMulAdd,     // a * b + c, broadcast; inputs: a, b, c
   FusedMulAddChain,   // a0*b0 + a1*b1 + ... in the rounding order of the Mul / Add chain it replaces; inputs: a0, b0, a1, b1, ...
+  Rotary,             // rotary position embedding over the first `value` features; inputs: x, cos, sin
   SqueezeExciteGate,  // act2(W2 act1(W1 mean_hw(x) + b1) + b2); consts: W1, [b1], W2, [b2]; has_bias / has_bias2 = b1 / b2 present; act, act2
 };
 const char *KindName(Kind k);

@@ -463,6 +463,77 @@ bool FuseMulAddChain(Rewriter &rw, const NodePtr &last) {
   return true;
 }
 
+// ---- Rotary position embedding as exported (GPT-NeoX):
+//   xr = x[..., :rot]; xp = x[..., rot:]
+//   out = Concat(xr * cos + Concat(-xr[..., rot/2:], xr[..., :rot/2]) * sin, xp)
+// Matched at the final Concat (after FuseMulAdd has made `xr * cos + (...)` one node); ten nodes per
+// projection (five of them launches) become one.
+bool FuseRotary(Rewriter &rw, const NodePtr &cat) {
+  if (cat->kind != Kind::Concat2 || cat->inputs.size() != 2) return false;
+  const RegionPtr &y = cat->output;
+  const size_t rank = y->meta.GetRank();
+  if (rank < 1 || y->meta.GetType() != Type::kFloat32) return false;
+  const int64_t last = (int64_t)rank - 1;
+  if (cat->axis != last && cat->axis != -1) return false;
+  auto producer_of = [&](const RegionPtr &r) -> NodePtr {
+    auto it = rw.producer.find(r.get());
+    return it == rw.producer.end() ? nullptr : it->second;
+  };
+  // a Slice along the last axis only: returns its start there, -1 otherwise
+  auto last_axis_slice = [&](const NodePtr &n) -> int64_t {
+    if (!n || n->kind != Kind::Slice || n->inputs.size() != 1 || n->starts.size() != rank) return -1;
+    const auto &is = n->inputs[0]->meta.GetShape(), &os = n->output->meta.GetShape();
+    if (is.size() != rank || os.size() != rank) return -1;
+    for (size_t i = 0; i + 1 < rank; ++i)
+      if (n->starts[i] != 0 || is[i] != os[i]) return -1;
+    return n->starts[rank - 1];
+  };
+  NodePtr fma = producer_of(cat->inputs[0]), pass = producer_of(cat->inputs[1]);
+  if (!fma || fma->kind != Kind::FusedMulAdd || fma->inputs.size() != 3 || rw.Sole(fma->output) != cat) return false;
+  NodePtr xr = producer_of(fma->inputs[0]);
+  RegionPtr cosv = fma->inputs[1];
+  if (last_axis_slice(xr) != 0) {  // the product may be written cos * xr
+    xr = producer_of(fma->inputs[1]);
+    cosv = fma->inputs[0];
+    if (last_axis_slice(xr) != 0) return false;
+  }
+  const RegionPtr &src = xr->inputs[0];
+  const int64_t rot = xr->output->meta.GetShape()[rank - 1], D = src->meta.GetShape()[rank - 1];
+  if (rot < 2 || (rot & 1) || last_axis_slice(pass) != rot || pass->inputs[0] != src ||
+      pass->output->meta.GetShape()[rank - 1] != D - rot || rw.Sole(pass->output) != cat)
+    return false;
+  NodePtr mul = producer_of(fma->inputs[2]);
+  if (!mul || mul->kind != Kind::MulCommon || mul->inputs.size() != 2 || rw.Sole(mul->output) != fma) return false;
+  NodePtr half_cat = producer_of(mul->inputs[0]);
+  RegionPtr sinv = mul->inputs[1];
+  if (!half_cat || half_cat->kind != Kind::Concat2) { half_cat = producer_of(mul->inputs[1]); sinv = mul->inputs[0]; }
+  if (!half_cat || half_cat->kind != Kind::Concat2 || half_cat->inputs.size() != 2 || rw.Sole(half_cat->output) != mul ||
+      (half_cat->axis != last && half_cat->axis != -1))
+    return false;
+  NodePtr neg = producer_of(half_cat->inputs[0]), lo = producer_of(half_cat->inputs[1]);
+  if (!neg || neg->kind != Kind::Neg || rw.Sole(neg->output) != half_cat) return false;
+  NodePtr hi = producer_of(neg->inputs[0]);
+  if (last_axis_slice(hi) != rot / 2 || last_axis_slice(lo) != 0 || hi->inputs[0] != xr->output || lo->inputs[0] != xr->output ||
+      hi->output->meta.GetShape()[rank - 1] != rot / 2 || lo->output->meta.GetShape()[rank - 1] != rot / 2 ||
+      rw.Sole(hi->output) != neg || rw.Sole(lo->output) != half_cat)
+    return false;
+  // xr is read by the two half slices and the product, by nobody else
+  {
+    auto it = rw.consumers.find(xr->output.get());
+    if (it == rw.consumers.end() || it->second.size() != 3 || xr->output->kind != flow::Region::kInner) return false;
+  }
+  for (const RegionPtr &t : {cosv, sinv}) {
+    const auto &ts = t->meta.GetShape();
+    if (t->meta.GetType() != Type::kFloat32 || ts.empty() || ts.size() > rank || ts.back() != rot) return false;
+  }
+  if (src->meta.GetType() != Type::kFloat32) return false;
+  cat->kind = Kind::Rotary;
+  cat->inputs = {src, cosv, sinv};
+  cat->value = (double)rot;
+  for (const NodePtr &n : {fma, pass, xr, mul, half_cat, neg, hi, lo}) rw.Kill(n);
+  return true;
+}
+
 // ---- Conv -> SiLU: the activation rides in the convolution's epilogue
 bool FuseSiluIntoConv(Rewriter &rw, const NodePtr &cv) {
   if ((cv->kind != Kind::ConvWithPadding && cv->kind != Kind::ConvWithoutPadding) || cv->act != 0) return false;
@@ -585,7 +656,7 @@ size_t FusionPasses::Run(flow::Flow &flow) {
   using Pass = bool (*)(Rewriter &, const NodePtr &);
   // order matters: bias before GELU / activation before residual, residual before Add+LN
   const Pass passes[] = {FuseEmbedding, FuseMask, FuseBias, FuseGeluIntoGemm, FuseBiasGelu, FuseActivation,
-                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseGateIntoConv, FuseMulAdd, FuseMulAddChain};
+                         FuseResidual, FuseAddLayerNorm, FuseScaledMaskedSoftmax, FuseAttention, FuseSilu, FuseSiluIntoConv, FuseSqueezeExcite, FuseGateIntoConv, FuseMulAdd, FuseRotary, FuseMulAddChain};
   for (Pass pass : passes) {
     bool again = true;
     while (again) {

@@ -232,6 +232,21 @@ public:
   }
 };
 
+// Slice, Slice, Neg, Concat, Mul, Mul, Add, Concat of a rotary position embedding in one launch
+class RotaryKernel : public Kernel {
+public:
+  explicit RotaryKernel(int64_t rot) : rot_(rot) {}
+  std::string GetKernelName() const override { return "RotaryKernel"; }
+  void Launch(LaunchRecorder &rec, const std::vector<fml_tensor> &in, const fml_tensor &output, const Buffer &) const override {
+    const fml_tensor x = in.at(0), c = in.at(1), sn = in.at(2);
+    const int64_t rot = rot_;
+    rec.Add(GetKernelName(), [=](void *s) { return fml_rotary(&x, &c, &sn, rot, &output, s); });
+  }
+
+private:
+  int64_t rot_;
+};
+
 // A chain MulCommon -> FusedMulAdd -> FusedMulAdd ... that sums products, in one launch
 class FusedMulAddChainKernel : public Kernel {
 public:
@@ -706,6 +721,7 @@ std::unique_ptr<Kernel> SelectKernel(const flow::Node &n, const ConstResolver &r
   case Kind::Silu: return std::make_unique<SiluKernel>();
   case Kind::FusedMulAdd: return std::make_unique<FusedMulAddKernel>();
   case Kind::FusedMulAddChain: return std::make_unique<FusedMulAddChainKernel>();
+  case Kind::Rotary: return std::make_unique<RotaryKernel>((int64_t)n.value);
   case Kind::SqueezeExciteGate: {
     size_t k = 0;
     const fml_tensor w1 = C(k++);
@@ -834,7 +850,7 @@ const char *KindName(Kind k) {
       "Not", "Pad", "Pow", "ReduceMean", "Relu", "Reshape", "Slice", "Softmax", "Sqrt", "Squeeze", "SubConstantLhs",
       "SubCommon", "Tanh", "Transpose", "Unsqueeze", "UnsqueezeSubLhsScalarMulRhsScalar",
       "WhereConstantCondConstantScalarY", "WhereConstantCondConstantTensorY", "Sigmoid", "Identity", "FusedGemm",
-      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd", "FusedMulAddChain", "SqueezeExciteGate"};
+      "FusedSoftmax", "FusedLayerNorm", "Silu", "FusedAttention", "FusedMulAdd", "FusedMulAddChain", "Rotary", "SqueezeExciteGate"};
   return names[(int)k];
 }
 }  // namespace flow

@@ -376,6 +376,64 @@ __global__ void sum_products_generic(Iter<2 * kMaxPairs + 1> it, float *out, Pai
   }
 }
 
+// Rotary position embedding over the first `rot` of D features (GPT-NeoX style halves), the
+// operator chain Slice, Slice, Neg, Concat, Mul, Mul, Add, Concat in one pass:
+//   j < rot/2        : out[j] = rn(rn(x[j] * cos[j]) + rn(-x[j + rot/2] * sin[j]))
+//   rot/2 <= j < rot : out[j] = rn(rn(x[j] * cos[j]) + rn( x[j - rot/2] * sin[j]))
+//   j >= rot         : out[j] = x[j]
+// with the chain's roundings (two products, one sum, no fused multiply-add): bit-equal to it.
+struct RotaryArgs {
+  int rank;                 // dims before the feature dim
+  int64_t shape[kMaxDims];  // their extents
+  int64_t xs[kMaxDims], os[kMaxDims], cs[kMaxDims], ss[kMaxDims];  // element strides of x, out, cos, sin over them
+  int64_t x_last, o_last, c_last, s_last;                          // strides along the features
+  int64_t rows;
+  int D, rot;
+  const float *x, *cosv, *sinv;
+  float *out;
+};
+template <int V>  // features per thread: 4 (16-byte accesses) or 1
+__global__ void rotary_kernel(const RotaryArgs a) {
+  pdl_prologue();
+  const int per_row = a.D / V, half = a.rot >> 1;
+  const int64_t total = a.rows * per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = i / per_row;
+    const int j = (int)(i - row * per_row) * V;
+    int64_t xo = 0, oo = 0, co = 0, so = 0;
+    for (int d = a.rank - 1; d >= 0; --d) {
+      const int64_t q = row / a.shape[d], c = row - q * a.shape[d];
+      row = q;
+      xo += c * a.xs[d]; oo += c * a.os[d]; co += c * a.cs[d]; so += c * a.ss[d];
+    }
+    if (V == 4) {
+      const float4 xv = *reinterpret_cast<const float4 *>(a.x + xo + j);
+      float4 r = xv;
+      if (j < a.rot) {
+        const int pj = j < half ? j + half : j - half;
+        const float sgn = j < half ? -1.0f : 1.0f;
+        const float4 pv = *reinterpret_cast<const float4 *>(a.x + xo + pj);
+        const float4 cv = *reinterpret_cast<const float4 *>(a.cosv + co + j);
+        const float4 sv = *reinterpret_cast<const float4 *>(a.sinv + so + j);
+        r.x = __fadd_rn(__fmul_rn(xv.x, cv.x), __fmul_rn(sgn * pv.x, sv.x));
+        r.y = __fadd_rn(__fmul_rn(xv.y, cv.y), __fmul_rn(sgn * pv.y, sv.y));
+        r.z = __fadd_rn(__fmul_rn(xv.z, cv.z), __fmul_rn(sgn * pv.z, sv.z));
+        r.w = __fadd_rn(__fmul_rn(xv.w, cv.w), __fmul_rn(sgn * pv.w, sv.w));
+      }
+      *reinterpret_cast<float4 *>(a.out + oo + j) = r;
+    } else {
+      const float xv = a.x[xo + j * a.x_last];
+      float r = xv;
+      if (j < a.rot) {
+        const int pj = j < half ? j + half : j - half;
+        const float pv = a.x[xo + pj * a.x_last];
+        r = __fadd_rn(__fmul_rn(xv, a.cosv[co + j * a.c_last]), __fmul_rn(j < half ? -pv : pv, a.sinv[so + j * a.s_last]));
+      }
+      a.out[oo + j * a.o_last] = r;
+    }
+  }
+}
+
 bool vec4_ok(const Iter<3> &it, const void *out, const void *a, const void *b) {
   int l = it.rank - 1;
   if (it.shape[l] % 4 != 0 || it.stride[0][l] != 1) return false;
@@ -545,6 +603,56 @@ extern "C" int fml_where(const fml_tensor *cond, const fml_tensor *x, const fml_
   FML_LAUNCH((where_generic), grid_for(it.total, 256), 256, 0, as_stream(stream), 
       it, (float *)out->data, (const uint8_t *)cond->data, (const float *)x->data,
       y ? (const float *)y->data : nullptr, y_scalar);
+  FML_CUDA(cudaGetLastError());
+  return FML_OK;
+}
+
+extern "C" int fml_rotary(const fml_tensor *x, const fml_tensor *cosv, const fml_tensor *sinv, int64_t rot,
+                          const fml_tensor *out, void *stream) {
+  FML_REQUIRE(valid_tensor(x) && valid_tensor(cosv) && valid_tensor(sinv) && valid_tensor(out), FML_BAD_ARG, "fml_rotary: bad tensor");
+  FML_REQUIRE(x->dtype == FML_F32 && cosv->dtype == FML_F32 && sinv->dtype == FML_F32 && out->dtype == FML_F32, FML_UNSUPPORTED,
+              "fml_rotary: fp32 only");
+  FML_REQUIRE(x->rank >= 1 && out->rank == x->rank && cosv->rank <= x->rank && sinv->rank <= x->rank, FML_BAD_ARG,
+              "fml_rotary: ranks");
+  const int r = x->rank - 1;
+  RotaryArgs a;
+  memset(&a, 0, sizeof(a));
+  a.D = (int)x->shape[r];
+  FML_REQUIRE(rot >= 2 && (rot & 1) == 0 && rot <= a.D && x->shape[r] < (1ll << 30), FML_BAD_ARG,
+              "fml_rotary: the rotated width must be even and at most the feature count");
+  a.rot = (int)rot;
+  a.rank = r;
+  a.rows = 1;
+  // cos / sin: [..., rot], leading dims broadcast to x's (numpy rules, right-aligned)
+  auto lead_strides = [&](const fml_tensor *t, int64_t *st, int64_t *last) {
+    if (t->rank < 1 || t->shape[t->rank - 1] != rot) return false;
+    *last = t->stride[t->rank - 1];
+    for (int i = 0; i < r; ++i) {
+      const int ti = i - (x->rank - t->rank);
+      if (ti < 0) { st[i] = 0; continue; }
+      if (t->shape[ti] == x->shape[i]) st[i] = t->shape[ti] == 1 ? 0 : t->stride[ti];
+      else if (t->shape[ti] == 1) st[i] = 0;
+      else return false;
+    }
+    return true;
+  };
+  for (int i = 0; i <= r; ++i) FML_REQUIRE(out->shape[i] == x->shape[i], FML_BAD_ARG, "fml_rotary: output shape");
+  for (int i = 0; i < r; ++i) {
+    a.shape[i] = x->shape[i]; a.xs[i] = x->stride[i]; a.os[i] = out->stride[i];
+    a.rows *= x->shape[i];
+  }
+  FML_REQUIRE(lead_strides(cosv, a.cs, &a.c_last) && lead_strides(sinv, a.ss, &a.s_last), FML_BAD_ARG,
+              "fml_rotary: cos / sin must be [..., rot] and broadcast to x's leading dims");
+  a.x_last = x->stride[r]; a.o_last = out->stride[r];
+  a.x = (const float *)x->data; a.cosv = (const float *)cosv->data; a.sinv = (const float *)sinv->data;
+  a.out = (float *)out->data;
+  if (a.rows == 0 || a.D == 0) return FML_OK;
+  bool vec = a.x_last == 1 && a.o_last == 1 && a.c_last == 1 && a.s_last == 1 && (a.D & 3) == 0 && (a.rot & 7) == 0 &&
+             aligned16(a.x) && aligned16(a.out) && aligned16(a.cosv) && aligned16(a.sinv);
+  for (int i = 0; i < r && vec; ++i) vec = (a.xs[i] & 3) == 0 && (a.os[i] & 3) == 0 && (a.cs[i] & 3) == 0 && (a.ss[i] & 3) == 0;
+  const int64_t work = a.rows * (vec ? a.D / 4 : a.D);
+  if (vec) FML_LAUNCH((rotary_kernel<4>), grid_for(work, 256), 256, 0, as_stream(stream), a);
+  else FML_LAUNCH((rotary_kernel<1>), grid_for(work, 256), 256, 0, as_stream(stream), a);
   FML_CUDA(cudaGetLastError());
   return FML_OK;
 }

@@ -156,6 +156,14 @@ int fml_bias_gelu(const fml_tensor *x, const fml_tensor *bias, const fml_tensor 
 int fml_mul_add(const fml_tensor *a, const fml_tensor *b, const fml_tensor *c, const fml_tensor *out,
                 void *stream);
 
+/* Rotary position embedding over the first `rot` of D features, halves convention (GPT-NeoX):
+ * the chain Slice, Slice, Neg (neg.cpp), Concat (concat.cpp), Mul, Mul (mul.cpp), Add (add.cpp),
+ * Concat of the exported graph in one pass.  x, out [..., D]; cos, sin [..., rot] broadcast to x's
+ * leading dims;  out[:rot] = x[:rot] * cos + rotate_half(x[:rot]) * sin,  out[rot:] = x[rot:],
+ * with the chain's roundings (two rounded products, one rounded sum). */
+int fml_rotary(const fml_tensor *x, const fml_tensor *cosv, const fml_tensor *sinv, int64_t rot,
+               const fml_tensor *out, void *stream);
+
 /* A chain of MulCommonKernel / AddCommonKernel launches (mul.cpp, add.cpp) that sums n products
  * (ConvBERT's span convolution: nine sliding windows times nine softmax columns) in one pass:
  *   acc = a[0] * b[0];  acc = a[i] * b[i] + acc  for i = 1 .. n-1,

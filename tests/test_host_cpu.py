@@ -238,6 +238,13 @@ def test_mul_add_pairs_are_fused_when_the_product_has_one_consumer():
     assert fused.count("MulCommon") == 1 and fused.count("AddCommon") == 2
 
 
+def test_rotary_embeddings_become_one_node_each():
+    m = models.build_gpt_neox(layers=2, hidden=256, heads=4, ffn=512, vocab=400, batch=2, seq=32)
+    unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
+    assert unfused.count("Neg") == 4 and unfused.count("Concat2") == 8
+    assert fused.count("Rotary") == 4 and fused.count("Neg") == 0 and fused.count("Concat2") == 0
+
+
 def test_convbert_span_convolution_is_one_sum_of_products():
     m = models.build_convbert(layers=2, hidden=256, heads=8, ffn=512, vocab=400, batch=3, seq=48)
     unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)

@@ -126,6 +126,36 @@ def test_squeeze_excite_gate_rejects_what_it_cannot_take():
         cabi.squeeze_excite_gate(x, DT.from_numpy(rnd(2, 8, 1, 1)), None, DT.from_numpy(rnd(8, 2, 1, 1)), None, 1, 4, gate)
 
 
+@pytest.mark.parametrize("shape,rot,cs_shape,strided", [
+    ((4, 16, 512, 64), 16, (512, 16), True),    # GPT-NeoX: a quarter of each head rotated, x a transposed view of [B, S, H, D]
+    ((2, 3, 10, 64), 64, (1, 1, 10, 64), False),  # the whole head rotated
+    ((2, 5, 6), 4, (5, 4), False),               # rot not a multiple of 8: element path
+    ((3, 7, 10), 10, (7, 10), False),            # odd everything
+])
+def test_rotary_equals_the_exported_chain(shape, rot, cs_shape, strided):
+    """fml_rotary against the oracle's kernels run as the exported graph runs them (Slice, Neg,
+    Concat, Mul, Mul, Add, Concat): bit-exact."""
+    x = rnd(*shape)
+    cosv, sinv = rnd(*cs_shape), rnd(*cs_shape)
+    half = rot // 2
+    xr = np.ascontiguousarray(x[..., :rot])
+    rh = np.concatenate([orc.unary("Neg", np.ascontiguousarray(xr[..., half:]), np.empty(xr[..., half:].shape, np.float32)),
+                         xr[..., :half]], axis=-1)
+    p_sin = orc.binary("Mul", np.ascontiguousarray(rh), sinv, np.empty(xr.shape, np.float32))
+    p_cos = orc.binary("Mul", xr, cosv, np.empty(xr.shape, np.float32))
+    ref = np.concatenate([orc.binary("Add", p_cos, p_sin, np.empty(xr.shape, np.float32)), x[..., rot:]], axis=-1)
+    if strided:  # stored [B, S, H, D], seen as [B, H, S, D]
+        base = DT.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 1, 3)))
+        st = list(base.strides)
+        st[1], st[2] = st[2], st[1]
+        dx = base.view(shape, st, 0)
+    else:
+        dx = DT.from_numpy(x)
+    out = DT(shape, np.float32)
+    cabi.rotary(dx, DT.from_numpy(cosv), DT.from_numpy(sinv), rot, out)
+    assert np.array_equal(out.numpy(), ref)
+
+
 @pytest.mark.parametrize("shape,bshape,n,windows", [
     ((8, 128, 6, 64), (8, 128, 6, 1), 9, True),    # ConvBERT's span convolution: sliding windows of one padded tensor x softmax columns
     ((2, 5, 7, 3), (2, 5, 7, 3), 3, False),       # odd sizes: element path
