@@ -38,6 +38,8 @@ working set fits in L2 say so in `config.l2`.
 from __future__ import annotations
 
 import argparse
+import contextlib
+import io
 import json
 import os
 import re
@@ -565,10 +567,25 @@ def main():
     args.repeats = max(1, args.repeats)
     if args.config != "bert_b1" and "--steps" not in sys.argv:
         args.steps = 20  # the larger configurations take milliseconds per pass
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    # Rank 0 prints ONE JSON line and nothing else on stdout: libraries that log to file
+    # descriptor 1 (NCCL prints its version there at the first collective) are sent to stderr for
+    # the duration of the run, and the line goes to the descriptor stdout had at start.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    line_out = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(line_out):
+            if args.impl == "reference":
+                run_reference(args)
+            else:
+                run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    sys.stdout.write(line_out.getvalue())
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":
