@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kDwThreads) conv_depthwise_tma_kernel(const __
       for (int q = 0; q < KH * KW; ++q) w[q] = __ldg(d.w + ch * d.ws0 + (q / KW) * d.ws2 + (q % KW) * d.ws3);
       if (d.bias) bias = __ldg(d.bias + ch * d.bias_stride);
     }
-    // (the verdict is made uniform: a thread that gave up must not leave the others at the barrier below)
+    // (the outcome is made uniform: a thread that gave up must not leave the others at the barrier below)
     ok = __syncthreads_and(mbar_wait(smem_u32(&bars[stage]), ((uint32_t)(k / NS)) & 1u, &abort_flag) ? 1 : 0) != 0;
     if (!ok) break;
     if (tid == 0) consumed = k + 1;

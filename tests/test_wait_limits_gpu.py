@@ -73,7 +73,7 @@ def test_attention_waits_run_out_and_the_context_survives():
 
 def test_depthwise_waits_run_out_and_the_context_survives():
     """The pipelined depthwise kernel (one tensor-map copy per tile, two buffers): with the copies
-    dropped both buffers' waits run out, every CTA leaves through the uniform verdict, and the next
+    dropped both buffers' waits run out, every CTA leaves through the uniform outcome, and the next
     launch is correct."""
     x, w, b = rnd(2, 24, 28, 28), rnd(24, 1, 3, 3), rnd(24)
     dx, dw, db, dy = DT.from_numpy(x), DT.from_numpy(w), DT.from_numpy(b), DT((2, 24, 28, 28), np.float32)
