@@ -81,6 +81,7 @@ __device__ __forceinline__ void load_tile(float *dst, int pitch, const float *sr
 //            per key, 4 P values and two 16-byte V reads feed 32 FMAs; the eight partial
 //            tiles are added in warp order through shared memory.
 __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
+  const ExactDivisor div(a.divisor);  // 1 / sqrt(head size) is usually a power of two: a multiply, same bits
   pdl_prologue();
   extern __shared__ __align__(16) float smem[];
   const int D = (int)a.D, Dv = (int)a.Dv, Sk = (int)a.Sk;
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
     if (live)
       for (int j = cg; j < Sk; j += 16) {
         float sc = p[j];
-        if (a.divisor != 1.0f) sc = sc / a.divisor;
+        if (a.divisor != 1.0f) sc = div(sc);
         if (m) sc += mr[j];
         p[j] = sc;
         mx = fmaxf(mx, sc);
@@ -258,6 +259,7 @@ __global__ void __launch_bounds__(kThreads) attention_kernel(AttnArgs a) {
 constexpr int kChunk = 128;
 
 __global__ void __launch_bounds__(kThreads) attention_flash_kernel(AttnArgs a) {
+  const ExactDivisor div(a.divisor);  // 1 / sqrt(head size) is usually a power of two: a multiply, same bits
   pdl_prologue();
   extern __shared__ __align__(16) float smem[];
   const int D = (int)a.D, Dv = (int)a.Dv, Sk = (int)a.Sk;
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kThreads) attention_flash_kernel(AttnArgs a) {
       if (live)
         for (int j = cg; j < kc; j += 16) {
           float sc = p[j];
-          if (a.divisor != 1.0f) sc = sc / a.divisor;
+          if (a.divisor != 1.0f) sc = div(sc);
           if (m) sc += mr[j];
           p[j] = sc;
           mx = fmaxf(mx, sc);

@@ -207,6 +207,21 @@ inline int grid_for(int64_t work, int block, int max_blocks = 148 * 16) {
   return static_cast<int>(g);
 }
 
+// x / d.  When d is a power of two whose reciprocal is a normal number, 1 / d is exact and x * (1 / d)
+// is the same correctly rounded value as x / d, bit for bit: the attention scale 1 / sqrt(64) = 1 / 8
+// costs one multiply instead of a ~10-instruction IEEE division per score.
+struct ExactDivisor {
+  float d, inv;
+  bool by_mul;
+  __host__ __device__ explicit ExactDivisor(float divisor) : d(divisor), inv(1.0f / divisor) {
+    uint32_t u;
+    memcpy(&u, &divisor, sizeof(u));
+    const uint32_t e = (u >> 23) & 0xffu;
+    by_mul = (u & 0x007fffffu) == 0 && e >= 2 && e <= 252;
+  }
+  __device__ __forceinline__ float operator()(float x) const { return by_mul ? x * inv : x / d; }
+};
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace fml

@@ -42,6 +42,7 @@ __global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const f
   const int64_t n4 = a.len >> 2;
   const float4 *x4 = reinterpret_cast<const float4 *>(in + off[1]);
   const bool mvec = mask && a.axis_stride[2] == 1;
+  const ExactDivisor div(divisor);
   float4 v[NV];
   float mx = -3.402823466e+38f;
 #pragma unroll
@@ -49,7 +50,7 @@ __global__ void softmax_rows_vec(RowArgs a, float *out, const float *in, const f
     int64_t c = lane + 32 * i;
     if (c < n4) {
       float4 t = x4[c];
-      if (divisor != 1.0f) { t.x = t.x / divisor; t.y = t.y / divisor; t.z = t.z / divisor; t.w = t.w / divisor; }
+      if (divisor != 1.0f) { t.x = div(t.x); t.y = div(t.y); t.z = div(t.z); t.w = div(t.w); }
       if (mask) {
         float4 m;
         if (mvec) m = *reinterpret_cast<const float4 *>(mask + off[2] + c * 4);
@@ -89,9 +90,10 @@ __global__ void softmax_rows_generic(RowArgs a, float *out, const float *in, con
   if (row >= a.rows.total) return;
   int64_t off[3];
   offsets_of(a.rows, row, off);
+  const ExactDivisor div(divisor);
   auto load = [&](int64_t c) {
     float t = in[off[1] + c * a.axis_stride[1]];
-    if (divisor != 1.0f) t = t / divisor;
+    if (divisor != 1.0f) t = div(t);
     if (mask) t += mask[off[2] + c * a.axis_stride[2]];
     return t;
   };
