@@ -245,6 +245,66 @@ def test_rotary_embeddings_become_one_node_each():
     assert fused.count("Rotary") == 4 and fused.count("Neg") == 0 and fused.count("Concat2") == 0
 
 
+def _rotary_graph(variant):
+    """x [2, 3, 8, 16] with the first 8 features rotated; `variant` breaks the pattern in one place."""
+    g = models.GraphBuilder("rot")
+    x = g.input("x", FLOAT, (2, 3, 8, 16))
+    cosv = g.const("cos", np.ones((8, 8), np.float32))
+    sinv = g.const("sin", np.ones((8, 8), np.float32))
+    rot = 8
+    xr = g.slice(x, [0], [rot], [3])
+    xp = g.slice(x, [rot if variant != "gap" else rot + 4], [16], [3])
+    hi = g.slice(xr, [rot // 2], [rot], [3])
+    lo = g.slice(xr, [0], [rot // 2], [3])
+    halves = g.concat(g.neg(hi), lo, 3) if variant != "swapped" else g.concat(lo, g.neg(hi), 3)
+    y = g.add(g.mul(xr, cosv), g.mul(halves, sinv))
+    if variant == "gap":
+        y = g.concat(y, g.concat(g.slice(x, [rot], [rot + 4], [3]), xp, 3), 3, out="y")
+    else:
+        y = g.concat(y, xp, 3, out="y")
+    g.output("y")
+    return g.finish()
+
+
+def test_rotary_pattern_is_matched_exactly_or_not_at_all():
+    assert kinds_of(_rotary_graph("plain").to_bytes(), fusion=1).count("Rotary") == 1
+    # halves concatenated the other way round, or a pass-through part that does not start where the
+    # rotated part ends: another function, left as the operators it is written with
+    for variant in ("swapped", "gap"):
+        ks = kinds_of(_rotary_graph(variant).to_bytes(), fusion=1)
+        assert ks.count("Rotary") == 0 and ks.count("Neg") == 1 and ks.count("Concat2") >= 2
+
+
+def test_gate_is_folded_only_into_a_group_one_convolution_that_is_its_sole_reader():
+    def graph(case):
+        g = models.GraphBuilder("gate")
+        x = g.input("x", FLOAT, (2, 8, 6, 6))
+        gate = g.input("gate", FLOAT, (2, 8, 1, 1) if case != "per_pixel" else (2, 8, 6, 6))
+        w = g.const("w", np.ones((4, 8, 1, 1), np.float32)) if case != "depthwise" else g.const("w", np.ones((8, 1, 3, 3), np.float32))
+        t = g.mul(x, gate)
+        if case == "depthwise":
+            y = g.conv(t, w, None, pads=[1] * 4, strides=[1, 1], dilations=[1, 1], group=8)
+        else:
+            y = g.conv(t, w, None, pads=[0] * 4, strides=[1, 1], dilations=[1, 1], group=1)
+        if case == "two_readers":
+            y = g.add(y, g.conv(g.relu(t), w, None, pads=[0] * 4, strides=[1, 1], dilations=[1, 1], group=1))
+        g.identity(y, out="y") if hasattr(g, "identity") else g.relu(y, out="y")
+        g.output("y")
+        return g.finish()
+    assert "MulCommon" not in kinds_of(graph("plain").to_bytes(), fusion=1)
+    for case in ("per_pixel", "depthwise", "two_readers"):
+        assert "MulCommon" in kinds_of(graph(case).to_bytes(), fusion=1), case
+
+
+def test_two_products_stay_a_fused_multiply_add():
+    g = models.GraphBuilder("two")
+    xs = [g.input(f"x{i}", FLOAT, (4, 8)) for i in range(4)]
+    g.add(g.mul(xs[0], xs[1]), g.mul(xs[2], xs[3]), out="y")
+    g.output("y")
+    ks = kinds_of(g.finish().to_bytes(), fusion=1)
+    assert ks.count("FusedMulAdd") == 1 and ks.count("FusedMulAddChain") == 0 and ks.count("MulCommon") == 1
+
+
 def test_convbert_span_convolution_is_one_sum_of_products():
     m = models.build_convbert(layers=2, hidden=256, heads=8, ffn=512, vocab=400, batch=3, seq=48)
     unfused, fused = kinds_of(m.to_bytes(), fusion=0), kinds_of(m.to_bytes(), fusion=1)
