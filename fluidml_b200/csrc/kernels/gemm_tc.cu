@@ -79,9 +79,10 @@ __device__ __forceinline__ unsigned long long gtime() {
 // cheap uniform predicates inside one short loop: every CTA runs each phase of this kernel
 // once, so the cost of a phase is largely the instruction fetch of its (cold) code, and a
 // compact, straight-line epilogue matters more than a branch-free one.
-// erf by Abramowitz & Stegun 7.1.26 with the fast exponential and reciprocal: absolute error below
-// 6e-7 (the formula's 1.5e-7 plus the rounding of ex2.approx on an argument up to ~16), i.e. a
-// GELU value off by at most 3e-7 |v| -- two orders below the 3xTF32 product it is applied to.
+// erf by Abramowitz & Stegun 7.1.26 with the fast exponential and reciprocal: absolute error about
+// 6e-7 in fp32 arithmetic (the formula's 1.5e-7 plus the cancellation in 1 - p t exp(-x^2) near 0;
+// tests/test_erf_formula_cpu.py restates it on the host), below 1e-6 with ex2.approx's rounding,
+// i.e. a GELU value off by at most 5e-7 |v| -- far below the 3xTF32 product it is applied to.
 // The exact erff is ~45 dependent instructions per element; with one epilogue warp per scheduler
 // that was 35 us of a 134 us FFN launch at 2048 rows (4096 columns each).
 __device__ __forceinline__ float erf_fast(float x) {
